@@ -1,0 +1,168 @@
+"""Builds and loads the CUDA library of the engine (sm_100a only).
+
+All `.cu` files of this folder are compiled by nvcc into one shared library whose entry
+points are plain `extern "C"` functions taking device pointers and a stream; Python
+calls them through ctypes, so no torch header is compiled and a full build takes well
+under a minute.  The library lives in `_build/<hash of the sources>/` beside the
+sources when that folder can be written, else under the system's temporary folder; it
+is rebuilt only when a source changes.  While compiling, a line is printed to stderr
+for every finished file and every few seconds in between.
+
+There is no fallback: without the library (no nvcc, or a failed build) every op raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+CSRC = Path(__file__).resolve().parent
+LIB_NAME = "libtokensprint_b200.so"
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC",
+    "-Xcompiler", "-fvisibility=hidden",
+]
+
+_lock = threading.Lock()
+_library: ctypes.CDLL | None = None
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def _say(msg: str) -> None:
+    print(f"[tokensprint_b200] {msg}", file=sys.stderr, flush=True)
+
+
+def find_nvcc() -> str:
+    candidates = []
+    for var in ("CUDA_HOME", "CUDA_PATH"):
+        if os.environ.get(var):
+            candidates.append(Path(os.environ[var]) / "bin" / "nvcc")
+    candidates.append(Path("/usr/local/cuda/bin/nvcc"))
+    for c in candidates:
+        if c.is_file():
+            return str(c)
+    found = shutil.which("nvcc")
+    if found:
+        return found
+    raise BuildError("nvcc was not found (CUDA_HOME, /usr/local/cuda, PATH): the CUDA library cannot be built")
+
+
+def sources() -> list[Path]:
+    return sorted(CSRC.glob("*.cu"))
+
+
+def source_hash() -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(NVCC_FLAGS).encode())
+    for p in sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    return h.hexdigest()[:16]
+
+
+def _build_root() -> Path:
+    in_tree = CSRC / "_build"
+    try:
+        in_tree.mkdir(exist_ok=True)
+        probe = in_tree / f".w{os.getpid()}"
+        probe.write_bytes(b"")
+        probe.unlink()
+        return in_tree
+    except OSError:
+        root = Path(tempfile.gettempdir()) / f"tokensprint_b200-build-{os.getuid()}"
+        root.mkdir(parents=True, exist_ok=True)
+        return root
+
+
+def library_path() -> Path:
+    """Where the library for the current sources is (or will be)."""
+    digest = source_hash()
+    in_tree = CSRC / "_build" / digest / LIB_NAME
+    if in_tree.is_file():
+        return in_tree
+    return _build_root() / digest / LIB_NAME
+
+
+def _compile_one(nvcc: str, src: Path, obj: Path) -> None:
+    cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise BuildError(f"nvcc failed on {src.name}:\n{proc.stdout}\n{proc.stderr}")
+
+
+def build(force: bool = False) -> Path:
+    """Compiles what is missing and returns the library's path."""
+    target = library_path()
+    if target.is_file() and not force:
+        return target
+    nvcc = find_nvcc()
+    out_dir = target.parent
+    out_dir.mkdir(parents=True, exist_ok=True)
+    srcs = sources()
+    if not srcs:
+        raise BuildError(f"no .cu sources in {CSRC}")
+    _say(f"compiling {len(srcs)} CUDA files for sm_100a into {out_dir} (first call only)")
+    start = time.time()
+    done = 0
+    stop = threading.Event()
+
+    def ticker() -> None:
+        while not stop.wait(8.0):
+            _say(f"still compiling: {done}/{len(srcs)} files done after {time.time() - start:.0f} s")
+
+    t = threading.Thread(target=ticker, daemon=True)
+    t.start()
+    try:
+        objs = [out_dir / (s.stem + f".{os.getpid()}.o") for s in srcs]
+        with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 2, 8)) as pool:
+            futures = [pool.submit(_compile_one, nvcc, s, o) for s, o in zip(srcs, objs)]
+            for s, f in zip(srcs, futures):
+                f.result()
+                done += 1
+                _say(f"compiled {s.name} ({done}/{len(srcs)})")
+        tmp = out_dir / f".{LIB_NAME}.{os.getpid()}"
+        cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(tmp), *map(str, objs)]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise BuildError(f"linking {LIB_NAME} failed:\n{proc.stdout}\n{proc.stderr}")
+        os.replace(tmp, target)
+        for o in objs:
+            try:
+                o.unlink()
+            except OSError:
+                pass
+    finally:
+        stop.set()
+    _say(f"built {target.name} in {time.time() - start:.0f} s")
+    return target
+
+
+def load() -> ctypes.CDLL:
+    """The loaded library; built on the first call of a fresh checkout."""
+    global _library
+    with _lock:
+        if _library is None:
+            path = build()
+            try:
+                _library = ctypes.CDLL(str(path))
+            except OSError as e:
+                raise BuildError(f"cannot load {path}: {e}") from e
+        return _library
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv))

@@ -1,0 +1,105 @@
+// Per-head q/k RMSNorm, rotary position encoding and the store of keys and values into
+// the paged cache, in one pass over the fused q|k|v projection.
+//
+// Reference order (engine/nn/attention.py:171-188): unflatten heads, q_norm/k_norm over
+// head_dim with one [head_dim] weight shared by all heads, then RoPE on q and k, then
+// store_kvcache(k, v) by slot.  RoPE is the rotate-half pairing (j, j + rot/2) with
+// angle = position * inv_freq[j], all float32 (engine/kernels/triton/rope.py:22-65,
+// engine/nn/rope.py:28-29,116-123).  Here the normed value is not rounded to the model
+// dtype before the rotation: one rounding at the store instead of two.
+//
+// One warp per (token, head).  Heads 0..nq-1 are queries (written to q_out), the next nkv
+// are keys, the last nkv are values (copied).  A slot of -1 skips the key/value store.
+// Without `slot_mapping` keys and values go to dense [T, nkv, d] buffers.
+#include "common.cuh"
+
+#define QKR_MAX_HEAD_DIM 512
+#define QKR_WARPS 4
+
+template <typename TA>
+__global__ void qk_norm_rope_store_kernel(const TA* __restrict__ qkv, TA* __restrict__ q_out,
+                                          TA* __restrict__ k_dst, TA* __restrict__ v_dst,
+                                          const int* __restrict__ slot_mapping,
+                                          const int* __restrict__ positions,
+                                          const float* __restrict__ q_norm_w,
+                                          const float* __restrict__ k_norm_w, float eps,
+                                          const float* __restrict__ inv_freq, int rot_dim, int T,
+                                          int nq, int nkv, int d) {
+  __shared__ float buf[QKR_WARPS][QKR_MAX_HEAD_DIM];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = nq + 2 * nkv;
+  const long long item = (long long)blockIdx.x * QKR_WARPS + warp;
+  if (item >= (long long)T * heads) return;
+  const int t = (int)(item / heads);
+  const int head = (int)(item - (long long)t * heads);
+  const TA* src = qkv + ((size_t)t * heads + head) * d;
+
+  const bool is_q = head < nq;
+  const bool is_k = !is_q && head < nq + nkv;
+  int slot = -1;
+  if (!is_q) {
+    slot = slot_mapping ? slot_mapping[t] : t;
+    if (slot < 0) return;
+  }
+  if (!is_q && !is_k) {  // value head: plain copy
+    TA* dst = v_dst + ((size_t)slot * nkv + (head - nq - nkv)) * d;
+    for (int i = lane; i < d; i += 32) dst[i] = src[i];
+    return;
+  }
+
+  float* x = buf[warp];
+  float ss = 0.f;
+  for (int i = lane; i < d; i += 32) {
+    float v = ts_to_float(src[i]);
+    x[i] = v;
+    ss += v * v;
+  }
+  const float* w = is_q ? q_norm_w : k_norm_w;
+  if (w) {
+    ss = ts_warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)d + eps);
+    for (int i = lane; i < d; i += 32) x[i] = x[i] * rstd * w[i];
+  }
+  __syncwarp();
+
+  TA* dst = is_q ? q_out + ((size_t)t * nq + head) * d
+                 : k_dst + ((size_t)slot * nkv + (head - nq)) * d;
+  const int half = inv_freq ? rot_dim / 2 : 0;
+  if (half > 0) {
+    const float pos = (float)positions[t];
+    for (int j = lane; j < half; j += 32) {
+      float s, c;
+      sincosf(pos * inv_freq[j], &s, &c);
+      const float re = x[j], im = x[j + half];
+      dst[j] = ts_from_float<TA>(re * c - im * s);
+      dst[j + half] = ts_from_float<TA>(im * c + re * s);
+    }
+  }
+  for (int i = 2 * half + lane; i < d; i += 32) dst[i] = ts_from_float<TA>(x[i]);
+}
+
+TS_EXPORT int ts_qk_norm_rope_store(const void* qkv, int act_dtype, void* q_out, void* k_dst,
+                                    void* v_dst, const int* slot_mapping, const int* positions,
+                                    const float* q_norm_w, const float* k_norm_w, float eps,
+                                    const float* inv_freq, int rot_dim, int T, int nq, int nkv,
+                                    int d, void* stream) {
+  if (T <= 0) return 0;
+  if (nq < 0 || nkv < 0 || nq + nkv <= 0 || d <= 0) return TS_ERR_BAD_ARGUMENT;
+  if (d > QKR_MAX_HEAD_DIM) return TS_ERR_UNSUPPORTED_SIZE;
+  if (inv_freq && (rot_dim <= 0 || rot_dim > d || (rot_dim & 1))) return TS_ERR_BAD_ARGUMENT;
+  long long items = (long long)T * (nq + 2 * nkv);
+  unsigned blocks = (unsigned)((items + QKR_WARPS - 1) / QKR_WARPS);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (act_dtype == TS_DTYPE_F32)
+    qk_norm_rope_store_kernel<float><<<blocks, QKR_WARPS * 32, 0, s>>>(
+        (const float*)qkv, (float*)q_out, (float*)k_dst, (float*)v_dst, slot_mapping, positions,
+        q_norm_w, k_norm_w, eps, inv_freq, rot_dim, T, nq, nkv, d);
+  else if (act_dtype == TS_DTYPE_BF16)
+    qk_norm_rope_store_kernel<__nv_bfloat16><<<blocks, QKR_WARPS * 32, 0, s>>>(
+        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_dst,
+        (__nv_bfloat16*)v_dst, slot_mapping, positions, q_norm_w, k_norm_w, eps, inv_freq, rot_dim,
+        T, nq, nkv, d);
+  else
+    return TS_ERR_BAD_ARGUMENT;
+  return ts_launch_status();
+}

@@ -1,0 +1,318 @@
+"""Python face of the CUDA kernels: argument checks, then one call into the library.
+
+Every function works on CUDA tensors, launches on torch's current stream and returns
+without synchronising.  A size that a kernel does not take raises `KernelError` with
+the limit in words; nothing falls back to another implementation.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from tokensprint_b200.csrc import build as _build
+
+DTYPE_CODES = {torch.float32: 0, torch.bfloat16: 1}
+
+_c_void_p = ctypes.c_void_p
+_c_int = ctypes.c_int
+_c_float = ctypes.c_float
+_c_ll = ctypes.c_longlong
+
+_SIGNATURES = {
+    "ts_embed_gather": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_add_rmsnorm": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
+    "ts_residual_add": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
+    "ts_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_qk_norm_rope_store": [
+        _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+        _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+    ],
+    "ts_attention_paged_simple": [
+        _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p,
+    ],
+    "ts_sample": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p],
+    "ts_sgemm_nt": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_void_p],
+}
+
+_functions: dict[str, object] = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def library() -> ctypes.CDLL:
+    return _build.load()
+
+
+def _fn(name: str):
+    f = _functions.get(name)
+    if f is None:
+        lib = library()
+        try:
+            f = getattr(lib, name)
+        except AttributeError as e:
+            raise KernelError(f"the CUDA library has no entry point {name}") from e
+        f.argtypes = _SIGNATURES[name]
+        f.restype = _c_int
+        _functions[name] = f
+    return f
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(name: str, status: int) -> None:
+    if status == 0:
+        return
+    if status == -1:
+        raise KernelError(f"{name}: bad argument")
+    if status == -2:
+        raise KernelError(f"{name}: size not supported by this kernel")
+    raise KernelError(f"{name}: CUDA error {status} at launch")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _cuda_contig(name: str, t: torch.Tensor, dtype: Optional[torch.dtype] = None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous, got strides {t.stride()} for shape {tuple(t.shape)}")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def _act_code(name: str, t: torch.Tensor) -> int:
+    code = DTYPE_CODES.get(t.dtype)
+    if code is None:
+        raise KernelError(f"{name} must be float32 or bfloat16, got {t.dtype}")
+    return code
+
+
+# ---------------------------------------------------------------------------
+
+
+def embed_gather(hidden: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
+    """hidden[t] = table[ids[t]] widened to float32.  hidden [T,H] f32, table [V,H], ids [T] i32."""
+    _cuda_contig("hidden", hidden, torch.float32)
+    _cuda_contig("table", table)
+    _cuda_contig("ids", ids, torch.int32)
+    T, H = hidden.shape
+    V = table.shape[0]
+    if table.shape[1] != H or ids.numel() < T:
+        raise KernelError(f"embed_gather: shapes disagree: hidden {tuple(hidden.shape)}, table {tuple(table.shape)}, ids {tuple(ids.shape)}")
+    _check("embed_gather", _fn("ts_embed_gather")(
+        hidden.data_ptr(), table.data_ptr(), _act_code("table", table), ids.data_ptr(), T, H, V, _stream()))
+
+
+def add_rmsnorm(
+    hidden: torch.Tensor,
+    delta: Optional[torch.Tensor],
+    weight: torch.Tensor,
+    out: torch.Tensor,
+    eps: float,
+    row_index: Optional[torch.Tensor] = None,
+) -> None:
+    """hidden += delta (float32, in place) and out = RMSNorm(hidden) * weight.
+
+    hidden [T,H] f32; delta [T,H] of out's dtype or None; weight [H] f32; out [rows,H].
+    With `row_index` ([rows] i32) only those rows are normed and hidden is left as it is.
+    """
+    _cuda_contig("hidden", hidden, torch.float32)
+    _cuda_contig("weight", weight, torch.float32)
+    _cuda_contig("out", out)
+    H = hidden.shape[-1]
+    rows = out.shape[0]
+    if out.shape[-1] != H or weight.numel() != H:
+        raise KernelError(f"add_rmsnorm: widths disagree: hidden {tuple(hidden.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if delta is not None:
+        _cuda_contig("delta", delta, out.dtype)
+        if delta.shape != hidden.shape:
+            raise KernelError("add_rmsnorm: delta must have hidden's shape")
+    if row_index is not None:
+        _cuda_contig("row_index", row_index, torch.int32)
+        if row_index.numel() < rows:
+            raise KernelError("add_rmsnorm: row_index is shorter than out")
+    elif rows != hidden.shape[0]:
+        raise KernelError("add_rmsnorm: out must have hidden's rows when no row_index is given")
+    _check("add_rmsnorm", _fn("ts_add_rmsnorm")(
+        hidden.data_ptr(), _ptr(delta), _act_code("out", out), weight.data_ptr(), out.data_ptr(),
+        _ptr(row_index), rows, H, float(eps), _stream()))
+
+
+def residual_add(hidden: torch.Tensor, delta: torch.Tensor) -> None:
+    """hidden += delta in float32.  hidden [T,H] f32, delta [T,H] f32 or bf16."""
+    _cuda_contig("hidden", hidden, torch.float32)
+    _cuda_contig("delta", delta)
+    if delta.shape != hidden.shape:
+        raise KernelError("residual_add: shapes disagree")
+    _check("residual_add", _fn("ts_residual_add")(
+        hidden.data_ptr(), delta.data_ptr(), _act_code("delta", delta), hidden.numel(), _stream()))
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t,i] = silu(gate_up[t,i]) * gate_up[t,I+i].  gate_up [T,2I], out [T,I]."""
+    _cuda_contig("gate_up", gate_up)
+    _cuda_contig("out", out, gate_up.dtype)
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I):
+        raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)} does not match out {tuple(out.shape)}")
+    _check("swiglu", _fn("ts_swiglu")(gate_up.data_ptr(), out.data_ptr(), _act_code("out", out), T, I, _stream()))
+
+
+QK_ROPE_MAX_HEAD_DIM = 512
+
+
+def qk_norm_rope_store(
+    qkv: torch.Tensor,
+    q_out: torch.Tensor,
+    k_dst: Optional[torch.Tensor],
+    v_dst: Optional[torch.Tensor],
+    slot_mapping: Optional[torch.Tensor],
+    positions: torch.Tensor,
+    q_norm_weight: Optional[torch.Tensor],
+    k_norm_weight: Optional[torch.Tensor],
+    eps: float,
+    inv_freq: Optional[torch.Tensor],
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+) -> None:
+    """Per-head q/k RMSNorm, rotary encoding, and the key/value store.
+
+    qkv [T,(nq+2nkv)*d]; q_out [T,nq*d]; k_dst/v_dst: the cache pools [slots,nkv,d] (with
+    `slot_mapping` [T] i32, -1 = skip) or dense [T,nkv,d] buffers (slot_mapping None).
+    Norm weights [d] f32 or None (no norm); inv_freq [rot/2] f32 or None (no rotation);
+    a rotation narrower than d leaves the upper dims as they are.
+    """
+    _cuda_contig("qkv", qkv)
+    _cuda_contig("q_out", q_out, qkv.dtype)
+    _cuda_contig("positions", positions, torch.int32)
+    T = qkv.shape[0]
+    nq, nkv, d = num_heads, num_kv_heads, head_dim
+    if d > QK_ROPE_MAX_HEAD_DIM or d % 2:
+        raise KernelError(f"qk_norm_rope_store: head_dim must be even and <= {QK_ROPE_MAX_HEAD_DIM}, got {d}")
+    if qkv.shape[1] != (nq + 2 * nkv) * d or q_out.numel() != T * nq * d:
+        raise KernelError(f"qk_norm_rope_store: qkv {tuple(qkv.shape)} / q_out {tuple(q_out.shape)} do not match heads {nq}+2*{nkv} of {d}")
+    if nkv > 0:
+        for name, c in (("k_dst", k_dst), ("v_dst", v_dst)):
+            if c is None:
+                raise KernelError(f"qk_norm_rope_store: {name} is required")
+            _cuda_contig(name, c, qkv.dtype)
+            if c.shape[-1] != d or c.shape[-2] != nkv:
+                raise KernelError(f"qk_norm_rope_store: {name} must end in [{nkv},{d}], got {tuple(c.shape)}")
+        if slot_mapping is None and (k_dst.numel() < T * nkv * d or v_dst.numel() < T * nkv * d):
+            raise KernelError("qk_norm_rope_store: dense k/v buffers are too small")
+    if slot_mapping is not None:
+        _cuda_contig("slot_mapping", slot_mapping, torch.int32)
+        if slot_mapping.numel() < T:
+            raise KernelError("qk_norm_rope_store: slot_mapping is shorter than the batch")
+    if positions.numel() < T:
+        raise KernelError("qk_norm_rope_store: positions is shorter than the batch")
+    for name, w in (("q_norm_weight", q_norm_weight), ("k_norm_weight", k_norm_weight)):
+        if w is not None:
+            _cuda_contig(name, w, torch.float32)
+            if w.numel() != d:
+                raise KernelError(f"qk_norm_rope_store: {name} must have {d} entries")
+    rot = 0
+    if inv_freq is not None:
+        _cuda_contig("inv_freq", inv_freq, torch.float32)
+        rot = 2 * inv_freq.numel()
+        if rot > d or rot <= 0:
+            raise KernelError(f"qk_norm_rope_store: rotary width {rot} does not fit head_dim {d}")
+    _check("qk_norm_rope_store", _fn("ts_qk_norm_rope_store")(
+        qkv.data_ptr(), _act_code("qkv", qkv), q_out.data_ptr(), _ptr(k_dst), _ptr(v_dst),
+        _ptr(slot_mapping), positions.data_ptr(), _ptr(q_norm_weight), _ptr(k_norm_weight),
+        float(eps), _ptr(inv_freq), rot, T, nq, nkv, d, _stream()))
+
+
+ATTENTION_SIMPLE_MAX_HEAD_DIM = 512
+
+
+def attention_paged_simple(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    out: torch.Tensor,
+    positions: torch.Tensor,
+    seq_index: torch.Tensor,
+    block_table: torch.Tensor,
+    page_size: int,
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    scale: float,
+    window: int = 0,
+) -> None:
+    """Causal attention over the paged cache on CUDA cores (float32 or bfloat16).
+
+    q/out [T,nq*d]; caches [pages,page,nkv,d]; positions, seq_index [T] i32;
+    block_table [B,max_blocks] i32.  window > 0: a query sees its last `window` keys.
+    """
+    _cuda_contig("q", q)
+    _cuda_contig("k_cache", k_cache, q.dtype)
+    _cuda_contig("v_cache", v_cache, q.dtype)
+    _cuda_contig("out", out, q.dtype)
+    _cuda_contig("positions", positions, torch.int32)
+    _cuda_contig("seq_index", seq_index, torch.int32)
+    _cuda_contig("block_table", block_table, torch.int32)
+    T = q.shape[0]
+    nq, nkv, d = num_heads, num_kv_heads, head_dim
+    if d > ATTENTION_SIMPLE_MAX_HEAD_DIM:
+        raise KernelError(f"attention_paged_simple: head_dim must be <= {ATTENTION_SIMPLE_MAX_HEAD_DIM}, got {d}")
+    if nq % nkv:
+        raise KernelError(f"attention: {nq} query heads are no multiple of {nkv} key/value heads")
+    if q.numel() != T * nq * d or out.numel() != T * nq * d:
+        raise KernelError("attention: q/out do not match [T, heads*head_dim]")
+    if tuple(k_cache.shape[-3:]) != (page_size, nkv, d) or k_cache.shape != v_cache.shape:
+        raise KernelError(f"attention: caches must be [pages,{page_size},{nkv},{d}], got {tuple(k_cache.shape)} and {tuple(v_cache.shape)}")
+    if block_table.dim() != 2 or positions.numel() < T or seq_index.numel() < T:
+        raise KernelError("attention: block_table must be [B,max_blocks]; positions and seq_index need T entries")
+    _check("attention_paged_simple", _fn("ts_attention_paged_simple")(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _act_code("q", q), out.data_ptr(),
+        positions.data_ptr(), seq_index.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+        page_size, T, nq, nkv, d, float(scale), int(window), _stream()))
+
+
+def sample(
+    logits: torch.Tensor,
+    temperature: torch.Tensor,
+    keys: Optional[torch.Tensor],
+    out: torch.Tensor,
+) -> None:
+    """One token per row of float32 logits [R,V]: argmax where temperature is 0, else the
+    exponential race keyed by keys[r] (int64, the noise stream of that row).  out [R] i32."""
+    if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be a float32 CUDA matrix with unit inner stride")
+    _cuda_contig("temperature", temperature, torch.float32)
+    _cuda_contig("out", out, torch.int32)
+    R, V = logits.shape
+    if keys is not None:
+        _cuda_contig("keys", keys, torch.int64)
+        if keys.numel() < R:
+            raise KernelError("sample: keys is shorter than the batch")
+    if temperature.numel() < R or out.numel() < R:
+        raise KernelError("sample: temperature/out are shorter than the batch")
+    _check("sample", _fn("ts_sample")(
+        logits.data_ptr(), V, logits.stride(0), temperature.data_ptr(), _ptr(keys), out.data_ptr(), R, _stream()))
+
+
+def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T in true float32 (FFMA)."""
+    for name, t in (("a", a), ("w", w), ("out", out)):
+        if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"sgemm_nt: {name} must be a float32 CUDA matrix with unit inner stride")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"sgemm_nt: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _check("sgemm_nt", _fn("ts_sgemm_nt")(
+        a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), w.stride(0), out.stride(0), _stream()))

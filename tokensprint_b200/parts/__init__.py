@@ -1,0 +1,26 @@
+"""Parts of a layer.  Importing this package registers the built-in ones."""
+
+from tokensprint_b200.parts import attention, blocks, feed_forward, norms, position  # noqa: F401
+from tokensprint_b200.parts.base import (  # noqa: F401
+    BLOCKS,
+    FEED_FORWARDS,
+    MIXERS,
+    NORMS,
+    POSITION_ENCODINGS,
+    Block,
+    BuildContext,
+    CacheNeed,
+    FeedForward,
+    GroupTables,
+    LayerCache,
+    Mixer,
+    Norm,
+    Part,
+    PartSpec,
+    PositionEncoding,
+    StepContext,
+    TensorSpec,
+    build_part,
+    register_part,
+    unregister_part,
+)

@@ -1,0 +1,161 @@
+"""Grouped-query attention over the paged cache, as a mixer part."""
+
+from __future__ import annotations
+
+from typing import Mapping, Optional
+
+import torch
+
+from tokensprint_b200 import ops
+from tokensprint_b200.parts.base import (
+    BuildContext,
+    CacheNeed,
+    LayerCache,
+    Mixer,
+    PartSpec,
+    StepContext,
+    TensorSpec,
+    build_part,
+    register_part,
+)
+from tokensprint_b200.parts.linear import linear
+
+
+@register_part("mixer", "attention")
+class AttentionMixer(Mixer):
+    """q/k/v projections, optional per-head q/k RMSNorm, position encoding, store of keys
+    and values into the cache, causal softmax attention over the cache, output projection
+    (engine/nn/attention.py:164-200).
+
+    Parameters: `hidden_size`, `num_heads`, `num_kv_heads`, `head_dim` (free of the width:
+    num_heads * head_dim need not equal hidden_size), `qk_norm` + `qk_norm_eps`, `window`
+    (0: every earlier key; n: the last n keys, the query's own included), `scale`
+    (default head_dim^-0.5, engine/nn/sdpa.py:56), `position` (a position-encoding spec or
+    None) and the checkpoint names of the tensors.  q, k, v weights are stacked at load
+    into one [(nq + 2 nkv) d, H] matrix.
+    """
+
+    def __init__(
+        self,
+        ctx: BuildContext,
+        *,
+        hidden_size: int,
+        num_heads: int,
+        num_kv_heads: int,
+        head_dim: int,
+        q: str,
+        k: str,
+        v: str,
+        o: str,
+        qk_norm: bool = False,
+        qk_norm_eps: float = 1e-6,
+        q_norm: Optional[str] = None,
+        k_norm: Optional[str] = None,
+        window: int = 0,
+        scale: Optional[float] = None,
+        position: Optional[PartSpec] = None,
+    ) -> None:
+        if num_heads % num_kv_heads:
+            raise ValueError(f"attention: {num_heads} heads are no multiple of {num_kv_heads} key/value heads")
+        if qk_norm and (q_norm is None or k_norm is None):
+            raise ValueError("attention: qk_norm needs the names of both norm weights")
+        self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
+        self.num_kv_heads, self.head_dim = int(num_kv_heads), int(head_dim)
+        self.qk_norm, self.qk_norm_eps = bool(qk_norm), float(qk_norm_eps)
+        self.window = int(window or 0)
+        self.scale = float(scale) if scale is not None else float(head_dim) ** -0.5
+        self.names = {"q": q, "k": k, "v": v, "o": o, "q_norm": q_norm, "k_norm": k_norm}
+        self.position = build_part("position_encoding", position, ctx) if position is not None else None
+        self.dtype = ctx.dtype
+        self.qkv_weight: Optional[torch.Tensor] = None
+        self.o_weight: Optional[torch.Tensor] = None
+        self.q_norm_weight: Optional[torch.Tensor] = None
+        self.k_norm_weight: Optional[torch.Tensor] = None
+
+    def cache_need(self) -> CacheNeed:
+        kind = "window" if self.window > 0 else "full"
+        return CacheNeed(kind=kind, window=self.window, kv_heads=self.num_kv_heads, head_dim=self.head_dim)
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        H, nq, nkv, d = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim
+        specs = [
+            TensorSpec(self.names["q"], (nq * d, H)),
+            TensorSpec(self.names["k"], (nkv * d, H)),
+            TensorSpec(self.names["v"], (nkv * d, H)),
+            TensorSpec(self.names["o"], (H, nq * d)),
+        ]
+        if self.qk_norm:
+            specs.append(TensorSpec(self.names["q_norm"], (d,), "vector"))
+            specs.append(TensorSpec(self.names["k_norm"], (d,), "vector"))
+        if self.position is not None:
+            specs.extend(self.position.tensor_specs())
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        n = self.names
+        self.qkv_weight = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
+        self.o_weight = tensors[n["o"]]
+        if self.qk_norm:
+            self.q_norm_weight = tensors[n["q_norm"]]
+            self.k_norm_weight = tensors[n["k_norm"]]
+        if self.position is not None:
+            self.position.load(tensors)
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
+        if cache.k_pages is None or cache.group < 0:
+            raise ops.KernelError("attention: this mixer needs cache pages (none were bound to its run)")
+        T = x.shape[0]
+        nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
+        tables = step.groups[cache.group]
+        qkv = linear(x, self.qkv_weight)
+        q = torch.empty((T, nq * d), device=x.device, dtype=x.dtype)
+        inv_freq = self.position.rotary_inv_freq() if self.position is not None else None
+        fused = self.position is None or inv_freq is not None
+        if fused and cache.writes:
+            ops.qk_norm_rope_store(
+                qkv, q, cache.k_pages, cache.v_pages, tables.slot_mapping, step.positions,
+                self.q_norm_weight, self.k_norm_weight, self.qk_norm_eps, inv_freq, nq, nkv, d)
+        elif fused:
+            # Reads a cache that another run filled: only the queries are prepared.
+            self._queries_only(qkv, q, step, inv_freq)
+        else:
+            self._unfused(qkv, q, step, cache, tables)
+        out = torch.empty((T, nq * d), device=x.device, dtype=x.dtype)
+        self._attend(q, out, step, cache, tables)
+        return linear(out, self.o_weight)
+
+    # -- attention proper ---------------------------------------------------
+
+    def _attend(self, q, out, step: StepContext, cache: LayerCache, tables) -> None:
+        ops.attention_paged_simple(
+            q, cache.k_pages, cache.v_pages, out, step.positions, step.seq_index, tables.block_table,
+            step.page_size, self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window)
+
+    # -- less common paths ----------------------------------------------------
+
+    def _queries_only(self, qkv, q, step: StepContext, inv_freq) -> None:
+        T = qkv.shape[0]
+        nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
+        k_tmp = torch.empty((T, nkv, d), device=qkv.device, dtype=qkv.dtype)
+        v_tmp = torch.empty((T, nkv, d), device=qkv.device, dtype=qkv.dtype)
+        ops.qk_norm_rope_store(
+            qkv, q, k_tmp, v_tmp, None, step.positions, self.q_norm_weight, self.k_norm_weight,
+            self.qk_norm_eps, inv_freq, nq, nkv, d)
+
+    def _unfused(self, qkv, q, step: StepContext, cache: LayerCache, tables) -> None:
+        """A position encoding that the fused kernel does not know: norm into dense
+        buffers, let the part rewrite q and k, then store keys and values."""
+        T = qkv.shape[0]
+        nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
+        k_tmp = torch.empty((T, nkv, d), device=qkv.device, dtype=qkv.dtype)
+        v_tmp = torch.empty((T, nkv, d), device=qkv.device, dtype=qkv.dtype)
+        ops.qk_norm_rope_store(
+            qkv, q, k_tmp, v_tmp, None, step.positions, self.q_norm_weight, self.k_norm_weight,
+            self.qk_norm_eps, None, nq, nkv, d)
+        self.position.apply(q.view(T, nq, d), k_tmp, step)
+        if cache.writes:
+            kv = torch.cat([k_tmp.view(T, nkv * d), v_tmp.view(T, nkv * d)], dim=1).contiguous()
+            scratch_q = torch.empty((T, 0), device=qkv.device, dtype=qkv.dtype)
+            ops.qk_norm_rope_store(
+                kv, scratch_q, cache.k_pages, cache.v_pages, tables.slot_mapping, step.positions,
+                None, None, self.qk_norm_eps, None, 0, nkv, d)

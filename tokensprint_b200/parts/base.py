@@ -1,0 +1,237 @@
+"""Interfaces of the parts a layer is put together from, and their registries.
+
+A layer is a *block* (the arrangement) around a *mixer* (attention here), a
+*feed-forward* and *norms*; a mixer may use a *position encoding*.  Each kind has a
+registry from a name to a class; a `PartSpec` (name + parameters) picks one, layer by
+layer, so one model can mix different parts.  No part knows which model it is in: it
+gets its sizes and constants as parameters and its tensor names as a table.
+
+Activations are [tokens, width] in the compute dtype (bfloat16 or float32); the
+residual stream is float32.  What a part needs of one step (positions, which request a
+token belongs to, block tables, state slots) comes in a `StepContext`.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Mapping, Optional
+
+import torch
+
+# ---------------------------------------------------------------------------
+# specifications (pure data; safe to build without a GPU)
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    """Which registered part, with which parameters."""
+
+    kind: str
+    params: Mapping[str, Any] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class TensorSpec:
+    """One tensor a part wants from the checkpoint.
+
+    role: "matrix" is cast to the compute dtype; "vector" is held in float32 (a stored
+    float32 stays exact, a stored bfloat16 widens without loss); "table" is held as int32.
+    """
+
+    name: str
+    shape: tuple[int, ...]
+    role: str = "matrix"
+
+
+@dataclass(frozen=True)
+class CacheNeed:
+    """What one run of a mixer needs from the cache manager.
+
+    kind "full": all keys stay; "window": keys older than `window` positions before the
+    next query may be given back; "none": no pages.  `state_shape` asks for a slot of
+    that fixed shape per request (None: no state).
+    """
+
+    kind: str = "none"
+    window: int = 0
+    kv_heads: int = 0
+    head_dim: int = 0
+    state_shape: Optional[tuple[int, ...]] = None
+    state_dtype: torch.dtype = torch.float32
+
+    @property
+    def group_key(self) -> tuple[str, int]:
+        return (self.kind, self.window if self.kind == "window" else 0)
+
+
+# ---------------------------------------------------------------------------
+# what one step brings
+
+
+@dataclass
+class GroupTables:
+    """Block table and new-token slots of one cache group for this step."""
+
+    block_table: torch.Tensor  # [B, max_blocks] i32, -1 where no page is held
+    slot_mapping: torch.Tensor  # [T] i32, page * page_size + offset, -1 = do not store
+
+
+@dataclass
+class StepContext:
+    """Device-side description of one batch of (request, its next tokens)."""
+
+    num_tokens: int
+    num_seqs: int
+    token_ids: torch.Tensor  # [T] i32
+    positions: torch.Tensor  # [T] i32 absolute position of each token in its request
+    seq_index: torch.Tensor  # [T] i32 row of the batch each token belongs to (-1: padding)
+    cu_seqlens_q: torch.Tensor  # [B+1] i32 prefix sums of the tokens per request
+    context_lens: torch.Tensor  # [B] i32 tokens in the cache after this step
+    state_slots: torch.Tensor  # [B] i32 per-request state slot
+    groups: list[GroupTables]
+    page_size: int
+    max_seqlen_q: int
+    max_context_len: int
+    # host copies for parts that plan on the host (toy parts in tests do)
+    host_seq_starts: list[int] = field(default_factory=list)
+    host_seq_lens: list[int] = field(default_factory=list)
+    host_state_slots: list[int] = field(default_factory=list)
+    decode_only: bool = False
+
+
+@dataclass
+class LayerCache:
+    """What one run of a mixer may touch of the cache."""
+
+    group: int = -1  # index into StepContext.groups; -1: no pages
+    k_pages: Optional[torch.Tensor] = None  # [pages, page, kv_heads, head_dim]
+    v_pages: Optional[torch.Tensor] = None
+    state: Optional[torch.Tensor] = None  # [slots, *state_shape]
+    writes: bool = True  # False: reads a cache that another run filled
+
+
+# ---------------------------------------------------------------------------
+# part interfaces
+
+
+class Part:
+    """Base of all parts: declares its tensors and takes them once loaded."""
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return []
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        """`tensors` maps the declared names to device tensors."""
+
+
+class Norm(Part):
+    def forward(
+        self,
+        hidden: torch.Tensor,
+        delta: Optional[torch.Tensor],
+        out: torch.Tensor,
+        row_index: Optional[torch.Tensor] = None,
+    ) -> None:
+        """hidden (float32 residual) += delta if given; out = norm(hidden)."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Either hands rotary parameters to the fused kernel or rewrites q and k itself."""
+
+    def rotary_inv_freq(self) -> Optional[torch.Tensor]:
+        """[rot/2] float32 inverse frequencies for the fused rotate-half kernel, or None."""
+        return None
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, step: StepContext) -> None:
+        """In-place encoding of q [T,nq,d] and k [T,nkv,d] for encodings the kernel lacks."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed()
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    """An arrangement of mixer, feed-forward and norms around the residual stream."""
+
+    mixer: Mixer
+
+    def forward(
+        self,
+        hidden: torch.Tensor,
+        pending: Optional[torch.Tensor],
+        step: StepContext,
+        cache: LayerCache,
+    ) -> Optional[torch.Tensor]:
+        """Runs the layer on the float32 residual `hidden` ([T,H], updated in place).
+
+        `pending` is a branch output not yet added to `hidden` (the next norm adds it
+        in the same pass); the return value is this layer's own pending output.
+        """
+        raise NotImplementedError
+
+
+# ---------------------------------------------------------------------------
+# registries
+
+
+@dataclass
+class BuildContext:
+    """What a part's constructor may ask about the run it is built for."""
+
+    device: torch.device
+    dtype: torch.dtype  # compute dtype: torch.bfloat16 or torch.float32
+
+
+PartFactory = Callable[..., Part]
+
+MIXERS: dict[str, PartFactory] = {}
+FEED_FORWARDS: dict[str, PartFactory] = {}
+NORMS: dict[str, PartFactory] = {}
+POSITION_ENCODINGS: dict[str, PartFactory] = {}
+BLOCKS: dict[str, PartFactory] = {}
+
+_TABLES = {
+    "mixer": MIXERS,
+    "feed_forward": FEED_FORWARDS,
+    "norm": NORMS,
+    "position_encoding": POSITION_ENCODINGS,
+    "block": BLOCKS,
+}
+
+
+def register_part(category: str, name: str, *, replace: bool = False) -> Callable[[PartFactory], PartFactory]:
+    """Decorator: `@register_part("mixer", "attention")` on a class or factory.
+
+    The factory is called as `factory(build_ctx, **spec.params)`.
+    """
+    table = _TABLES[category]
+
+    def _register(factory: PartFactory) -> PartFactory:
+        if name in table and not replace:
+            raise ValueError(f"{category} '{name}' already registered.")
+        table[name] = factory
+        return factory
+
+    return _register
+
+
+def unregister_part(category: str, name: str) -> None:
+    _TABLES[category].pop(name, None)
+
+
+def build_part(category: str, spec: PartSpec, ctx: BuildContext) -> Part:
+    table = _TABLES[category]
+    if spec.kind not in table:
+        raise ValueError(f"Unknown {category} '{spec.kind}'. Registered: {sorted(table)}")
+    return table[spec.kind](ctx, **dict(spec.params))
