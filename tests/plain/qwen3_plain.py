@@ -90,40 +90,45 @@ def attention_layer(
     rope_theta: float,
     eps: float,
     window: Optional[int] = None,
+    rounding=None,
 ) -> torch.Tensor:
     """q/k/v projections, reshape to heads, q_norm/k_norm over head_dim (one weight for all
     heads), RoPE on q and k, attention, output projection  (engine/nn/attention.py:164-200)."""
+    r = rounding or (lambda t: t)
     T = x.shape[0]
-    q = (x @ w[prefix + "q_proj.weight"].T).view(T, num_heads, head_dim)
-    k = (x @ w[prefix + "k_proj.weight"].T).view(T, num_kv_heads, head_dim)
-    v = (x @ w[prefix + "v_proj.weight"].T).view(T, num_kv_heads, head_dim)
+    q = r(x @ w[prefix + "q_proj.weight"].T).view(T, num_heads, head_dim)
+    k = r(x @ w[prefix + "k_proj.weight"].T).view(T, num_kv_heads, head_dim)
+    v = r(x @ w[prefix + "v_proj.weight"].T).view(T, num_kv_heads, head_dim)
     q = rms_norm(q, w[prefix + "q_norm.weight"], eps)
     k = rms_norm(k, w[prefix + "k_norm.weight"], eps)
     angles = rope_angles(positions, head_dim, rope_theta)
-    q, k = apply_rope(q, angles), apply_rope(k, angles)
-    o = causal_attention(q, k, v, scale=head_dim**-0.5, window=window)
-    return o.reshape(T, num_heads * head_dim) @ w[prefix + "o_proj.weight"].T
+    q, k = r(apply_rope(q, angles)), r(apply_rope(k, angles))
+    o = r(causal_attention(q, k, v, scale=head_dim**-0.5, window=window))
+    return r(o.reshape(T, num_heads * head_dim) @ w[prefix + "o_proj.weight"].T)
 
 
-def swiglu_ffn(x: torch.Tensor, w: Mapping[str, torch.Tensor], prefix: str) -> torch.Tensor:
+def swiglu_ffn(x: torch.Tensor, w: Mapping[str, torch.Tensor], prefix: str, rounding=None) -> torch.Tensor:
     """down(silu(gate(x)) * up(x)), silu(z) = z * sigmoid(z)  (engine/nn/layers.py:61-66)."""
-    g = x @ w[prefix + "gate_proj.weight"].T
-    u = x @ w[prefix + "up_proj.weight"].T
-    return (g * torch.sigmoid(g) * u) @ w[prefix + "down_proj.weight"].T
+    r = rounding or (lambda t: t)
+    g = r(x @ w[prefix + "gate_proj.weight"].T)
+    u = r(x @ w[prefix + "up_proj.weight"].T)
+    return r(r(g * torch.sigmoid(g) * u) @ w[prefix + "down_proj.weight"].T)
 
 
 def block(
-    h: torch.Tensor, w: Mapping[str, torch.Tensor], layer: int, positions: Sequence[int], cfg: Mapping, window: Optional[int]
+    h: torch.Tensor, w: Mapping[str, torch.Tensor], layer: int, positions: Sequence[int], cfg: Mapping,
+    window: Optional[int], rounding=None,
 ) -> torch.Tensor:
     """Pre-norm: h = h + Attn(RMSNorm(h)); h = h + FFN(RMSNorm(h))  (engine/nn/layers.py:111-121)."""
     p = f"model.layers.{layer}."
     eps = cfg["rms_norm_eps"]
+    r = rounding or (lambda t: t)
     a = attention_layer(
-        rms_norm(h, w[p + "input_layernorm.weight"], eps), w, p + "self_attn.", positions,
+        r(rms_norm(h, w[p + "input_layernorm.weight"], eps)), w, p + "self_attn.", positions,
         num_heads=cfg["num_attention_heads"], num_kv_heads=cfg["num_key_value_heads"],
-        head_dim=cfg["head_dim"], rope_theta=cfg["rope_theta"], eps=eps, window=window)
+        head_dim=cfg["head_dim"], rope_theta=cfg["rope_theta"], eps=eps, window=window, rounding=rounding)
     h = h + a
-    f = swiglu_ffn(rms_norm(h, w[p + "post_attention_layernorm.weight"], eps), w, p + "mlp.")
+    f = swiglu_ffn(r(rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)), w, p + "mlp.", rounding)
     return h + f
 
 
@@ -142,18 +147,29 @@ def layer_windows(cfg: Mapping) -> list[Optional[int]]:
 
 
 def forward_logits(
-    weights: Mapping[str, torch.Tensor], cfg: Mapping, token_ids: Sequence[int], dtype: torch.dtype = torch.float64
+    weights: Mapping[str, torch.Tensor], cfg: Mapping, token_ids: Sequence[int], dtype: torch.dtype = torch.float64,
+    rounding=None,
 ) -> torch.Tensor:
     """Logits [T, V] of one whole sequence: embedding, blocks, final norm, head (tied: the
-    embedding table)  (engine/model.py:58-95, engine/nn/layers.py:22-23)."""
-    w = {k: v.to(dtype) for k, v in weights.items()}
+    embedding table)  (engine/model.py:58-95, engine/nn/layers.py:22-23).
+
+    `rounding` (a function tensor -> tensor) is applied to every matrix weight and to every
+    activation that one operation hands to the next, the residual stream excepted.  With
+    `round_to_bfloat16` this shows how far 8-bit mantissas alone move the logits of a given
+    model and input: the yardstick for a bfloat16 engine's tolerance."""
+    r = rounding or (lambda t: t)
+    w = {k: (v.to(dtype) if v.dim() == 1 else r(v.to(dtype))) for k, v in weights.items()}
     positions = list(range(len(token_ids)))
     h = embedding(w["model.embed_tokens.weight"], token_ids)
     for i, window in enumerate(layer_windows(cfg)):
-        h = block(h, w, i, positions, cfg, window)
-    h = rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"])
+        h = block(h, w, i, positions, cfg, window, rounding)
+    h = r(rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"]))
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") else w["lm_head.weight"]
     return h @ head.T
+
+
+def round_to_bfloat16(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.bfloat16).to(t.dtype)
 
 
 # ---------------------------------------------------------------------------

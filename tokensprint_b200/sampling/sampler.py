@@ -1,0 +1,52 @@
+"""Greedy and temperature sampling on the device.
+
+The reference samples with an exponential race over the softmax (engine/generation/
+sampler.py:11-16) from torch's global random stream; greedy is refused there
+(engine/generation/config.py:13-15).  Here temperature 0 is greedy, and the race's noise
+is a pure function of (seed, request's stream, position of the new token, vocabulary
+index), so a request draws the same tokens whatever it is batched with and however often
+it is preempted and recomputed.
+"""
+
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+
+from tokensprint_b200 import ops
+
+_MASK = (1 << 64) - 1
+
+
+def _mix64(z: int) -> int:
+    z = (z + 0x9E3779B97F4A7C15) & _MASK
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK
+    return z ^ (z >> 31)
+
+
+def sample_key(seed: int, stream: int, position: int) -> int:
+    """The 64-bit key of one draw, as a signed integer (it travels in an int64 tensor)."""
+    k = _mix64(_mix64(seed & _MASK) ^ (stream & _MASK))
+    k = _mix64(k ^ (position & _MASK))
+    return k - (1 << 64) if k >= (1 << 63) else k
+
+
+class Sampler:
+    def __init__(self, device: torch.device | str) -> None:
+        self.device = torch.device(device)
+
+    @torch.inference_mode()
+    def sample(self, logits: torch.Tensor, temperatures: Sequence[float], keys: Sequence[int]) -> list[int]:
+        """One token id per row of float32 logits [R, V]."""
+        R = logits.shape[0]
+        if len(temperatures) != R or len(keys) != R:
+            raise ValueError(f"{R} rows of logits, {len(temperatures)} temperatures, {len(keys)} keys")
+        if R == 0:
+            return []
+        temps = torch.tensor(list(temperatures), dtype=torch.float32).to(self.device, non_blocking=True)
+        key_t = torch.tensor(list(keys), dtype=torch.int64).to(self.device, non_blocking=True)
+        out = torch.empty(R, dtype=torch.int32, device=self.device)
+        ops.sample(logits, temps, key_t, out)
+        return out.tolist()
