@@ -1,0 +1,356 @@
+"""Decode and prefill throughput of the engine on one B200: Qwen3-8B sizes, random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  A "step" is one decode step of a batch of 8 requests (1,024-token
+random prompts, context limit 4,096, cache pages of 16 tokens).  `value` is decoded tokens
+a second, timed on the device with CUDA events around K steps after W warm-up steps;
+`e2e` is the same through `LLMEngine.add_request/step` with host token ids in and sampled
+ids out every step.  `prefill` is one 2,048-token prompt; `roofline` compares the decode
+step's bytes (every weight once, the cache of the live requests) with the HBM peak;
+`points` adds decode at batch 1 and 64.  The weights (16 GB) are far larger than the L2,
+so no flush is needed between steps.  More than one GPU is not supported.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+MODEL_NAME = "qwen/qwen3-8b"
+PROMPT_LEN = 1024
+PREFILL_TOKENS = 2048
+CONTEXT_LEN = 4096
+PAGE_SIZE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def load_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            d = json.loads(path.read_text())
+            out = {"source": "measured"}
+            for key in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+                if key in d:
+                    out[key] = float(d[key])
+            if "hbm_gbs" in out and "bf16_tflops" in out:
+                return out
+        except (ValueError, OSError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons through NVML while a timed region runs."""
+
+    REASONS = {
+        0x8: "hw_slowdown",
+        0x40: "hw_thermal_slowdown",
+        0x20: "sw_thermal_slowdown",
+        0x4: "sw_power_cap",
+        0x80: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, index: int = 0, period: float = 0.1) -> None:
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self.period = period
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nvml = None
+
+    def _run(self) -> None:
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(self._nvml.nvmlDeviceGetClockInfo(self._handle, self._nvml.NVML_CLOCK_SM)))
+                mask = int(self._nvml.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+            self._thread = None
+
+    def summary(self) -> dict:
+        s = sorted(self.samples)
+        return {
+            "sm_mhz": s[len(s) // 2] if s else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+        }
+
+
+def prefill_flops(cfg, T: int) -> float:
+    """GEMM flops of T tokens through every layer, causal attention over T keys, head for one row."""
+    H, I, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+    nq, nkv, L = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.num_hidden_layers
+    per_token = 2 * (H * (nq + 2 * nkv) * d + nq * d * H + 3 * H * I)
+    attention = 4 * nq * d * (T * (T + 1) / 2)
+    return L * (per_token * T + attention) + 2 * H * cfg.vocab_size
+
+
+def random_ids(n: int, vocab: int, seed: int) -> list[int]:
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def measure_decode(runner, cfg, batch: int, steps: int, warmup: int, clocks=None):
+    """Device-timed decode: `batch` requests prefilled with PROMPT_LEN tokens, then
+    warmup + steps single-token steps with sampling.  Returns (ms per step, mean context)."""
+    import torch
+
+    from tokensprint_b200 import ops
+    from tokensprint_b200.engine.runner import StepEntry
+
+    cm = runner.cache_manager
+    vocab = cfg.vocab_size
+    reqs = []
+    for b in range(batch):
+        rc = cm.admit(("bench", batch, b))
+        reqs.append(rc)
+    per_step = max(1, 8192 // PROMPT_LEN)
+    for i in range(0, batch, per_step):
+        entries = []
+        for b in range(i, min(batch, i + per_step)):
+            cm.extend(reqs[b], 0, PROMPT_LEN)
+            entries.append(StepEntry(reqs[b], random_ids(PROMPT_LEN, vocab, 100 + b), 0, []))
+        runner.step(entries)
+    temps = torch.full((batch,), 0.6, dtype=torch.float32, device=runner.device)
+    keys = torch.arange(batch, dtype=torch.int64, device=runner.device)
+    sampled = torch.empty(batch, dtype=torch.int32, device=runner.device)
+    next_tokens = [random_ids(warmup + steps, vocab, 500 + b) for b in range(batch)]
+
+    def one_step(i: int) -> None:
+        pos = PROMPT_LEN + i
+        entries = []
+        for b in range(batch):
+            cm.extend(reqs[b], pos, pos + 1)
+            entries.append(StepEntry(reqs[b], [next_tokens[b][i]], pos, [0]))
+        logits = runner.step(entries)
+        ops.sample(logits, temps, keys, sampled)
+
+    for i in range(warmup):
+        one_step(i)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = ops.launch_count + getattr(runner, "graph_launches", 0)
+    if clocks is not None:
+        clocks.__enter__()
+    start.record()
+    for i in range(warmup, warmup + steps):
+        one_step(i)
+    end.record()
+    torch.cuda.synchronize()
+    if clocks is not None:
+        clocks.__exit__()
+    launches = ops.launch_count + getattr(runner, "graph_launches", 0) - launches0
+    ms = start.elapsed_time(end) / steps
+    mean_ctx = PROMPT_LEN + warmup + (steps - 1) / 2 + 1
+    for rc in reqs:
+        runner.free(rc)
+    return ms, mean_ctx, launches
+
+
+def measure_prefill(runner, cfg, reps: int = 5):
+    import torch
+
+    from tokensprint_b200.engine.runner import StepEntry
+
+    cm = runner.cache_manager
+    times = []
+    for r in range(reps + 2):
+        rc = cm.admit(("prefill", r))
+        cm.extend(rc, 0, PREFILL_TOKENS)
+        entry = StepEntry(rc, random_ids(PREFILL_TOKENS, cfg.vocab_size, 900 + r), 0, [PREFILL_TOKENS - 1])
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.step([entry])
+        end.record()
+        torch.cuda.synchronize()
+        if r >= 2:
+            times.append(start.elapsed_time(end))
+        runner.free(rc)
+    times.sort()
+    return times[len(times) // 2]
+
+
+def measure_e2e(model, cfg, batch: int, steps: int, warmup: int):
+    """Decode through the public entry point: LLMEngine.add_request + step(), token ids from
+    host lists, sampled ids back on the host every step."""
+    import torch
+
+    from tokensprint_b200.config.engine_config import Config, SamplingParams
+    from tokensprint_b200.engine.llm_engine import LLMEngine
+
+    pages = batch * (-(-(PROMPT_LEN + warmup + steps + 8) // PAGE_SIZE)) + 64
+    config = Config(model=str(ROOT), max_model_len=CONTEXT_LEN, max_num_seqs=max(batch, 8), max_num_batched_tokens=8192,
+                    kvcache_block_size=PAGE_SIZE, num_kvcache_blocks=pages, chunked_prefill=True, dtype="bfloat16")
+    engine = LLMEngine(model, config)
+    sp = SamplingParams(temperature=0.6, max_tokens=warmup + steps + 4, ignore_eos=True, seed=1)
+    for b in range(batch):
+        engine.add_request(random_ids(PROMPT_LEN, cfg.vocab_size, 300 + b), sp)
+    while any(s.num_cached_tokens < s.num_prompt_tokens for s in list(engine.scheduler.running) + list(engine.scheduler.waiting)) or engine.scheduler.waiting:
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    runner = engine.model_runner
+    h2d0 = runner.h2d_bytes
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        engine.step()
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - t0
+    h2d = (runner.h2d_bytes - h2d0) / steps + batch * 12  # + temperatures (4 B) and keys (8 B) per row
+    for seq in list(engine.scheduler.running):
+        engine.scheduler.abort(seq)
+    del engine
+    return batch * steps / elapsed, int(h2d), batch * 4
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from tokensprint_b200.config.registry import get_model_config, get_preset_dict
+    from tokensprint_b200.config.model_config import Qwen3Config
+    from tokensprint_b200.engine.runner import ModelRunner
+    from tokensprint_b200.models.api import random_model
+
+    torch.cuda.set_device(0)
+    peaks = load_peaks()
+    full_cfg = get_model_config(MODEL_NAME)
+    cfg = full_cfg
+    if args.layers and args.layers < full_cfg.num_hidden_layers:
+        d = get_preset_dict(MODEL_NAME)
+        d["num_hidden_layers"] = args.layers
+        cfg = Qwen3Config.from_dict(d)
+    model = random_model(cfg, seed=0, dtype="bfloat16", generate_on_device=True)
+    torch.cuda.synchronize()
+
+    max_batch = 64 if not args.skip_points else args.batch
+    tokens_per_req = PROMPT_LEN + args.warmup + max(args.steps, 32) + 16
+    pages = max_batch * (-(-tokens_per_req // PAGE_SIZE)) + PREFILL_TOKENS // PAGE_SIZE + 64
+    runner = ModelRunner(model, page_size=PAGE_SIZE, num_pages=pages, num_slots=max_batch + 8,
+                         max_num_batched_tokens=8192)
+
+    clocks = ClockSampler()
+    ms, mean_ctx, launches = measure_decode(runner, cfg, args.batch, args.steps, args.warmup, clocks)
+    value = args.batch * 1000.0 / ms
+
+    kv_bytes_per_token = sum(runner.page_bytes) / PAGE_SIZE
+    step_bytes = model.weight_bytes() + args.batch * mean_ctx * kv_bytes_per_token
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            pms, _, _ = measure_decode(runner, cfg, b, min(args.steps, 32), min(args.warmup, 4))
+            points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
+
+    pf_ms = measure_prefill(runner, cfg)
+    pf_flops = prefill_flops(cfg, PREFILL_TOKENS)
+    pf_frac = pf_flops / (pf_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)
+
+    del runner
+    torch.cuda.empty_cache()
+    e2e_value, h2d, d2h = measure_e2e(model, cfg, args.batch, args.steps, args.warmup)
+
+    return {
+        "metric": "decode tokens/s, Qwen3-8B sizes, batch 8, 1 B200",
+        "value": round(value, 1),
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(ms, 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic: seeded random weights N(0,0.02), uniform-random token ids",
+        "impl": "ours",
+        "config": {
+            "model": "qwen3-8b",
+            "layers": cfg.num_hidden_layers,
+            "layers_full": full_cfg.num_hidden_layers,
+            "hidden": cfg.hidden_size,
+            "heads": cfg.num_attention_heads,
+            "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim,
+            "intermediate": cfg.intermediate_size,
+            "vocab": cfg.vocab_size,
+            "global_batch": args.batch,
+            "prompt_len": PROMPT_LEN,
+            "seq_len": CONTEXT_LEN,
+            "kv_block": PAGE_SIZE,
+            "parallelism": "single GPU",
+            "l2": "inputs larger than L2 (16 GB of weights per step)",
+            "peaks": peaks["source"],
+        },
+        "clocks": clocks.summary(),
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "prefill": {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3), "frac": round(pf_frac, 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": points,
+    }
+
+
+def run_reference(args) -> dict:
+    return {"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref"}
+
+
+def main() -> int:
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=64)
+    p.add_argument("--warmup", type=int, default=8)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in the record)")
+    p.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
+    args = p.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

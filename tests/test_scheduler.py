@@ -1,0 +1,196 @@
+"""The scheduler's decisions on the host: admission, portions, decoding, preemption, finishing (no GPU).
+
+Modelled on the reference's tests/test_scheduler_invariants.py and
+tests/test_scheduler_edge_cases.py, restated at a page size of 16.
+"""
+
+import random
+
+import pytest
+
+from tokensprint_b200.cache.manager import CacheManager, GroupSpec
+from tokensprint_b200.config.engine_config import Config, SamplingParams
+from tokensprint_b200.engine.scheduler import Scheduler
+from tokensprint_b200.engine.sequence import Sequence, SequenceStatus
+
+
+def make_scheduler(tmp_path, *, num_pages=8, page_size=16, budget=512, max_num_seqs=8, max_model_len=4096,
+                   chunked=False, eos=-1, groups=None):
+    config = Config(model=str(tmp_path), num_kvcache_blocks=num_pages, kvcache_block_size=page_size,
+                    max_num_batched_tokens=budget, max_num_seqs=max_num_seqs, max_model_len=max_model_len,
+                    chunked_prefill=chunked, eos=eos)
+    groups = groups or [GroupSpec("full")]
+    cm = CacheManager(groups, page_size, [num_pages] * len(groups), max_num_seqs)
+    return Scheduler(config, cm)
+
+
+def seq(n, **kw):
+    return Sequence([1] * n, SamplingParams(**kw))
+
+
+def check_queues(s: Scheduler):
+    assert not (set(map(id, s.waiting)) & set(map(id, s.running)))
+    assert all(x.status == SequenceStatus.WAITING and x.cache is None for x in s.waiting)
+    assert all(x.status == SequenceStatus.RUNNING and x.cache is not None for x in s.running)
+    s.cache_manager.check_invariants()
+
+
+def test_admission_sets_the_counters(tmp_path):
+    s = make_scheduler(tmp_path, num_pages=16)
+    a = seq(200)
+    s.add_sequence(a)
+    out = s.schedule()
+    assert out == [a] and a.status == SequenceStatus.RUNNING
+    assert a.num_cached_tokens == 0 and a.num_new_tokens == 200
+    assert len(a.cache.tables[0]) == 13
+    check_queues(s)
+    s.postprocess(out, [7], [0])
+    assert a.num_cached_tokens == 200 and a.num_new_tokens == 0 and len(a) == 201
+    assert len(a.cache.tables[0]) == 13
+    out = s.schedule()
+    assert a.num_new_tokens == 1
+    check_queues(s)
+
+
+def test_finish_frees_everything(tmp_path):
+    s = make_scheduler(tmp_path, eos=9)
+    a, b, c = seq(10, max_tokens=1), seq(10), seq(10, ignore_eos=True, max_tokens=2)
+    for x in (a, b, c):
+        s.add_sequence(x)
+    out = s.schedule()
+    s.postprocess(out, [3, 9, 9], [0, 1, 2])
+    assert a.is_finished and b.is_finished and not c.is_finished  # max_tokens, eos, eos ignored
+    assert a.cache is None and b.cache is None and s.running == [c]
+    assert s.cache_manager.pages_in_use() == 1
+    out = s.schedule()
+    s.postprocess(out, [9], [0])
+    assert c.is_finished and s.is_finished() and s.cache_manager.pages_in_use() == 0
+    check_queues(s)
+
+
+def test_max_model_len_finishes_and_refuses(tmp_path):
+    s = make_scheduler(tmp_path, max_model_len=12)
+    with pytest.raises(ValueError, match="exceeds max_model_len"):
+        s.add_sequence(seq(12))
+    a = seq(11, max_tokens=50)
+    s.add_sequence(a)
+    s.postprocess(s.schedule(), [5], [0])
+    assert a.is_finished and len(a) == 12
+
+
+def test_chunked_prefill_cuts_portions_under_the_budget(tmp_path):
+    s = make_scheduler(tmp_path, num_pages=64, budget=128, chunked=True)
+    a, b = seq(200), seq(100)
+    s.add_sequence(a); s.add_sequence(b)
+    out = s.schedule()
+    assert out == [a] and a.num_new_tokens == 128  # the budget is spent on the first
+    s.postprocess(out, [], [])
+    out = s.schedule()
+    assert out == [a, b] and a.num_new_tokens == 72 and b.num_new_tokens == 56
+    s.postprocess(out, [4], [0])  # a reached its end, b did not
+    out = s.schedule()
+    assert a.num_new_tokens == 1 and b.num_new_tokens == 44
+    check_queues(s)
+
+
+def test_without_chunking_a_prompt_waits_for_a_step_it_fits(tmp_path):
+    s = make_scheduler(tmp_path, num_pages=64, budget=128, chunked=False)
+    a, b = seq(100), seq(100)
+    s.add_sequence(a); s.add_sequence(b)
+    assert s.schedule() == [a]  # b does not fit the remaining 28 tokens
+    s.postprocess([a], [4], [0])
+    assert s.schedule() == [a, b]
+    with pytest.raises(ValueError, match="could never be scheduled"):
+        s.add_sequence(seq(200))
+
+
+def test_a_prompt_larger_than_the_pool_is_refused_when_added(tmp_path):
+    s = make_scheduler(tmp_path, num_pages=4, budget=4096)
+    with pytest.raises(ValueError, match="could never be scheduled"):
+        s.add_sequence(seq(64))  # 65 positions need 5 pages
+    s.add_sequence(seq(63))
+
+
+def test_out_of_pages_preempts_the_last_running_request(tmp_path):
+    s = make_scheduler(tmp_path, num_pages=4, budget=4096)
+    a, b = seq(32), seq(32)
+    s.add_sequence(a); s.add_sequence(b)
+    out = s.schedule()
+    assert out == [a, b] and s.cache_manager.pages_in_use() == 4
+    s.postprocess(out, [5, 6], [0, 1])
+    out = s.schedule()  # a needs a third page: b, the last, is preempted and gives its pages
+    assert out == [a] and b.status == SequenceStatus.WAITING and s.waiting[0] is b
+    assert b.cache is None and b.num_cached_tokens == 0 and b.num_preemptions == 1 and s.num_preemptions == 1
+    assert len(b) == 33  # keeps its sampled token; it is recomputed with the prompt
+    check_queues(s)
+    s.postprocess(out, [7], [0])
+    # nothing is admitted in the step of a preemption; in the next, b does not fit beside a (3 + 3 pages)
+    out = s.schedule()
+    assert out == [a]
+    a.max_tokens = 3
+    s.postprocess(out, [8], [0])
+    assert a.is_finished
+    out = s.schedule()
+    assert out == [b] and b.num_new_tokens == 33 and b.num_cached_tokens == 0
+    check_queues(s)
+
+
+def test_a_request_that_outgrows_the_pool_alone_raises(tmp_path):
+    s = make_scheduler(tmp_path, num_pages=1, budget=4096)
+    a = seq(15, max_tokens=10)
+    s.add_sequence(a)
+    s.postprocess(s.schedule(), [2], [0])  # 15 cached, 16 known
+    s.postprocess(s.schedule(), [2], [0])  # 16 cached: the page is full
+    with pytest.raises(RuntimeError, match="empty schedule"):
+        s.schedule()  # the 17th position needs a second page: it preempts itself
+    assert a.status == SequenceStatus.WAITING and s.cache_manager.pages_in_use() == 0
+    # with a second page it goes on
+    s2 = make_scheduler(tmp_path, num_pages=2, budget=4096)
+    b = seq(15, max_tokens=10)
+    s2.add_sequence(b)
+    s2.postprocess(s2.schedule(), [2], [0])
+    s2.postprocess(s2.schedule(), [2], [0])
+    assert s2.schedule() == [b] and b.num_new_tokens == 1 and len(b.cache.tables[0]) == 2
+
+
+def test_sequence_slots_limit_admission(tmp_path):
+    s = make_scheduler(tmp_path, num_pages=64, max_num_seqs=2, budget=4096)
+    xs = [seq(5) for _ in range(3)]
+    for x in xs:
+        s.add_sequence(x)
+    assert s.schedule() == xs[:2]
+    s.postprocess(xs[:2], [1, 1], [0, 1])
+    assert s.schedule() == xs[:2]
+
+
+def test_window_groups_free_pages_while_decoding(tmp_path):
+    s = make_scheduler(tmp_path, num_pages=6, budget=4096, groups=[GroupSpec("full"), GroupSpec("window", 20)])
+    a = seq(60, max_tokens=30)
+    s.add_sequence(a)
+    s.postprocess(s.schedule(), [1], [0])
+    for _ in range(10):
+        s.postprocess(s.schedule(), [1], [0])
+    assert sum(p >= 0 for p in a.cache.tables[1]) <= 3 and sum(p >= 0 for p in a.cache.tables[0]) == 5
+    check_queues(s)
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_workloads_finish_with_nothing_held(tmp_path, seed):
+    rng = random.Random(seed)
+    s = make_scheduler(tmp_path, num_pages=rng.randint(12, 30), budget=rng.choice([32, 64, 256]), chunked=True,
+                       max_num_seqs=rng.randint(2, 6), eos=0)
+    seqs = [Sequence([rng.randint(1, 50) for _ in range(rng.randint(1, 90))],
+                     SamplingParams(max_tokens=rng.randint(1, 40), ignore_eos=rng.random() < 0.5)) for _ in range(12)]
+    for x in seqs:
+        s.add_sequence(x)
+    steps = 0
+    while not s.is_finished():
+        out = s.schedule()
+        assert sum(x.num_new_tokens for x in out) <= s.max_num_batched_tokens
+        need = [i for i, x in enumerate(out) if x.num_cached_tokens + x.num_new_tokens == len(x)]
+        s.postprocess(out, [rng.randint(0, 20) for _ in need], need)
+        check_queues(s)
+        steps += 1
+        assert steps < 5000
+    assert all(x.is_finished for x in seqs)
+    assert s.cache_manager.pages_in_use() == 0 and len(s.cache_manager.free_slots) == s.cache_manager.num_slots

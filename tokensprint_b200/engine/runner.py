@@ -118,6 +118,7 @@ class ModelRunner:
         self._pinned_events: list[Optional[torch.cuda.Event]] = []
         self._pinned_next = 0
         self.steps_run = 0
+        self.h2d_bytes = 0  # bytes of step inputs copied to the device so far
 
     # -- sizing ---------------------------------------------------------------------
 
@@ -223,6 +224,7 @@ class ModelRunner:
 
         dev = torch.empty(layout.total, dtype=torch.int32, device=self.device)
         dev.copy_(pinned[: layout.total], non_blocking=True)
+        self.h2d_bytes += layout.total * 4
         ev = torch.cuda.Event()
         ev.record()
         self._pinned_events[slot_i] = ev

@@ -67,8 +67,14 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+# Launches of this library's kernels since import (library GEMMs are not counted).
+launch_count = 0
+
+
 def _check(name: str, status: int) -> None:
+    global launch_count
     if status == 0:
+        launch_count += 1
         return
     if status == -1:
         raise KernelError(f"{name}: bad argument")
