@@ -1,0 +1,361 @@
+"""Each kernel alone against a plain reference, at sizes other than the engine tests use."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from tests.plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
+    got, want = got.double().cpu(), want.double().cpu()
+    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
+TOL = {torch.float32: 2e-6, torch.bfloat16: 1e-2}
+
+
+# ---------------------------------------------------------------------------
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("V,H,T", [(37, 50, 9), (1000, 1032, 3)])
+def test_embed_gather(dtype, V, H, T):
+    from tokensprint_b200 import ops
+
+    table = torch.randn(V, H, device=DEV).to(dtype)
+    ids = torch.randint(0, V, (T,), device=DEV, dtype=torch.int32)
+    hidden = torch.empty(T, H, device=DEV)
+    ops.embed_gather(hidden, table, ids)
+    assert torch.equal(hidden.cpu(), plain.embedding(table.float().cpu(), ids.tolist()))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,eps", [(5, 96, 1e-5), (3, 1000, 1e-6), (2, 4104, 1e-3), (1, 7, 1e-6)])
+def test_add_rmsnorm(dtype, T, H, eps):
+    from tokensprint_b200 import ops
+
+    hidden = torch.randn(T, H, device=DEV) * 3
+    delta = torch.randn(T, H, device=DEV).to(dtype)
+    w = 1 + 0.1 * torch.randn(H, device=DEV)
+    out = torch.empty(T, H, device=DEV, dtype=dtype)
+    h0 = hidden.clone()
+    ops.add_rmsnorm(hidden, delta, w, out, eps)
+    want_h = h0.double() + delta.double()
+    assert rel_err(hidden, want_h) < 2e-7
+    assert rel_err(out, plain.rms_norm(want_h.cpu(), w.double().cpu(), eps)) < TOL[dtype]
+    # without a delta the residual is untouched; with row_index only those rows are read
+    h1 = hidden.clone()
+    ops.add_rmsnorm(hidden, None, w, out, eps)
+    assert torch.equal(hidden, h1)
+    rows = torch.tensor([T - 1, 0], device=DEV, dtype=torch.int32)
+    out2 = torch.empty(2, H, device=DEV, dtype=dtype)
+    ops.add_rmsnorm(hidden, delta, w, out2, eps, rows)
+    assert torch.equal(hidden, h1)
+    want = plain.rms_norm((h1.double() + delta.double()).cpu()[[T - 1, 0]], w.double().cpu(), eps)
+    assert rel_err(out2, want) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(dtype):
+    from tokensprint_b200 import ops
+
+    T, I = 7, 136
+    gu = (torch.randn(T, 2 * I, device=DEV) * 4).to(dtype)
+    out = torch.empty(T, I, device=DEV, dtype=dtype)
+    ops.swiglu(gu, out)
+    g, u = gu[:, :I].double().cpu(), gu[:, I:].double().cpu()
+    assert rel_err(out, g * torch.sigmoid(g) * u) < TOL[dtype]
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 5, 3), (70, 130, 100), (257, 64, 1025)])
+def test_sgemm_is_true_float32(M, N, K):
+    from tokensprint_b200 import ops
+
+    a = torch.randn(M, K, device=DEV)
+    w = torch.randn(N, K, device=DEV)
+    out = torch.empty(M, N, device=DEV)
+    ops.sgemm_nt(a, w, out)
+    want = a.double() @ w.double().T
+    # float32 products summed in float32: error grows like sqrt(K) * 2^-24, far below any
+    # reduced-precision matrix mode (2^-11 per product)
+    assert float((out.double() - want).abs().max()) < 4e-7 * math.sqrt(K) * float(want.abs().max())
+    # a row's result does not depend on the rows beside it
+    out1 = torch.empty(1, N, device=DEV)
+    ops.sgemm_nt(a[M - 1 :], w, out1)
+    assert torch.equal(out1[0], out[M - 1])
+
+
+# ---------------------------------------------------------------------------
+# q/k norm + rope + store
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,d,theta,rot", [(5, 1, 48, 5e4, 48), (4, 2, 16, 1e4, 16), (3, 3, 80, 1e6, 32), (8, 2, 256, 1e6, 256)])
+def test_qk_norm_rope_store(dtype, nq, nkv, d, theta, rot):
+    from tokensprint_b200 import ops
+
+    T, page, pages = 11, 4, 9
+    eps = 1e-5
+    qkv = torch.randn(T, (nq + 2 * nkv) * d, device=DEV).to(dtype)
+    positions = torch.tensor([0, 1, 2, 3, 500, 501, 40000, 7, 8, 9, 10], device=DEV, dtype=torch.int32)
+    slots = torch.randperm(pages * page, device=DEV)[:T].to(torch.int32)
+    slots[5] = -1  # not stored
+    qw = 1 + 0.2 * torch.randn(d, device=DEV)
+    kw = 1 + 0.2 * torch.randn(d, device=DEV)
+    inv_freq = plain.rope_inverse_frequencies(rot, theta).to(DEV)
+    q_out = torch.empty(T, nq * d, device=DEV, dtype=dtype)
+    kc = torch.full((pages, page, nkv, d), 7.0, device=DEV, dtype=dtype)
+    vc = torch.full((pages, page, nkv, d), 7.0, device=DEV, dtype=dtype)
+    ops.qk_norm_rope_store(qkv, q_out, kc, vc, slots, positions, qw, kw, eps, inv_freq, nq, nkv, d)
+
+    x = qkv.double().cpu()
+    q = x[:, : nq * d].view(T, nq, d)
+    k = x[:, nq * d : (nq + nkv) * d].view(T, nkv, d)
+    v = x[:, (nq + nkv) * d :].view(T, nkv, d)
+    ang = plain.rope_angles(positions.tolist(), rot, theta)
+
+    def enc(t, w):
+        t = plain.rms_norm(t, w.double().cpu(), eps)
+        return torch.cat([plain.apply_rope(t[..., :rot], ang), t[..., rot:]], dim=-1)
+
+    # float32 angles reach 4e4 rad: sin/cos of the device and of the host agree to ~1e-6 there
+    tol = 3e-6 if dtype == torch.float32 else 1e-2
+    assert rel_err(q_out.view(T, nq, d), enc(q, qw)) < tol
+    kc_flat, vc_flat = kc.view(-1, nkv, d), vc.view(-1, nkv, d)
+    want_k = enc(k, kw)
+    touched = set()
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        touched.add(s)
+        assert rel_err(kc_flat[s], want_k[t]) < tol
+        assert torch.equal(vc_flat[s].double().cpu(), v[t])
+    for s in range(pages * page):
+        if s not in touched:
+            assert float(kc_flat[s].float().min()) == 7.0 and float(vc_flat[s].float().max()) == 7.0
+
+
+# ---------------------------------------------------------------------------
+# attention
+
+
+def paged_case(seqs, nq, nkv, d, page, dtype, seed=0, shuffle=True, poison=True):
+    """Random q for the new tokens of every sequence, random k/v for its whole context,
+    scattered over shuffled pages.  seqs: list of (q_len, ctx_len).  Returns the tensors
+    the kernels take and per-sequence dense (q, k, v)."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(seqs)
+    blocks = [-(-c // page) for _, c in seqs]
+    total_pages = sum(blocks) + 3
+    order = torch.randperm(total_pages, generator=g).tolist() if shuffle else list(range(total_pages))
+    fill = float("nan") if poison else 0.0
+    kc = torch.full((total_pages, page, nkv, d), fill, dtype=torch.float32)
+    vc = torch.full((total_pages, page, nkv, d), fill, dtype=torch.float32)
+    table = torch.full((B, max(blocks)), -1, dtype=torch.int32)
+    qs, dense = [], []
+    positions, seq_index, cu, ctxs = [], [], [0], []
+    used = 0
+    for b, (ql, ctx) in enumerate(seqs):
+        q = torch.randn(ql, nq, d, generator=g)
+        k = torch.randn(ctx, nkv, d, generator=g)
+        v = torch.randn(ctx, nkv, d, generator=g)
+        dense.append([q, k, v])
+        qs.append(q)
+        for i in range(blocks[b]):
+            table[b, i] = order[used]
+            used += 1
+        positions += list(range(ctx - ql, ctx))
+        seq_index += [b] * ql
+        cu.append(cu[-1] + ql)
+        ctxs.append(ctx)
+    case = dict(B=B, nq=nq, nkv=nkv, d=d, page=page, dtype=dtype, seqs=seqs, dense=dense, table=table, kc=kc, vc=vc,
+                positions=positions, seq_index=seq_index, cu=cu, ctxs=ctxs)
+    return case
+
+
+def finish_case(case):
+    """Rounds to the dtype, scatters k/v into the pages and moves everything to the device."""
+    dtype, page = case["dtype"], case["page"]
+    for b, (q, k, v) in enumerate(case["dense"]):
+        q, k, v = (t.to(dtype).float() for t in (q, k, v))
+        case["dense"][b] = [q, k, v]
+        for j in range(k.shape[0]):
+            pg = int(case["table"][b, j // page])
+            case["kc"][pg, j % page] = k[j]
+            case["vc"][pg, j % page] = v[j]
+    case["q"] = torch.cat([d[0] for d in case["dense"]]).reshape(-1, case["nq"] * case["d"]).to(DEV, dtype)
+    for name in ("kc", "vc"):
+        case[name] = case[name].to(DEV, dtype)
+    case["table"] = case["table"].to(DEV)
+    for name in ("positions", "seq_index", "cu", "ctxs"):
+        case[name] = torch.tensor(case[name], dtype=torch.int32, device=DEV)
+    return case
+
+
+def plain_attention(case, window=0):
+    outs = []
+    for (ql, ctx), (q, k, v) in zip(case["seqs"], case["dense"]):
+        qfull = torch.zeros(ctx, case["nq"], case["d"], dtype=torch.float64)
+        qfull[ctx - ql :] = q.double()
+        o = plain.causal_attention(qfull, k.double(), v.double(), scale=case["d"] ** -0.5, window=window or None)
+        outs.append(o[ctx - ql :])
+    return torch.cat(outs).reshape(-1, case["nq"] * case["d"])
+
+
+def run_simple(case, window=0):
+    from tokensprint_b200 import ops
+
+    out = torch.full_like(case["q"], float("nan"))
+    ops.attention_paged_simple(case["q"], case["kc"], case["vc"], out, case["positions"], case["seq_index"], case["table"],
+                               case["page"], case["nq"], case["nkv"], case["d"], case["d"] ** -0.5, window)
+    return out
+
+
+def run_mma(case, window=0, splits=1):
+    from tokensprint_b200 import ops
+
+    out = torch.full_like(case["q"], float("nan"))
+    T = case["q"].shape[0]
+    scratch = None
+    if splits > 1:
+        scratch = torch.full((ops.attention_scratch_floats(T * case["nq"], splits, case["d"]),), float("nan"), device=DEV)
+    max_q = max(ql for ql, _ in case["seqs"])
+    ops.attention_paged_mma(case["q"], case["kc"], case["vc"], out, case["cu"], case["ctxs"], case["table"], case["seq_index"],
+                            case["page"], case["B"], max_q, case["nq"], case["nkv"], case["d"], case["d"] ** -0.5, window, splits, scratch)
+    return out
+
+
+MIXED = [(1, 1), (1, 77), (5, 5), (3, 130), (64, 64), (37, 200), (2, 65), (1, 64), (130, 131)]
+DECODE = [(1, 1), (1, 63), (1, 64), (1, 65), (1, 300), (1, 1000), (1, 129)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(4, 2, 16, 16, 0), (5, 1, 48, 4, 0), (6, 3, 32, 32, 24), (2, 2, 80, 1, 7), (3, 1, 272, 8, 0)])
+def test_attention_simple(dtype, nq, nkv, d, page, window):
+    case = finish_case(paged_case(MIXED, nq, nkv, d, page, dtype, seed=d))
+    got = run_simple(case, window)
+    want = plain_attention(case, window)
+    assert rel_err(got, want) < (3e-6 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize(
+    "nq,nkv,d,page,window",
+    [(4, 2, 16, 16, 0), (5, 1, 48, 4, 0), (6, 3, 32, 32, 24), (2, 2, 80, 1, 7), (32, 8, 128, 16, 0), (8, 1, 64, 16, 100),
+     (2, 1, 256, 8, 0), (20, 1, 112, 16, 0), (4, 4, 96, 256, 0)],
+)
+def test_attention_mma_mixed(nq, nkv, d, page, window):
+    case = finish_case(paged_case(MIXED, nq, nkv, d, page, torch.bfloat16, seed=d + 1))
+    got = run_mma(case, window)
+    want = plain_attention(case, window)
+    assert rel_err(got, want) < 1e-2
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 32])
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(32, 8, 128, 16, 0), (4, 2, 16, 16, 0), (16, 1, 64, 32, 0), (5, 1, 48, 4, 90), (40, 2, 80, 16, 0)])
+def test_attention_mma_decode_with_key_splits(splits, nq, nkv, d, page, window):
+    case = finish_case(paged_case(DECODE, nq, nkv, d, page, torch.bfloat16, seed=3 * d))
+    got = run_mma(case, window, splits)
+    want = plain_attention(case, window)
+    assert rel_err(got, want) < 1e-2
+
+
+@pytest.mark.parametrize("kernel", ["simple32", "simple16", "mma", "mma_split"])
+@pytest.mark.parametrize("target", ["first", "far", "page_edge_before", "page_edge_after", "block_edge", "last", "window_first", "window_out"])
+def test_attention_finds_one_key_that_stands_out(kernel, target):
+    """One key is made to match the query; its value is a marker.  Whatever position it has
+    (the first key of all, a far one among hundreds, either side of a page's edge, the edge of a
+    64-key block, the last key, the oldest key inside a window, the newest key outside it), the
+    output must be its value, or must not be for the key outside the window."""
+    nq, nkv, d, page, ctx = 4, 1, 64, 16, 700
+    window = 0
+    where = {"first": 0, "far": 3, "page_edge_before": 16 * 20 - 1, "page_edge_after": 16 * 20, "block_edge": 64 * 7,
+             "last": ctx - 1}.get(target)
+    if target == "window_first":
+        window, where = 100, ctx - 100
+    if target == "window_out":
+        window, where = 100, ctx - 101
+    dtype = torch.float32 if kernel == "simple32" else torch.bfloat16
+    case = paged_case([(1, ctx)], nq, nkv, d, page, dtype, seed=5)
+    q, k, v = case["dense"][0]
+    k.mul_(0.05)
+    k[where, 0] = q[0, 2] * 3.0  # head 2's query finds itself at `where`
+    v[where, 0] = 10.0
+    case = finish_case(case)
+    if kernel.startswith("simple"):
+        got = run_simple(case, window)
+    else:
+        got = run_mma(case, window, 4 if kernel == "mma_split" else 1)
+    head2 = got.view(1, nq, d)[0, 2].float()
+    if target == "window_out":
+        assert float(head2.abs().max()) < 5.0, "a key outside the window was seen"
+    else:
+        assert float((head2 - 10.0).abs().max()) < 0.05, f"the key at {where} was not found"
+    assert rel_err(got, plain_attention(case, window)) < (3e-6 if dtype == torch.float32 else 1e-2)
+
+
+def test_attention_ignores_pages_that_are_not_held():
+    """Table entries of -1 (pages a window gave back) and NaN in unused pages must not leak."""
+    nq, nkv, d, page, ctx, window = 4, 2, 32, 8, 200, 40
+    case = finish_case(paged_case([(3, ctx), (1, 90)], nq, nkv, d, page, torch.bfloat16, seed=9))
+    want = plain_attention(case, window)
+    # give back every page wholly before the window of the first query of each sequence
+    for b, (ql, c) in enumerate(case["seqs"]):
+        first_needed = max(0, c - ql - window + 1) // page
+        for i in range(first_needed):
+            pg = int(case["table"][b, i])
+            case["kc"][pg] = float("nan")
+            case["vc"][pg] = float("nan")
+            case["table"][b, i] = -1
+    for got in (run_simple(case, window), run_mma(case, window), run_mma(case, window, 3)):
+        assert rel_err(got, want) < 1e-2
+
+
+# ---------------------------------------------------------------------------
+# sampling
+
+
+def test_sample_greedy_and_ties():
+    from tokensprint_b200 import ops
+
+    R, V = 5, 1031
+    logits = torch.randn(R, V, device=DEV)
+    logits[1, 100] = logits[1, 900] = 50.0  # a tie: the lower index wins
+    logits[2, V - 1] = 60.0
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.sample(logits, torch.zeros(R, device=DEV), None, out)
+    want = [int(torch.argmax(logits[r])) for r in range(R)]
+    want[1] = 100
+    assert out.tolist() == want
+
+
+def test_sample_matches_the_plain_race_and_the_distribution():
+    from tokensprint_b200 import ops
+
+    V = 12
+    base = torch.tensor([2.0, 1.0, 0.5, 0.0, -1.0, 3.0, 0.1, 0.2, -3.0, 1.5, 0.7, 0.3])
+    R = 4000
+    logits = base.repeat(R, 1).to(DEV)
+    temps = torch.full((R,), 0.7, device=DEV)
+    keys = torch.arange(R, dtype=torch.int64, device=DEV) * 7919 - 1000
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.sample(logits, temps, keys, out)
+    got = out.tolist()
+    for r in range(0, 60):
+        assert got[r] == plain.sample_token(base, 0.7, int(keys[r]))
+    freq = np.bincount(got, minlength=V) / R
+    p = torch.softmax(base.double() / 0.7, dim=-1).numpy()
+    assert np.abs(freq - p).max() < 4 * np.sqrt(0.25 / R)
+    # the same keys give the same tokens; other keys give other tokens
+    out2 = torch.empty_like(out)
+    ops.sample(logits, temps, keys, out2)
+    assert out2.tolist() == got
+    ops.sample(logits, temps, keys + 1, out2)
+    assert out2.tolist() != got

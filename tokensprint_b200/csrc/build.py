@@ -164,5 +164,79 @@ def load() -> ctypes.CDLL:
         return _library
 
 
+# ---------------------------------------------------------------------------
+# variants: kernels compiled for one value of a size (a head size), each a library of its own,
+# built the first time a model needs that size
+
+VARIANTS = CSRC / "variants"
+ATTENTION_HEAD_DIMS = tuple(range(16, 257, 16))
+_variants: dict[tuple[str, tuple], ctypes.CDLL] = {}
+
+
+def variant_path(name: str, defines: dict[str, int]) -> Path:
+    src = VARIANTS / f"{name}.cu"
+    h = hashlib.sha256()
+    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(repr(sorted(defines.items())).encode())
+    h.update(src.read_bytes())
+    for p in sorted(CSRC.glob("*.cuh")):
+        h.update(p.read_bytes())
+    tag = "_".join(f"{k.lower()}{v}" for k, v in sorted(defines.items()))
+    rel = Path(h.hexdigest()[:16]) / f"libtokensprint_b200_{name}_{tag}.so"
+    in_tree = CSRC / "_build" / rel
+    if in_tree.is_file():
+        return in_tree
+    return _build_root() / rel
+
+
+def build_variant(name: str, defines: dict[str, int]) -> Path:
+    target = variant_path(name, defines)
+    if target.is_file():
+        return target
+    src = VARIANTS / f"{name}.cu"
+    if not src.is_file():
+        raise BuildError(f"no kernel source {src}")
+    nvcc = find_nvcc()
+    target.parent.mkdir(parents=True, exist_ok=True)
+    what = ", ".join(f"{k}={v}" for k, v in sorted(defines.items()))
+    _say(f"compiling {src.name} for {what} (first use of this size only)")
+    start = time.time()
+    tmp = target.parent / f".{target.name}.{os.getpid()}"
+    cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), *[f"-D{k}={v}" for k, v in sorted(defines.items())],
+           "-shared", str(src), "-o", str(tmp)]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise BuildError(f"nvcc failed on {src.name} ({what}):\n{proc.stdout}\n{proc.stderr}")
+    os.replace(tmp, target)
+    _say(f"built {target.name} in {time.time() - start:.0f} s")
+    return target
+
+
+def load_variant(name: str, defines: dict[str, int]) -> ctypes.CDLL:
+    key = (name, tuple(sorted(defines.items())))
+    with _lock:
+        lib = _variants.get(key)
+        if lib is None:
+            path = build_variant(name, defines)
+            try:
+                lib = ctypes.CDLL(str(path))
+            except OSError as e:
+                raise BuildError(f"cannot load {path}: {e}") from e
+            _variants[key] = lib
+        return lib
+
+
+def build_all() -> list[Path]:
+    """The main library and every head-size variant of the attention kernel."""
+    paths = [build()]
+    with ThreadPoolExecutor(max_workers=min(os.cpu_count() or 2, 8)) as pool:
+        paths += list(pool.map(lambda d: build_variant("attention_mma", {"TS_HEAD_DIM": d}), ATTENTION_HEAD_DIMS))
+    return paths
+
+
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv))
+    if "--all" in sys.argv:
+        for path in build_all():
+            print(path)
+    else:
+        print(build(force="--force" in sys.argv))

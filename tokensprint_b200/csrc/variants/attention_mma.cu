@@ -1,0 +1,446 @@
+// Paged causal attention on tensor cores (bfloat16 in, float32 softmax and accumulation).
+//
+// Compiled once per head size: -DTS_HEAD_DIM=<multiple of 16, at most 256>.
+//
+// What it computes is what attention_simple.cu computes (engine/nn/sdpa.py:56,85-102 of the
+// reference: scale, causal mask, GQA by head ratio, keys and values through the block
+// table; a sliding window where the layer has one).  How: for one sequence and one KV
+// head, the rows of the work tile are (query token, query head of the group) pairs, so
+// all heads that share a KV head share each loaded key/value tile.  Keys are walked in
+// blocks of BN with an online softmax; K and V blocks arrive by cp.async (16-byte
+// chunks, zero-filled where a key does not exist) two blocks ahead of the math.
+// Prefill uses 4 warps x 16 rows per CTA; decode (a few rows per sequence) uses one
+// warp per CTA and splits the keys of a sequence over several CTAs, whose partial
+// results (running max, sum, unnormalised output, float32) go to a scratch buffer and
+// are merged by attention_combine_kernel.
+//
+// The order of the sums for one query row depends on its own keys and on the number of
+// splits only, never on what else is in the batch.
+#include "../common.cuh"
+
+#ifndef TS_HEAD_DIM
+#error "compile with -DTS_HEAD_DIM=<head size>"
+#endif
+#if (TS_HEAD_DIM % 16) != 0 || TS_HEAD_DIM > 256 || TS_HEAD_DIM < 16
+#error "TS_HEAD_DIM must be a multiple of 16 between 16 and 256"
+#endif
+
+namespace {
+
+constexpr int D = TS_HEAD_DIM;
+constexpr int BN = 64;            // keys per block
+constexpr int LD = D + 8;         // padded row of a shared-memory tile (odd count of 16-byte chunks)
+constexpr int CH = D / 8;         // 16-byte chunks per row
+constexpr int STAGES = 2;
+constexpr bool Q_IN_REGS = D <= 128;
+
+struct AttnParams {
+  const __nv_bfloat16* q;         // [T, nq, D]
+  const __nv_bfloat16* kcache;    // [slots, nkv, D]
+  const __nv_bfloat16* vcache;
+  __nv_bfloat16* out;             // [T, nq, D]
+  float* part_o;                  // [T * nq, splits, D]   (splits > 1)
+  float* part_ml;                 // [T * nq, splits, 2]
+  const int* cu_q;                // [B + 1]
+  const int* ctx_len;             // [B] keys in the cache after this step
+  const int* block_table;         // [B, max_blocks]
+  int max_blocks, page, nq, nkv, window, splits, row_tiles;
+  float scale_log2;               // scale * log2(e)
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Copies keys [kbase, kbase + BN) of one KV head into a [BN][LD] tile; keys that do not
+// exist (beyond `kend`, or in a page that is not held) become zeros.
+template <int NT>
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* tile, const __nv_bfloat16* cache, const int* table,
+                                             int page, int nkv, int hk, int kbase, int kend, int tid) {
+  for (int c = tid; c < BN * CH; c += NT) {
+    const int row = c / CH, ch = c - row * CH;
+    const int j = kbase + row;
+    bool valid = j <= kend;
+    const __nv_bfloat16* src = cache;
+    if (valid) {
+      const int pg = table[j / page];
+      valid = pg >= 0;
+      if (valid) src = cache + (((size_t)pg * page + (j % page)) * nkv + hk) * D + ch * 8;
+    }
+    cp_async16(tile + row * LD + ch * 8, src, valid);
+  }
+}
+
+template <int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnParams p) {
+  constexpr int NT = NWARPS * 32;
+  constexpr int BM = NWARPS * 16;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [BM][LD]
+  __nv_bfloat16* k_s = q_s + BM * LD;                                        // [STAGES][BN][LD]
+  __nv_bfloat16* v_s = k_s + STAGES * BN * LD;                               // [STAGES][BN][LD]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, tq = lane & 3;
+  const int b = blockIdx.z, hk = blockIdx.y;
+  const int row_tile = blockIdx.x % p.row_tiles, split = blockIdx.x / p.row_tiles;
+  const int G = p.nq / p.nkv;
+
+  const int q_begin = p.cu_q[b];
+  const int q_len = p.cu_q[b + 1] - q_begin;
+  const int ctx = p.ctx_len[b];
+  const int start_pos = ctx - q_len;
+  const int rows_total = q_len * G;
+  const int r0 = row_tile * BM;
+  if (q_len <= 0 || r0 >= rows_total) return;
+
+  // Keys this tile can see at all.
+  const int last_row = min(r0 + BM, rows_total) - 1;
+  const int hi = start_pos + last_row / G;
+  const int lo = p.window > 0 ? max(0, start_pos + r0 / G - p.window + 1) : 0;
+  int kb0 = lo / BN, kb1 = hi / BN;
+  if (p.splits > 1) {
+    const int per = (kb1 - kb0 + p.splits) / p.splits;
+    kb0 = kb0 + split * per;
+    kb1 = min(kb1, kb0 + per - 1);
+  }
+  const int nblocks = kb1 - kb0 + 1;  // may be <= 0 for a split without work
+  const int* table = p.block_table + (size_t)b * p.max_blocks;
+
+  // Rows of this thread: (warp * 16 + g) and (+ 8).
+  int row_pos[2], row_lo[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = r0 + warp * 16 + g + 8 * h;
+    row_pos[h] = r < rows_total ? start_pos + r / G : -1;
+    row_lo[h] = (p.window > 0 && row_pos[h] >= 0) ? max(0, row_pos[h] - p.window + 1) : 0;
+  }
+
+  // Queries of the tile.
+  for (int c = tid; c < BM * CH; c += NT) {
+    const int row = c / CH, ch = c - row * CH;
+    const int r = r0 + row;
+    const bool valid = r < rows_total;
+    const __nv_bfloat16* src = p.q;
+    if (valid) src = p.q + ((size_t)(q_begin + r / G) * p.nq + hk * G + r % G) * D + ch * 8;
+    cp_async16(q_s + row * LD + ch * 8, src, valid);
+  }
+  cp_async_commit();
+  if (nblocks > 0) {
+    load_kv_tile<NT>(k_s, p.kcache, table, p.page, p.nkv, hk, kb0 * BN, hi, tid);
+    cp_async_commit();
+    load_kv_tile<NT>(v_s, p.vcache, table, p.page, p.nkv, hk, kb0 * BN, hi, tid);
+    cp_async_commit();
+  }
+
+  float o_acc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  unsigned q_frag[Q_IN_REGS ? D / 16 : 1][4];
+  const __nv_bfloat16* q_warp = q_s + (warp * 16) * LD;
+  if (nblocks > 0) {
+    cp_async_wait<2>();  // the queries have landed (K and V of block 0 may still fly)
+  } else {
+    cp_async_wait<0>();
+  }
+  __syncthreads();
+  if constexpr (Q_IN_REGS) {
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks)
+      ldmatrix_x4(q_frag[ks][0], q_frag[ks][1], q_frag[ks][2], q_frag[ks][3],
+                  q_warp + ((lane & 7) + ((lane >> 3) & 1) * 8) * LD + ks * 16 + (lane >> 4) * 8);
+  }
+
+  for (int it = 0; it < nblocks; ++it) {
+    const int stage = it & 1;
+    const int kbase = (kb0 + it) * BN;
+    const bool more = it + 1 < nblocks;
+    if (more) {
+      load_kv_tile<NT>(k_s + (stage ^ 1) * BN * LD, p.kcache, table, p.page, p.nkv, hk, kbase + BN, hi, tid);
+      cp_async_commit();
+      load_kv_tile<NT>(v_s + (stage ^ 1) * BN * LD, p.vcache, table, p.page, p.nkv, hk, kbase + BN, hi, tid);
+      cp_async_commit();
+      cp_async_wait<3>();
+    } else {
+      cp_async_wait<1>();
+    }
+    __syncthreads();
+
+    // S = Q K^T
+    float s[BN / 8][4];
+#pragma unroll
+    for (int i = 0; i < BN / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+    const __nv_bfloat16* k_tile = k_s + stage * BN * LD;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      unsigned a[4];
+      if constexpr (Q_IN_REGS) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a[j] = q_frag[ks][j];
+      } else {
+        ldmatrix_x4(a[0], a[1], a[2], a[3],
+                    q_warp + ((lane & 7) + ((lane >> 3) & 1) * 8) * LD + ks * 16 + (lane >> 4) * 8);
+      }
+#pragma unroll
+      for (int np = 0; np < BN / 16; ++np) {
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3,
+                    k_tile + (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[2 * np], a, b0, b1);
+        mma_bf16(s[2 * np + 1], a, b2, b3);
+      }
+    }
+
+    // scale, mask, online softmax (log2 domain)
+    float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+    for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        const int j = kbase + nt * 8 + tq * 2 + (e & 1);
+        const bool ok = j <= row_pos[h] && j >= row_lo[h];
+        const float v = ok ? s[nt][e] * p.scale_log2 : -INFINITY;
+        s[nt][e] = v;
+        m_new[h] = fmaxf(m_new[h], v);
+      }
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
+      m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
+      m_use[h] = m_new[h] == -INFINITY ? 0.f : m_new[h];  // a row that has seen no key yet
+      corr[h] = exp2f(m_run[h] - m_use[h]);               // m_run = -inf gives 0
+      m_run[h] = m_new[h];
+    }
+    float l_add[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        const float pv = exp2f(s[nt][e] - m_use[h]);
+        s[nt][e] = pv;
+        l_add[h] += pv;
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * corr[h] + l_add[h];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o_acc[i][0] *= corr[0];
+      o_acc[i][1] *= corr[0];
+      o_acc[i][2] *= corr[1];
+      o_acc[i][3] *= corr[1];
+    }
+
+    if (more) {
+      cp_async_wait<2>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    // O += P V
+    const __nv_bfloat16* v_tile = v_s + stage * BN * LD;
+#pragma unroll
+    for (int kk = 0; kk < BN / 16; ++kk) {
+      unsigned a[4];
+      a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int np = 0; np < D / 16; ++np) {
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4_trans(b0, b1, b2, b3,
+                          v_tile + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + np * 16 + ((lane >> 4) & 1) * 8);
+        mma_bf16(o_acc[2 * np], a, b0, b1);
+        mma_bf16(o_acc[2 * np + 1], a, b2, b3);
+      }
+    }
+    __syncthreads();  // the next round's prefetch overwrites this stage
+  }
+
+  // Row sums live spread over the four threads of a quad.
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = r0 + warp * 16 + g + 8 * h;
+    if (r >= rows_total) continue;
+    const size_t qrow = (size_t)(q_begin + r / G) * p.nq + hk * G + r % G;
+    if (p.splits == 1) {
+      const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+      __nv_bfloat16* dst = p.out + qrow * D;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(o_acc[i][2 * h] * inv, o_acc[i][2 * h + 1] * inv);
+        *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + tq * 2) = v;
+      }
+    } else {
+      float* dst = p.part_o + (qrow * p.splits + split) * D;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i)
+        *reinterpret_cast<float2*>(dst + i * 8 + tq * 2) = make_float2(o_acc[i][2 * h], o_acc[i][2 * h + 1]);
+      if (tq == 0) {
+        float* ml = p.part_ml + (qrow * p.splits + split) * 2;
+        ml[0] = m_run[h];
+        ml[1] = l_run[h];
+      }
+    }
+  }
+}
+
+// Merges the partial results of the key splits of one (token, head): one warp each.
+__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         __nv_bfloat16* __restrict__ out, const int* __restrict__ seq_index,
+                                         int rows, int nq, int splits) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  __nv_bfloat16* dst = out + (size_t)row * D;
+  if (seq_index && seq_index[row / nq] < 0) {  // a padded lane of a fixed-size batch
+    for (int d = lane; d < D; d += 32) dst[d] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const float* ml = part_ml + (size_t)row * splits * 2;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s)
+    if (ml[2 * s + 1] > 0.f) m = fmaxf(m, ml[2 * s]);
+  float l = 0.f;
+  float acc[(D + 31) / 32];
+#pragma unroll
+  for (int i = 0; i < (D + 31) / 32; ++i) acc[i] = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ls = ml[2 * s + 1];
+    if (!(ls > 0.f)) continue;  // a split without keys wrote nothing worth reading
+    const float w = exp2f(ml[2 * s] - m);
+    l += w * ls;
+    const float* src = part_o + ((size_t)row * splits + s) * D;
+#pragma unroll
+    for (int i = 0; i < (D + 31) / 32; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) acc[i] += w * src[d];
+    }
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+  for (int i = 0; i < (D + 31) / 32; ++i) {
+    const int d = lane + 32 * i;
+    if (d < D) dst[d] = __float2bfloat16_rn(acc[i] * inv);
+  }
+}
+
+template <int NWARPS>
+int launch(const AttnParams& p, int B, cudaStream_t stream) {
+  constexpr int BM = NWARPS * 16;
+  const size_t smem = (size_t)(BM + 2 * STAGES * BN) * LD * sizeof(__nv_bfloat16);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<NWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(p.row_tiles * p.splits, p.nkv, B);
+  attention_mma_kernel<NWARPS><<<grid, NWARPS * 32, smem, stream>>>(p);
+  return ts_launch_status();
+}
+
+}  // namespace
+
+// Scratch floats needed for `rows` = tokens * query heads and `splits` key splits.
+TS_EXPORT long long ts_attention_mma_scratch_floats(long long rows, int splits) {
+  return splits > 1 ? rows * splits * (long long)(D + 2) : 0;
+}
+
+TS_EXPORT int ts_attention_mma_head_dim() { return D; }
+
+// q/out [T, nq, D] bf16; caches [slots, nkv, D] bf16; cu_q [B+1]; ctx_len [B]; block_table
+// [B, max_blocks].  max_q: the most tokens any sequence brings in this step.  splits > 1
+// needs `scratch` of ts_attention_mma_scratch_floats(T * nq, splits) floats; seq_index
+// ([T], -1 marks padding) is only read when splits > 1.
+TS_EXPORT int ts_attention_paged_mma(const void* q, const void* kcache, const void* vcache, void* out,
+                                     float* scratch, const int* cu_q, const int* ctx_len,
+                                     const int* block_table, const int* seq_index, int max_blocks,
+                                     int page, int T, int B, int max_q, int nq, int nkv, float scale,
+                                     int window, int splits, void* stream_) {
+  if (T <= 0 || B <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page <= 0 || max_blocks <= 0 || max_q <= 0 || splits < 1)
+    return TS_ERR_BAD_ARGUMENT;
+  if (splits > 1 && scratch == nullptr) return TS_ERR_BAD_ARGUMENT;
+  if (nkv > 65535 || B > 65535) return TS_ERR_UNSUPPORTED_SIZE;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const int G = nq / nkv;
+  AttnParams p;
+  p.q = (const __nv_bfloat16*)q;
+  p.kcache = (const __nv_bfloat16*)kcache;
+  p.vcache = (const __nv_bfloat16*)vcache;
+  p.out = (__nv_bfloat16*)out;
+  p.part_o = scratch;
+  p.part_ml = scratch ? scratch + (size_t)T * nq * splits * D : nullptr;
+  p.cu_q = cu_q;
+  p.ctx_len = ctx_len;
+  p.block_table = block_table;
+  p.max_blocks = max_blocks;
+  p.page = page;
+  p.nq = nq;
+  p.nkv = nkv;
+  p.window = window;
+  p.splits = splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const long long rows = (long long)max_q * G;
+  int status;
+  if (rows <= 16) {
+    p.row_tiles = 1;
+    status = launch<1>(p, B, stream);
+  } else {
+    p.row_tiles = (int)((rows + 63) / 64);
+    status = launch<4>(p, B, stream);
+  }
+  if (status != 0) return status;
+  if (splits > 1) {
+    const int total = T * nq;
+    attention_combine_kernel<<<(total + 3) / 4, 128, 0, stream>>>(p.part_o, p.part_ml, p.out, seq_index, total, nq, splits);
+    status = ts_launch_status();
+  }
+  return status;
+}

@@ -322,3 +322,107 @@ def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError(f"sgemm_nt: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     _check("sgemm_nt", _fn("ts_sgemm_nt")(
         a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), w.stride(0), out.stride(0), _stream()))
+
+
+# ---------------------------------------------------------------------------
+# tensor-core attention (one library per head size)
+
+ATTENTION_MMA_MAX_HEAD_DIM = 256
+ATTENTION_MMA_MAX_SPLITS = 32
+_attention_mma: dict[int, tuple] = {}
+
+
+def attention_mma_supported(head_dim: int) -> bool:
+    return head_dim % 16 == 0 and 16 <= head_dim <= ATTENTION_MMA_MAX_HEAD_DIM
+
+
+def _attention_mma_fns(head_dim: int):
+    fns = _attention_mma.get(head_dim)
+    if fns is None:
+        if not attention_mma_supported(head_dim):
+            raise KernelError(
+                f"attention_paged_mma: head_dim must be a multiple of 16 between 16 and {ATTENTION_MMA_MAX_HEAD_DIM}, got {head_dim}")
+        lib = _build.load_variant("attention_mma", {"TS_HEAD_DIM": head_dim})
+        run = lib.ts_attention_paged_mma
+        run.argtypes = [_c_void_p] * 9 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_void_p]
+        run.restype = _c_int
+        scratch = lib.ts_attention_mma_scratch_floats
+        scratch.argtypes = [_c_ll, _c_int]
+        scratch.restype = _c_ll
+        if lib.ts_attention_mma_head_dim() != head_dim:
+            raise KernelError("attention_paged_mma: the loaded library was built for another head size")
+        fns = (run, scratch)
+        _attention_mma[head_dim] = fns
+    return fns
+
+
+def attention_decode_splits(num_seqs: int, num_kv_heads: int, max_context: int) -> int:
+    """How many CTAs share the keys of one sequence in a decode step: enough to fill the
+    GPU's 148 SMs a few times over, never more than there are key blocks."""
+    ctas = max(1, num_seqs * num_kv_heads)
+    want = -(-4 * 148 // ctas)
+    blocks = max(1, -(-max_context // 64))
+    return max(1, min(want, blocks, ATTENTION_MMA_MAX_SPLITS))
+
+
+def attention_paged_mma(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    out: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    context_lens: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_index: torch.Tensor,
+    page_size: int,
+    num_seqs: int,
+    max_seqlen_q: int,
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    scale: float,
+    window: int = 0,
+    splits: int = 1,
+    scratch: Optional[torch.Tensor] = None,
+) -> None:
+    """Causal attention over the paged cache on tensor cores (bfloat16).
+
+    q/out [T,nq*d]; caches [pages,page,nkv,d]; cu_seqlens_q [B+1], context_lens [B],
+    seq_index [T] i32; block_table [B,max_blocks] i32.  The tokens of a sequence are
+    consecutive and end at context_lens[b] - 1.  splits > 1 spreads the keys of a
+    sequence over several CTAs and needs `scratch` (float32, see attention_scratch_floats).
+    """
+    run, _ = _attention_mma_fns(head_dim)
+    for name, t in (("q", q), ("k_cache", k_cache), ("v_cache", v_cache), ("out", out)):
+        _cuda_contig(name, t, torch.bfloat16)
+    for name, t in (("cu_seqlens_q", cu_seqlens_q), ("context_lens", context_lens), ("block_table", block_table), ("seq_index", seq_index)):
+        _cuda_contig(name, t, torch.int32)
+    T = q.shape[0]
+    nq, nkv, d = num_heads, num_kv_heads, head_dim
+    if nq % nkv:
+        raise KernelError(f"attention: {nq} query heads are no multiple of {nkv} key/value heads")
+    if q.numel() != T * nq * d or out.numel() != T * nq * d:
+        raise KernelError("attention: q/out do not match [T, heads*head_dim]")
+    if tuple(k_cache.shape[-3:]) != (page_size, nkv, d) or k_cache.shape != v_cache.shape:
+        raise KernelError(f"attention: caches must be [pages,{page_size},{nkv},{d}], got {tuple(k_cache.shape)} and {tuple(v_cache.shape)}")
+    if block_table.dim() != 2 or block_table.shape[0] < num_seqs:
+        raise KernelError("attention: block_table must be [B,max_blocks]")
+    if cu_seqlens_q.numel() < num_seqs + 1 or context_lens.numel() < num_seqs or seq_index.numel() < T:
+        raise KernelError("attention: cu_seqlens_q/context_lens/seq_index are shorter than the batch")
+    if not (1 <= splits <= ATTENTION_MMA_MAX_SPLITS):
+        raise KernelError(f"attention: splits must be 1..{ATTENTION_MMA_MAX_SPLITS}, got {splits}")
+    if splits > 1:
+        need = attention_scratch_floats(T * nq, splits, d)
+        if scratch is None or scratch.dtype != torch.float32 or not scratch.is_cuda or scratch.numel() < need:
+            raise KernelError(f"attention: splits={splits} needs {need} float32 of scratch")
+    _check("attention_paged_mma", run(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _ptr(scratch),
+        cu_seqlens_q.data_ptr(), context_lens.data_ptr(), block_table.data_ptr(), seq_index.data_ptr(),
+        block_table.shape[1], page_size, T, num_seqs, max_seqlen_q, nq, nkv, float(scale), int(window), int(splits), _stream()))
+    if splits > 1:
+        global launch_count
+        launch_count += 1  # the combine kernel
+
+
+def attention_scratch_floats(rows: int, splits: int, head_dim: int) -> int:
+    return rows * splits * (head_dim + 2) if splits > 1 else 0

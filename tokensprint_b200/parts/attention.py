@@ -127,6 +127,21 @@ class AttentionMixer(Mixer):
     # -- attention proper ---------------------------------------------------
 
     def _attend(self, q, out, step: StepContext, cache: LayerCache, tables) -> None:
+        nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
+        if q.dtype == torch.bfloat16 and ops.attention_mma_supported(d):
+            splits, scratch = 1, None
+            if step.max_seqlen_q * (nq // nkv) <= 16:  # decode: spread each sequence's keys over CTAs
+                context = step.max_context_len if self.window <= 0 else min(step.max_context_len, self.window + 64)
+                splits = ops.attention_decode_splits(step.num_seqs, nkv, context)
+                if splits > 1:
+                    scratch = torch.empty(ops.attention_scratch_floats(q.shape[0] * nq, splits, d),
+                                          device=q.device, dtype=torch.float32)
+            ops.attention_paged_mma(
+                q, cache.k_pages, cache.v_pages, out, step.cu_seqlens_q, step.context_lens, tables.block_table,
+                step.seq_index, step.page_size, step.num_seqs, step.max_seqlen_q, nq, nkv, d, self.scale,
+                self.window, splits, scratch)
+            return
+        # float32 runs, and head sizes the tensor-core kernel does not take
         ops.attention_paged_simple(
             q, cache.k_pages, cache.v_pages, out, step.positions, step.seq_index, tables.block_table,
             step.page_size, self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window)
