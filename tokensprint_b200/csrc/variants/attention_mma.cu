@@ -444,3 +444,60 @@ TS_EXPORT int ts_attention_paged_mma(const void* q, const void* kcache, const vo
   }
   return status;
 }
+
+// ---------------------------------------------------------------------------
+// The entry point that allocates nothing (see attention_mma_noalloc.h for who needs it,
+// the limit and the rules of use).  It changes nothing above: it looks up the address of
+// a scratch array that lives in this library and calls ts_attention_paged_mma with it.
+#include "attention_mma_noalloc.h"
+
+// File-scope scratch: in host code this name is only a handle for cudaGetSymbolAddress,
+// never a pointer a kernel may be given.
+static __device__ __align__(256) float ts_attention_noalloc_scratch[TS_ATTENTION_NOALLOC_SCRATCH_FLOATS];
+
+#define TS_NOALLOC_MAX_DEVICES 64
+static float* ts_noalloc_scratch_address[TS_NOALLOC_MAX_DEVICES];  // per device, filled at its first call
+
+TS_EXPORT long long ts_attention_noalloc_scratch_floats(void) { return TS_ATTENTION_NOALLOC_SCRATCH_FLOATS; }
+
+TS_EXPORT const char* ts_attention_noalloc_error_text(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case TS_ERR_BAD_ARGUMENT: return "bad argument (sizes must be positive, heads a multiple of kv heads)";
+    case TS_ERR_UNSUPPORTED_SIZE: return "size not supported by this kernel";
+    case TS_ERR_SCRATCH_LIMIT:
+      return "tokens * query_heads * splits * (head_dim + 2) exceeds the library's built-in scratch "
+             "(TS_ATTENTION_NOALLOC_SCRATCH_FLOATS floats): use fewer splits or tokens, or the entry "
+             "point that takes scratch from the caller";
+    default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
+  }
+}
+
+TS_EXPORT int ts_attention_paged_mma_noalloc(const void* q, const void* kcache, const void* vcache, void* out,
+                                             const int* cu_q, const int* ctx_len, const int* block_table,
+                                             const int* seq_index, int max_blocks, int page, int T, int B,
+                                             int max_q, int nq, int nkv, float scale, int window, int splits,
+                                             void* stream) {
+  if (T <= 0 || B <= 0) return 0;
+  if (nq <= 0 || splits < 1) return TS_ERR_BAD_ARGUMENT;
+  float* scratch = nullptr;
+  if (splits > 1) {
+    if (ts_attention_mma_scratch_floats((long long)T * nq, splits) > (long long)TS_ATTENTION_NOALLOC_SCRATCH_FLOATS)
+      return TS_ERR_SCRATCH_LIMIT;
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= TS_NOALLOC_MAX_DEVICES) return TS_ERR_UNSUPPORTED_SIZE;
+    if (ts_noalloc_scratch_address[device] == nullptr) {
+      // First call on this device: turn the symbol into the address the kernels can use.
+      float* address = nullptr;
+      e = cudaGetSymbolAddress((void**)&address, ts_attention_noalloc_scratch);
+      if (e != cudaSuccess) return (int)e;
+      if (address == nullptr) return (int)cudaErrorInvalidSymbol;
+      ts_noalloc_scratch_address[device] = address;
+    }
+    scratch = ts_noalloc_scratch_address[device];
+  }
+  return ts_attention_paged_mma(q, kcache, vcache, out, scratch, cu_q, ctx_len, block_table, seq_index,
+                                max_blocks, page, T, B, max_q, nq, nkv, scale, window, splits, stream);
+}
