@@ -205,7 +205,7 @@ def measure_prefill(runner, cfg, reps: int = 5):
     return times[len(times) // 2]
 
 
-def measure_e2e(model, cfg, batch: int, steps: int, warmup: int):
+def measure_e2e(model, cfg, batch: int, steps: int, warmup: int, eager: bool = False):
     """Decode through the public entry point: LLMEngine.add_request + step(), token ids from
     host lists, sampled ids back on the host every step."""
     import torch
@@ -215,7 +215,8 @@ def measure_e2e(model, cfg, batch: int, steps: int, warmup: int):
 
     pages = batch * (-(-(PROMPT_LEN + warmup + steps + 8) // PAGE_SIZE)) + 64
     config = Config(model=str(ROOT), max_model_len=CONTEXT_LEN, max_num_seqs=max(batch, 8), max_num_batched_tokens=8192,
-                    kvcache_block_size=PAGE_SIZE, num_kvcache_blocks=pages, chunked_prefill=True, dtype="bfloat16")
+                    kvcache_block_size=PAGE_SIZE, num_kvcache_blocks=pages, chunked_prefill=True, dtype="bfloat16",
+                    enforce_eager=eager)
     engine = LLMEngine(model, config)
     sp = SamplingParams(temperature=0.6, max_tokens=warmup + steps + 4, ignore_eos=True, seed=1)
     for b in range(batch):
@@ -262,7 +263,7 @@ def run_ours(args) -> dict:
     tokens_per_req = PROMPT_LEN + args.warmup + max(args.steps, 32) + 16
     pages = max_batch * (-(-tokens_per_req // PAGE_SIZE)) + PREFILL_TOKENS // PAGE_SIZE + 64
     runner = ModelRunner(model, page_size=PAGE_SIZE, num_pages=pages, num_slots=max_batch + 8,
-                         max_num_batched_tokens=8192)
+                         max_num_batched_tokens=8192, enforce_eager=args.eager, max_model_len=CONTEXT_LEN)
 
     clocks = ClockSampler()
     ms, mean_ctx, launches = measure_decode(runner, cfg, args.batch, args.steps, args.warmup, clocks)
@@ -284,7 +285,7 @@ def run_ours(args) -> dict:
 
     del runner
     torch.cuda.empty_cache()
-    e2e_value, h2d, d2h = measure_e2e(model, cfg, args.batch, args.steps, args.warmup)
+    e2e_value, h2d, d2h = measure_e2e(model, cfg, args.batch, args.steps, args.warmup, args.eager)
 
     return {
         "metric": "decode tokens/s, Qwen3-8B sizes, batch 8, 1 B200",
@@ -341,6 +342,7 @@ def main() -> int:
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in the record)")
     p.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
+    p.add_argument("--eager", action="store_true", help="no CUDA graphs for decode steps")
     args = p.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")

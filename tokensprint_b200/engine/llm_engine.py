@@ -35,6 +35,8 @@ class LLMEngine:
             num_slots=config.max_num_seqs,
             max_num_batched_tokens=config.max_num_batched_tokens,
             gpu_memory_utilization=config.gpu_memory_utilization,
+            enforce_eager=config.enforce_eager,
+            max_model_len=config.max_model_len,
         )
         config.num_kvcache_blocks = self.model_runner.num_pages[0]
         self.scheduler = Scheduler(config, self.model_runner.cache_manager)

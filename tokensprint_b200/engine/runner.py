@@ -38,6 +38,18 @@ class StepEntry:
     want: Sequence[int] = ()  # places among `tokens` whose logits are asked for
 
 
+@dataclass
+class _DecodeGraph:
+    bucket: int
+    layout: "_Layout"
+    dev: torch.Tensor  # static index buffer the captured kernels read
+    host: torch.Tensor  # its pinned staging copy
+    graph: "torch.cuda.CUDAGraph"
+    logits: torch.Tensor  # [bucket, vocab] float32, rewritten by every replay
+    kernels: int  # kernels of this library inside the graph
+    event: Optional["torch.cuda.Event"] = None
+
+
 def _round4(n: int) -> int:
     return (n + 3) & ~3
 
@@ -83,6 +95,9 @@ class ModelRunner:
         max_num_batched_tokens: int = 8192,
         gpu_memory_utilization: float = 0.9,
         poison_freed_pages: bool = False,
+        enforce_eager: bool = True,
+        max_model_len: int = 4096,
+        max_graph_batch: int = 256,
     ) -> None:
         if model.device.type != "cuda":
             raise RuntimeError("ModelRunner needs a CUDA device: the engine has no CPU path")
@@ -119,6 +134,17 @@ class ModelRunner:
         self._pinned_next = 0
         self.steps_run = 0
         self.h2d_bytes = 0  # bytes of step inputs copied to the device so far
+        # Decode-only steps replay a CUDA graph per batch bucket (engine/generation/
+        # model_runner.py:310-390 of the reference); here the graph holds the whole step,
+        # final norm and head included.
+        self.max_model_len = max_model_len
+        self.use_graphs = (not enforce_eager) and all(
+            getattr(b.mixer, "graph_safe", False) for b in model.blocks)
+        self.graph_buckets = [b for b in (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
+                              if b <= max(1, min(max_graph_batch, num_slots))]
+        self._graphs: dict[int, "_DecodeGraph"] = {}
+        self._graph_pool = None
+        self.graph_launches = 0  # kernels of this library replayed inside graphs so far
 
     # -- sizing ---------------------------------------------------------------------
 
@@ -174,7 +200,25 @@ class ModelRunner:
         layout = _Layout(T, B, R, widths)
         pinned, slot_i = self._pinned_buffer(layout.total)
         host = pinned.numpy()[: layout.total]
+        self._fill(host, layout, entries, lens)
 
+        dev = torch.empty(layout.total, dtype=torch.int32, device=self.device)
+        dev.copy_(pinned[: layout.total], non_blocking=True)
+        self.h2d_bytes += layout.total * 4
+        ev = torch.cuda.Event()
+        ev.record()
+        self._pinned_events[slot_i] = ev
+        step = self._context(dev, layout, max(lens), max(e.start + n for e, n in zip(entries, lens)))
+        step.host_seq_starts = [e.start for e in entries]
+        step.host_seq_lens = lens
+        step.host_state_slots = [e.cache.slot for e in entries]
+        return step, layout.view(dev, "rows"), R
+
+    def _fill(self, host, layout: _Layout, entries: Sequence[StepEntry], lens: Sequence[int]) -> None:
+        """Writes the step's index arrays into `host` (a numpy view of pinned memory).  A
+        layout larger than the step (a graph bucket) is padded with lanes that belong to no
+        request: sequence index -1, no cache slot, no tokens in their sequence."""
+        B, widths = layout.B, layout.widths
         tok = layout.view(host, "token_ids")
         pos = layout.view(host, "positions")
         sidx = layout.view(host, "seq_index")
@@ -186,6 +230,8 @@ class ModelRunner:
         t0 = 0
         r0 = 0
         seen = set()
+        tables = [layout.view(host, f"table{g}").reshape(B, widths[g]) for g in range(len(self.groups))]
+        slot_maps = [layout.view(host, f"slots{g}") for g in range(len(self.groups))]
         for b, (e, n) in enumerate(zip(entries, lens)):
             rc = e.cache
             if rc.released:
@@ -212,32 +258,42 @@ class ModelRunner:
                 rows[r0] = t0 + w
                 r0 += 1
             for g in range(len(self.groups)):
-                layout.view(host, f"slots{g}")[t0 : t0 + n] = self.cache_manager.slots_for(rc, g, e.start, n)
-                table = layout.view(host, f"table{g}").reshape(B, widths[g])
+                slot_maps[g][t0 : t0 + n] = self.cache_manager.slots_for(rc, g, e.start, n)
                 have = rc.tables[g][: widths[g]]
-                table[b, : len(have)] = have
-                table[b, len(have) :] = -1
+                tables[g][b, : len(have)] = have
+                tables[g][b, len(have) :] = -1
             if rc.fresh_slot:
                 self.cache_tensors.zero_slot(rc.slot)
                 rc.fresh_slot = False
             t0 += n
+        # padding lanes of a fixed-size layout
+        nb = len(entries)
+        if t0 < layout.T:
+            tok[t0:] = 0
+            pos[t0:] = 0
+            sidx[t0:] = -1
+            for g in range(len(self.groups)):
+                slot_maps[g][t0:] = -1
+        if nb < B:
+            cu[nb + 1 :] = t0
+            ctx_lens[nb:] = 0
+            slots[nb:] = 0
+            for g in range(len(self.groups)):
+                tables[g][nb:] = -1
+        if r0 < layout.R:
+            rows[r0:] = 0
 
-        dev = torch.empty(layout.total, dtype=torch.int32, device=self.device)
-        dev.copy_(pinned[: layout.total], non_blocking=True)
-        self.h2d_bytes += layout.total * 4
-        ev = torch.cuda.Event()
-        ev.record()
-        self._pinned_events[slot_i] = ev
-
+    def _context(self, dev: torch.Tensor, layout: _Layout, max_q: int, max_context: int) -> StepContext:
+        B = layout.B
         groups = [
             GroupTables(
-                block_table=layout.view(dev, f"table{g}").view(B, widths[g]),
+                block_table=layout.view(dev, f"table{g}").view(B, layout.widths[g]),
                 slot_mapping=layout.view(dev, f"slots{g}"),
             )
             for g in range(len(self.groups))
         ]
-        step = StepContext(
-            num_tokens=T,
+        return StepContext(
+            num_tokens=layout.T,
             num_seqs=B,
             token_ids=layout.view(dev, "token_ids"),
             positions=layout.view(dev, "positions"),
@@ -246,21 +302,97 @@ class ModelRunner:
             context_lens=layout.view(dev, "context_lens"),
             state_slots=layout.view(dev, "state_slots"),
             groups=groups,
-            page_size=P,
-            max_seqlen_q=max(lens),
-            max_context_len=max(e.start + n for e, n in zip(entries, lens)),
-            host_seq_starts=[e.start for e in entries],
-            host_seq_lens=lens,
-            host_state_slots=[e.cache.slot for e in entries],
-            decode_only=max(lens) == 1,
+            page_size=self.page_size,
+            max_seqlen_q=max_q,
+            max_context_len=max_context,
+            decode_only=max_q == 1,
         )
-        return step, layout.view(dev, "rows"), R
+
+    # -- decode graphs ------------------------------------------------------------------------
+
+    def _graph_bucket(self, entries: Sequence[StepEntry]) -> Optional[int]:
+        if not self.use_graphs:
+            return None
+        B = len(entries)
+        if B > self.graph_buckets[-1]:
+            return None
+        for e in entries:
+            if len(e.tokens) != 1 or e.start + 1 > self.max_model_len:
+                return None
+        for b in self.graph_buckets:
+            if b >= B:
+                return b
+        return None
+
+    def _capture(self, bucket: int) -> "_DecodeGraph":
+        """Captures one decode step for `bucket` sequences: every kernel from the embedding to
+        the logits, reading its indices from one static buffer."""
+        from tokensprint_b200 import ops
+
+        width = max(1, -(-self.max_model_len // self.page_size))
+        layout = _Layout(bucket, bucket, bucket, [width] * len(self.groups))
+        dev = torch.zeros(layout.total, dtype=torch.int32, device=self.device)
+        host = torch.empty(layout.total, dtype=torch.int32, pin_memory=True)
+        # a harmless content for the warm-up and the capture: padding lanes only
+        self._fill(host.numpy(), layout, [], [])
+        host.numpy()[layout.sections["rows"][0] : layout.sections["rows"][0] + bucket] = np.arange(bucket)
+        dev.copy_(host)
+        step = self._context(dev, layout, 1, self.max_model_len)
+        rows = layout.view(dev, "rows")
+        torch.cuda.synchronize(self.device)
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):  # warm-up: loads libraries, sets kernel attributes, fills the allocator
+            for _ in range(2):
+                self.model.forward(step, self.layer_caches, rows, bucket)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = self.model.forward(step, self.layer_caches, rows, bucket)
+        kernels = ops.launch_count - before
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        return _DecodeGraph(bucket, layout, dev, host, graph, logits, kernels)
+
+    def _step_graph(self, bucket: int, entries: Sequence[StepEntry]) -> torch.Tensor:
+        g = self._graphs.get(bucket)
+        if g is None:
+            g = self._graphs[bucket] = self._capture(bucket)
+        if g.event is not None:
+            g.event.synchronize()
+        self._fill(g.host.numpy(), g.layout, entries, [1] * len(entries))
+        # in a graph every lane's logits are computed; the wanted ones are picked afterwards
+        rows_off = g.layout.sections["rows"][0]
+        g.host.numpy()[rows_off : rows_off + bucket] = np.arange(bucket)
+        g.dev.copy_(g.host, non_blocking=True)
+        self.h2d_bytes += g.layout.total * 4
+        if g.event is None:
+            g.event = torch.cuda.Event()
+        g.event.record()
+        g.graph.replay()
+        self.graph_launches += g.kernels
+        wanted = [b for b, e in enumerate(entries) if len(e.want)]
+        if len(wanted) == len(entries):
+            return g.logits[: len(entries)]
+        if not wanted:
+            return torch.empty((0, self.vocab_size), device=self.device, dtype=torch.float32)
+        return g.logits.index_select(0, torch.tensor(wanted, device=self.device))
 
     @torch.inference_mode()
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Float32 logits [wanted, vocab], in the order of the entries and of their `want`."""
-        step, rows, R = self.build_context(entries)
         self.steps_run += 1
+        bucket = self._graph_bucket(entries)
+        if bucket is not None:
+            for e in entries:
+                if e.cache.released or e.start + 1 > e.cache.num_tokens or not (0 <= e.tokens[0] < self.vocab_size):
+                    raise ValueError(f"request {e.cache.request!r}: bad decode entry")
+                if any(w != 0 for w in e.want):
+                    raise ValueError(f"request {e.cache.request!r}: wanted place outside its 1 token")
+            return self._step_graph(bucket, entries)
+        step, rows, R = self.build_context(entries)
         hidden, pending = self.model.forward_hidden(step, self.layer_caches)
         if R == 0:
             return torch.empty((0, self.vocab_size), device=self.device, dtype=torch.float32)

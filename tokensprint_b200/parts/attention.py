@@ -35,6 +35,8 @@ class AttentionMixer(Mixer):
     into one [(nq + 2 nkv) d, H] matrix.
     """
 
+    graph_safe = True
+
     def __init__(
         self,
         ctx: BuildContext,

@@ -149,6 +149,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True when a decode step of this mixer is a fixed sequence of kernels that read all
+    # per-step values from device memory (no host decisions): such a step may be captured
+    # in a CUDA graph.
+    graph_safe = False
+
     def cache_need(self) -> CacheNeed:
         return CacheNeed()
 
