@@ -78,6 +78,96 @@ __global__ void qk_norm_rope_store_kernel(const TA* __restrict__ qkv, TA* __rest
   for (int i = 2 * half + lane; i < d; i += 32) dst[i] = ts_from_float<TA>(x[i]);
 }
 
+// Fast path: full-width rotation (or none), head_dim a multiple of 4.  A lane owns the element
+// pairs (2l, 2l+1) (+64 per round) of the lower half and their partners in the upper half, keeps
+// them in registers from the norm to the rotation, and moves them with 4- or 8-byte accesses.
+#define QKR_ROUNDS 4
+
+__device__ __forceinline__ float2 ts_load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 ts_load2(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ void ts_store2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void ts_store2(__nv_bfloat16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+template <typename TA>
+__global__ void qk_norm_rope_store_pairs_kernel(const TA* __restrict__ qkv, TA* __restrict__ q_out,
+                                                TA* __restrict__ k_dst, TA* __restrict__ v_dst,
+                                                const int* __restrict__ slot_mapping,
+                                                const int* __restrict__ positions,
+                                                const float* __restrict__ q_norm_w,
+                                                const float* __restrict__ k_norm_w, float eps,
+                                                const float* __restrict__ inv_freq, int T, int nq, int nkv, int d) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = nq + 2 * nkv;
+  const long long item = (long long)blockIdx.x * QKR_WARPS + warp;
+  if (item >= (long long)T * heads) return;
+  const int t = (int)(item / heads);
+  const int head = (int)(item - (long long)t * heads);
+  const TA* src = qkv + ((size_t)t * heads + head) * d;
+  const bool is_q = head < nq;
+  const bool is_k = !is_q && head < nq + nkv;
+  int slot = -1;
+  if (!is_q) {
+    slot = slot_mapping ? slot_mapping[t] : t;
+    if (slot < 0) return;
+  }
+  if (!is_q && !is_k) {
+    TA* dst = v_dst + ((size_t)slot * nkv + (head - nq - nkv)) * d;
+    for (int i = 2 * lane; i < d; i += 64) {
+      const float2 v = ts_load2(src + i);
+      ts_store2(dst + i, v.x, v.y);
+    }
+    return;
+  }
+  const int half = d >> 1;
+  float2 lo[QKR_ROUNDS], hi[QKR_ROUNDS];
+  float ss = 0.f;
+#pragma unroll
+  for (int r = 0; r < QKR_ROUNDS; ++r) {
+    const int j = 2 * lane + 64 * r;
+    if (j < half) {
+      lo[r] = ts_load2(src + j);
+      hi[r] = ts_load2(src + half + j);
+      ss += lo[r].x * lo[r].x + lo[r].y * lo[r].y + hi[r].x * hi[r].x + hi[r].y * hi[r].y;
+    }
+  }
+  const float* w = is_q ? q_norm_w : k_norm_w;
+  float rstd = 1.f;
+  if (w) {
+    ss = ts_warp_sum(ss);
+    rstd = rsqrtf(ss / (float)d + eps);
+  }
+  TA* dst = is_q ? q_out + ((size_t)t * nq + head) * d : k_dst + ((size_t)slot * nkv + (head - nq)) * d;
+  const float pos = inv_freq ? (float)positions[t] : 0.f;
+#pragma unroll
+  for (int r = 0; r < QKR_ROUNDS; ++r) {
+    const int j = 2 * lane + 64 * r;
+    if (j < half) {
+      float2 a = lo[r], b = hi[r];
+      if (w) {
+        const float2 wl = ts_load2(w + j), wh = ts_load2(w + half + j);
+        a.x *= rstd * wl.x; a.y *= rstd * wl.y;
+        b.x *= rstd * wh.x; b.y *= rstd * wh.y;
+      }
+      if (inv_freq) {
+        const float2 f = ts_load2(inv_freq + j);
+        float s0, c0, s1, c1;
+        sincosf(pos * f.x, &s0, &c0);
+        sincosf(pos * f.y, &s1, &c1);
+        const float2 ra = make_float2(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+        const float2 rb = make_float2(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
+        a = ra;
+        b = rb;
+      }
+      ts_store2(dst + j, a.x, a.y);
+      ts_store2(dst + half + j, b.x, b.y);
+    }
+  }
+}
+
 TS_EXPORT int ts_qk_norm_rope_store(const void* qkv, int act_dtype, void* q_out, void* k_dst,
                                     void* v_dst, const int* slot_mapping, const int* positions,
                                     const float* q_norm_w, const float* k_norm_w, float eps,
@@ -90,6 +180,21 @@ TS_EXPORT int ts_qk_norm_rope_store(const void* qkv, int act_dtype, void* q_out,
   long long items = (long long)T * (nq + 2 * nkv);
   unsigned blocks = (unsigned)((items + QKR_WARPS - 1) / QKR_WARPS);
   cudaStream_t s = (cudaStream_t)stream;
+  const bool pairs = (d % 4 == 0) && (d / 2 <= 64 * QKR_ROUNDS) && (!inv_freq || rot_dim == d) &&
+                     (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_dst | (uintptr_t)v_dst | (uintptr_t)q_norm_w |
+                       (uintptr_t)k_norm_w | (uintptr_t)inv_freq) % 8 == 0);
+  if (pairs && act_dtype == TS_DTYPE_F32) {
+    qk_norm_rope_store_pairs_kernel<float><<<blocks, QKR_WARPS * 32, 0, s>>>(
+        (const float*)qkv, (float*)q_out, (float*)k_dst, (float*)v_dst, slot_mapping, positions, q_norm_w,
+        k_norm_w, eps, inv_freq, T, nq, nkv, d);
+    return ts_launch_status();
+  }
+  if (pairs && act_dtype == TS_DTYPE_BF16) {
+    qk_norm_rope_store_pairs_kernel<__nv_bfloat16><<<blocks, QKR_WARPS * 32, 0, s>>>(
+        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_dst, (__nv_bfloat16*)v_dst,
+        slot_mapping, positions, q_norm_w, k_norm_w, eps, inv_freq, T, nq, nkv, d);
+    return ts_launch_status();
+  }
   if (act_dtype == TS_DTYPE_F32)
     qk_norm_rope_store_kernel<float><<<blocks, QKR_WARPS * 32, 0, s>>>(
         (const float*)qkv, (float*)q_out, (float*)k_dst, (float*)v_dst, slot_mapping, positions,

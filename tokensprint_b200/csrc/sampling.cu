@@ -23,63 +23,101 @@ __device__ __forceinline__ float ts_exp_noise(uint64_t key, int index) {
   return -logf(u);
 }
 
-__global__ void sample_kernel(const float* __restrict__ logits, int V, long long row_stride,
-                              const float* __restrict__ temperature,
-                              const unsigned long long* __restrict__ keys, int* __restrict__ out) {
-  __shared__ float best_v[32];
-  __shared__ int best_i[32];
-  const int r = blockIdx.x;
+#define SAMPLE_CHUNK 2048
+#define SAMPLE_THREADS 256
+
+struct Best {
+  float v;
+  int i;
+};
+
+__device__ __forceinline__ Best better(Best a, Best b) {
+  // the larger value wins; on equal values the lower index; i = INT_MAX marks "nothing yet"
+  if (b.i != 0x7fffffff && (a.i == 0x7fffffff || b.v > a.v || (b.v == a.v && b.i < a.i))) return b;
+  return a;
+}
+
+__device__ __forceinline__ Best block_best(Best x, Best* shared /* [32] */) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best y;
+    y.v = __shfl_xor_sync(0xffffffffu, x.v, o);
+    y.i = __shfl_xor_sync(0xffffffffu, x.i, o);
+    x = better(x, y);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) shared[warp] = x;
+  __syncthreads();
+  if (warp == 0) {
+    const int nwarps = (blockDim.x + 31) >> 5;
+    Best none;
+    none.v = -INFINITY;
+    none.i = 0x7fffffff;
+    x = lane < nwarps ? shared[lane] : none;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      Best y;
+      y.v = __shfl_xor_sync(0xffffffffu, x.v, o);
+      y.i = __shfl_xor_sync(0xffffffffu, x.i, o);
+      x = better(x, y);
+    }
+  }
+  return x;  // valid in warp 0
+}
+
+// Stage 1: one CTA per (chunk of the vocabulary, row) finds the best entry of its chunk.
+__global__ void sample_partial_kernel(const float* __restrict__ logits, int V, long long row_stride,
+                                      const float* __restrict__ temperature,
+                                      const unsigned long long* __restrict__ keys, Best* __restrict__ partial) {
+  __shared__ Best shared[32];
+  const int r = blockIdx.y, chunk = blockIdx.x;
   const float* row = logits + (size_t)r * row_stride;
   const float temp = temperature[r];
   const bool greedy = !(temp > 1e-10f);
   const uint64_t key = keys ? keys[r] : 0ull;
-  float bv = -INFINITY;
-  int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  Best best;
+  best.v = -INFINITY;
+  best.i = 0x7fffffff;
+  const int end = min(V, (chunk + 1) * SAMPLE_CHUNK);
+  for (int i = chunk * SAMPLE_CHUNK + threadIdx.x; i < end; i += SAMPLE_THREADS) {
     float v = row[i];
     if (!greedy) v = v / temp - logf(fmaxf(ts_exp_noise(key, i), 1e-10f));
-    if (v > bv || (v == bv && i < bi) || bi == 0x7fffffff) {
-      bv = v;
-      bi = i;
-    }
+    Best cand;
+    cand.v = v;
+    cand.i = i;
+    best = better(best, cand);
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
-      bv = ov;
-      bi = oi;
-    }
-  }
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (lane == 0) {
-    best_v[warp] = bv;
-    best_i[warp] = bi;
-  }
-  __syncthreads();
-  if (warp == 0) {
-    const int nwarps = (blockDim.x + 31) >> 5;
-    bv = lane < nwarps ? best_v[lane] : -INFINITY;
-    bi = lane < nwarps ? best_i[lane] : 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
-        bv = ov;
-        bi = oi;
-      }
-    }
-    if (lane == 0) out[r] = bi;
-  }
+  best = block_best(best, shared);
+  if (threadIdx.x == 0) partial[(size_t)r * gridDim.x + chunk] = best;
+}
+
+// Stage 2: one CTA per row picks among the chunk winners.
+__global__ void sample_final_kernel(const Best* __restrict__ partial, int chunks, int* __restrict__ out) {
+  __shared__ Best shared[32];
+  const int r = blockIdx.x;
+  Best best;
+  best.v = -INFINITY;
+  best.i = 0x7fffffff;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) best = better(best, partial[(size_t)r * chunks + c]);
+  best = block_best(best, shared);
+  if (threadIdx.x == 0) out[r] = best.i;
+}
+
+TS_EXPORT long long ts_sample_scratch_bytes(int R, int V) {
+  const long long chunks = (V + SAMPLE_CHUNK - 1) / SAMPLE_CHUNK;
+  return (long long)R * chunks * (long long)sizeof(Best);
 }
 
 TS_EXPORT int ts_sample(const float* logits, int V, long long row_stride, const float* temperature,
-                        const unsigned long long* keys, int* out, int R, void* stream) {
+                        const unsigned long long* keys, int* out, int R, void* scratch, void* stream) {
   if (R <= 0) return 0;
-  if (V <= 0 || row_stride < V) return TS_ERR_BAD_ARGUMENT;
-  int threads = V >= 8192 ? 1024 : (V >= 1024 ? 256 : 64);
-  sample_kernel<<<R, threads, 0, (cudaStream_t)stream>>>(logits, V, row_stride, temperature, keys, out);
+  if (V <= 0 || row_stride < V || scratch == nullptr) return TS_ERR_BAD_ARGUMENT;
+  if (R > 65535) return TS_ERR_UNSUPPORTED_SIZE;
+  const int chunks = (V + SAMPLE_CHUNK - 1) / SAMPLE_CHUNK;
+  cudaStream_t s = (cudaStream_t)stream;
+  sample_partial_kernel<<<dim3(chunks, R), SAMPLE_THREADS, 0, s>>>(logits, V, row_stride, temperature, keys, (Best*)scratch);
+  int status = ts_launch_status();
+  if (status != 0) return status;
+  sample_final_kernel<<<R, 128, 0, s>>>((const Best*)scratch, chunks, out);
   return ts_launch_status();
 }

@@ -9,10 +9,10 @@
 // all heads that share a KV head share each loaded key/value tile.  Keys are walked in
 // blocks of BN with an online softmax; K and V blocks arrive by cp.async (16-byte
 // chunks, zero-filled where a key does not exist) two blocks ahead of the math.
-// Prefill uses 4 warps x 16 rows per CTA; decode (a few rows per sequence) uses one
-// warp per CTA and splits the keys of a sequence over several CTAs, whose partial
-// results (running max, sum, unnormalised output, float32) go to a scratch buffer and
-// are merged by attention_combine_kernel.
+// Prefill uses 8 warps x 16 rows per CTA.  Decode (at most 16 rows per sequence and KV head)
+// uses 4 warps that share the rows and take 16 keys each of every block, and splits the keys
+// of a sequence over several CTAs, whose partial results (running max, sum, unnormalised
+// output, float32) go to a scratch buffer and are merged by attention_combine_kernel.
 //
 // The order of the sums for one query row depends on its own keys and on the number of
 // splits only, never on what else is in the batch.
@@ -80,28 +80,37 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 
 // Copies keys [kbase, kbase + BN) of one KV head into a [BN][LD] tile; keys that do not
-// exist (beyond `kend`, or in a page that is not held) become zeros.
+// exist (beyond `kend`, or in a page that is not held) become zeros.  NT / BN threads share
+// a row and interleave its 16-byte chunks, so a thread looks its page up once per tile and
+// neighbouring lanes fetch neighbouring chunks.
 template <int NT>
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* tile, const __nv_bfloat16* cache, const int* table,
                                              int page, int nkv, int hk, int kbase, int kend, int tid) {
-  for (int c = tid; c < BN * CH; c += NT) {
-    const int row = c / CH, ch = c - row * CH;
-    const int j = kbase + row;
-    bool valid = j <= kend;
-    const __nv_bfloat16* src = cache;
-    if (valid) {
-      const int pg = table[j / page];
-      valid = pg >= 0;
-      if (valid) src = cache + (((size_t)pg * page + (j % page)) * nkv + hk) * D + ch * 8;
-    }
-    cp_async16(tile + row * LD + ch * 8, src, valid);
+  constexpr int TPR = NT / BN;  // threads per row
+  static_assert(NT % BN == 0 && TPR >= 1, "thread count must be a multiple of the key block");
+  const int row = tid / TPR;
+  const int j = kbase + row;
+  bool valid = j <= kend;
+  const __nv_bfloat16* src = cache;
+  if (valid) {
+    const int pg = table[j / page];
+    valid = pg >= 0;
+    if (valid) src = cache + (((size_t)pg * page + (j % page)) * nkv + hk) * D;
   }
+  __nv_bfloat16* dst = tile + row * LD;
+#pragma unroll
+  for (int ch = tid % TPR; ch < CH; ch += TPR) cp_async16(dst + ch * 8, valid ? src + ch * 8 : cache, valid);
 }
 
-template <int NWARPS>
+// SPLIT_KEYS = false (prefill): the CTA's warps own 16 query rows each and all walk every key.
+// SPLIT_KEYS = true (decode, at most 16 rows): the warps share the rows and own 16 keys each of
+// every 64-key block, with running max/sum/output of their own, merged when the keys are done.
+template <int NWARPS, bool SPLIT_KEYS>
 __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnParams p) {
   constexpr int NT = NWARPS * 32;
-  constexpr int BM = NWARPS * 16;
+  constexpr int BM = SPLIT_KEYS ? 16 : NWARPS * 16;
+  constexpr int NTILES = SPLIT_KEYS ? 2 : BN / 8;  // 8-key score tiles per warp and block
+  static_assert(!SPLIT_KEYS || NWARPS * 16 == BN, "key-split mode: the warps must cover one key block");
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [BM][LD]
   __nv_bfloat16* k_s = q_s + BM * LD;                                        // [STAGES][BN][LD]
@@ -134,11 +143,13 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   const int nblocks = kb1 - kb0 + 1;  // may be <= 0 for a split without work
   const int* table = p.block_table + (size_t)b * p.max_blocks;
 
-  // Rows of this thread: (warp * 16 + g) and (+ 8).
+  // Rows of this thread: g and g + 8 of the warp's 16-row tile.
+  const int warp_row0 = SPLIT_KEYS ? 0 : warp * 16;
+  const int key0 = SPLIT_KEYS ? warp * 16 : 0;  // first key of the block this warp scores
   int row_pos[2], row_lo[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const int r = r0 + warp * 16 + g + 8 * h;
+    const int r = r0 + warp_row0 + g + 8 * h;
     row_pos[h] = r < rows_total ? start_pos + r / G : -1;
     row_lo[h] = (p.window > 0 && row_pos[h] >= 0) ? max(0, row_pos[h] - p.window + 1) : 0;
   }
@@ -168,7 +179,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
   unsigned q_frag[Q_IN_REGS ? D / 16 : 1][4];
-  const __nv_bfloat16* q_warp = q_s + (warp * 16) * LD;
+  const __nv_bfloat16* q_warp = q_s + warp_row0 * LD;
   if (nblocks > 0) {
     cp_async_wait<2>();  // the queries have landed (K and V of block 0 may still fly)
   } else {
@@ -197,13 +208,13 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     }
     __syncthreads();
 
-    // S = Q K^T
-    float s[BN / 8][4];
+    // S = Q K^T over this warp's keys of the block
+    float s[NTILES][4];
 #pragma unroll
-    for (int i = 0; i < BN / 8; ++i)
+    for (int i = 0; i < NTILES; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
-    const __nv_bfloat16* k_tile = k_s + stage * BN * LD;
+    const __nv_bfloat16* k_tile = k_s + stage * BN * LD + key0 * LD;
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) {
       unsigned a[4];
@@ -215,7 +226,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
                     q_warp + ((lane & 7) + ((lane >> 3) & 1) * 8) * LD + ks * 16 + (lane >> 4) * 8);
       }
 #pragma unroll
-      for (int np = 0; np < BN / 16; ++np) {
+      for (int np = 0; np < NTILES / 2; ++np) {
         unsigned b0, b1, b2, b3;
         ldmatrix_x4(b0, b1, b2, b3,
                     k_tile + (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
@@ -227,11 +238,11 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     // scale, mask, online softmax (log2 domain)
     float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
-    for (int nt = 0; nt < BN / 8; ++nt) {
+    for (int nt = 0; nt < NTILES; ++nt) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int h = e >> 1;
-        const int j = kbase + nt * 8 + tq * 2 + (e & 1);
+        const int j = kbase + key0 + nt * 8 + tq * 2 + (e & 1);
         const bool ok = j <= row_pos[h] && j >= row_lo[h];
         const float v = ok ? s[nt][e] * p.scale_log2 : -INFINITY;
         s[nt][e] = v;
@@ -249,7 +260,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     }
     float l_add[2] = {0.f, 0.f};
 #pragma unroll
-    for (int nt = 0; nt < BN / 8; ++nt) {
+    for (int nt = 0; nt < NTILES; ++nt) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int h = e >> 1;
@@ -276,9 +287,9 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     __syncthreads();
 
     // O += P V
-    const __nv_bfloat16* v_tile = v_s + stage * BN * LD;
+    const __nv_bfloat16* v_tile = v_s + stage * BN * LD + key0 * LD;
 #pragma unroll
-    for (int kk = 0; kk < BN / 16; ++kk) {
+    for (int kk = 0; kk < NTILES / 2; ++kk) {
       unsigned a[4];
       a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
       a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -303,9 +314,58 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
   }
 
+  if constexpr (SPLIT_KEYS) {
+    // Merge the warps (each saw its own quarter of the keys) through shared memory, which
+    // is free now: the loop's last barrier is behind us and no copy is in flight.
+    float* m_s = reinterpret_cast<float*>(k_s);        // [NWARPS][16]
+    float* l_s = m_s + NWARPS * 16;                    // [NWARPS][16]
+    float* o_s = l_s + NWARPS * 16;                    // [NWARPS][16][D]
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = g + 8 * h;
+      if (tq == 0) {
+        m_s[warp * 16 + r] = m_run[h];
+        l_s[warp * 16 + r] = l_run[h];
+      }
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i)
+        *reinterpret_cast<float2*>(o_s + (warp * 16 + r) * D + i * 8 + tq * 2) = make_float2(o_acc[i][2 * h], o_acc[i][2 * h + 1]);
+    }
+    __syncthreads();
+    for (int r = warp; r < 16; r += NWARPS) {  // a warp per row, lanes over the head dims
+      const int row = r0 + r;
+      if (row >= rows_total) continue;
+      float m = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < NWARPS; ++w)
+        if (l_s[w * 16 + r] > 0.f) m = fmaxf(m, m_s[w * 16 + r]);
+      float l = 0.f, wgt[NWARPS];
+#pragma unroll
+      for (int w = 0; w < NWARPS; ++w) {
+        wgt[w] = l_s[w * 16 + r] > 0.f ? exp2f(m_s[w * 16 + r] - m) : 0.f;
+        l += wgt[w] * l_s[w * 16 + r];
+      }
+      const size_t qrow = (size_t)(q_begin + row / G) * p.nq + hk * G + row % G;
+      const float inv = (p.splits == 1) ? (l > 0.f ? 1.f / l : 0.f) : 1.f;
+      for (int d = lane; d < D; d += 32) {
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) acc += wgt[w] * o_s[(w * 16 + r) * D + d];
+        if (p.splits == 1)
+          p.out[qrow * D + d] = __float2bfloat16_rn(acc * inv);
+        else
+          p.part_o[(qrow * p.splits + split) * D + d] = acc;
+      }
+      if (p.splits > 1 && lane == 0) {
+        float* ml = p.part_ml + (qrow * p.splits + split) * 2;
+        ml[0] = m;
+        ml[1] = l;
+      }
+    }
+  } else {
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const int r = r0 + warp * 16 + g + 8 * h;
+    const int r = r0 + warp_row0 + g + 8 * h;
     if (r >= rows_total) continue;
     const size_t qrow = (size_t)(q_begin + r / G) * p.nq + hk * G + r % G;
     if (p.splits == 1) {
@@ -327,6 +387,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
         ml[1] = l_run[h];
       }
     }
+  }
   }
 }
 
@@ -370,18 +431,19 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
   }
 }
 
-template <int NWARPS>
+template <int NWARPS, bool SPLIT_KEYS>
 int launch(const AttnParams& p, int B, cudaStream_t stream) {
-  constexpr int BM = NWARPS * 16;
+  constexpr int BM = SPLIT_KEYS ? 16 : NWARPS * 16;
   const size_t smem = (size_t)(BM + 2 * STAGES * BN) * LD * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<NWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<NWARPS, SPLIT_KEYS>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid(p.row_tiles * p.splits, p.nkv, B);
-  attention_mma_kernel<NWARPS><<<grid, NWARPS * 32, smem, stream>>>(p);
+  attention_mma_kernel<NWARPS, SPLIT_KEYS><<<grid, NWARPS * 32, smem, stream>>>(p);
   return ts_launch_status();
 }
 
@@ -431,10 +493,10 @@ TS_EXPORT int ts_attention_paged_mma(const void* q, const void* kcache, const vo
   int status;
   if (rows <= 16) {
     p.row_tiles = 1;
-    status = launch<1>(p, B, stream);
+    status = launch<4, true>(p, B, stream);
   } else {
-    p.row_tiles = (int)((rows + 63) / 64);
-    status = launch<4>(p, B, stream);
+    p.row_tiles = (int)((rows + 127) / 128);
+    status = launch<8, false>(p, B, stream);
   }
   if (status != 0) return status;
   if (splits > 1) {

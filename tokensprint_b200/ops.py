@@ -34,7 +34,7 @@ _SIGNATURES = {
         _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p,
     ],
-    "ts_sample": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p],
+    "ts_sample": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p],
     "ts_sgemm_nt": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_void_p],
 }
 
@@ -307,8 +307,13 @@ def sample(
             raise KernelError("sample: keys is shorter than the batch")
     if temperature.numel() < R or out.numel() < R:
         raise KernelError("sample: temperature/out are shorter than the batch")
+    # stage 1 leaves one (value, index) pair per 2048-entry chunk of each row for stage 2
+    scratch = torch.empty(R * (-(-V // 2048)) * 2, dtype=torch.int32, device=logits.device)
     _check("sample", _fn("ts_sample")(
-        logits.data_ptr(), V, logits.stride(0), temperature.data_ptr(), _ptr(keys), out.data_ptr(), R, _stream()))
+        logits.data_ptr(), V, logits.stride(0), temperature.data_ptr(), _ptr(keys), out.data_ptr(), R,
+        scratch.data_ptr(), _stream()))
+    global launch_count
+    launch_count += 1  # two kernels per call
 
 
 def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
