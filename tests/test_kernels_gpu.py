@@ -359,3 +359,46 @@ def test_sample_matches_the_plain_race_and_the_distribution():
     assert out2.tolist() == got
     ops.sample(logits, temps, keys + 1, out2)
     assert out2.tolist() != got
+
+
+# ---------------------------------------------------------------------------
+# skinny GEMM on tcgen05
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize(
+    "M,N,K",
+    [(1, 128, 64), (8, 6144, 4096), (16, 4096, 12288), (3, 200, 72), (17, 384, 1000), (33, 1000, 4096), (64, 2048, 1024),
+     (100, 300, 520), (128, 256, 512), (5, 24576, 1024)],
+)
+def test_gemm_skinny_tcgen05(M, N, K, out_dtype):
+    from tokensprint_b200 import ops
+
+    g = torch.Generator().manual_seed(M * 7 + N)
+    x = torch.randn(M, K, generator=g).to(DEV, torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(DEV, torch.bfloat16)
+    out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
+    ops.gemm_skinny_bf16(x, w, out)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    want = x.double() @ w.double().T
+    tol = 1e-2 if out_dtype == torch.bfloat16 else 1e-5
+    assert rel_err(out, want) < tol
+    # twice in a row (the ticket counters must be back at zero), and a row alone gives the same bits
+    out2 = torch.full_like(out, float("nan"))
+    ops.gemm_skinny_bf16(x, w, out2)
+    assert torch.equal(out, out2)
+    out1 = torch.empty((1, N), device=DEV, dtype=out_dtype)
+    ops.gemm_skinny_bf16(x[M - 1 :], w, out1)
+    assert torch.equal(out1[0], out[M - 1])
+
+
+def test_gemm_skinny_refuses_what_it_cannot_take():
+    from tokensprint_b200 import ops
+
+    x = torch.zeros(129, 64, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(ops.KernelError):
+        ops.gemm_skinny_bf16(x, w, torch.empty(129, 128, device=DEV, dtype=torch.bfloat16))
+    with pytest.raises(ops.KernelError):
+        ops.gemm_skinny_bf16(x[:4, :60], w[:, :60], torch.empty(4, 128, device=DEV, dtype=torch.bfloat16))

@@ -15,6 +15,7 @@ from typing import Any, Optional, Sequence as Seq
 
 import torch
 
+from tokensprint_b200 import ops
 from tokensprint_b200.config.engine_config import Config, SamplingParams
 from tokensprint_b200.engine.runner import ModelRunner, StepEntry
 from tokensprint_b200.engine.scheduler import Scheduler
@@ -80,6 +81,7 @@ class LLMEngine:
                 keys.append(sample_key(seq.seed, seq.sample_stream, len(seq)))
         logits = self.model_runner.step(entries)
         token_ids = self.sampler.sample(logits, temps, keys)
+        ops.check_device_errors()  # the copy of the sampled ids has just synchronised
         self.scheduler.postprocess(seqs, token_ids, need)
         outputs = [(seq.seq_id, seq.completion_token_ids) for seq in seqs if seq.is_finished]
         num_total_tokens = sum(len(seq) for seq in seqs if seq.is_finished)

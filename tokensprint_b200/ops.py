@@ -431,3 +431,72 @@ def attention_paged_mma(
 
 def attention_scratch_floats(rows: int, splits: int, head_dim: int) -> int:
     return rows * splits * (head_dim + 2) if splits > 1 else 0
+
+
+# ---------------------------------------------------------------------------
+# skinny GEMM on tcgen05 tensor cores (decode steps)
+
+GEMM_SKINNY_MAX_ROWS = 128
+_SIGNATURES["ts_gemm_skinny_bf16"] = [
+    _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_int,
+    _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+]
+_gemm_workspaces: dict[tuple[int, int], tuple[torch.Tensor, torch.Tensor]] = {}
+_GEMM_MAX_TILES = 1 << 16
+
+
+def _gemm_workspace(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per (device, stream): the ticket counters of the K-split tiles (zero between launches)
+    and the error word, which lives in pinned host memory so the host can look at it without
+    a copy."""
+    key = (device.index or 0, _stream())
+    ws = _gemm_workspaces.get(key)
+    if ws is None:
+        counters = torch.zeros(_GEMM_MAX_TILES, dtype=torch.int32, device=device)
+        error = torch.zeros(1, dtype=torch.int32).pin_memory()
+        ws = _gemm_workspaces[key] = (counters, error)
+    return ws
+
+
+def gemm_skinny_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    M, K = x.shape
+    return (
+        x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < M <= GEMM_SKINNY_MAX_ROWS
+        and K % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+        and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and -(-w.shape[0] // 128) <= _GEMM_MAX_TILES
+    )
+
+
+def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M,N] = x[M,K] @ w[N,K]^T for M <= 128 on the tcgen05 tensor cores.
+
+    x, w bfloat16 with unit inner stride and rows that start on 16-byte boundaries; out
+    bfloat16 or float32.  Layers with few weight rows are cut along K; the slices meet in a
+    float32 scratch that this wrapper allocates.
+    """
+    if not (x.is_cuda and w.is_cuda and out.is_cuda):
+        raise KernelError("gemm_skinny_bf16: CUDA tensors only (there is no CPU path)")
+    if not gemm_skinny_supported(x, w):
+        raise KernelError(
+            f"gemm_skinny_bf16: needs bfloat16, at most {GEMM_SKINNY_MAX_ROWS} rows, K a multiple of 8 and 16-byte "
+            f"aligned rows; got x {tuple(x.shape)} {x.dtype} strides {x.stride()}, w {tuple(w.shape)} {w.dtype}")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"gemm_skinny_bf16: shapes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
+    lib = library()
+    splits = lib.ts_gemm_skinny_splits(N, K)
+    partial = torch.empty(splits * M * N, dtype=torch.float32, device=x.device) if splits > 1 else None
+    counters, error = _gemm_workspace(x.device)
+    _check("gemm_skinny_bf16", _fn("ts_gemm_skinny_bf16")(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0), out.stride(0),
+        1 if out.dtype == torch.float32 else 0, _ptr(partial), counters.data_ptr(), error.data_ptr(), _stream()))
+
+
+def check_device_errors() -> None:
+    """Raises if a kernel reported that one of its bounded waits gave up.  Cheap: reads
+    pinned host words; call it wherever the host has just synchronised anyway."""
+    for (dev, _), (_, error) in _gemm_workspaces.items():
+        if int(error[0]) != 0:
+            error[0] = 0
+            raise KernelError(f"gemm_skinny_bf16 on cuda:{dev}: a wait on an mbarrier gave up (the kernel returned early)")

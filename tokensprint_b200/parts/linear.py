@@ -1,9 +1,11 @@
 """Matrix product of activations with a row-major [out, in] weight.
 
-bfloat16 runs use the library GEMM (cuBLAS through torch.mm), as the reference does
-with nn.Linear (engine/nn/attention.py:122-135, engine/nn/layers.py:61-66); float32
-runs use the engine's own FFMA kernel, so no reduced-precision matrix mode can slip
-into the 32-bit path whatever torch's global switches say.
+bfloat16: steps of up to 128 tokens (decode, short portions) stream the weights through
+the engine's own tcgen05 kernel (csrc/gemm_tcgen05.cu); larger steps use the library
+GEMM (cuBLAS through torch.mm), as the reference does with nn.Linear
+(engine/nn/attention.py:122-135, engine/nn/layers.py:61-66).  float32 runs use the
+engine's own FFMA kernel, so no reduced-precision matrix mode can slip into the 32-bit
+path whatever torch's global switches say.
 """
 
 from __future__ import annotations
@@ -29,7 +31,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
     elif x.dtype == torch.bfloat16:
         if not x.is_cuda:
             raise ops.KernelError("linear: there is no CPU path")
-        torch.mm(x, weight.t(), out=out)
+        if T <= ops.GEMM_SKINNY_MAX_ROWS and ops.gemm_skinny_supported(x, weight):
+            ops.gemm_skinny_bf16(x, weight, out)
+        else:
+            torch.mm(x, weight.t(), out=out)
     else:
         raise ops.KernelError(f"linear: unsupported dtype {x.dtype}")
     return out
@@ -39,4 +44,8 @@ def linear_float32_out(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """Same product with a float32 result (the logits)."""
     if x.dtype == torch.float32:
         return linear(x, weight)
+    if x.shape[0] <= ops.GEMM_SKINNY_MAX_ROWS and ops.gemm_skinny_supported(x, weight):
+        out = torch.empty((x.shape[0], weight.shape[0]), device=x.device, dtype=torch.float32)
+        ops.gemm_skinny_bf16(x, weight, out)
+        return out
     return linear(x, weight).float()
