@@ -2,20 +2,31 @@
 //   out[M, N] = X[M, K] * W[N, K]^T,  M <= 128 tokens, float32 accumulation in tensor memory.
 //
 // A decode step reads every weight once and does little math with it, so the kernel is built
-// to stream W at HBM speed.  The roles are swapped against the usual picture: the 128 rows
-// of a W tile are the MMA's M dimension, the (padded) tokens its N dimension, so even one
-// token fills the tensor core's rows.  Per CTA: one 128-row tile of W and one slice of K.
-//   * thread 0 of warp 0 issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of
-//     [128 x 64] W tiles and [MPAD x 64] X tiles into a ring of shared-memory stages;
-//   * thread 0 of warp 1 issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=MPAD, K=16)
-//     from those stages into a TMEM accumulator and frees each stage with tcgen05.commit;
-//   * all four warps read the accumulator back with tcgen05.ld and store it.
-// Layers with few rows (o_proj, down_proj) would leave most SMs idle, so K is cut into
-// `splits` slices; each CTA writes its float32 partial tile to scratch, takes a ticket, and
-// the CTA that arrives last adds the slices in their fixed order and writes the result.
-// Nobody waits for anybody there; the only waits are on mbarriers fed by this CTA's own
-// copies and MMAs, and each of them gives up after a bounded number of tries, raises the
-// error word and lets the CTA free its tensor memory and return.
+// to stream W at HBM speed from every SM at once.  The roles are swapped against the usual
+// picture: the 128 rows of a W tile are the MMA's M dimension, the (padded) tokens its N
+// dimension, so even one token fills the tensor core's rows.
+//
+// Work is counted in units of (128-row tile of W) x (64-wide chunk of K).  The grid is one
+// persistent CTA per SM; CTA c takes the contiguous unit range [c * U/P, (c+1) * U/P), which
+// may start and end in the middle of a tile (stream-K), so all SMs stream the same number of
+// bytes whatever the layer's shape.  Inside a CTA, six warps:
+//   * warp 0, one thread: TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of [128 x 64] W
+//     tiles and [MPAD x 64] X tiles into a ring of shared-memory stages, running ahead
+//     across tile boundaries;
+//   * warp 1, one thread: tcgen05.mma (cta_group::1, kind::f16, M=128, N=MPAD, K=16) from the
+//     stages into one of two TMEM accumulators; tcgen05.commit frees each stage and hands
+//     each finished accumulator over;
+//   * warps 2-5: read an accumulator back with tcgen05.ld while the next one fills, and
+//     store it.  A tile that one CTA covered alone goes straight to the output.  A tile
+//     shared by several CTAs goes to a float32 scratch slot; each contributor takes a
+//     ticket, and the one that arrives last adds the slots in contributor order and writes
+//     the result.  Nobody waits for another CTA.
+// Every wait is on an mbarrier fed by this CTA's own copies and MMAs and gives up after a
+// bounded number of tries; then the CTA raises the error word, frees its tensor memory and
+// returns.
+//
+// The split of the work depends on the weight's shape and the SM count only, so a token's
+// result does not depend on what else is in the batch.
 //
 // The reference runs these products through nn.Linear (engine/nn/attention.py:122-135,
 // engine/nn/layers.py:61-66); W is row-major [out, in] as there.
@@ -26,20 +37,43 @@
 
 #include "common.cuh"
 
+// Optional timestamps for tuning (compile with -DTS_GEMM_PROBE): every CTA records the
+// nanosecond timer at a few points into args.probe[cta * 8 + i].
+#ifdef TS_GEMM_PROBE
+#define TS_PROBE(i) do { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); args.probe[blockIdx.x * 8 + (i)] = t_; } while (0)
+#else
+#define TS_PROBE(i) do { } while (0)
+#endif
+
 namespace {
 
-constexpr int TILE_N = 128;   // W rows per CTA (the MMA's M)
+constexpr int TILE_N = 128;   // W rows per tile (the MMA's M)
 constexpr int TILE_K = 64;    // bf16 per stage and row: one 128-byte swizzle atom
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 6;
+constexpr int NUM_THREADS = 192;
+constexpr int MAX_CONTRIB = 8;   // most CTAs that may share one tile
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+template <int MPAD>
+struct Cfg {
+  static constexpr uint32_t A_BYTES = TILE_N * TILE_K * 2;
+  static constexpr uint32_t B_BYTES = MPAD * TILE_K * 2;
+  static constexpr uint32_t STAGE_BYTES = A_BYTES + ((B_BYTES + 1023) / 1024) * 1024;
+  static constexpr int STAGES = MPAD <= 16 ? 10 : (MPAD <= 32 ? 9 : (MPAD <= 64 ? 8 : 6));
+  static constexpr uint32_t TMEM_COLS = 2 * MPAD < 32 ? 32 : 2 * MPAD;
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;
+};
 
 struct GemmArgs {
   void* out;             // [M, ldo] bf16 or f32
-  float* partial;        // [splits, M, N] f32 (splits > 1)
+  float* partial;        // [ctas, 2, M, 128] f32: at most two shared tiles per CTA
   int* counters;         // [n_tiles] zero before the first launch, zero again after each
   int* error;            // set to 1 when a wait gave up
-  int M, N, K, ldo, splits, out_f32;
+  int M, N, K, ldo, out_f32;
+  int tiles, chunks, units_per;  // chunks of K per tile; units (tile x chunk) per CTA
+#ifdef TS_GEMM_PROBE
+  unsigned long long* probe;
+#endif
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -49,6 +83,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // Bounded wait for a phase of an mbarrier.  False: gave up (or another role already did).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
@@ -84,33 +121,44 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// The share of one CTA: units [u0, u1) of tiles * chunks.
+struct Range {
+  int u0, u1;
+};
+__device__ __forceinline__ Range cta_range(const GemmArgs& a, int cta) {
+  const long long total = (long long)a.tiles * a.chunks;
+  Range r;
+  r.u0 = (int)min(total, (long long)cta * a.units_per);
+  r.u1 = (int)min(total, (long long)(cta + 1) * a.units_per);
+  return r;
+}
 
 template <int MPAD>
-__global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
-                                                          const __grid_constant__ CUtensorMap map_x,
-                                                          const GemmArgs args) {
-  constexpr uint32_t A_BYTES = TILE_N * TILE_K * 2;
-  constexpr uint32_t B_BYTES = MPAD * TILE_K * 2;
-  constexpr uint32_t STAGE_BYTES = A_BYTES + ((B_BYTES + 1023) / 1024) * 1024;
-  constexpr uint32_t TMEM_COLS = MPAD < 32 ? 32 : MPAD;
+__global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                  const __grid_constant__ CUtensorMap map_x,
+                                                                  const GemmArgs args) {
+  using C = Cfg<MPAD>;
+  constexpr int STAGES = C::STAGES;
   constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MPAD >> 3) << 17) | ((uint32_t)(TILE_N >> 4) << 24);
 
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t full_bar[STAGES];
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
-  __shared__ __align__(8) uint64_t acc_bar;
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   __shared__ int last_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n0 = blockIdx.x * TILE_N;
-  const int split = blockIdx.y;
-  const int chunks = (args.K + TILE_K - 1) / TILE_K;
-  const int per = (chunks + args.splits - 1) / args.splits;
-  const int kc0 = split * per;
-  const int nk = max(0, min(chunks, kc0 + per) - kc0);
+  if (tid == 0) TS_PROBE(0);
+  const Range range = cta_range(args, blockIdx.x);
+  const int chunks = args.chunks;
+  const int t_first = range.u0 / chunks;
+  const int t_last = range.u1 > range.u0 ? (range.u1 - 1) / chunks : t_first - 1;
 
   if (tid == 0) {
     abort_s = 0;
@@ -119,13 +167,16 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
-    mbar_init(smem_u32(&acc_bar), 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&acc_full[a]), 1);
+      mbar_init(smem_u32(&acc_empty[a]), 4);  // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 0) {
     __syncwarp();
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(C::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -133,121 +184,179 @@ __global__ void __launch_bounds__(128) gemm_skinny_kernel(const __grid_constant_
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_s;
   volatile int* abort_flag = &abort_s;
+  if (tid == 0) TS_PROBE(1);
 
-  if (nk > 0) {
-    if (warp == 0 && lane == 0) {
-      // Producer: TMA loads into the ring.
-      int issued = 0;
-      for (int i = 0; i < nk; ++i) {
-        const int s = i % STAGES;
-        const uint32_t round = (uint32_t)(i / STAGES);
-        if (i >= STAGES && !mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, abort_flag)) break;
+  if (warp == 0) {
+    if (lane == 0) {
+      // Producer: TMA loads into the ring, unit after unit, across tile boundaries.
+      const int n_units = range.u1 - range.u0;
+      int it = 0;
+      for (; it < n_units; ++it) {
+        const int u = range.u0 + it;
+        const int t = u / chunks, kc = u - t * chunks;
+        const int s = it % STAGES;
+        const uint32_t round = (uint32_t)(it / STAGES);
+        if (round > 0 && !mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, abort_flag)) break;
         const uint32_t bar = smem_u32(&full_bar[s]);
-        const uint32_t dst = smem_u32(smem + (size_t)s * STAGE_BYTES);
-        mbar_expect_tx(bar, A_BYTES + B_BYTES);
-        tma_load_2d(dst, &map_w, bar, (kc0 + i) * TILE_K, n0);
-        tma_load_2d(dst + A_BYTES, &map_x, bar, (kc0 + i) * TILE_K, 0);
-        issued = i + 1;
+        const uint32_t dst = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
+        mbar_expect_tx(bar, C::A_BYTES + C::B_BYTES);
+        tma_load_2d(dst, &map_w, bar, kc * TILE_K, t * TILE_N);
+        tma_load_2d(dst + C::A_BYTES, &map_x, bar, kc * TILE_K, 0);
       }
       if (*abort_flag) {
         // Let the copies that are still in flight land before shared memory is given up.
-        for (int i = max(0, issued - STAGES); i < issued; ++i)
+        for (int i = max(0, it - STAGES); i < it; ++i)
           mbar_wait(smem_u32(&full_bar[i % STAGES]), (uint32_t)(i / STAGES) & 1, abort_flag);
       }
-    } else if (warp == 1 && lane == 0) {
-      // MMA issuer.
-      bool ok = true;
-      for (int i = 0; i < nk && ok; ++i) {
-        const int s = i % STAGES;
-        ok = mbar_wait(smem_u32(&full_bar[s]), (uint32_t)(i / STAGES) & 1, abort_flag);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
-        const uint64_t adesc = umma_desc_sw128(a_addr);
-        const uint64_t bdesc = umma_desc_sw128(a_addr + A_BYTES);
-#pragma unroll
-        for (int k = 0; k < TILE_K / UMMA_K; ++k) {
-          // 16 bf16 = 32 bytes further along K inside the swizzle atom: +2 in the address field
-          umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);
-        }
-        umma_commit(smem_u32(&empty_bar[s]));  // arrives when these MMAs have read the stage
-      }
-      if (ok) umma_commit(smem_u32(&acc_bar));  // arrives when the accumulator is complete
     }
-    __syncwarp();
-    // Everybody: wait for the accumulator.
-    mbar_wait(smem_u32(&acc_bar), 0, abort_flag);
-  }
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  __syncthreads();
-  const bool aborted = abort_s != 0;
-
-  if (!aborted) {
-    const int n = n0 + warp * 32 + lane;  // this thread's W row = output column
-    const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // MMA issuer.
+      int it = 0, item = 0;
+      bool ok = true;
+      for (int t = t_first; t <= t_last && ok; ++t, ++item) {
+        const int k0 = max(range.u0, t * chunks) - t * chunks;
+        const int k1 = min(range.u1, (t + 1) * chunks) - t * chunks;
+        const int acc = item & 1;
+        const uint32_t use = (uint32_t)(item >> 1);
+        if (use > 0 && !mbar_wait(smem_u32(&acc_empty[acc]), (use - 1) & 1, abort_flag)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * MPAD);
+        for (int kc = k0; kc < k1; ++kc, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(smem_u32(&full_bar[s]), (uint32_t)(it / STAGES) & 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if (it == 0) TS_PROBE(2);
+          const uint32_t a_addr = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
+          const uint64_t adesc = umma_desc_sw128(a_addr);
+          const uint64_t bdesc = umma_desc_sw128(a_addr + C::A_BYTES);
 #pragma unroll
-    for (int c = 0; c < MPAD / 16; ++c) {
-      uint32_t r[16];
-      if (nk > 0) {
+          for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+            // 16 bf16 = 32 bytes further along K inside the swizzle atom: +2 in the address field
+            umma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, IDESC, (kc > k0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&empty_bar[s]));  // arrives when these MMAs have read the stage
+        }
+        if (ok) umma_commit(smem_u32(&acc_full[acc]));  // arrives when this accumulator is complete
+      }
+      TS_PROBE(3);
+    }
+  } else {
+    // Epilogue warps 2..5: TMEM lanes 32 * (warp % 4) .. + 31.
+    const int quarter = warp & 3;
+    const int etid = (warp - 2) * 32 + lane;  // 0..127 among the epilogue threads
+    int item = 0;
+    for (int t = t_first; t <= t_last; ++t, ++item) {
+      const int k0 = max(range.u0, t * chunks) - t * chunks;
+      const int k1 = min(range.u1, (t + 1) * chunks) - t * chunks;
+      const bool whole = (k0 == 0 && k1 == chunks);
+      const int acc = item & 1;
+      if (!mbar_wait(smem_u32(&acc_full[acc]), (uint32_t)(item >> 1) & 1, abort_flag)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (etid == 0 && t == t_last) TS_PROBE(4);
+      const int n_local = quarter * 32 + lane;
+      const int n = t * TILE_N + n_local;
+      const int slot = (t == t_first) ? 0 : 1;
+      float* part = args.partial + ((size_t)(blockIdx.x * 2 + slot) * args.M) * TILE_N;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * MPAD);
+      uint32_t r[MPAD / 16][16];
+#pragma unroll
+      for (int c = 0; c < MPAD / 16; ++c) {
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+            : "=r"(r[c][0]), "=r"(r[c][1]), "=r"(r[c][2]), "=r"(r[c][3]), "=r"(r[c][4]), "=r"(r[c][5]), "=r"(r[c][6]),
+              "=r"(r[c][7]), "=r"(r[c][8]), "=r"(r[c][9]), "=r"(r[c][10]), "=r"(r[c][11]), "=r"(r[c][12]), "=r"(r[c][13]),
+              "=r"(r[c][14]), "=r"(r[c][15])
             : "r"(taddr + c * 16));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) r[i] = 0u;
       }
-      if (n < args.N) {
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      // The accumulator is in registers: hand it back to the MMA warp before storing.
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
+#pragma unroll
+      for (int c = 0; c < MPAD / 16; ++c) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const int m = c * 16 + i;
-          if (m >= args.M) break;
-          const float v = __uint_as_float(r[i]);
-          if (args.splits > 1)
-            args.partial[((size_t)split * args.M + m) * args.N + n] = v;
-          else if (args.out_f32)
-            reinterpret_cast<float*>(args.out)[(size_t)m * args.ldo + n] = v;
-          else
-            reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)m * args.ldo + n] = __float2bfloat16_rn(v);
-        }
-      }
-    }
-    if (args.splits > 1) {
-      // Ticket: whoever arrives last for this tile adds the slices, in slice order.
-      __threadfence();
-      __syncthreads();
-      if (tid == 0) {
-        const int ticket = atomicAdd(&args.counters[blockIdx.x], 1);
-        last_s = (ticket == args.splits - 1) ? 1 : 0;
-      }
-      __syncthreads();
-      if (last_s) {
-        __threadfence();
-        const int nn = n0 + tid;
-        if (nn < args.N) {
-          for (int m = 0; m < args.M; ++m) {
-            float acc = 0.f;
-            for (int s = 0; s < args.splits; ++s) acc += __ldcg(&args.partial[((size_t)s * args.M + m) * args.N + nn]);
-            if (args.out_f32)
-              reinterpret_cast<float*>(args.out)[(size_t)m * args.ldo + nn] = acc;
-            else
-              reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)m * args.ldo + nn] = __float2bfloat16_rn(acc);
+          if (m < args.M) {
+            const float v = __uint_as_float(r[c][i]);
+            if (!whole)
+              part[(size_t)m * TILE_N + n_local] = v;
+            else if (n < args.N) {
+              if (args.out_f32)
+                reinterpret_cast<float*>(args.out)[(size_t)m * args.ldo + n] = v;
+              else
+                reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)m * args.ldo + n] = __float2bfloat16_rn(v);
+            }
           }
         }
-        if (tid == 0) args.counters[blockIdx.x] = 0;
+      }
+      if (!whole) {
+        // Ticket: whoever arrives last for this tile adds the slots, in contributor order.
+        const int c_first = (int)(((long long)t * chunks) / args.units_per);
+        const int c_last = (int)(((long long)(t + 1) * chunks - 1) / args.units_per);
+        __threadfence();
+        epilogue_sync();
+        if (etid == 0) {
+          const int ticket = atomicAdd(&args.counters[t], 1);
+          last_s = (ticket == c_last - c_first) ? 1 : 0;
+        }
+        epilogue_sync();
+        const bool last = last_s != 0;
+        epilogue_sync();  // everyone has read the flag before the next tile may rewrite it
+        if (last) {
+          __threadfence();
+          // Slot of every contributor for this tile (0: it is that CTA's first tile, else 1).
+          const float* src[MAX_CONTRIB];
+          const int nc = min(c_last - c_first + 1, MAX_CONTRIB);
+#pragma unroll
+          for (int j = 0; j < MAX_CONTRIB; ++j) {
+            const int c = c_first + min(j, nc - 1);
+            const int c_t_first = (int)(((long long)c * args.units_per) / chunks);
+            src[j] = args.partial + (size_t)(c * 2 + ((t == c_t_first) ? 0 : 1)) * args.M * TILE_N;
+          }
+          for (int idx = etid; idx < args.M * (TILE_N / 4); idx += 128) {
+            const int m = idx / (TILE_N / 4), nl = (idx % (TILE_N / 4)) * 4;
+            const size_t off = (size_t)m * TILE_N + nl;
+            // all loads first (they are independent), then the sum in contributor order
+            float4 v[MAX_CONTRIB];
+#pragma unroll
+            for (int j = 0; j < MAX_CONTRIB; ++j)
+              if (j < nc) v[j] = __ldcg(reinterpret_cast<const float4*>(src[j] + off));
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < MAX_CONTRIB; ++j)
+              if (j < nc) { sum.x += v[j].x; sum.y += v[j].y; sum.z += v[j].z; sum.w += v[j].w; }
+            const int nn = t * TILE_N + nl;
+            const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (nn + j < args.N) {
+                if (args.out_f32)
+                  reinterpret_cast<float*>(args.out)[(size_t)m * args.ldo + nn + j] = vals[j];
+                else
+                  reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)m * args.ldo + nn + j] = __float2bfloat16_rn(vals[j]);
+              }
+            }
+          }
+          if (etid == 0) args.counters[t] = 0;
+        }
       }
     }
-  } else if (tid == 0) {
-    *args.error = 1;
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (tid == 0) TS_PROBE(5);
+  if (abort_s != 0 && tid == 0) *args.error = 1;
   if (warp == 0) {
     __syncwarp();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
   }
 }
 
@@ -317,61 +426,81 @@ int tensor_map(const void* ptr, long long rows, long long cols, long long ld, in
 }
 
 template <int MPAD>
-int launch_skinny(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, int n_tiles, cudaStream_t stream) {
-  constexpr size_t A_BYTES = TILE_N * TILE_K * 2;
-  constexpr size_t B_BYTES = MPAD * TILE_K * 2;
-  constexpr size_t STAGE_BYTES = A_BYTES + ((B_BYTES + 1023) / 1024) * 1024;
-  const size_t smem = STAGES * STAGE_BYTES + 1024;
+int launch_skinny(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, int ctas, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<MPAD>::SMEM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  gemm_skinny_kernel<MPAD><<<dim3(n_tiles, a.splits), 128, smem, stream>>>(mw, mx, a);
+  gemm_skinny_kernel<MPAD><<<ctas, NUM_THREADS, Cfg<MPAD>::SMEM, stream>>>(mw, mx, a);
   return ts_launch_status();
+}
+
+int sm_count() {
+  static int count = 0;
+#ifdef TS_GEMM_PROBE
+  if (getenv("TS_GEMM_CTAS")) return atoi(getenv("TS_GEMM_CTAS"));
+#endif
+  if (count == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || count <= 0)
+      count = 148;
+  }
+  return count;
+}
+
+// Units (tile x chunk) per CTA for an [N, K] weight: the work is spread over all SMs, but no
+// tile is shared by more than MAX_CONTRIB CTAs.
+void plan(int N, int K, int* tiles, int* chunks, int* units_per, int* ctas) {
+  *tiles = (N + TILE_N - 1) / TILE_N;
+  *chunks = (K + TILE_K - 1) / TILE_K;
+  const long long total = (long long)*tiles * *chunks;
+  long long per = (total + sm_count() - 1) / sm_count();
+  const long long least = (*chunks + MAX_CONTRIB - 2) / (MAX_CONTRIB - 1);
+  if (per < least) per = least;
+  if (per < 1) per = 1;
+  *units_per = (int)per;
+  *ctas = (int)((total + per - 1) / per);
 }
 
 }  // namespace
 
-// How many K slices the kernel would use for an [N, K] weight (depends on the shape only,
-// so a token's result never depends on the batch around it).
-TS_EXPORT int ts_gemm_skinny_splits(int N, int K) {
-  const int tiles = (N + TILE_N - 1) / TILE_N;
-  const int chunks = (K + TILE_K - 1) / TILE_K;
-  int s = 1;
-  while (s < 8 && tiles * s < 148 && chunks / (s * 2) >= 8) s *= 2;
-  return s;
-}
+#ifdef TS_GEMM_PROBE
+unsigned long long* ts_gemm_probe_buffer = nullptr;
+#endif
 
-// Scratch the caller brings: floats for the partial tiles (splits * M * N when splits > 1).
+// Floats of scratch the caller brings for an [N, K] weight and M rows: two shared-tile slots
+// per CTA.
 TS_EXPORT long long ts_gemm_skinny_scratch_floats(int M, int N, int K) {
-  const int s = ts_gemm_skinny_splits(N, K);
-  return s > 1 ? (long long)s * M * N : 0;
+  int tiles, chunks, units_per, ctas;
+  plan(N, K, &tiles, &chunks, &units_per, &ctas);
+  return (long long)ctas * 2 * M * TILE_N;
 }
 
 TS_EXPORT int ts_gemm_skinny_max_rows() { return 128; }
 
 // out[M, ldo] (bf16, or f32 when out_f32) = x[M, K] (row stride ldx) * w[N, K]^T (row stride ldw).
-// `counters`: ints, one per 128-row tile of W, zero before the first call (the kernel leaves
-// them zero).  `error`: one int the kernel sets to 1 if one of its waits gave up.
+// `partial`: ts_gemm_skinny_scratch_floats(M, N, K) floats.  `counters`: ints, one per 128-row
+// tile of W, zero before the first call (the kernel leaves them zero).  `error`: one int the
+// kernel sets to 1 if one of its waits gave up.
 TS_EXPORT int ts_gemm_skinny_bf16(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
                                   long long ldw, long long ldo, int out_f32, float* partial, int* counters,
                                   int* error, void* stream_) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || ldx < K || ldw < K || ldo < N || counters == nullptr || error == nullptr) return TS_ERR_BAD_ARGUMENT;
-  if (M > 128 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x % 16) || ((uintptr_t)w % 16))
+  if (K <= 0 || ldx < K || ldw < K || ldo < N || counters == nullptr || error == nullptr || partial == nullptr)
+    return TS_ERR_BAD_ARGUMENT;
+  if (M > 128 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)partial % 16))
     return TS_ERR_UNSUPPORTED_SIZE;
-  const int splits = ts_gemm_skinny_splits(N, K);
-  if (splits > 1 && partial == nullptr) return TS_ERR_BAD_ARGUMENT;
   const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
-  const int n_tiles = (N + TILE_N - 1) / TILE_N;
+  GemmArgs a;
+  int ctas;
+  plan(N, K, &a.tiles, &a.chunks, &a.units_per, &ctas);
   CUtensorMap mw, mx;
   int st = tensor_map(w, N, K, ldw, TILE_N, &mw);
   if (st != 0) return st;
   st = tensor_map(x, M, K, ldx, mpad, &mx);
   if (st != 0) return st;
-  GemmArgs a;
   a.out = out;
   a.partial = partial;
   a.counters = counters;
@@ -380,13 +509,15 @@ TS_EXPORT int ts_gemm_skinny_bf16(const void* x, const void* w, void* out, int M
   a.N = N;
   a.K = K;
   a.ldo = (int)ldo;
-  a.splits = splits;
   a.out_f32 = out_f32;
+#ifdef TS_GEMM_PROBE
+  a.probe = ts_gemm_probe_buffer;
+#endif
   cudaStream_t stream = (cudaStream_t)stream_;
   switch (mpad) {
-    case 16: return launch_skinny<16>(mw, mx, a, n_tiles, stream);
-    case 32: return launch_skinny<32>(mw, mx, a, n_tiles, stream);
-    case 64: return launch_skinny<64>(mw, mx, a, n_tiles, stream);
-    default: return launch_skinny<128>(mw, mx, a, n_tiles, stream);
+    case 16: return launch_skinny<16>(mw, mx, a, ctas, stream);
+    case 32: return launch_skinny<32>(mw, mx, a, ctas, stream);
+    case 64: return launch_skinny<64>(mw, mx, a, ctas, stream);
+    default: return launch_skinny<128>(mw, mx, a, ctas, stream);
   }
 }

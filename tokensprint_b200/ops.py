@@ -471,8 +471,8 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> Non
     """out[M,N] = x[M,K] @ w[N,K]^T for M <= 128 on the tcgen05 tensor cores.
 
     x, w bfloat16 with unit inner stride and rows that start on 16-byte boundaries; out
-    bfloat16 or float32.  Layers with few weight rows are cut along K; the slices meet in a
-    float32 scratch that this wrapper allocates.
+    bfloat16 or float32.  The work is spread evenly over all SMs; tiles that two CTAs share
+    meet in a float32 scratch that this wrapper allocates.
     """
     if not (x.is_cuda and w.is_cuda and out.is_cuda):
         raise KernelError("gemm_skinny_bf16: CUDA tensors only (there is no CPU path)")
@@ -484,9 +484,9 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> Non
     N = w.shape[0]
     if w.shape[1] != K or tuple(out.shape) != (M, N) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"gemm_skinny_bf16: shapes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
-    lib = library()
-    splits = lib.ts_gemm_skinny_splits(N, K)
-    partial = torch.empty(splits * M * N, dtype=torch.float32, device=x.device) if splits > 1 else None
+    scratch_floats = library().ts_gemm_skinny_scratch_floats
+    scratch_floats.restype = _c_ll
+    partial = torch.empty(max(4, scratch_floats(M, N, K)), dtype=torch.float32, device=x.device)
     counters, error = _gemm_workspace(x.device)
     _check("gemm_skinny_bf16", _fn("ts_gemm_skinny_bf16")(
         x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0), out.stride(0),

@@ -1,6 +1,6 @@
 """Matrix product of activations with a row-major [out, in] weight.
 
-bfloat16: steps of up to 128 tokens (decode, short portions) stream the weights through
+bfloat16: steps of up to SKINNY_ROWS tokens (decode, short portions) stream the weights through
 the engine's own tcgen05 kernel (csrc/gemm_tcgen05.cu); larger steps use the library
 GEMM (cuBLAS through torch.mm), as the reference does with nn.Linear
 (engine/nn/attention.py:122-135, engine/nn/layers.py:61-66).  float32 runs use the
@@ -17,6 +17,12 @@ import torch
 from tokensprint_b200 import ops
 
 
+# Up to this many rows the engine's own weight-streaming kernel is used; above it the
+# library GEMM is (measured on B200 at Qwen3-8B sizes: the own kernel wins while the step is
+# bound by reading the weights).
+SKINNY_ROWS = 32
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [T, in] @ weight[out, in]^T -> [T, out] in x's dtype."""
     if x.dtype != weight.dtype:
@@ -31,7 +37,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
     elif x.dtype == torch.bfloat16:
         if not x.is_cuda:
             raise ops.KernelError("linear: there is no CPU path")
-        if T <= ops.GEMM_SKINNY_MAX_ROWS and ops.gemm_skinny_supported(x, weight):
+        if T <= SKINNY_ROWS and ops.gemm_skinny_supported(x, weight):
             ops.gemm_skinny_bf16(x, weight, out)
         else:
             torch.mm(x, weight.t(), out=out)
@@ -44,7 +50,7 @@ def linear_float32_out(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """Same product with a float32 result (the logits)."""
     if x.dtype == torch.float32:
         return linear(x, weight)
-    if x.shape[0] <= ops.GEMM_SKINNY_MAX_ROWS and ops.gemm_skinny_supported(x, weight):
+    if x.shape[0] <= SKINNY_ROWS and ops.gemm_skinny_supported(x, weight):
         out = torch.empty((x.shape[0], weight.shape[0]), device=x.device, dtype=torch.float32)
         ops.gemm_skinny_bf16(x, weight, out)
         return out
