@@ -1,0 +1,336 @@
+"""Each part alone against the plain functions, and the generality of the layer machinery:
+a toy mixer with state of its own, a layer that runs twice, a layer that reads another's cache.
+The toy parts are defined here; no file of the framework changes for them."""
+
+from dataclasses import asdict, dataclass
+
+import pytest
+import torch
+
+from tests.plain import qwen3_plain as plain
+from tests.replay_helpers import replay_in_process, trace_decode_tail, trace_mixed, trace_portions, trace_whole
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rel_err(got, want):
+    got, want = got.double().cpu(), want.double().cpu()
+    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
+def ctx(dtype):
+    from tokensprint_b200.parts.base import BuildContext
+
+    return BuildContext(device=torch.device(DEV), dtype=dtype)
+
+
+def one_sequence_step(T, page, dtype, start=0):
+    """A StepContext for one sequence of T tokens at positions start..start+T-1, pages 3, 1, 4, ... ."""
+    from tokensprint_b200.parts.base import GroupTables, StepContext
+
+    n_pages = -(-(start + T) // page)
+    table = [(7 * i + 3) % (n_pages + 5) for i in range(n_pages)]
+    assert len(set(table)) == n_pages
+    slots = [table[p // page] * page + p % page for p in range(start, start + T)]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    step = StepContext(
+        num_tokens=T, num_seqs=1, token_ids=i32([0] * T), positions=i32(list(range(start, start + T))),
+        seq_index=i32([0] * T), cu_seqlens_q=i32([0, T]), context_lens=i32([start + T]), state_slots=i32([0]),
+        groups=[GroupTables(block_table=i32([table]), slot_mapping=i32(slots))], page_size=page,
+        max_seqlen_q=T, max_context_len=start + T, host_seq_starts=[start], host_seq_lens=[T], host_state_slots=[0])
+    return step, n_pages + 5
+
+
+TOL = {torch.float32: 1e-5, torch.bfloat16: 2e-2}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from tokensprint_b200.parts.base import PartSpec, build_part
+
+    H, T, eps = 200, 6, 1e-4
+    norm = build_part("norm", PartSpec("rmsnorm", {"dim": H, "eps": eps, "weight": "w"}), ctx(dtype))
+    assert [(s.name, s.shape, s.role) for s in norm.tensor_specs()] == [("w", (H,), "vector")]
+    w = 1 + 0.1 * torch.randn(H, device=DEV)
+    norm.load({"w": w})
+    hidden = torch.randn(T, H, device=DEV)
+    delta = torch.randn(T, H, device=DEV).to(dtype)
+    want_h = hidden.double() + delta.double()
+    out = torch.empty(T, H, device=DEV, dtype=dtype)
+    norm.forward(hidden, delta, out)
+    assert rel_err(hidden, want_h) < 1e-6
+    assert rel_err(out, plain.rms_norm(want_h.cpu(), w.double().cpu(), eps)) < TOL[dtype]
+
+
+def test_position_part_owns_the_reference_frequencies():
+    from tokensprint_b200.parts.base import PartSpec, build_part
+
+    rope = build_part("position_encoding", PartSpec("rotary", {"dim": 48, "theta": 5e4}), ctx(torch.float32))
+    assert torch.equal(rope.rotary_inv_freq().cpu(), plain.rope_inverse_frequencies(48, 5e4))
+    with pytest.raises(ValueError):
+        build_part("position_encoding", PartSpec("rotary", {"dim": 7, "theta": 1e4}), ctx(torch.float32))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part(dtype):
+    from tokensprint_b200.parts.base import PartSpec, build_part
+
+    H, I, T = 72, 104, 9
+    ffn = build_part("feed_forward", PartSpec("swiglu", {"hidden_size": H, "intermediate_size": I, "gate": "g", "up": "u", "down": "d"}), ctx(dtype))
+    assert {s.name: s.shape for s in ffn.tensor_specs()} == {"g": (I, H), "u": (I, H), "d": (H, I)}
+    w = {"g": torch.randn(I, H) * 0.2, "u": torch.randn(I, H) * 0.2, "d": torch.randn(H, I) * 0.2}
+    ffn.load({k: v.to(DEV, dtype) for k, v in w.items()})
+    x = torch.randn(T, H)
+    got = ffn.forward(x.to(DEV, dtype), None)
+    wd = {f"p.{k}_proj.weight": v.to(dtype).double() for k, v in (("gate", w["g"]), ("up", w["u"]), ("down", w["d"]))}
+    want = plain.swiglu_ffn(x.to(dtype).double(), wd, "p.")
+    assert rel_err(got, want) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 10])
+def test_attention_part_and_block(dtype, window):
+    """The attention mixer alone (prefill of a portion that starts mid-sequence is covered by the
+    replay tests; here one whole sequence), then a whole pre-norm block around it."""
+    from tokensprint_b200.parts.base import LayerCache, PartSpec, build_part
+
+    H, nq, nkv, d, I, T, page, eps, theta = 80, 6, 2, 32, 96, 37, 8, 1e-5, 1e4
+    names = {k: f"a.{k}" for k in ("q", "k", "v", "o", "q_norm", "k_norm")}
+    mixer_spec = PartSpec("attention", {"hidden_size": H, "num_heads": nq, "num_kv_heads": nkv, "head_dim": d, "qk_norm": True,
+                                        "qk_norm_eps": eps, "window": window, "position": PartSpec("rotary", {"dim": d, "theta": theta}), **names})
+    g = torch.Generator().manual_seed(3)
+    w = {"a.q": torch.randn(nq * d, H, generator=g) * 0.2, "a.k": torch.randn(nkv * d, H, generator=g) * 0.2,
+         "a.v": torch.randn(nkv * d, H, generator=g) * 0.2, "a.o": torch.randn(H, nq * d, generator=g) * 0.2,
+         "a.q_norm": 1 + 0.1 * torch.randn(d, generator=g), "a.k_norm": 1 + 0.1 * torch.randn(d, generator=g),
+         "f.g": torch.randn(I, H, generator=g) * 0.2, "f.u": torch.randn(I, H, generator=g) * 0.2, "f.d": torch.randn(H, I, generator=g) * 0.2,
+         "n1": 1 + 0.1 * torch.randn(H, generator=g), "n2": 1 + 0.1 * torch.randn(H, generator=g)}
+    dev_w = {k: (v.to(DEV) if v.dim() == 1 else v.to(DEV, dtype)) for k, v in w.items()}
+    pw = {}
+    for k, v in w.items():
+        v = v.double() if v.dim() == 1 else v.to(dtype).double()
+        pw[{"a.q": "p.self_attn.q_proj.weight", "a.k": "p.self_attn.k_proj.weight", "a.v": "p.self_attn.v_proj.weight",
+            "a.o": "p.self_attn.o_proj.weight", "a.q_norm": "p.self_attn.q_norm.weight", "a.k_norm": "p.self_attn.k_norm.weight",
+            "f.g": "p.mlp.gate_proj.weight", "f.u": "p.mlp.up_proj.weight", "f.d": "p.mlp.down_proj.weight",
+            "n1": "p.input_layernorm.weight", "n2": "p.post_attention_layernorm.weight"}[k]] = v
+
+    step, n_pages = one_sequence_step(T, page, dtype)
+    cache = LayerCache(group=0, k_pages=torch.zeros(n_pages, page, nkv, d, device=DEV, dtype=dtype),
+                       v_pages=torch.zeros(n_pages, page, nkv, d, device=DEV, dtype=dtype))
+    mixer = build_part("mixer", mixer_spec, ctx(dtype))
+    need = mixer.cache_need()
+    assert (need.kind, need.window, need.kv_heads, need.head_dim) == ("window" if window else "full", window, nkv, d)
+    mixer.load(dev_w)
+    x = torch.randn(T, H, generator=g)
+    got = mixer.forward(x.to(DEV, dtype), step, cache)
+    want = plain.attention_layer(x.to(dtype).double(), pw, "p.self_attn.", list(range(T)), num_heads=nq, num_kv_heads=nkv,
+                                 head_dim=d, rope_theta=theta, eps=eps, window=window or None)
+    assert rel_err(got, want) < TOL[dtype]
+
+    block = build_part("block", PartSpec("pre_norm", {
+        "mixer": mixer_spec,
+        "feed_forward": PartSpec("swiglu", {"hidden_size": H, "intermediate_size": I, "gate": "f.g", "up": "f.u", "down": "f.d"}),
+        "mixer_norm": PartSpec("rmsnorm", {"dim": H, "eps": eps, "weight": "n1"}),
+        "ffn_norm": PartSpec("rmsnorm", {"dim": H, "eps": eps, "weight": "n2"})}), ctx(dtype))
+    block.load(dev_w)
+    hidden = torch.randn(T, H, generator=g).to(DEV)
+    h0 = hidden.double().cpu()
+    pending = block.forward(hidden, None, step, cache)
+    cfg = {"rms_norm_eps": eps, "num_attention_heads": nq, "num_key_value_heads": nkv, "head_dim": d, "rope_theta": theta}
+    pw2 = {"model.layers.0." + k[2:]: v for k, v in pw.items()}
+    want_h = plain.block(h0, pw2, 0, list(range(T)), cfg, window or None)
+    assert rel_err(hidden.double().cpu() + pending.double().cpu(), want_h) < TOL[dtype]
+
+
+# ---------------------------------------------------------------------------
+# a toy architecture defined here: attention layers beside a mixer with per-request state
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    vocab_size: int = 97
+    hidden_size: int = 48
+    num_hidden_layers: int = 3
+    intermediate_size: int = 64
+    rms_norm_eps: float = 1e-5
+    architectures: tuple = ("ToyStateForCausalLM",)
+
+    def to_dict(self):
+        d = asdict(self)
+        d["architectures"] = list(self.architectures)
+        return d
+
+    def save(self, folder):
+        import json
+        from pathlib import Path
+
+        Path(folder).mkdir(parents=True, exist_ok=True)
+        (Path(folder) / "config.json").write_text(json.dumps(self.to_dict()))
+
+
+def _register_toy():
+    from tokensprint_b200.config.registry import register_architecture
+    from tokensprint_b200.models.spec import ModelSpec
+    from tokensprint_b200.parts.base import CacheNeed, Mixer, PartSpec, TensorSpec, register_part
+
+    @register_part("mixer", "toy_running_mean", replace=True)
+    class RunningMeanMixer(Mixer):
+        """y_t = W * mean(x_0 .. x_t).  Its cache is no page at all but one slot per request:
+        the running sum of the inputs and their count (width + 1 floats)."""
+
+        def __init__(self, bctx, *, hidden_size, weight):
+            self.H, self.weight_name, self.dtype = hidden_size, weight, bctx.dtype
+            self.weight = None
+
+        def cache_need(self):
+            return CacheNeed(kind="none", state_shape=(self.H + 1,), state_dtype=torch.float32)
+
+        def tensor_specs(self):
+            return [TensorSpec(self.weight_name, (self.H, self.H))]
+
+        def load(self, tensors):
+            self.weight = tensors[self.weight_name]
+
+        def forward(self, x, step, cache):
+            out = torch.empty_like(x)
+            t0 = 0
+            for n, slot in zip(step.host_seq_lens, step.host_state_slots):
+                state = cache.state[slot]
+                sums = state[: self.H] + torch.cumsum(x[t0 : t0 + n].float(), dim=0)
+                counts = state[self.H] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+                out[t0 : t0 + n] = ((sums / counts[:, None]).to(x.dtype) @ self.weight.t())
+                state[: self.H] = sums[-1]
+                state[self.H] = counts[-1]
+                t0 += n
+            return out
+
+    @register_architecture("ToyStateForCausalLM", config_from_dict=lambda d: ToyConfig(**{k: (tuple(v) if isinstance(v, list) else v) for k, v in d.items()}))
+    def build_toy(cfg: ToyConfig):
+        layers = []
+        for i in range(cfg.num_hidden_layers):
+            p = f"toy.{i}."
+            if i % 2 == 0:
+                mixer = PartSpec("toy_running_mean", {"hidden_size": cfg.hidden_size, "weight": p + "mix.weight"})
+            else:
+                mixer = PartSpec("attention", {"hidden_size": cfg.hidden_size, "num_heads": 3, "num_kv_heads": 1, "head_dim": 16,
+                                               "position": PartSpec("rotary", {"dim": 16, "theta": 1e4}),
+                                               "q": p + "q", "k": p + "k", "v": p + "v", "o": p + "o"})
+            norm = {"dim": cfg.hidden_size, "eps": cfg.rms_norm_eps}
+            layers.append(PartSpec("pre_norm", {
+                "mixer": mixer,
+                "feed_forward": PartSpec("swiglu", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size,
+                                                    "gate": p + "gate", "up": p + "up", "down": p + "down"}),
+                "mixer_norm": PartSpec("rmsnorm", {**norm, "weight": p + "n1"}),
+                "ffn_norm": PartSpec("rmsnorm", {**norm, "weight": p + "n2"})}))
+        return ModelSpec(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, embedding="toy.embed", layers=layers,
+                         final_norm=PartSpec("rmsnorm", {"dim": cfg.hidden_size, "eps": cfg.rms_norm_eps, "weight": "toy.norm"}),
+                         lm_head="toy.head", max_positions=512)
+
+
+def _plain_toy(weights, cfg: ToyConfig, ids):
+    w = {k: v.double() for k, v in weights.items()}
+    T = len(ids)
+    h = plain.embedding(w["toy.embed"], ids)
+    for i in range(cfg.num_hidden_layers):
+        p = f"toy.{i}."
+        x = plain.rms_norm(h, w[p + "n1"], cfg.rms_norm_eps)
+        if i % 2 == 0:
+            mean = torch.cumsum(x, dim=0) / torch.arange(1, T + 1, dtype=torch.float64)[:, None]
+            a = mean @ w[p + "mix.weight"].T
+        else:
+            q = (x @ w[p + "q"].T).view(T, 3, 16)
+            k = (x @ w[p + "k"].T).view(T, 1, 16)
+            v = (x @ w[p + "v"].T).view(T, 1, 16)
+            ang = plain.rope_angles(range(T), 16, 1e4)
+            o = plain.causal_attention(plain.apply_rope(q, ang), plain.apply_rope(k, ang), v, scale=16**-0.5)
+            a = o.reshape(T, 48) @ w[p + "o"].T
+        h = h + a
+        x = plain.rms_norm(h, w[p + "n2"], cfg.rms_norm_eps)
+        g, u = x @ w[p + "gate"].T, x @ w[p + "up"].T
+        h = h + (g * torch.sigmoid(g) * u) @ w[p + "down"].T
+    return plain.rms_norm(h, w["toy.norm"], cfg.rms_norm_eps) @ w["toy.head"].T
+
+
+def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
+    from tokensprint_b200.config.registry import unregister_architecture
+    from tokensprint_b200.engine.replay import TraceReplayer
+    from tokensprint_b200.parts.base import unregister_part
+    from tokensprint_b200.weights.loader import write_random_model
+    from tokensprint_b200.weights.safetensors_io import SafetensorsFolder
+
+    _register_toy()
+    try:
+        cfg = ToyConfig()
+        folder = write_random_model(tmp_path / "toy", cfg, seed=4, dtype="float32", std=0.15)
+        files = SafetensorsFolder(folder)
+        weights = {n: files.tensor(n).clone() for n in files.keys()}
+        assert "toy.0.mix.weight" in weights and "toy.1.q" in weights
+        g = torch.Generator().manual_seed(8)
+        requests = {f"r{i}": torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for i, n in enumerate((3, 20, 41, 64))}
+        want = {rid: _plain_toy(weights, cfg, ids) for rid, ids in requests.items()}
+        many = dict(requests)
+        many.update({k + "x": v for k, v in requests.items()})
+        for steps, reqs in ((trace_whole(requests), requests), (trace_decode_tail(requests, 16), requests),
+                            (trace_portions(requests), requests), (trace_mixed(many, 256, seed=3), many)):
+            replayer = TraceReplayer.from_folder(folder, "float32", 256)
+            runner = replayer.runner
+            assert [g.kind for g in runner.groups] == ["full"]  # one page group; the toy mixer has none
+            assert runner.cache_tensors.state[0] is not None and runner.cache_tensors.k[0] is None
+            assert not runner.use_graphs
+            got = replay_in_process(replayer, steps)
+            for (rid, pos), row in got.items():
+                ref = want[rid.rstrip("x")][pos].numpy()
+                assert abs(row - ref).max() < 1e-4 * abs(want[rid.rstrip("x")]).max(), f"{rid} position {pos}"
+            assert len(got) == sum(len(v) for v in reqs.values())
+    finally:
+        unregister_architecture("ToyStateForCausalLM")
+        unregister_part("mixer", "toy_running_mean")
+
+
+def test_run_order_is_data_a_layer_twice_and_a_shared_cache(tmp_path):
+    """Run order: layer 0, layer 1, layer 0 again (own cache), layer 2 reading layer 1's cache."""
+    from tests.tiny_configs import TINY_B, tiny_weights, write_model_folder
+    from tokensprint_b200.config.model_config import Qwen3Config
+    from tokensprint_b200.engine.replay import TraceReplayer
+    from tokensprint_b200.engine.runner import ModelRunner
+    from tokensprint_b200.models.model import Model
+    from tokensprint_b200.models.qwen3 import build_qwen3_spec
+    from tokensprint_b200.models.spec import RunSpec
+    from tokensprint_b200.weights.loader import FolderSource
+
+    cfg = TINY_B
+    weights = tiny_weights(cfg, 21, std=0.05, sharp=2.0)
+    folder = write_model_folder(tmp_path / "m", cfg, weights)
+    spec = build_qwen3_spec(Qwen3Config.from_dict(cfg))
+    spec.run_order = [RunSpec(0), RunSpec(1, cache=7), RunSpec(0), RunSpec(2, cache=7, writes_cache=False)]
+    model = Model(spec, DEV, torch.float32)
+    assert len(model.cache_plan) == 3 and model.run_cache == [0, 1, 2, 1]
+    model.load(FolderSource(folder))
+    runner = ModelRunner(model, page_size=16, num_pages=32, num_slots=4)
+
+    # plain: the same order; the last run attends with its own queries over layer 1's keys and values
+    w = {k: v.double() for k, v in weights.items()}
+    ids = torch.randint(0, cfg["vocab_size"], (45,), generator=torch.Generator().manual_seed(2)).tolist()
+    T, pos = len(ids), list(range(len(ids)))
+    nq, nkv, d, eps, theta = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"], cfg["rope_theta"]
+    h = plain.embedding(w["model.embed_tokens.weight"], ids)
+    h = plain.block(h, w, 0, pos, cfg, None)
+    x1 = plain.rms_norm(h, w["model.layers.1.input_layernorm.weight"], eps)
+    ang = plain.rope_angles(pos, d, theta)
+    k1 = plain.apply_rope(plain.rms_norm((x1 @ w["model.layers.1.self_attn.k_proj.weight"].T).view(T, nkv, d), w["model.layers.1.self_attn.k_norm.weight"], eps), ang)
+    v1 = (x1 @ w["model.layers.1.self_attn.v_proj.weight"].T).view(T, nkv, d)
+    h = plain.block(h, w, 1, pos, cfg, None)
+    h = plain.block(h, w, 0, pos, cfg, None)
+    p = "model.layers.2."
+    x2 = plain.rms_norm(h, w[p + "input_layernorm.weight"], eps)
+    q2 = plain.apply_rope(plain.rms_norm((x2 @ w[p + "self_attn.q_proj.weight"].T).view(T, nq, d), w[p + "self_attn.q_norm.weight"], eps), ang)
+    a = plain.causal_attention(q2, k1, v1, scale=d**-0.5).reshape(T, nq * d) @ w[p + "self_attn.o_proj.weight"].T
+    h = h + a
+    h = h + plain.swiglu_ffn(plain.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps), w, p + "mlp.")
+    want = plain.rms_norm(h, w["model.norm.weight"], eps) @ w["lm_head.weight"].T
+
+    for steps in (trace_whole({"a": ids}), trace_portions({"a": ids}), trace_decode_tail({"a": ids}, 20)):
+        got = replay_in_process(TraceReplayer(runner), steps)
+        for (rid, position), row in got.items():
+            assert abs(row - want[position].numpy()).max() < 1e-4 * float(want.abs().max()), f"position {position}"
+    assert runner.cache_manager.pages_in_use() == 0
