@@ -330,7 +330,108 @@ def run_ours(args) -> dict:
 
 
 def run_reference(args) -> dict:
-    return {"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref"}
+    """The unmodified reference (installed under baseline/_ref) through its own public API:
+    build_model for the same sizes, random weights, LLMEngine.add_request/step.  The reference
+    cannot load a checkpoint here (its loader downloads from a hub and there is no network), so
+    the model object comes from its own builder and is filled with random values."""
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "engine").is_dir():
+        return {"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref"}
+    try:
+        return _run_reference(args, ref_root)
+    except Exception as e:  # an import or launch error of the reference's stack on this box
+        reason = f"{type(e).__name__}: {e}".replace("\n", " ")[:300]
+        return {"impl": "reference", "unavailable": f"the reference failed to run on this box: {reason}"}
+
+
+def _run_reference(args, ref_root: Path) -> dict:
+    import tempfile
+
+    sys.path.insert(0, str(ref_root))
+    import torch
+    from engine.generation.config import Config as RefConfig
+    from engine.generation.config import SamplingParams as RefSamplingParams
+    from engine.generation.llm_engine import LLMEngine as RefEngine
+    from engine.models import build_model
+    from engine.models.qwen._archs import QwenModelConfig
+    from engine.nn.attention import AttentionConfig
+    from engine.nn.layers import FFNConfig
+    from engine.utils import reset_non_persistent_buffers
+
+    from tokensprint_b200.config.registry import get_model_config
+
+    cfg = get_model_config(MODEL_NAME)
+    peaks = load_peaks()
+    device = torch.device("cuda")
+    ref_cfg = QwenModelConfig(
+        attn_config=AttentionConfig(model_dim=cfg.hidden_size, num_heads=cfg.num_attention_heads,
+                                    num_kv_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim, qk_norm=True,
+                                    qk_norm_eps=cfg.rms_norm_eps),
+        ffn_config=FFNConfig(model_dim=cfg.hidden_size, inner_dim=cfg.intermediate_size),
+        vocab_dim=cfg.vocab_size, num_layers=cfg.num_hidden_layers, max_seq_len=CONTEXT_LEN, rope_theta=cfg.rope_theta,
+        rope_impl="triton", norm_eps=cfg.rms_norm_eps, rmsnorm_impl="triton", tie_weights=cfg.tie_word_embeddings)
+    with torch.inference_mode():
+        model = build_model(ref_cfg, device=device, dtype=torch.bfloat16)
+        g = torch.Generator(device=device).manual_seed(0)
+        for name, p in model.named_parameters():
+            if p.dim() == 1:
+                p.fill_(0.0 if name.endswith("bias") else 1.0)
+            else:
+                p.normal_(0.0, 0.02, generator=g)
+        reset_non_persistent_buffers(model)
+        batch, steps, warmup = args.batch, args.steps, args.warmup
+        with tempfile.TemporaryDirectory() as model_dir:
+            # its paged attention wants cache blocks of 256 tokens (engine/generation/config.py:38-42)
+            config = RefConfig(model=model_dir, max_model_len=CONTEXT_LEN, max_num_seqs=max(batch, 8), max_num_batched_tokens=8192,
+                               kvcache_block_size=256, chunked_prefill=True, eos=-1, dtype=torch.bfloat16, gpu_memory_utilization=0.5)
+            engine = RefEngine(model=model, config=config, tokenizer=None)
+            sp = RefSamplingParams(temperature=0.6, max_tokens=warmup + steps + 4, ignore_eos=True)
+            for b in range(batch):
+                engine.add_request(random_ids(PROMPT_LEN, cfg.vocab_size, 300 + b), sp)
+            sched = engine.scheduler
+            while sched.waiting or any(s.num_cached_tokens < s.num_prompt_tokens for s in sched.running):
+                engine.step()
+            for _ in range(warmup):
+                engine.step()
+            torch.cuda.synchronize()
+            clocks = ClockSampler()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with clocks:
+                t0 = time.perf_counter()
+                start.record()
+                for _ in range(steps):
+                    engine.step()
+                end.record()
+                torch.cuda.synchronize()
+                wall = time.perf_counter() - t0
+            ms = start.elapsed_time(end) / steps
+            while not engine.is_finished():
+                engine.step()
+            # prefill: one 2,048-token prompt, one generated token
+            pf = []
+            for r in range(4):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                engine.generate([random_ids(PREFILL_TOKENS, cfg.vocab_size, 900 + r)], RefSamplingParams(temperature=0.6, max_tokens=1, ignore_eos=True), use_tqdm=False)
+                torch.cuda.synchronize()
+                pf.append((time.perf_counter() - t0) * 1e3)
+            pf_ms = sorted(pf[1:])[len(pf[1:]) // 2]
+    value = batch * 1000.0 / ms
+    return {
+        "metric": "decode tokens/s, Qwen3-8B sizes, batch 8, 1 B200",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02) in the reference's own model object, uniform-random token ids",
+        "impl": "reference",
+        "config": {"model": "qwen3-8b", "layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size, "global_batch": batch,
+                   "prompt_len": PROMPT_LEN, "seq_len": CONTEXT_LEN, "kv_block": 256, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (16 GB of weights per step)", "peaks": peaks["source"]},
+        "clocks": clocks.summary(),
+        "e2e": {"value": round(batch * steps / wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": batch * 8},
+        "gpu_launches": 0,
+        "prefill": {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3),
+                    "frac": round(prefill_flops(cfg, PREFILL_TOKENS) / (pf_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)},
+    }
 
 
 def main() -> int:
