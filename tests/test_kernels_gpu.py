@@ -97,14 +97,17 @@ def test_sgemm_is_true_float32(M, N, K):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nq,nkv,d,theta,rot", [(5, 1, 48, 5e4, 48), (4, 2, 16, 1e4, 16), (3, 3, 80, 1e6, 32), (8, 2, 256, 1e6, 256)])
-def test_qk_norm_rope_store(dtype, nq, nkv, d, theta, rot):
+@pytest.mark.parametrize("T", [11, 300])
+@pytest.mark.parametrize("nq,nkv,d,theta,rot", [(5, 1, 48, 5e4, 48), (4, 2, 16, 1e4, 16), (3, 3, 80, 1e6, 32), (8, 2, 256, 1e6, 256), (32, 8, 128, 1e6, 128)])
+def test_qk_norm_rope_store(dtype, nq, nkv, d, theta, rot, T):
     from tokensprint_b200 import ops
 
-    T, page, pages = 11, 4, 9
+    page = 4
+    pages = -(-T // page) + 6
     eps = 1e-5
     qkv = torch.randn(T, (nq + 2 * nkv) * d, device=DEV).to(dtype)
-    positions = torch.tensor([0, 1, 2, 3, 500, 501, 40000, 7, 8, 9, 10], device=DEV, dtype=torch.int32)
+    positions = torch.randint(0, 3000, (T,), device=DEV, dtype=torch.int32)
+    positions[:11] = torch.tensor([0, 1, 2, 3, 500, 501, 40000, 7, 8, 9, 10], device=DEV, dtype=torch.int32)
     slots = torch.randperm(pages * page, device=DEV)[:T].to(torch.int32)
     slots[5] = -1  # not stored
     qw = 1 + 0.2 * torch.randn(d, device=DEV)

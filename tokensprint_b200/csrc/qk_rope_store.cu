@@ -99,71 +99,85 @@ __global__ void qk_norm_rope_store_pairs_kernel(const TA* __restrict__ qkv, TA* 
                                                 const int* __restrict__ positions,
                                                 const float* __restrict__ q_norm_w,
                                                 const float* __restrict__ k_norm_w, float eps,
-                                                const float* __restrict__ inv_freq, int T, int nq, int nkv, int d) {
+                                                const float* __restrict__ inv_freq, int T, int nq, int nkv, int d,
+                                                int heads_per_warp) {
+  // A warp takes `heads_per_warp` consecutive heads of one token: the sines and cosines of the
+  // token's position are computed once and serve all of them.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = nq + 2 * nkv;
+  const int groups = (heads + heads_per_warp - 1) / heads_per_warp;
   const long long item = (long long)blockIdx.x * QKR_WARPS + warp;
-  if (item >= (long long)T * heads) return;
-  const int t = (int)(item / heads);
-  const int head = (int)(item - (long long)t * heads);
-  const TA* src = qkv + ((size_t)t * heads + head) * d;
-  const bool is_q = head < nq;
-  const bool is_k = !is_q && head < nq + nkv;
-  int slot = -1;
-  if (!is_q) {
-    slot = slot_mapping ? slot_mapping[t] : t;
-    if (slot < 0) return;
-  }
-  if (!is_q && !is_k) {
-    TA* dst = v_dst + ((size_t)slot * nkv + (head - nq - nkv)) * d;
-    for (int i = 2 * lane; i < d; i += 64) {
-      const float2 v = ts_load2(src + i);
-      ts_store2(dst + i, v.x, v.y);
-    }
-    return;
-  }
+  if (item >= (long long)T * groups) return;
+  const int t = (int)(item / groups);
+  const int head0 = (int)(item - (long long)t * groups) * heads_per_warp;
+  const int head1 = min(heads, head0 + heads_per_warp);
   const int half = d >> 1;
-  float2 lo[QKR_ROUNDS], hi[QKR_ROUNDS];
-  float ss = 0.f;
+  const int slot = slot_mapping ? slot_mapping[t] : t;
+
+  float cs[QKR_ROUNDS][4];  // cos, sin of the two pairs this lane owns in every round
+  if (inv_freq && head0 < nq + nkv) {
+    const float pos = (float)positions[t];
 #pragma unroll
-  for (int r = 0; r < QKR_ROUNDS; ++r) {
-    const int j = 2 * lane + 64 * r;
-    if (j < half) {
-      lo[r] = ts_load2(src + j);
-      hi[r] = ts_load2(src + half + j);
-      ss += lo[r].x * lo[r].x + lo[r].y * lo[r].y + hi[r].x * hi[r].x + hi[r].y * hi[r].y;
+    for (int r = 0; r < QKR_ROUNDS; ++r) {
+      const int j = 2 * lane + 64 * r;
+      if (j < half) {
+        const float2 f = ts_load2(inv_freq + j);
+        sincosf(pos * f.x, &cs[r][1], &cs[r][0]);
+        sincosf(pos * f.y, &cs[r][3], &cs[r][2]);
+      }
     }
   }
-  const float* w = is_q ? q_norm_w : k_norm_w;
-  float rstd = 1.f;
-  if (w) {
-    ss = ts_warp_sum(ss);
-    rstd = rsqrtf(ss / (float)d + eps);
-  }
-  TA* dst = is_q ? q_out + ((size_t)t * nq + head) * d : k_dst + ((size_t)slot * nkv + (head - nq)) * d;
-  const float pos = inv_freq ? (float)positions[t] : 0.f;
+
+  for (int head = head0; head < head1; ++head) {
+    const TA* src = qkv + ((size_t)t * heads + head) * d;
+    const bool is_q = head < nq;
+    const bool is_k = !is_q && head < nq + nkv;
+    if (!is_q && slot < 0) continue;
+    if (!is_q && !is_k) {
+      TA* dst = v_dst + ((size_t)slot * nkv + (head - nq - nkv)) * d;
+      for (int i = 2 * lane; i < d; i += 64) {
+        const float2 v = ts_load2(src + i);
+        ts_store2(dst + i, v.x, v.y);
+      }
+      continue;
+    }
+    float2 lo[QKR_ROUNDS], hi[QKR_ROUNDS];
+    float ss = 0.f;
 #pragma unroll
-  for (int r = 0; r < QKR_ROUNDS; ++r) {
-    const int j = 2 * lane + 64 * r;
-    if (j < half) {
-      float2 a = lo[r], b = hi[r];
-      if (w) {
-        const float2 wl = ts_load2(w + j), wh = ts_load2(w + half + j);
-        a.x *= rstd * wl.x; a.y *= rstd * wl.y;
-        b.x *= rstd * wh.x; b.y *= rstd * wh.y;
+    for (int r = 0; r < QKR_ROUNDS; ++r) {
+      const int j = 2 * lane + 64 * r;
+      if (j < half) {
+        lo[r] = ts_load2(src + j);
+        hi[r] = ts_load2(src + half + j);
+        ss += lo[r].x * lo[r].x + lo[r].y * lo[r].y + hi[r].x * hi[r].x + hi[r].y * hi[r].y;
       }
-      if (inv_freq) {
-        const float2 f = ts_load2(inv_freq + j);
-        float s0, c0, s1, c1;
-        sincosf(pos * f.x, &s0, &c0);
-        sincosf(pos * f.y, &s1, &c1);
-        const float2 ra = make_float2(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
-        const float2 rb = make_float2(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
-        a = ra;
-        b = rb;
+    }
+    const float* w = is_q ? q_norm_w : k_norm_w;
+    float rstd = 1.f;
+    if (w) {
+      ss = ts_warp_sum(ss);
+      rstd = rsqrtf(ss / (float)d + eps);
+    }
+    TA* dst = is_q ? q_out + ((size_t)t * nq + head) * d : k_dst + ((size_t)slot * nkv + (head - nq)) * d;
+#pragma unroll
+    for (int r = 0; r < QKR_ROUNDS; ++r) {
+      const int j = 2 * lane + 64 * r;
+      if (j < half) {
+        float2 a = lo[r], b = hi[r];
+        if (w) {
+          const float2 wl = ts_load2(w + j), wh = ts_load2(w + half + j);
+          a.x *= rstd * wl.x; a.y *= rstd * wl.y;
+          b.x *= rstd * wh.x; b.y *= rstd * wh.y;
+        }
+        if (inv_freq) {
+          const float2 ra = make_float2(a.x * cs[r][0] - b.x * cs[r][1], a.y * cs[r][2] - b.y * cs[r][3]);
+          const float2 rb = make_float2(b.x * cs[r][0] + a.x * cs[r][1], b.y * cs[r][2] + a.y * cs[r][3]);
+          a = ra;
+          b = rb;
+        }
+        ts_store2(dst + j, a.x, a.y);
+        ts_store2(dst + half + j, b.x, b.y);
       }
-      ts_store2(dst + j, a.x, a.y);
-      ts_store2(dst + half + j, b.x, b.y);
     }
   }
 }
@@ -183,16 +197,21 @@ TS_EXPORT int ts_qk_norm_rope_store(const void* qkv, int act_dtype, void* q_out,
   const bool pairs = (d % 4 == 0) && (d / 2 <= 64 * QKR_ROUNDS) && (!inv_freq || rot_dim == d) &&
                      (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_dst | (uintptr_t)v_dst | (uintptr_t)q_norm_w |
                        (uintptr_t)k_norm_w | (uintptr_t)inv_freq) % 8 == 0);
+  // Many tokens: a warp takes 8 heads of a token and shares the trigonometry among them; few
+  // tokens (decode): one head per warp, for the most warps in flight.
+  const int heads_per_warp = T >= 256 ? 8 : 1;
+  const int groups = (nq + 2 * nkv + heads_per_warp - 1) / heads_per_warp;
+  const unsigned pair_blocks = (unsigned)(((long long)T * groups + QKR_WARPS - 1) / QKR_WARPS);
   if (pairs && act_dtype == TS_DTYPE_F32) {
-    qk_norm_rope_store_pairs_kernel<float><<<blocks, QKR_WARPS * 32, 0, s>>>(
+    qk_norm_rope_store_pairs_kernel<float><<<pair_blocks, QKR_WARPS * 32, 0, s>>>(
         (const float*)qkv, (float*)q_out, (float*)k_dst, (float*)v_dst, slot_mapping, positions, q_norm_w,
-        k_norm_w, eps, inv_freq, T, nq, nkv, d);
+        k_norm_w, eps, inv_freq, T, nq, nkv, d, heads_per_warp);
     return ts_launch_status();
   }
   if (pairs && act_dtype == TS_DTYPE_BF16) {
-    qk_norm_rope_store_pairs_kernel<__nv_bfloat16><<<blocks, QKR_WARPS * 32, 0, s>>>(
+    qk_norm_rope_store_pairs_kernel<__nv_bfloat16><<<pair_blocks, QKR_WARPS * 32, 0, s>>>(
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_dst, (__nv_bfloat16*)v_dst,
-        slot_mapping, positions, q_norm_w, k_norm_w, eps, inv_freq, T, nq, nkv, d);
+        slot_mapping, positions, q_norm_w, k_norm_w, eps, inv_freq, T, nq, nkv, d, heads_per_warp);
     return ts_launch_status();
   }
   if (act_dtype == TS_DTYPE_F32)

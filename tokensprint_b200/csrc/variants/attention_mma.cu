@@ -74,6 +74,11 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float fast_exp2(float x) {  // one MUFU op; -inf gives 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
@@ -391,6 +396,253 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   }
 }
 
+// Prefill for head sizes up to 128: 4 warps, each with 32 query rows (two 16-row MMA tiles), so
+// every key/value fragment fetched from shared memory feeds two MMAs.  128 rows per tile.  A
+// causal tile's work grows with its position, so a CTA takes two tiles: number x from the end
+// and number x from the start of its sequence; every CTA then walks about the same number of
+// keys and one wave of CTAs ends together.  Blocks of keys that lie wholly below the diagonal
+// (and inside the window) skip the mask.
+constexpr int PF_WARPS = 4;
+constexpr int PF_MT = 2;                      // 16-row tiles per warp
+constexpr int PF_BM = PF_WARPS * 16 * PF_MT;  // 128
+
+__global__ void __launch_bounds__(PF_WARPS * 32, 2) attention_prefill_kernel(const AttnParams p) {
+  constexpr int NT = PF_WARPS * 32;
+  constexpr int NTILES = BN / 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [PF_BM][LD]
+  __nv_bfloat16* k_s = q_s + PF_BM * LD;                                     // [STAGES][BN][LD]
+  __nv_bfloat16* v_s = k_s + STAGES * BN * LD;                               // [STAGES][BN][LD]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, tq = lane & 3;
+  const int b = blockIdx.z, hk = blockIdx.y;
+  const int G = p.nq / p.nkv;
+
+  const int q_begin = p.cu_q[b];
+  const int q_len = p.cu_q[b + 1] - q_begin;
+  const int ctx = p.ctx_len[b];
+  const int start_pos = ctx - q_len;
+  const int rows_total = q_len * G;
+  if (q_len <= 0) return;
+  const int seq_tiles = (rows_total + PF_BM - 1) / PF_BM;  // tiles of this sequence
+  if ((int)blockIdx.x * 2 >= seq_tiles) return;
+
+  for (int pass = 0; pass < 2; ++pass) {
+  const int row_tile = pass == 0 ? seq_tiles - 1 - (int)blockIdx.x : (int)blockIdx.x;
+  if (pass == 1 && row_tile >= seq_tiles - 1 - (int)blockIdx.x) break;  // the middle tile was done in pass 0
+  if (pass == 1) __syncthreads();  // every warp is done with the first tile's shared memory
+  const int r0 = row_tile * PF_BM;
+
+  const int last_row = min(r0 + PF_BM, rows_total) - 1;
+  const int hi = start_pos + last_row / G;
+  const int first_pos = start_pos + r0 / G;  // position of the tile's first row
+  const int lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+  const int kb0 = lo / BN, kb1 = hi / BN;
+  const int nblocks = kb1 - kb0 + 1;
+  const int* table = p.block_table + (size_t)b * p.max_blocks;
+
+  const int warp_row0 = warp * 16 * PF_MT;
+  int row_pos[PF_MT][2], row_lo[PF_MT][2];
+#pragma unroll
+  for (int mt = 0; mt < PF_MT; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = r0 + warp_row0 + mt * 16 + g + 8 * h;
+      row_pos[mt][h] = r < rows_total ? start_pos + r / G : -1;
+      row_lo[mt][h] = (p.window > 0 && row_pos[mt][h] >= 0) ? max(0, row_pos[mt][h] - p.window + 1) : 0;
+    }
+  // Positions of this warp's first and last row: blocks of keys between them need no mask.
+  const int warp_first_pos = start_pos + min(r0 + warp_row0, rows_total - 1) / G;
+  const int warp_rows_valid = (r0 + warp_row0 + 16 * PF_MT <= rows_total);
+
+  for (int c = tid; c < PF_BM * CH; c += NT) {
+    const int row = c / CH, ch = c - row * CH;
+    const int r = r0 + row;
+    const bool valid = r < rows_total;
+    const __nv_bfloat16* src = p.q;
+    if (valid) src = p.q + ((size_t)(q_begin + r / G) * p.nq + hk * G + r % G) * D + ch * 8;
+    cp_async16(q_s + row * LD + ch * 8, src, valid);
+  }
+  load_kv_tile<NT>(k_s, p.kcache, table, p.page, p.nkv, hk, kb0 * BN, hi, tid);
+  load_kv_tile<NT>(v_s, p.vcache, table, p.page, p.nkv, hk, kb0 * BN, hi, tid);
+  cp_async_commit();
+
+  float o_acc[PF_MT][D / 8][4];
+#pragma unroll
+  for (int mt = 0; mt < PF_MT; ++mt)
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o_acc[mt][i][j] = 0.f;
+  float m_run[PF_MT][2], l_run[PF_MT][2];
+#pragma unroll
+  for (int mt = 0; mt < PF_MT; ++mt) {
+    m_run[mt][0] = m_run[mt][1] = -INFINITY;
+    l_run[mt][0] = l_run[mt][1] = 0.f;
+  }
+  const __nv_bfloat16* q_warp = q_s + warp_row0 * LD;
+
+  for (int it = 0; it < nblocks; ++it) {
+    const int stage = it & 1;
+    const int kbase = (kb0 + it) * BN;
+    if (it + 1 < nblocks) {
+      load_kv_tile<NT>(k_s + (stage ^ 1) * BN * LD, p.kcache, table, p.page, p.nkv, hk, kbase + BN, hi, tid);
+      load_kv_tile<NT>(v_s + (stage ^ 1) * BN * LD, p.vcache, table, p.page, p.nkv, hk, kbase + BN, hi, tid);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    float s[PF_MT][NTILES][4];
+#pragma unroll
+    for (int mt = 0; mt < PF_MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < NTILES; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[mt][i][j] = 0.f;
+    const __nv_bfloat16* k_tile = k_s + stage * BN * LD;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      unsigned a[PF_MT][4];
+#pragma unroll
+      for (int mt = 0; mt < PF_MT; ++mt)
+        ldmatrix_x4(a[mt][0], a[mt][1], a[mt][2], a[mt][3],
+                    q_warp + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int np = 0; np < NTILES / 2; ++np) {
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3,
+                    k_tile + (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
+#pragma unroll
+        for (int mt = 0; mt < PF_MT; ++mt) {
+          mma_bf16(s[mt][2 * np], a[mt], b0, b1);
+          mma_bf16(s[mt][2 * np + 1], a[mt], b2, b3);
+        }
+      }
+    }
+
+    // A block whose last key is at or before the warp's first position, whose first key is
+    // inside every row's window, and whose rows all exist needs no mask.
+    const bool unmasked = warp_rows_valid && (kbase + BN - 1 <= warp_first_pos) &&
+                          (p.window <= 0 || kbase >= start_pos + (r0 + warp_row0 + 16 * PF_MT - 1) / G - p.window + 1);
+#pragma unroll
+    for (int mt = 0; mt < PF_MT; ++mt) {
+      // Running max in raw score units (the scale is positive, so it commutes with max); the
+      // scale is folded into the exponent's multiply-add: p = 2^(s * scale - max * scale).
+      float m_new[2] = {m_run[mt][0], m_run[mt][1]};
+      if (unmasked) {
+#pragma unroll
+        for (int nt = 0; nt < NTILES; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) m_new[e >> 1] = fmaxf(m_new[e >> 1], s[mt][nt][e]);
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < NTILES; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int h = e >> 1;
+            const int j = kbase + nt * 8 + tq * 2 + (e & 1);
+            const bool ok = j <= row_pos[mt][h] && j >= row_lo[mt][h];
+            const float v = ok ? s[mt][nt][e] : -INFINITY;
+            s[mt][nt][e] = v;
+            m_new[h] = fmaxf(m_new[h], v);
+          }
+      }
+      float corr[2], m_off[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
+        m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
+        m_off[h] = m_new[h] == -INFINITY ? 0.f : m_new[h] * p.scale_log2;  // a row that has seen no key yet
+        corr[h] = fast_exp2(m_run[mt][h] * p.scale_log2 - m_off[h]);       // m_run = -inf gives 0
+        m_run[mt][h] = m_new[h];
+      }
+      float l_add[2] = {0.f, 0.f};
+#pragma unroll
+      for (int nt = 0; nt < NTILES; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pv = fast_exp2(fmaf(s[mt][nt][e], p.scale_log2, -m_off[e >> 1]));
+          s[mt][nt][e] = pv;
+          l_add[e >> 1] += pv;
+        }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) l_run[mt][h] = l_run[mt][h] * corr[h] + l_add[h];
+      // The output only needs rescaling when some row's max moved in this block.
+      if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+          o_acc[mt][i][0] *= corr[0];
+          o_acc[mt][i][1] *= corr[0];
+          o_acc[mt][i][2] *= corr[1];
+          o_acc[mt][i][3] *= corr[1];
+        }
+      }
+    }
+
+    const __nv_bfloat16* v_tile = v_s + stage * BN * LD;
+#pragma unroll
+    for (int kk = 0; kk < NTILES / 2; ++kk) {
+      unsigned a[PF_MT][4];
+#pragma unroll
+      for (int mt = 0; mt < PF_MT; ++mt) {
+        a[mt][0] = pack_bf16(s[mt][2 * kk][0], s[mt][2 * kk][1]);
+        a[mt][1] = pack_bf16(s[mt][2 * kk][2], s[mt][2 * kk][3]);
+        a[mt][2] = pack_bf16(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
+        a[mt][3] = pack_bf16(s[mt][2 * kk + 1][2], s[mt][2 * kk + 1][3]);
+      }
+#pragma unroll
+      for (int np = 0; np < D / 16; ++np) {
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4_trans(b0, b1, b2, b3,
+                          v_tile + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + np * 16 + ((lane >> 4) & 1) * 8);
+#pragma unroll
+        for (int mt = 0; mt < PF_MT; ++mt) {
+          mma_bf16(o_acc[mt][2 * np], a[mt], b0, b1);
+          mma_bf16(o_acc[mt][2 * np + 1], a[mt], b2, b3);
+        }
+      }
+    }
+    __syncthreads();  // the next round's prefetch overwrites this stage
+  }
+
+#pragma unroll
+  for (int mt = 0; mt < PF_MT; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float l = l_run[mt][h];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      const int r = r0 + warp_row0 + mt * 16 + g + 8 * h;
+      if (r >= rows_total) continue;
+      const size_t qrow = (size_t)(q_begin + r / G) * p.nq + hk * G + r % G;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = p.out + qrow * D;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(o_acc[mt][i][2 * h] * inv, o_acc[mt][i][2 * h + 1] * inv);
+        *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + tq * 2) = v;
+      }
+    }
+  }  // pass
+}
+
+int launch_prefill(const AttnParams& p, int B, cudaStream_t stream) {
+  const size_t smem = (size_t)(PF_BM + 2 * STAGES * BN) * LD * sizeof(__nv_bfloat16);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((p.row_tiles + 1) / 2, p.nkv, B);
+  attention_prefill_kernel<<<grid, PF_WARPS * 32, smem, stream>>>(p);
+  return ts_launch_status();
+}
+
 // Merges the partial results of the key splits of one (token, head): one warp each.
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          __nv_bfloat16* __restrict__ out, const int* __restrict__ seq_index,
@@ -496,7 +748,10 @@ TS_EXPORT int ts_attention_paged_mma(const void* q, const void* kcache, const vo
     status = launch<4, true>(p, B, stream);
   } else {
     p.row_tiles = (int)((rows + 127) / 128);
-    status = launch<8, false>(p, B, stream);
+    if (D <= 128 && splits == 1)
+      status = launch_prefill(p, B, stream);
+    else
+      status = launch<8, false>(p, B, stream);
   }
   if (status != 0) return status;
   if (splits > 1) {
