@@ -24,6 +24,7 @@ __global__ void attention_paged_simple_kernel(
     TA* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_index,
     const int* __restrict__ block_table, int max_blocks, int page, int T, int nq, int nkv, int d,
     float scale, int window) {
+  ts_pdl_prologue();
   __shared__ float qs[ATS_WARPS][ATS_MAX_HEAD_DIM];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * ATS_WARPS + warp;
@@ -103,11 +104,11 @@ TS_EXPORT int ts_attention_paged_simple(const void* q, const void* kcache, const
   unsigned blocks = (unsigned)((items + ATS_WARPS - 1) / ATS_WARPS);
   cudaStream_t s = (cudaStream_t)stream;
   if (act_dtype == TS_DTYPE_F32)
-    attention_paged_simple_kernel<float><<<blocks, ATS_WARPS * 32, 0, s>>>(
+    return ts_launch(attention_paged_simple_kernel<float>, dim3(blocks), dim3(ATS_WARPS * 32), 0, s,
         (const float*)q, (const float*)kcache, (const float*)vcache, (float*)out, positions,
         seq_index, block_table, max_blocks, page, T, nq, nkv, d, scale, window);
   else if (act_dtype == TS_DTYPE_BF16)
-    attention_paged_simple_kernel<__nv_bfloat16><<<blocks, ATS_WARPS * 32, 0, s>>>(
+    return ts_launch(attention_paged_simple_kernel<__nv_bfloat16>, dim3(blocks), dim3(ATS_WARPS * 32), 0, s,
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache,
         (__nv_bfloat16*)out, positions, seq_index, block_table, max_blocks, page, T, nq, nkv, d,
         scale, window);

@@ -18,6 +18,47 @@
 
 #define TS_EXPORT extern "C" __attribute__((visibility("default")))
 
+// Programmatic dependent launch: every kernel of this library is launched with the attribute
+// that lets it start while the kernel before it in the stream is still running, and begins with
+// ts_pdl_prologue(): it first lets its own successor start launching, then waits until the
+// kernels before it have completed and their writes are visible.  What a kernel does before that
+// wait (set-up, loads of weights that no kernel writes) overlaps with its predecessor; launch
+// latency overlaps in any case.  TS_PDL=0 in the environment turns the attribute off.
+#include <stdlib.h>
+
+__device__ __forceinline__ void ts_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void ts_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void ts_pdl_prologue() {
+  ts_pdl_launch_dependents();
+  ts_pdl_wait();
+}
+
+static inline bool ts_pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* v = getenv("TS_PDL");
+    enabled = (v && v[0] == '0') ? 0 : 1;
+  }
+  return enabled == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int ts_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = ts_pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaGetLastError();
+}
+
 static inline int ts_launch_status() {
   cudaError_t e = cudaGetLastError();
   return (int)e;

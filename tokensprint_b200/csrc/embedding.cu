@@ -5,6 +5,7 @@
 template <typename TW>
 __global__ void embed_gather_kernel(float* __restrict__ hidden, const TW* __restrict__ table,
                                     const int* __restrict__ ids, int H, int V) {
+  ts_pdl_prologue();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* dst = hidden + (size_t)t * H;
@@ -19,6 +20,8 @@ __global__ void embed_gather_kernel(float* __restrict__ hidden, const TW* __rest
 
 __global__ void embed_gather_bf16x8_kernel(float* __restrict__ hidden, const __nv_bfloat16* __restrict__ table,
                                            const int* __restrict__ ids, int H, int V) {
+  ts_pdl_prologue();
+  ts_pdl_prologue();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* dst = hidden + (size_t)t * H;
@@ -49,11 +52,11 @@ TS_EXPORT int ts_embed_gather(float* hidden, const void* table, int table_dtype,
   int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
   cudaStream_t s = (cudaStream_t)stream;
   if (table_dtype == TS_DTYPE_F32)
-    embed_gather_kernel<float><<<T, threads, 0, s>>>(hidden, (const float*)table, ids, H, V);
+    return ts_launch(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, s, hidden, (const float*)table, ids, H, V);
   else if (table_dtype == TS_DTYPE_BF16 && H % 8 == 0 && ((uintptr_t)hidden | (uintptr_t)table) % 16 == 0)
-    embed_gather_bf16x8_kernel<<<T, min(1024, max(32, (H / 8 + 31) / 32 * 32)), 0, s>>>(hidden, (const __nv_bfloat16*)table, ids, H, V);
+    return ts_launch(embed_gather_bf16x8_kernel, dim3(T), dim3(min(1024, max(32, (H / 8 + 31) / 32 * 32))), 0, s, hidden, (const __nv_bfloat16*)table, ids, H, V);
   else if (table_dtype == TS_DTYPE_BF16)
-    embed_gather_kernel<__nv_bfloat16><<<T, threads, 0, s>>>(hidden, (const __nv_bfloat16*)table, ids, H, V);
+    return ts_launch(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, s, hidden, (const __nv_bfloat16*)table, ids, H, V);
   else
     return TS_ERR_BAD_ARGUMENT;
   return ts_launch_status();

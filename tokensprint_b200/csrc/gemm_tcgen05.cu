@@ -154,6 +154,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
   __shared__ int last_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  ts_pdl_launch_dependents();  // the next kernel may begin its own set-up now
   if (tid == 0) TS_PROBE(0);
   const Range range = cta_range(args, blockIdx.x);
   const int chunks = args.chunks;
@@ -190,7 +191,23 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
     if (lane == 0) {
       // Producer: TMA loads into the ring, unit after unit, across tile boundaries.
       const int n_units = range.u1 - range.u0;
-      int it = 0;
+      // The weights are written by no kernel, so the first ring of W tiles is requested before
+      // the kernels ahead in the stream have finished; X (their output) only after the wait.
+      const int early = min(n_units, STAGES);
+      for (int i = 0; i < early; ++i) {
+        const int u = range.u0 + i;
+        const int t = u / chunks, kc = u - t * chunks;
+        const uint32_t bar = smem_u32(&full_bar[i]);
+        mbar_expect_tx(bar, C::A_BYTES + C::B_BYTES);
+        tma_load_2d(smem_u32(smem + (size_t)i * C::STAGE_BYTES), &map_w, bar, kc * TILE_K, t * TILE_N);
+      }
+      ts_pdl_wait();
+      for (int i = 0; i < early; ++i) {
+        const int u = range.u0 + i;
+        const int kc = u % chunks;
+        tma_load_2d(smem_u32(smem + (size_t)i * C::STAGE_BYTES) + C::A_BYTES, &map_x, smem_u32(&full_bar[i]), kc * TILE_K, 0);
+      }
+      int it = early;
       for (; it < n_units; ++it) {
         const int u = range.u0 + it;
         const int t = u / chunks, kc = u - t * chunks;
@@ -248,6 +265,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
     // Epilogue warps 2..5: TMEM lanes 32 * (warp % 4) .. + 31.
     const int quarter = warp & 3;
     const int etid = (warp - 2) * 32 + lane;  // 0..127 among the epilogue threads
+    ts_pdl_wait();  // nothing is stored before the kernels ahead in the stream are done
     int item = 0;
     for (int t = t_first; t <= t_last; ++t, ++item) {
       const int k0 = max(range.u0, t * chunks) - t * chunks;
@@ -433,8 +451,7 @@ int launch_skinny(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  gemm_skinny_kernel<MPAD><<<ctas, NUM_THREADS, Cfg<MPAD>::SMEM, stream>>>(mw, mx, a);
-  return ts_launch_status();
+  return ts_launch(gemm_skinny_kernel<MPAD>, dim3(ctas), dim3(NUM_THREADS), Cfg<MPAD>::SMEM, stream, mw, mx, a);
 }
 
 int sm_count() {

@@ -25,6 +25,7 @@ __global__ void qk_norm_rope_store_kernel(const TA* __restrict__ qkv, TA* __rest
                                           const float* __restrict__ k_norm_w, float eps,
                                           const float* __restrict__ inv_freq, int rot_dim, int T,
                                           int nq, int nkv, int d) {
+  ts_pdl_prologue();
   __shared__ float buf[QKR_WARPS][QKR_MAX_HEAD_DIM];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = nq + 2 * nkv;
@@ -101,6 +102,7 @@ __global__ void qk_norm_rope_store_pairs_kernel(const TA* __restrict__ qkv, TA* 
                                                 const float* __restrict__ k_norm_w, float eps,
                                                 const float* __restrict__ inv_freq, int T, int nq, int nkv, int d,
                                                 int heads_per_warp) {
+  ts_pdl_prologue();
   // A warp takes `heads_per_warp` consecutive heads of one token: the sines and cosines of the
   // token's position are computed once and serve all of them.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -203,23 +205,21 @@ TS_EXPORT int ts_qk_norm_rope_store(const void* qkv, int act_dtype, void* q_out,
   const int groups = (nq + 2 * nkv + heads_per_warp - 1) / heads_per_warp;
   const unsigned pair_blocks = (unsigned)(((long long)T * groups + QKR_WARPS - 1) / QKR_WARPS);
   if (pairs && act_dtype == TS_DTYPE_F32) {
-    qk_norm_rope_store_pairs_kernel<float><<<pair_blocks, QKR_WARPS * 32, 0, s>>>(
+    return ts_launch(qk_norm_rope_store_pairs_kernel<float>, dim3(pair_blocks), dim3(QKR_WARPS * 32), 0, s,
         (const float*)qkv, (float*)q_out, (float*)k_dst, (float*)v_dst, slot_mapping, positions, q_norm_w,
         k_norm_w, eps, inv_freq, T, nq, nkv, d, heads_per_warp);
-    return ts_launch_status();
   }
   if (pairs && act_dtype == TS_DTYPE_BF16) {
-    qk_norm_rope_store_pairs_kernel<__nv_bfloat16><<<pair_blocks, QKR_WARPS * 32, 0, s>>>(
+    return ts_launch(qk_norm_rope_store_pairs_kernel<__nv_bfloat16>, dim3(pair_blocks), dim3(QKR_WARPS * 32), 0, s,
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_dst, (__nv_bfloat16*)v_dst,
         slot_mapping, positions, q_norm_w, k_norm_w, eps, inv_freq, T, nq, nkv, d, heads_per_warp);
-    return ts_launch_status();
   }
   if (act_dtype == TS_DTYPE_F32)
-    qk_norm_rope_store_kernel<float><<<blocks, QKR_WARPS * 32, 0, s>>>(
+    return ts_launch(qk_norm_rope_store_kernel<float>, dim3(blocks), dim3(QKR_WARPS * 32), 0, s,
         (const float*)qkv, (float*)q_out, (float*)k_dst, (float*)v_dst, slot_mapping, positions,
         q_norm_w, k_norm_w, eps, inv_freq, rot_dim, T, nq, nkv, d);
   else if (act_dtype == TS_DTYPE_BF16)
-    qk_norm_rope_store_kernel<__nv_bfloat16><<<blocks, QKR_WARPS * 32, 0, s>>>(
+    return ts_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, dim3(blocks), dim3(QKR_WARPS * 32), 0, s,
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_dst,
         (__nv_bfloat16*)v_dst, slot_mapping, positions, q_norm_w, k_norm_w, eps, inv_freq, rot_dim,
         T, nq, nkv, d);

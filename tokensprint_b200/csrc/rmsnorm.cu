@@ -14,6 +14,7 @@ template <typename TA>
 __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const TA* __restrict__ delta,
                                    const float* __restrict__ weight, TA* __restrict__ out,
                                    const int* __restrict__ row_index, int H, float eps) {
+  ts_pdl_prologue();
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const int row = row_index ? row_index[r] : r;
@@ -63,6 +64,7 @@ template <typename TA>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ hidden, const TA* __restrict__ delta,
                                        const float* __restrict__ weight, TA* __restrict__ out,
                                        const int* __restrict__ row_index, int H, float eps) {
+  ts_pdl_prologue();
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const int row = row_index ? row_index[r] : r;
@@ -113,12 +115,11 @@ static int launch_add_rmsnorm(float* hidden, const void* delta, const float* wei
     int threads = (chunks + RN_MAX_CHUNKS - 1) / RN_MAX_CHUNKS;
     if (rows <= 512) threads = chunks;  // few rows: one piece per thread, shortest latency
     threads = min(1024, max(32, (threads + 31) / 32 * 32));
-    add_rmsnorm_vec_kernel<TA><<<rows, threads, 0, s>>>(hidden, (const TA*)delta, weight, (TA*)out, row_index, H, eps);
+    return ts_launch(add_rmsnorm_vec_kernel<TA>, dim3(rows), dim3(threads), 0, s, hidden, (const TA*)delta, weight, (TA*)out, row_index, H, eps);
   } else {
     int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : (H >= 256 ? 128 : 64));
-    add_rmsnorm_kernel<TA><<<rows, threads, 0, s>>>(hidden, (const TA*)delta, weight, (TA*)out, row_index, H, eps);
+    return ts_launch(add_rmsnorm_kernel<TA>, dim3(rows), dim3(threads), 0, s, hidden, (const TA*)delta, weight, (TA*)out, row_index, H, eps);
   }
-  return ts_launch_status();
 }
 
 TS_EXPORT int ts_add_rmsnorm(float* hidden, const void* delta, int act_dtype, const float* weight,
@@ -137,6 +138,7 @@ TS_EXPORT int ts_add_rmsnorm(float* hidden, const void* delta, int act_dtype, co
 // hidden[row] += delta[row] without a norm (the last residual sum when nothing follows it).
 template <typename TA>
 __global__ void residual_add_kernel(float* __restrict__ hidden, const TA* __restrict__ delta, size_t n) {
+  ts_pdl_prologue();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) hidden[i] += ts_to_float(delta[i]);
 }
@@ -146,9 +148,9 @@ TS_EXPORT int ts_residual_add(float* hidden, const void* delta, int act_dtype, l
   cudaStream_t s = (cudaStream_t)stream;
   unsigned blocks = (unsigned)((n + 255) / 256);
   if (act_dtype == TS_DTYPE_F32)
-    residual_add_kernel<float><<<blocks, 256, 0, s>>>(hidden, (const float*)delta, (size_t)n);
+    return ts_launch(residual_add_kernel<float>, dim3(blocks), dim3(256), 0, s, hidden, (const float*)delta, (size_t)n);
   else if (act_dtype == TS_DTYPE_BF16)
-    residual_add_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(hidden, (const __nv_bfloat16*)delta, (size_t)n);
+    return ts_launch(residual_add_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, s, hidden, (const __nv_bfloat16*)delta, (size_t)n);
   else
     return TS_ERR_BAD_ARGUMENT;
   return ts_launch_status();

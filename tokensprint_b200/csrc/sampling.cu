@@ -69,6 +69,7 @@ __device__ __forceinline__ Best block_best(Best x, Best* shared /* [32] */) {
 __global__ void sample_partial_kernel(const float* __restrict__ logits, int V, long long row_stride,
                                       const float* __restrict__ temperature,
                                       const unsigned long long* __restrict__ keys, Best* __restrict__ partial) {
+  ts_pdl_prologue();
   __shared__ Best shared[32];
   const int r = blockIdx.y, chunk = blockIdx.x;
   const float* row = logits + (size_t)r * row_stride;
@@ -93,6 +94,7 @@ __global__ void sample_partial_kernel(const float* __restrict__ logits, int V, l
 
 // Stage 2: one CTA per row picks among the chunk winners.
 __global__ void sample_final_kernel(const Best* __restrict__ partial, int chunks, int* __restrict__ out) {
+  ts_pdl_prologue();
   __shared__ Best shared[32];
   const int r = blockIdx.x;
   Best best;
@@ -115,9 +117,7 @@ TS_EXPORT int ts_sample(const float* logits, int V, long long row_stride, const 
   if (R > 65535) return TS_ERR_UNSUPPORTED_SIZE;
   const int chunks = (V + SAMPLE_CHUNK - 1) / SAMPLE_CHUNK;
   cudaStream_t s = (cudaStream_t)stream;
-  sample_partial_kernel<<<dim3(chunks, R), SAMPLE_THREADS, 0, s>>>(logits, V, row_stride, temperature, keys, (Best*)scratch);
-  int status = ts_launch_status();
+  int status = ts_launch(sample_partial_kernel, dim3(chunks, R), dim3(SAMPLE_THREADS), 0, s, logits, V, row_stride, temperature, keys, (Best*)scratch);
   if (status != 0) return status;
-  sample_final_kernel<<<R, 128, 0, s>>>((const Best*)scratch, chunks, out);
-  return ts_launch_status();
+  return ts_launch(sample_final_kernel, dim3(R), dim3(128), 0, s, (const Best*)scratch, chunks, out);
 }

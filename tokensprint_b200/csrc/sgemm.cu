@@ -15,6 +15,7 @@ __global__ void __launch_bounds__(256) sgemm_nt_kernel(const float* __restrict__
                                                        const float* __restrict__ W,
                                                        float* __restrict__ C, int M, int N, int K,
                                                        long long lda, long long ldw, long long ldc) {
+  ts_pdl_prologue();
   __shared__ float As[SG_BK][SG_BM + 1];
   __shared__ float Ws[SG_BK][SG_BN + 1];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -60,6 +61,5 @@ TS_EXPORT int ts_sgemm_nt(const float* A, const float* W, float* C, int M, int N
   if (K <= 0 || lda < K || ldw < K || ldc < N) return TS_ERR_BAD_ARGUMENT;
   dim3 grid((N + SG_BN - 1) / SG_BN, (M + SG_BM - 1) / SG_BM);
   if (grid.y > 65535) return TS_ERR_UNSUPPORTED_SIZE;
-  sgemm_nt_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
-  return ts_launch_status();
+  return ts_launch(sgemm_nt_kernel, grid, dim3(256), 0, (cudaStream_t)stream, A, W, C, M, N, K, lda, ldw, ldc);
 }

@@ -5,6 +5,7 @@
 
 template <typename TA>
 __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I, size_t total) {
+  ts_pdl_prologue();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   size_t t = idx / I;
@@ -18,6 +19,7 @@ __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, i
 
 // Eight bfloat16 per thread (16-byte loads) when the inner size allows it.
 __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I, size_t total8) {
+  ts_pdl_prologue();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total8) return;
   const int per_row = I >> 3;
@@ -45,12 +47,12 @@ TS_EXPORT int ts_swiglu(const void* gu, void* out, int act_dtype, int T, int I, 
   unsigned blocks = (unsigned)((total + 255) / 256);
   cudaStream_t s = (cudaStream_t)stream;
   if (act_dtype == TS_DTYPE_F32)
-    swiglu_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, (float*)out, I, total);
+    return ts_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)gu, (float*)out, I, total);
   else if (act_dtype == TS_DTYPE_BF16 && I % 8 == 0 && ((uintptr_t)gu | (uintptr_t)out) % 16 == 0) {
     const size_t total8 = total >> 3;
-    swiglu_bf16x8_kernel<<<(unsigned)((total8 + 255) / 256), 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total8);
+    return ts_launch(swiglu_bf16x8_kernel, dim3((unsigned)((total8 + 255) / 256)), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total8);
   } else if (act_dtype == TS_DTYPE_BF16)
-    swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total);
+    return ts_launch(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total);
   else
     return TS_ERR_BAD_ARGUMENT;
   return ts_launch_status();

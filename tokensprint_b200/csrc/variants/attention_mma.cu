@@ -115,6 +115,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   constexpr int NT = NWARPS * 32;
   constexpr int BM = SPLIT_KEYS ? 16 : NWARPS * 16;
   constexpr int NTILES = SPLIT_KEYS ? 2 : BN / 8;  // 8-key score tiles per warp and block
+  ts_pdl_prologue();
   static_assert(!SPLIT_KEYS || NWARPS * 16 == BN, "key-split mode: the warps must cover one key block");
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [BM][LD]
@@ -408,6 +409,7 @@ constexpr int PF_BM = PF_WARPS * 16 * PF_MT;  // 128
 
 __global__ void __launch_bounds__(PF_WARPS * 32, 2) attention_prefill_kernel(const AttnParams p) {
   constexpr int NT = PF_WARPS * 32;
+  ts_pdl_prologue();
   constexpr int NTILES = BN / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [PF_BM][LD]
@@ -639,14 +641,14 @@ int launch_prefill(const AttnParams& p, int B, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid((p.row_tiles + 1) / 2, p.nkv, B);
-  attention_prefill_kernel<<<grid, PF_WARPS * 32, smem, stream>>>(p);
-  return ts_launch_status();
+  return ts_launch(attention_prefill_kernel, grid, dim3(PF_WARPS * 32), smem, stream, p);
 }
 
 // Merges the partial results of the key splits of one (token, head): one warp each.
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          __nv_bfloat16* __restrict__ out, const int* __restrict__ seq_index,
                                          int rows, int nq, int splits) {
+  ts_pdl_prologue();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -695,8 +697,7 @@ int launch(const AttnParams& p, int B, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid(p.row_tiles * p.splits, p.nkv, B);
-  attention_mma_kernel<NWARPS, SPLIT_KEYS><<<grid, NWARPS * 32, smem, stream>>>(p);
-  return ts_launch_status();
+  return ts_launch(attention_mma_kernel<NWARPS, SPLIT_KEYS>, grid, dim3(NWARPS * 32), smem, stream, p);
 }
 
 }  // namespace
@@ -756,8 +757,7 @@ TS_EXPORT int ts_attention_paged_mma(const void* q, const void* kcache, const vo
   if (status != 0) return status;
   if (splits > 1) {
     const int total = T * nq;
-    attention_combine_kernel<<<(total + 3) / 4, 128, 0, stream>>>(p.part_o, p.part_ml, p.out, seq_index, total, nq, splits);
-    status = ts_launch_status();
+    status = ts_launch(attention_combine_kernel, dim3((total + 3) / 4), dim3(128), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, seq_index, total, nq, splits);
   }
   return status;
 }
