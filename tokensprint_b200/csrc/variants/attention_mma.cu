@@ -84,27 +84,33 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
-// Copies keys [kbase, kbase + BN) of one KV head into a [BN][LD] tile; keys that do not
-// exist (beyond `kend`, or in a page that is not held) become zeros.  NT / BN threads share
-// a row and interleave its 16-byte chunks, so a thread looks its page up once per tile and
-// neighbouring lanes fetch neighbouring chunks.
+// NT / BN threads share a row of a key block and interleave its 16-byte chunks, so a thread
+// needs one page of the block table per block, and neighbouring lanes fetch neighbouring chunks.
+// The page is looked up one block ahead of its use, so the dependent load hides behind the math.
 template <int NT>
-__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* tile, const __nv_bfloat16* cache, const int* table,
-                                             int page, int nkv, int hk, int kbase, int kend, int tid) {
+__device__ __forceinline__ int lookup_page(const int* table, int page, int kbase, int kend, int tid) {
+  const int j = kbase + tid / (NT / BN);
+  return j <= kend ? table[j / page] : -1;
+}
+
+// Copies keys [kbase, kbase + BN) of one KV head into [BN][LD] tiles of K and V; keys that do
+// not exist (beyond the sequence, or in a page that is not held: pg < 0) become zeros.
+template <int NT>
+__device__ __forceinline__ void load_kv_tiles(__nv_bfloat16* k_tile, __nv_bfloat16* v_tile, const __nv_bfloat16* kcache,
+                                              const __nv_bfloat16* vcache, int pg, int page, int nkv, int hk, int kbase,
+                                              int tid, bool k_and_v_in_one_group) {
   constexpr int TPR = NT / BN;  // threads per row
   static_assert(NT % BN == 0 && TPR >= 1, "thread count must be a multiple of the key block");
   const int row = tid / TPR;
   const int j = kbase + row;
-  bool valid = j <= kend;
-  const __nv_bfloat16* src = cache;
-  if (valid) {
-    const int pg = table[j / page];
-    valid = pg >= 0;
-    if (valid) src = cache + (((size_t)pg * page + (j % page)) * nkv + hk) * D;
-  }
-  __nv_bfloat16* dst = tile + row * LD;
+  const bool valid = pg >= 0;
+  const size_t off = valid ? (((size_t)pg * page + (j % page)) * nkv + hk) * D : 0;
 #pragma unroll
-  for (int ch = tid % TPR; ch < CH; ch += TPR) cp_async16(dst + ch * 8, valid ? src + ch * 8 : cache, valid);
+  for (int ch = tid % TPR; ch < CH; ch += TPR) cp_async16(k_tile + row * LD + ch * 8, kcache + off + ch * 8, valid);
+  if (!k_and_v_in_one_group) cp_async_commit();
+#pragma unroll
+  for (int ch = tid % TPR; ch < CH; ch += TPR) cp_async16(v_tile + row * LD + ch * 8, vcache + off + ch * 8, valid);
+  cp_async_commit();
 }
 
 // SPLIT_KEYS = false (prefill): the CTA's warps own 16 query rows each and all walk every key.
@@ -170,11 +176,11 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     cp_async16(q_s + row * LD + ch * 8, src, valid);
   }
   cp_async_commit();
+  int pg_next = -1;
   if (nblocks > 0) {
-    load_kv_tile<NT>(k_s, p.kcache, table, p.page, p.nkv, hk, kb0 * BN, hi, tid);
-    cp_async_commit();
-    load_kv_tile<NT>(v_s, p.vcache, table, p.page, p.nkv, hk, kb0 * BN, hi, tid);
-    cp_async_commit();
+    const int pg0 = lookup_page<NT>(table, p.page, kb0 * BN, hi, tid);
+    if (nblocks > 1) pg_next = lookup_page<NT>(table, p.page, (kb0 + 1) * BN, hi, tid);
+    load_kv_tiles<NT>(k_s, v_s, p.kcache, p.vcache, pg0, p.page, p.nkv, hk, kb0 * BN, tid, false);
   }
 
   float o_acc[D / 8][4];
@@ -204,10 +210,9 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     const int kbase = (kb0 + it) * BN;
     const bool more = it + 1 < nblocks;
     if (more) {
-      load_kv_tile<NT>(k_s + (stage ^ 1) * BN * LD, p.kcache, table, p.page, p.nkv, hk, kbase + BN, hi, tid);
-      cp_async_commit();
-      load_kv_tile<NT>(v_s + (stage ^ 1) * BN * LD, p.vcache, table, p.page, p.nkv, hk, kbase + BN, hi, tid);
-      cp_async_commit();
+      load_kv_tiles<NT>(k_s + (stage ^ 1) * BN * LD, v_s + (stage ^ 1) * BN * LD, p.kcache, p.vcache, pg_next, p.page,
+                        p.nkv, hk, kbase + BN, tid, false);
+      if (it + 2 < nblocks) pg_next = lookup_page<NT>(table, p.page, kbase + 2 * BN, hi, tid);
       cp_async_wait<3>();
     } else {
       cp_async_wait<1>();
@@ -466,9 +471,12 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 2) attention_prefill_kernel(con
     if (valid) src = p.q + ((size_t)(q_begin + r / G) * p.nq + hk * G + r % G) * D + ch * 8;
     cp_async16(q_s + row * LD + ch * 8, src, valid);
   }
-  load_kv_tile<NT>(k_s, p.kcache, table, p.page, p.nkv, hk, kb0 * BN, hi, tid);
-  load_kv_tile<NT>(v_s, p.vcache, table, p.page, p.nkv, hk, kb0 * BN, hi, tid);
-  cp_async_commit();
+  int pg_next = -1;
+  {
+    const int pg0 = lookup_page<NT>(table, p.page, kb0 * BN, hi, tid);
+    if (nblocks > 1) pg_next = lookup_page<NT>(table, p.page, (kb0 + 1) * BN, hi, tid);
+    load_kv_tiles<NT>(k_s, v_s, p.kcache, p.vcache, pg0, p.page, p.nkv, hk, kb0 * BN, tid, true);
+  }
 
   float o_acc[PF_MT][D / 8][4];
 #pragma unroll
@@ -489,9 +497,9 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 2) attention_prefill_kernel(con
     const int stage = it & 1;
     const int kbase = (kb0 + it) * BN;
     if (it + 1 < nblocks) {
-      load_kv_tile<NT>(k_s + (stage ^ 1) * BN * LD, p.kcache, table, p.page, p.nkv, hk, kbase + BN, hi, tid);
-      load_kv_tile<NT>(v_s + (stage ^ 1) * BN * LD, p.vcache, table, p.page, p.nkv, hk, kbase + BN, hi, tid);
-      cp_async_commit();
+      load_kv_tiles<NT>(k_s + (stage ^ 1) * BN * LD, v_s + (stage ^ 1) * BN * LD, p.kcache, p.vcache, pg_next, p.page,
+                        p.nkv, hk, kbase + BN, tid, true);
+      if (it + 2 < nblocks) pg_next = lookup_page<NT>(table, p.page, kbase + 2 * BN, hi, tid);
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();

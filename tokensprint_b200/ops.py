@@ -361,11 +361,14 @@ def _attention_mma_fns(head_dim: int):
     return fns
 
 
-def attention_decode_splits(num_seqs: int, num_kv_heads: int, max_context: int) -> int:
-    """How many CTAs share the keys of one sequence in a decode step: enough to fill the
-    GPU's 148 SMs a few times over, never more than there are key blocks."""
+def attention_decode_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: int = 128) -> int:
+    """How many CTAs share the keys of one sequence in a decode step: as many as run at the
+    same time on the GPU's 148 SMs (shared memory allows a few per SM, fewer for large heads),
+    so the step is one wave; never more than there are key blocks."""
+    smem = (16 + 4 * 64) * (head_dim + 8) * 2
+    per_sm = max(1, (227 * 1024) // smem)
     ctas = max(1, num_seqs * num_kv_heads)
-    want = -(-4 * 148 // ctas)
+    want = (per_sm * 148) // ctas
     blocks = max(1, -(-max_context // 64))
     return max(1, min(want, blocks, ATTENTION_MMA_MAX_SPLITS))
 

@@ -134,7 +134,7 @@ class AttentionMixer(Mixer):
             splits, scratch = 1, None
             if step.max_seqlen_q * (nq // nkv) <= 16:  # decode: spread each sequence's keys over CTAs
                 context = step.max_context_len if self.window <= 0 else min(step.max_context_len, self.window + 64)
-                splits = ops.attention_decode_splits(step.num_seqs, nkv, context)
+                splits = ops.attention_decode_splits(step.num_seqs, nkv, context, d)
                 if splits > 1:
                     scratch = torch.empty(ops.attention_scratch_floats(q.shape[0] * nq, splits, d),
                                           device=q.device, dtype=torch.float32)
