@@ -329,6 +329,68 @@ def run_ours(args) -> dict:
     }
 
 
+def run_probe(args) -> int:
+    """A few steps between cudaProfilerStart/Stop, for `ncu --profile-from-start off`: the
+    8B layer sizes with `--layers` layers (small enough for a full-metric capture), decode at
+    `--batch` requests of 1,024 cached tokens, or one 2,048-token prefill.  Prints `ok`."""
+    import torch
+
+    from tokensprint_b200 import ops
+    from tokensprint_b200.config.model_config import Qwen3Config
+    from tokensprint_b200.config.registry import get_preset_dict
+    from tokensprint_b200.engine.runner import ModelRunner, StepEntry
+    from tokensprint_b200.models.api import random_model
+
+    d = get_preset_dict(MODEL_NAME)
+    d["num_hidden_layers"] = args.layers or 4
+    cfg = Qwen3Config.from_dict(d)
+    model = random_model(cfg, seed=0, dtype="bfloat16", generate_on_device=True)
+    batch = args.batch
+    runner = ModelRunner(model, page_size=PAGE_SIZE, num_pages=batch * 80 + 400, num_slots=batch + 2,
+                         enforce_eager=True, max_model_len=CONTEXT_LEN)
+    cm = runner.cache_manager
+    if args.probe == "decode":
+        reqs = [cm.admit(b) for b in range(batch)]
+        for b in range(batch):
+            cm.extend(reqs[b], 0, PROMPT_LEN)
+            runner.step([StepEntry(reqs[b], random_ids(PROMPT_LEN, cfg.vocab_size, b), 0, [])])
+        temps = torch.full((batch,), 0.6, device="cuda")
+        keys = torch.arange(batch, dtype=torch.int64, device="cuda")
+        out = torch.empty(batch, dtype=torch.int32, device="cuda")
+
+        def step(i: int) -> None:
+            entries = []
+            for b in range(batch):
+                cm.extend(reqs[b], PROMPT_LEN + i, PROMPT_LEN + i + 1)
+                entries.append(StepEntry(reqs[b], [7 + b], PROMPT_LEN + i, [0]))
+            ops.sample(runner.step(entries), temps, keys, out)
+
+        for i in range(3):
+            step(i)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        for i in range(3, 5):
+            step(i)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    else:
+        def prefill(r: int) -> None:
+            rc = cm.admit(("p", r))
+            cm.extend(rc, 0, PREFILL_TOKENS)
+            runner.step([StepEntry(rc, random_ids(PREFILL_TOKENS, cfg.vocab_size, r), 0, [PREFILL_TOKENS - 1])])
+            runner.free(rc)
+
+        prefill(0)
+        prefill(1)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        prefill(2)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    print("ok")
+    return 0
+
+
 def run_reference(args) -> dict:
     """The unmodified reference (installed under baseline/_ref) through its own public API:
     build_model for the same sizes, random weights, LLMEngine.add_request/step.  The reference
@@ -444,10 +506,14 @@ def main() -> int:
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in the record)")
     p.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
     p.add_argument("--eager", action="store_true", help="no CUDA graphs for decode steps")
+    p.add_argument("--probe", choices=["decode", "prefill"], default=None,
+                   help="run a few steps inside cudaProfilerStart/Stop for ncu and exit (see profiles/)")
     args = p.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.probe:
+        return run_probe(args)
     if args.warmup < 3:
         args.warmup = 3
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
