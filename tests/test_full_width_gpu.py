@@ -1,0 +1,66 @@
+"""Qwen3-8B layer sizes (two layers, so it is quick): the bfloat16 kernels at the widths that
+serving uses — head size 128, four query heads per KV head, width 4096, vocabulary 151936 —
+under several cuttings, against the float32 path, and the float32 path against the plain model."""
+
+import pytest
+import torch
+
+from tests.plain import qwen3_plain as plain
+from tests.replay_helpers import random_tokens, replay_in_process, trace_decode_tail, trace_mixed, trace_portions, trace_whole
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folder(tmp_path_factory):
+    from tokensprint_b200.config.model_config import Qwen3Config
+    from tokensprint_b200.config.registry import get_preset_dict
+    from tokensprint_b200.weights.loader import write_random_model
+
+    d = get_preset_dict("qwen3-8b")
+    d["num_hidden_layers"] = 2
+    cfg = Qwen3Config.from_dict(d)
+    path = write_random_model(tmp_path_factory.mktemp("wide") / "m", cfg, seed=3, dtype="bfloat16", std=0.02)
+    return path, d
+
+
+def _logits(folder, dtype, steps, graphs=False):
+    from tokensprint_b200.engine.replay import TraceReplayer
+    from tokensprint_b200.engine.runner import ModelRunner
+    from tokensprint_b200.models.api import load_model
+
+    model, _ = load_model(folder, device="cuda", dtype=dtype)
+    runner = ModelRunner(model, page_size=16, num_pages=64, num_slots=8, enforce_eager=not graphs, max_model_len=512)
+    got = replay_in_process(TraceReplayer(runner), steps)
+    assert not graphs or runner._graphs
+    return got
+
+
+def test_full_width_cuttings(folder):
+    path, cfg = folder
+    requests = {"a": random_tokens(cfg, 150, 1), "b": random_tokens(cfg, 70, 2), "c": random_tokens(cfg, 33, 3)}
+    ref = _logits(path, "float32", trace_whole(requests))
+
+    # float32 engine against the plain model on the CPU (a short request: the head is 151936 wide)
+    from tokensprint_b200.weights.safetensors_io import SafetensorsFolder
+
+    files = SafetensorsFolder(path)
+    weights = {n: files.tensor(n) for n in files.keys()}
+    want = plain.forward_logits(weights, cfg, requests["c"], dtype=torch.float64).numpy()
+    for pos in range(len(requests["c"])):
+        assert abs(ref[("c", pos)] - want[pos]).max() < 1e-4 * abs(want).max()
+
+    # bfloat16 in every cutting, eager and in graphs, against float32
+    scale = max(float(abs(v).max()) for v in ref.values())
+    for name, steps, graphs in (
+        ("whole", trace_whole(requests), False),
+        ("tail", trace_decode_tail(requests), False),
+        ("tail in graphs", trace_decode_tail(requests), True),
+        ("portions", trace_portions(requests), False),
+        ("mixed", trace_mixed(requests, 512, seed=1), False),
+        ("mixed with graphs", trace_mixed(requests, 512, seed=2), True),
+    ):
+        got = _logits(path, "bfloat16", steps, graphs)
+        assert len(got) == len(ref)
+        worst = max(float(abs(got[k] - ref[k]).max()) for k in ref)
+        assert worst < 4e-2 * scale, f"{name}: bfloat16 strays {worst / scale:.3g} from float32"
