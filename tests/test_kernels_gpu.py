@@ -222,7 +222,7 @@ def run_simple(case, window=0):
     return out
 
 
-def run_mma(case, window=0, splits=1):
+def run_mma(case, window=0, splits=1, keys_per_split=0):
     from tokensprint_b200 import ops
 
     out = torch.full_like(case["q"], float("nan"))
@@ -232,7 +232,8 @@ def run_mma(case, window=0, splits=1):
         scratch = torch.full((ops.attention_scratch_floats(T * case["nq"], splits, case["d"]),), float("nan"), device=DEV)
     max_q = max(ql for ql, _ in case["seqs"])
     ops.attention_paged_mma(case["q"], case["kc"], case["vc"], out, case["cu"], case["ctxs"], case["table"], case["seq_index"],
-                            case["page"], case["B"], max_q, case["nq"], case["nkv"], case["d"], case["d"] ** -0.5, window, splits, scratch)
+                            case["page"], case["B"], max_q, case["nq"], case["nkv"], case["d"], case["d"] ** -0.5, window, splits, scratch,
+                            keys_per_split)
     return out
 
 
@@ -268,6 +269,22 @@ def test_attention_mma_decode_with_key_splits(splits, nq, nkv, d, page, window):
     got = run_mma(case, window, splits)
     want = plain_attention(case, window)
     assert rel_err(got, want) < 1e-2
+
+
+@pytest.mark.parametrize("splits,chunk", [(16, 64), (8, 128), (4, 256), (2, 512), (64, 64)])
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(32, 8, 128, 16, 0), (4, 2, 16, 16, 0), (5, 1, 48, 4, 90), (16, 1, 64, 32, 700)])
+def test_attention_mma_decode_with_fixed_key_chunks(splits, chunk, nq, nkv, d, page, window):
+    """Sequences of very different lengths in one batch; every CTA takes `chunk` keys, CTAs
+    beyond a sequence's end do nothing, and the plan from ops covers the longest one."""
+    from tokensprint_b200 import ops
+
+    case = finish_case(paged_case(DECODE, nq, nkv, d, page, torch.bfloat16, seed=5 * d))
+    got = run_mma(case, window, splits, chunk)
+    want = plain_attention(case, window)
+    assert rel_err(got, want) < 1e-2
+    plan_splits, plan_chunk = ops.attention_decode_plan(len(DECODE), nkv, 1000, d)
+    assert plan_splits * max(plan_chunk, 1) >= 1000 or plan_splits == 1
+    assert rel_err(run_mma(case, window, plan_splits, plan_chunk), want) < 1e-2
 
 
 @pytest.mark.parametrize("kernel", ["simple32", "simple16", "mma", "mma_split"])

@@ -45,6 +45,7 @@ struct AttnParams {
   const int* ctx_len;             // [B] keys in the cache after this step
   const int* block_table;         // [B, max_blocks]
   int max_blocks, page, nq, nkv, window, splits, row_tiles;
+  int keys_per_split;             // > 0: split s covers this many keys (a multiple of BN); 0: the range is divided evenly
   float scale_log2;               // scale * log2(e)
 };
 
@@ -148,12 +149,23 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   const int lo = p.window > 0 ? max(0, start_pos + r0 / G - p.window + 1) : 0;
   int kb0 = lo / BN, kb1 = hi / BN;
   if (p.splits > 1) {
-    const int per = (kb1 - kb0 + p.splits) / p.splits;
+    const int per = p.keys_per_split > 0 ? p.keys_per_split / BN : (kb1 - kb0 + p.splits) / p.splits;
     kb0 = kb0 + split * per;
     kb1 = min(kb1, kb0 + per - 1);
   }
   const int nblocks = kb1 - kb0 + 1;  // may be <= 0 for a split without work
   const int* table = p.block_table + (size_t)b * p.max_blocks;
+  if (nblocks <= 0 && p.splits > 1) {
+    // A split beyond this sequence's keys: mark its partial as empty and leave.
+    for (int r = tid; r < min(BM, rows_total - r0); r += NT) {
+      const int row = r0 + r;
+      const size_t qrow = (size_t)(q_begin + row / G) * p.nq + hk * G + row % G;
+      float* ml = p.part_ml + (qrow * p.splits + split) * 2;
+      ml[0] = -INFINITY;
+      ml[1] = 0.f;
+    }
+    return;
+  }
 
   // Rows of this thread: g and g + 8 of the warp's 16-row tile.
   const int warp_row0 = SPLIT_KEYS ? 0 : warp * 16;
@@ -721,13 +733,18 @@ TS_EXPORT int ts_attention_mma_head_dim() { return D; }
 // [B, max_blocks].  max_q: the most tokens any sequence brings in this step.  splits > 1
 // needs `scratch` of ts_attention_mma_scratch_floats(T * nq, splits) floats; seq_index
 // ([T], -1 marks padding) is only read when splits > 1.
-TS_EXPORT int ts_attention_paged_mma(const void* q, const void* kcache, const void* vcache, void* out,
-                                     float* scratch, const int* cu_q, const int* ctx_len,
-                                     const int* block_table, const int* seq_index, int max_blocks,
-                                     int page, int T, int B, int max_q, int nq, int nkv, float scale,
-                                     int window, int splits, void* stream_) {
+// As ts_attention_paged_mma, with the keys of a sequence cut into fixed chunks of
+// `keys_per_split` keys (a multiple of 64; split s takes chunk s, splits beyond the sequence do
+// nothing), so that sequences of different lengths give CTAs of equal work.  0 divides each
+// sequence's keys evenly over the splits.
+TS_EXPORT int ts_attention_paged_mma_chunked(const void* q, const void* kcache, const void* vcache, void* out,
+                                             float* scratch, const int* cu_q, const int* ctx_len,
+                                             const int* block_table, const int* seq_index, int max_blocks,
+                                             int page, int T, int B, int max_q, int nq, int nkv, float scale,
+                                             int window, int splits, int keys_per_split, void* stream_) {
   if (T <= 0 || B <= 0) return 0;
-  if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page <= 0 || max_blocks <= 0 || max_q <= 0 || splits < 1)
+  if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page <= 0 || max_blocks <= 0 || max_q <= 0 || splits < 1 ||
+      keys_per_split < 0 || keys_per_split % BN != 0)
     return TS_ERR_BAD_ARGUMENT;
   if (splits > 1 && scratch == nullptr) return TS_ERR_BAD_ARGUMENT;
   if (nkv > 65535 || B > 65535) return TS_ERR_UNSUPPORTED_SIZE;
@@ -749,6 +766,7 @@ TS_EXPORT int ts_attention_paged_mma(const void* q, const void* kcache, const vo
   p.nkv = nkv;
   p.window = window;
   p.splits = splits;
+  p.keys_per_split = keys_per_split;
   p.scale_log2 = scale * 1.4426950408889634f;
   const long long rows = (long long)max_q * G;
   int status;
@@ -768,6 +786,15 @@ TS_EXPORT int ts_attention_paged_mma(const void* q, const void* kcache, const vo
     status = ts_launch(attention_combine_kernel, dim3((total + 3) / 4), dim3(128), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, seq_index, total, nq, splits);
   }
   return status;
+}
+
+TS_EXPORT int ts_attention_paged_mma(const void* q, const void* kcache, const void* vcache, void* out,
+                                     float* scratch, const int* cu_q, const int* ctx_len,
+                                     const int* block_table, const int* seq_index, int max_blocks,
+                                     int page, int T, int B, int max_q, int nq, int nkv, float scale,
+                                     int window, int splits, void* stream_) {
+  return ts_attention_paged_mma_chunked(q, kcache, vcache, out, scratch, cu_q, ctx_len, block_table, seq_index,
+                                        max_blocks, page, T, B, max_q, nq, nkv, scale, window, splits, 0, stream_);
 }
 
 // ---------------------------------------------------------------------------

@@ -333,7 +333,7 @@ def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 # tensor-core attention (one library per head size)
 
 ATTENTION_MMA_MAX_HEAD_DIM = 256
-ATTENTION_MMA_MAX_SPLITS = 32
+ATTENTION_MMA_MAX_SPLITS = 64
 _attention_mma: dict[int, tuple] = {}
 
 
@@ -348,8 +348,8 @@ def _attention_mma_fns(head_dim: int):
             raise KernelError(
                 f"attention_paged_mma: head_dim must be a multiple of 16 between 16 and {ATTENTION_MMA_MAX_HEAD_DIM}, got {head_dim}")
         lib = _build.load_variant("attention_mma", {"TS_HEAD_DIM": head_dim})
-        run = lib.ts_attention_paged_mma
-        run.argtypes = [_c_void_p] * 9 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_void_p]
+        run = lib.ts_attention_paged_mma_chunked
+        run.argtypes = [_c_void_p] * 9 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_int, _c_void_p]
         run.restype = _c_int
         scratch = lib.ts_attention_mma_scratch_floats
         scratch.argtypes = [_c_ll, _c_int]
@@ -362,15 +362,42 @@ def _attention_mma_fns(head_dim: int):
 
 
 def attention_decode_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: int = 128) -> int:
-    """How many CTAs share the keys of one sequence in a decode step: as many as run at the
-    same time on the GPU's 148 SMs (shared memory allows a few per SM, fewer for large heads),
-    so the step is one wave; never more than there are key blocks."""
+    """How many CTAs share the keys of one sequence in a decode step.
+
+    Each (sequence, KV head) pair is one unit of work that `splits` CTAs divide evenly.  The
+    GPU runs `slots` CTAs at a time (shared memory allows a few per SM, fewer for large
+    heads); the step takes ceil(pairs * splits / slots) waves, each as long as one CTA's
+    share, so the count is chosen to fill whole waves: one wave for small batches, and for
+    batches with more pairs than slots a count that makes the last wave nearly full.
+    """
     smem = (16 + 4 * 64) * (head_dim + 8) * 2
-    per_sm = max(1, (227 * 1024) // smem)
-    ctas = max(1, num_seqs * num_kv_heads)
-    want = (per_sm * 148) // ctas
+    slots = max(1, (227 * 1024) // smem) * 148
+    pairs = max(1, num_seqs * num_kv_heads)
     blocks = max(1, -(-max_context // 64))
-    return max(1, min(want, blocks, ATTENTION_MMA_MAX_SPLITS))
+    best, best_cost = 1, None
+    for s in range(1, min(blocks, 16) + 1):
+        waves = -(-pairs * s // slots)
+        # per CTA: start and merge (about 3 us) + 2.5 us per 64-key block; + the combine kernel
+        cost = waves * (3.0 + 2.5 * -(-blocks // s)) + (0.3 * s if s > 1 else 0.0)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
+
+
+def attention_decode_plan(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: int = 128) -> tuple[int, int]:
+    """(splits, keys_per_split) for fixed-size key chunks: every (sequence, KV head) pair is cut
+    into chunks of `keys_per_split` keys, one CTA each; `splits` chunks cover `max_context`, and
+    sequences shorter than that use fewer of their CTAs.  For batches whose longest context is
+    known when the step is launched."""
+    pairs = max(1, num_seqs * num_kv_heads)
+    chunk = 64 if pairs <= 16 else (128 if pairs <= 64 else 256)
+    splits = -(-max(1, max_context) // chunk)
+    while splits > ATTENTION_MMA_MAX_SPLITS:
+        chunk *= 2
+        splits = -(-max_context // chunk)
+    if splits <= 1:
+        return 1, 0
+    return splits, chunk
 
 
 def attention_paged_mma(
@@ -392,13 +419,16 @@ def attention_paged_mma(
     window: int = 0,
     splits: int = 1,
     scratch: Optional[torch.Tensor] = None,
+    keys_per_split: int = 0,
 ) -> None:
     """Causal attention over the paged cache on tensor cores (bfloat16).
 
     q/out [T,nq*d]; caches [pages,page,nkv,d]; cu_seqlens_q [B+1], context_lens [B],
     seq_index [T] i32; block_table [B,max_blocks] i32.  The tokens of a sequence are
     consecutive and end at context_lens[b] - 1.  splits > 1 spreads the keys of a
-    sequence over several CTAs and needs `scratch` (float32, see attention_scratch_floats).
+    sequence over several CTAs and needs `scratch` (float32, see attention_scratch_floats);
+    keys_per_split > 0 (a multiple of 64) gives split s the keys [s * keys_per_split, ...),
+    0 divides each sequence's keys evenly.
     """
     run, _ = _attention_mma_fns(head_dim)
     for name, t in (("q", q), ("k_cache", k_cache), ("v_cache", v_cache), ("out", out)):
@@ -417,6 +447,8 @@ def attention_paged_mma(
         raise KernelError("attention: block_table must be [B,max_blocks]")
     if cu_seqlens_q.numel() < num_seqs + 1 or context_lens.numel() < num_seqs or seq_index.numel() < T:
         raise KernelError("attention: cu_seqlens_q/context_lens/seq_index are shorter than the batch")
+    if keys_per_split < 0 or keys_per_split % 64:
+        raise KernelError(f"attention: keys_per_split must be a multiple of 64, got {keys_per_split}")
     if not (1 <= splits <= ATTENTION_MMA_MAX_SPLITS):
         raise KernelError(f"attention: splits must be 1..{ATTENTION_MMA_MAX_SPLITS}, got {splits}")
     if splits > 1:
@@ -426,7 +458,8 @@ def attention_paged_mma(
     _check("attention_paged_mma", run(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _ptr(scratch),
         cu_seqlens_q.data_ptr(), context_lens.data_ptr(), block_table.data_ptr(), seq_index.data_ptr(),
-        block_table.shape[1], page_size, T, num_seqs, max_seqlen_q, nq, nkv, float(scale), int(window), int(splits), _stream()))
+        block_table.shape[1], page_size, T, num_seqs, max_seqlen_q, nq, nkv, float(scale), int(window), int(splits),
+        int(keys_per_split), _stream()))
     if splits > 1:
         global launch_count
         launch_count += 1  # the combine kernel

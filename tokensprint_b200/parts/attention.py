@@ -131,9 +131,12 @@ class AttentionMixer(Mixer):
     def _attend(self, q, out, step: StepContext, cache: LayerCache, tables) -> None:
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         if q.dtype == torch.bfloat16 and ops.attention_mma_supported(d):
-            splits, scratch = 1, None
+            splits, chunk, scratch = 1, 0, None
             if step.max_seqlen_q * (nq // nkv) <= 16:  # decode: spread each sequence's keys over CTAs
-                context = step.max_context_len if self.window <= 0 else min(step.max_context_len, self.window + 64)
+                # The count must not depend on the step's actual lengths (a captured graph is
+                # replayed for all of them): plan for a typical context, each sequence then
+                # divides its own keys evenly.
+                context = min(step.max_context_len, 2048) if self.window <= 0 else min(step.max_context_len, self.window + 64)
                 splits = ops.attention_decode_splits(step.num_seqs, nkv, context, d)
                 if splits > 1:
                     scratch = torch.empty(ops.attention_scratch_floats(q.shape[0] * nq, splits, d),
@@ -141,7 +144,7 @@ class AttentionMixer(Mixer):
             ops.attention_paged_mma(
                 q, cache.k_pages, cache.v_pages, out, step.cu_seqlens_q, step.context_lens, tables.block_table,
                 step.seq_index, step.page_size, step.num_seqs, step.max_seqlen_q, nq, nkv, d, self.scale,
-                self.window, splits, scratch)
+                self.window, splits, scratch, chunk)
             return
         # float32 runs, and head sizes the tensor-core kernel does not take
         ops.attention_paged_simple(
