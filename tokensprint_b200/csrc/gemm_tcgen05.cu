@@ -71,6 +71,8 @@ struct GemmArgs {
   int* error;            // set to 1 when a wait gave up
   int M, N, K, ldo, out_f32;
   int tiles, chunks, units_per;  // chunks of K per tile; units (tile x chunk) per CTA
+  const char* prefetch;          // weights of the GEMM that follows (may be null)
+  unsigned long long prefetch_bytes;
 #ifdef TS_GEMM_PROBE
   unsigned long long* probe;
 #endif
@@ -219,6 +221,18 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
         mbar_expect_tx(bar, C::A_BYTES + C::B_BYTES);
         tma_load_2d(dst, &map_w, bar, kc * TILE_K, t * TILE_N);
         tma_load_2d(dst + C::A_BYTES, &map_x, bar, kc * TILE_K, 0);
+      }
+      // All loads of this GEMM are on their way.  While its last tiles are multiplied and stored
+      // (and while the small kernels after it run) HBM would idle: ask for this CTA's share of the
+      // next GEMM's weights to be brought into L2.
+      if (args.prefetch != nullptr && !*abort_flag) {
+        constexpr unsigned long long PIECE = 32 * 1024;
+        const unsigned long long pieces = (args.prefetch_bytes + PIECE - 1) / PIECE;
+        for (unsigned long long i = blockIdx.x; i < pieces; i += gridDim.x) {
+          const unsigned long long off = i * PIECE;
+          const unsigned bytes = (unsigned)min(PIECE, args.prefetch_bytes - off) & ~15u;
+          if (bytes) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(args.prefetch + off), "r"(bytes) : "memory");
+        }
       }
       if (*abort_flag) {
         // Let the copies that are still in flight land before shared memory is given up.
@@ -501,9 +515,11 @@ TS_EXPORT int ts_gemm_skinny_max_rows() { return 128; }
 // `partial`: ts_gemm_skinny_scratch_floats(M, N, K) floats.  `counters`: ints, one per 128-row
 // tile of W, zero before the first call (the kernel leaves them zero).  `error`: one int the
 // kernel sets to 1 if one of its waits gave up.
+// `prefetch` / `prefetch_bytes`: optionally the start of the weights the next GEMM will read (16-byte
+// aligned); the kernel asks for them to be brought into L2 once its own loads are issued.
 TS_EXPORT int ts_gemm_skinny_bf16(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
                                   long long ldw, long long ldo, int out_f32, float* partial, int* counters,
-                                  int* error, void* stream_) {
+                                  int* error, const void* prefetch, long long prefetch_bytes, void* stream_) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || ldx < K || ldw < K || ldo < N || counters == nullptr || error == nullptr || partial == nullptr)
     return TS_ERR_BAD_ARGUMENT;
@@ -527,6 +543,8 @@ TS_EXPORT int ts_gemm_skinny_bf16(const void* x, const void* w, void* out, int M
   a.K = K;
   a.ldo = (int)ldo;
   a.out_f32 = out_f32;
+  a.prefetch = (prefetch_bytes > 0 && ((uintptr_t)prefetch % 16) == 0) ? (const char*)prefetch : nullptr;
+  a.prefetch_bytes = prefetch_bytes > 0 ? (unsigned long long)prefetch_bytes : 0ull;
 #ifdef TS_GEMM_PROBE
   a.probe = ts_gemm_probe_buffer;
 #endif

@@ -113,8 +113,12 @@ class Model:
         hidden = torch.empty((T, self.spec.hidden_size), device=self.device, dtype=torch.float32)
         ops.embed_gather(hidden, self.embedding, step.token_ids)
         pending = None
-        for i, run in enumerate(self.spec.run_order):
+        order = self.spec.run_order
+        for i, run in enumerate(order):
+            # what is read after this block: the next block's first matrix, or the head
+            step.weight_after = self.blocks[order[i + 1].layer].first_weight() if i + 1 < len(order) else self.head
             pending = self.blocks[run.layer].forward(hidden, pending, step, caches[i])
+        step.weight_after = None
         return hidden, pending
 
     def logits(self, hidden: torch.Tensor, pending: Optional[torch.Tensor], rows: torch.Tensor, num_rows: int) -> torch.Tensor:

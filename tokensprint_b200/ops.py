@@ -475,8 +475,9 @@ def attention_scratch_floats(rows: int, splits: int, head_dim: int) -> int:
 GEMM_SKINNY_MAX_ROWS = 128
 _SIGNATURES["ts_gemm_skinny_bf16"] = [
     _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_int,
-    _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+    _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll, _c_void_p,
 ]
+GEMM_PREFETCH_BYTES = 48 << 20  # how much of the next GEMM's weights a GEMM asks into L2 (the L2 holds 126 MB)
 _gemm_workspaces: dict[tuple[int, int], tuple[torch.Tensor, torch.Tensor]] = {}
 _GEMM_MAX_TILES = 1 << 16
 
@@ -503,12 +504,13 @@ def gemm_skinny_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
     )
 
 
-def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, prefetch: Optional[torch.Tensor] = None) -> None:
     """out[M,N] = x[M,K] @ w[N,K]^T for M <= 128 on the tcgen05 tensor cores.
 
     x, w bfloat16 with unit inner stride and rows that start on 16-byte boundaries; out
     bfloat16 or float32.  The work is spread evenly over all SMs; tiles that two CTAs share
-    meet in a float32 scratch that this wrapper allocates.
+    meet in a float32 scratch that this wrapper allocates.  `prefetch`: the weights the next
+    product will read; the kernel asks for their start to be brought into L2 while it finishes.
     """
     if not (x.is_cuda and w.is_cuda and out.is_cuda):
         raise KernelError("gemm_skinny_bf16: CUDA tensors only (there is no CPU path)")
@@ -526,7 +528,9 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> Non
     counters, error = _gemm_workspace(x.device)
     _check("gemm_skinny_bf16", _fn("ts_gemm_skinny_bf16")(
         x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0), out.stride(0),
-        1 if out.dtype == torch.float32 else 0, _ptr(partial), counters.data_ptr(), error.data_ptr(), _stream()))
+        1 if out.dtype == torch.float32 else 0, _ptr(partial), counters.data_ptr(), error.data_ptr(),
+        _ptr(prefetch), 0 if prefetch is None else min(prefetch.numel() * prefetch.element_size(), GEMM_PREFETCH_BYTES),
+        _stream()))
 
 
 def check_device_errors() -> None:

@@ -74,6 +74,9 @@ class AttentionMixer(Mixer):
         self.q_norm_weight: Optional[torch.Tensor] = None
         self.k_norm_weight: Optional[torch.Tensor] = None
 
+    def first_weight(self) -> Optional[torch.Tensor]:
+        return self.qkv_weight
+
     def cache_need(self) -> CacheNeed:
         kind = "window" if self.window > 0 else "full"
         return CacheNeed(kind=kind, window=self.window, kv_heads=self.num_kv_heads, head_dim=self.head_dim)
@@ -109,7 +112,7 @@ class AttentionMixer(Mixer):
         T = x.shape[0]
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         tables = step.groups[cache.group]
-        qkv = linear(x, self.qkv_weight)
+        qkv = linear(x, self.qkv_weight, next_weight=self.o_weight)
         q = torch.empty((T, nq * d), device=x.device, dtype=x.dtype)
         inv_freq = self.position.rotary_inv_freq() if self.position is not None else None
         fused = self.position is None or inv_freq is not None
@@ -124,7 +127,7 @@ class AttentionMixer(Mixer):
             self._unfused(qkv, q, step, cache, tables)
         out = torch.empty((T, nq * d), device=x.device, dtype=x.dtype)
         self._attend(q, out, step, cache, tables)
-        return linear(out, self.o_weight)
+        return linear(out, self.o_weight, next_weight=step.weight_after)
 
     # -- attention proper ---------------------------------------------------
 

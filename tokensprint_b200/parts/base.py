@@ -97,6 +97,9 @@ class StepContext:
     host_seq_lens: list[int] = field(default_factory=list)
     host_state_slots: list[int] = field(default_factory=list)
     decode_only: bool = False
+    # A hint, set by whoever calls a part: the first weight matrix that will be read after the
+    # part returns (the part may hand it to its last product for prefetching; may be None).
+    weight_after: Optional[torch.Tensor] = None
 
 
 @dataclass
@@ -116,6 +119,10 @@ class LayerCache:
 
 class Part:
     """Base of all parts: declares its tensors and takes them once loaded."""
+
+    def first_weight(self) -> Optional[torch.Tensor]:
+        """The first large weight this part reads in a step, for the part before it to prefetch."""
+        return None
 
     def tensor_specs(self) -> list[TensorSpec]:
         return []

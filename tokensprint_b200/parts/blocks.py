@@ -44,7 +44,13 @@ class PreNormBlock(Block):
 
     def forward(self, hidden, pending, step: StepContext, cache: LayerCache) -> Optional[torch.Tensor]:
         normed = torch.empty(hidden.shape, device=hidden.device, dtype=self.dtype)
+        after_block = step.weight_after
         self.mixer_norm.forward(hidden, pending, normed)
+        step.weight_after = self.feed_forward.first_weight()
         mixed = self.mixer.forward(normed, step, cache)
         self.ffn_norm.forward(hidden, mixed, normed)
+        step.weight_after = after_block
         return self.feed_forward.forward(normed, step)
+
+    def first_weight(self):
+        return self.mixer.first_weight()

@@ -25,6 +25,9 @@ class SwiGLUFeedForward(FeedForward):
         self.gate_up: Optional[torch.Tensor] = None
         self.down: Optional[torch.Tensor] = None
 
+    def first_weight(self) -> Optional[torch.Tensor]:
+        return self.gate_up
+
     def tensor_specs(self) -> list[TensorSpec]:
         H, I = self.hidden_size, self.intermediate_size
         return [
@@ -38,7 +41,7 @@ class SwiGLUFeedForward(FeedForward):
         self.down = tensors[self.names["down"]]
 
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
-        gu = linear(x, self.gate_up)
+        gu = linear(x, self.gate_up, next_weight=self.down)
         act = torch.empty((x.shape[0], self.intermediate_size), device=x.device, dtype=x.dtype)
         ops.swiglu(gu, act)
-        return linear(act, self.down)
+        return linear(act, self.down, next_weight=step.weight_after if step is not None else None)

@@ -23,8 +23,10 @@ from tokensprint_b200 import ops
 SKINNY_ROWS = 32
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x [T, in] @ weight[out, in]^T -> [T, out] in x's dtype."""
+def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
+           next_weight: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [T, in] @ weight[out, in]^T -> [T, out] in x's dtype.  `next_weight`: the matrix the
+    following product reads, if the caller knows it (a hint for prefetching, never needed)."""
     if x.dtype != weight.dtype:
         raise ops.KernelError(f"linear: activation {x.dtype} and weight {weight.dtype} differ")
     T, N = x.shape[0], weight.shape[0]
@@ -38,7 +40,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
         if not x.is_cuda:
             raise ops.KernelError("linear: there is no CPU path")
         if T <= SKINNY_ROWS and ops.gemm_skinny_supported(x, weight):
-            ops.gemm_skinny_bf16(x, weight, out)
+            ops.gemm_skinny_bf16(x, weight, out, next_weight)
         else:
             torch.mm(x, weight.t(), out=out)
     else:
