@@ -222,7 +222,7 @@ def run_simple(case, window=0):
     return out
 
 
-def run_mma(case, window=0, splits=1, keys_per_split=0):
+def run_mma(case, window=0, splits=1, keys_per_split=0, fuse_merge=True):
     from tokensprint_b200 import ops
 
     out = torch.full_like(case["q"], float("nan"))
@@ -233,7 +233,7 @@ def run_mma(case, window=0, splits=1, keys_per_split=0):
     max_q = max(ql for ql, _ in case["seqs"])
     ops.attention_paged_mma(case["q"], case["kc"], case["vc"], out, case["cu"], case["ctxs"], case["table"], case["seq_index"],
                             case["page"], case["B"], max_q, case["nq"], case["nkv"], case["d"], case["d"] ** -0.5, window, splits, scratch,
-                            keys_per_split)
+                            keys_per_split, fuse_merge)
     return out
 
 
@@ -269,6 +269,9 @@ def test_attention_mma_decode_with_key_splits(splits, nq, nkv, d, page, window):
     got = run_mma(case, window, splits)
     want = plain_attention(case, window)
     assert rel_err(got, want) < 1e-2
+    # the merge as a kernel of its own gives the same, and twice in a row (the tickets reset)
+    assert rel_err(run_mma(case, window, splits, fuse_merge=False), want) < 1e-2
+    assert torch.equal(run_mma(case, window, splits), got)
 
 
 @pytest.mark.parametrize("splits,chunk", [(16, 64), (8, 128), (4, 256), (2, 512), (64, 64)])

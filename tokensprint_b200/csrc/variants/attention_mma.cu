@@ -45,6 +45,7 @@ struct AttnParams {
   const int* ctx_len;             // [B] keys in the cache after this step
   const int* block_table;         // [B, max_blocks]
   int max_blocks, page, nq, nkv, window, splits, row_tiles;
+  int* counters;                  // [B * nkv] tickets of the key splits (zero between launches), or null: merge in a kernel of its own
   int keys_per_split;             // > 0: split s covers this many keys (a multiple of BN); 0: the range is divided evenly
   float scale_log2;               // scale * log2(e)
 };
@@ -114,6 +115,57 @@ __device__ __forceinline__ void load_kv_tiles(__nv_bfloat16* k_tile, __nv_bfloat
   cp_async_commit();
 }
 
+// The key splits of one (sequence, KV head) pair meet here when the caller gave ticket counters:
+// every split CTA has written its partial rows, takes a ticket, and the one that arrives last
+// merges all splits of the pair (in split order) and writes the output rows.  No CTA waits.
+template <int NT>
+__device__ __forceinline__ void merge_splits_by_last_arriver(const AttnParams& p, int b, int hk, int q_begin, int rows_total,
+                                                             int G, int* last_flag) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int ticket = atomicAdd(&p.counters[b * p.nkv + hk], 1);
+    *last_flag = (ticket == p.splits - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!*last_flag) return;
+  __threadfence();
+  for (int row = warp; row < rows_total; row += NT / 32) {
+    const size_t qrow = (size_t)(q_begin + row / G) * p.nq + hk * G + row % G;
+    const float* ml = p.part_ml + qrow * p.splits * 2;
+    float m = -INFINITY;
+    for (int s = 0; s < p.splits; ++s) {
+      const float ls = __ldcg(ml + 2 * s + 1);
+      if (ls > 0.f) m = fmaxf(m, __ldcg(ml + 2 * s));
+    }
+    float l = 0.f;
+    float acc[(D + 31) / 32];
+#pragma unroll
+    for (int i = 0; i < (D + 31) / 32; ++i) acc[i] = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+      const float ls = __ldcg(ml + 2 * s + 1);
+      if (!(ls > 0.f)) continue;
+      const float w = exp2f(__ldcg(ml + 2 * s) - m);
+      l += w * ls;
+      const float* src = p.part_o + (qrow * p.splits + s) * D;
+#pragma unroll
+      for (int i = 0; i < (D + 31) / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < D) acc[i] += w * __ldcg(src + d);
+      }
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    __nv_bfloat16* dst = p.out + qrow * D;
+#pragma unroll
+    for (int i = 0; i < (D + 31) / 32; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) dst[d] = __float2bfloat16_rn(acc[i] * inv);
+    }
+  }
+  if (tid == 0) p.counters[b * p.nkv + hk] = 0;
+}
+
 // SPLIT_KEYS = false (prefill): the CTA's warps own 16 query rows each and all walk every key.
 // SPLIT_KEYS = true (decode, at most 16 rows): the warps share the rows and own 16 keys each of
 // every 64-key block, with running max/sum/output of their own, merged when the keys are done.
@@ -128,6 +180,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [BM][LD]
   __nv_bfloat16* k_s = q_s + BM * LD;                                        // [STAGES][BN][LD]
   __nv_bfloat16* v_s = k_s + STAGES * BN * LD;                               // [STAGES][BN][LD]
+  __shared__ int last_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
@@ -164,6 +217,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
       ml[0] = -INFINITY;
       ml[1] = 0.f;
     }
+    if (SPLIT_KEYS && p.counters != nullptr) merge_splits_by_last_arriver<NT>(p, b, hk, q_begin, rows_total, G, &last_flag);
     return;
   }
 
@@ -385,6 +439,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
         ml[1] = l;
       }
     }
+    if (p.splits > 1 && p.counters != nullptr) merge_splits_by_last_arriver<NT>(p, b, hk, q_begin, rows_total, G, &last_flag);
   } else {
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -737,11 +792,15 @@ TS_EXPORT int ts_attention_mma_head_dim() { return D; }
 // `keys_per_split` keys (a multiple of 64; split s takes chunk s, splits beyond the sequence do
 // nothing), so that sequences of different lengths give CTAs of equal work.  0 divides each
 // sequence's keys evenly over the splits.
-TS_EXPORT int ts_attention_paged_mma_chunked(const void* q, const void* kcache, const void* vcache, void* out,
-                                             float* scratch, const int* cu_q, const int* ctx_len,
-                                             const int* block_table, const int* seq_index, int max_blocks,
-                                             int page, int T, int B, int max_q, int nq, int nkv, float scale,
-                                             int window, int splits, int keys_per_split, void* stream_) {
+// `counters` (B * nkv ints, zero before the first call; the kernel leaves them zero): with it the
+// last CTA of every (sequence, KV head) pair merges the pair's splits itself and no second kernel
+// runs; only for decode steps (at most 16 query rows per pair).  Null: the merge is a kernel of
+// its own.
+TS_EXPORT int ts_attention_paged_mma_fused(const void* q, const void* kcache, const void* vcache, void* out,
+                                           float* scratch, const int* cu_q, const int* ctx_len,
+                                           const int* block_table, const int* seq_index, int max_blocks,
+                                           int page, int T, int B, int max_q, int nq, int nkv, float scale,
+                                           int window, int splits, int keys_per_split, int* counters, void* stream_) {
   if (T <= 0 || B <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page <= 0 || max_blocks <= 0 || max_q <= 0 || splits < 1 ||
       keys_per_split < 0 || keys_per_split % BN != 0)
@@ -767,6 +826,7 @@ TS_EXPORT int ts_attention_paged_mma_chunked(const void* q, const void* kcache, 
   p.window = window;
   p.splits = splits;
   p.keys_per_split = keys_per_split;
+  p.counters = (counters != nullptr && splits > 1 && (long long)max_q * (nq / nkv) <= 16) ? counters : nullptr;
   p.scale_log2 = scale * 1.4426950408889634f;
   const long long rows = (long long)max_q * G;
   int status;
@@ -781,11 +841,21 @@ TS_EXPORT int ts_attention_paged_mma_chunked(const void* q, const void* kcache, 
       status = launch<8, false>(p, B, stream);
   }
   if (status != 0) return status;
-  if (splits > 1) {
+  if (splits > 1 && p.counters == nullptr) {
     const int total = T * nq;
     status = ts_launch(attention_combine_kernel, dim3((total + 3) / 4), dim3(128), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, seq_index, total, nq, splits);
   }
   return status;
+}
+
+TS_EXPORT int ts_attention_paged_mma_chunked(const void* q, const void* kcache, const void* vcache, void* out,
+                                             float* scratch, const int* cu_q, const int* ctx_len,
+                                             const int* block_table, const int* seq_index, int max_blocks,
+                                             int page, int T, int B, int max_q, int nq, int nkv, float scale,
+                                             int window, int splits, int keys_per_split, void* stream_) {
+  return ts_attention_paged_mma_fused(q, kcache, vcache, out, scratch, cu_q, ctx_len, block_table, seq_index,
+                                      max_blocks, page, T, B, max_q, nq, nkv, scale, window, splits, keys_per_split,
+                                      nullptr, stream_);
 }
 
 TS_EXPORT int ts_attention_paged_mma(const void* q, const void* kcache, const void* vcache, void* out,
@@ -793,8 +863,8 @@ TS_EXPORT int ts_attention_paged_mma(const void* q, const void* kcache, const vo
                                      const int* block_table, const int* seq_index, int max_blocks,
                                      int page, int T, int B, int max_q, int nq, int nkv, float scale,
                                      int window, int splits, void* stream_) {
-  return ts_attention_paged_mma_chunked(q, kcache, vcache, out, scratch, cu_q, ctx_len, block_table, seq_index,
-                                        max_blocks, page, T, B, max_q, nq, nkv, scale, window, splits, 0, stream_);
+  return ts_attention_paged_mma_fused(q, kcache, vcache, out, scratch, cu_q, ctx_len, block_table, seq_index,
+                                      max_blocks, page, T, B, max_q, nq, nkv, scale, window, splits, 0, nullptr, stream_);
 }
 
 // ---------------------------------------------------------------------------

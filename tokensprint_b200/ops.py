@@ -8,6 +8,7 @@ the limit in words; nothing falls back to another implementation.
 from __future__ import annotations
 
 import ctypes
+import os as _os
 from typing import Optional
 
 import torch
@@ -15,6 +16,7 @@ import torch
 from tokensprint_b200.csrc import build as _build
 
 DTYPE_CODES = {torch.float32: 0, torch.bfloat16: 1}
+_GEMM_MAX_TILES = 1 << 16  # size of the ticket-counter arrays of the GEMM and of the decode attention
 
 _c_void_p = ctypes.c_void_p
 _c_int = ctypes.c_int
@@ -348,8 +350,8 @@ def _attention_mma_fns(head_dim: int):
             raise KernelError(
                 f"attention_paged_mma: head_dim must be a multiple of 16 between 16 and {ATTENTION_MMA_MAX_HEAD_DIM}, got {head_dim}")
         lib = _build.load_variant("attention_mma", {"TS_HEAD_DIM": head_dim})
-        run = lib.ts_attention_paged_mma_chunked
-        run.argtypes = [_c_void_p] * 9 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_int, _c_void_p]
+        run = lib.ts_attention_paged_mma_fused
+        run.argtypes = [_c_void_p] * 9 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_int, _c_void_p, _c_void_p]
         run.restype = _c_int
         scratch = lib.ts_attention_mma_scratch_floats
         scratch.argtypes = [_c_ll, _c_int]
@@ -374,6 +376,8 @@ def attention_decode_splits(num_seqs: int, num_kv_heads: int, max_context: int, 
     slots = max(1, (227 * 1024) // smem) * 148
     pairs = max(1, num_seqs * num_kv_heads)
     blocks = max(1, -(-max_context // 64))
+    if _os.environ.get("TS_DECODE_SPLITS"):
+        return max(1, min(int(_os.environ["TS_DECODE_SPLITS"]), blocks, ATTENTION_MMA_MAX_SPLITS))
     best, best_cost = 1, None
     for s in range(1, min(blocks, 16) + 1):
         waves = -(-pairs * s // slots)
@@ -420,6 +424,7 @@ def attention_paged_mma(
     splits: int = 1,
     scratch: Optional[torch.Tensor] = None,
     keys_per_split: int = 0,
+    fuse_merge: bool = True,
 ) -> None:
     """Causal attention over the paged cache on tensor cores (bfloat16).
 
@@ -428,7 +433,8 @@ def attention_paged_mma(
     consecutive and end at context_lens[b] - 1.  splits > 1 spreads the keys of a
     sequence over several CTAs and needs `scratch` (float32, see attention_scratch_floats);
     keys_per_split > 0 (a multiple of 64) gives split s the keys [s * keys_per_split, ...),
-    0 divides each sequence's keys evenly.
+    0 divides each sequence's keys evenly.  In decode steps the last CTA of each (sequence, KV
+    head) pair merges the pair's splits itself (`fuse_merge`); otherwise a second kernel does.
     """
     run, _ = _attention_mma_fns(head_dim)
     for name, t in (("q", q), ("k_cache", k_cache), ("v_cache", v_cache), ("out", out)):
@@ -455,14 +461,30 @@ def attention_paged_mma(
         need = attention_scratch_floats(T * nq, splits, d)
         if scratch is None or scratch.dtype != torch.float32 or not scratch.is_cuda or scratch.numel() < need:
             raise KernelError(f"attention: splits={splits} needs {need} float32 of scratch")
+    counters = None
+    if fuse_merge and _FUSE_ATTENTION_MERGE and splits > 1 and max_seqlen_q * (nq // nkv) <= 16 and num_seqs * nkv <= _GEMM_MAX_TILES:
+        counters = _attention_counters(q.device).data_ptr()
     _check("attention_paged_mma", run(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _ptr(scratch),
         cu_seqlens_q.data_ptr(), context_lens.data_ptr(), block_table.data_ptr(), seq_index.data_ptr(),
         block_table.shape[1], page_size, T, num_seqs, max_seqlen_q, nq, nkv, float(scale), int(window), int(splits),
-        int(keys_per_split), _stream()))
-    if splits > 1:
+        int(keys_per_split), counters, _stream()))
+    if splits > 1 and counters is None:
         global launch_count
         launch_count += 1  # the combine kernel
+
+
+_FUSE_ATTENTION_MERGE = _os.environ.get("TS_FUSE_ATTENTION_MERGE", "0") != "0"  # measured: the separate merge kernel is a little faster
+_attention_counter_tensors: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _attention_counters(device: torch.device) -> torch.Tensor:
+    """Per (device, stream): ticket counters of the decode attention's key splits (zero between launches)."""
+    key = (device.index or 0, _stream())
+    t = _attention_counter_tensors.get(key)
+    if t is None:
+        t = _attention_counter_tensors[key] = torch.zeros(_GEMM_MAX_TILES, dtype=torch.int32, device=device)
+    return t
 
 
 def attention_scratch_floats(rows: int, splits: int, head_dim: int) -> int:
@@ -479,7 +501,6 @@ _SIGNATURES["ts_gemm_skinny_bf16"] = [
 ]
 GEMM_PREFETCH_BYTES = 48 << 20  # how much of the next GEMM's weights a GEMM asks into L2 (the L2 holds 126 MB)
 _gemm_workspaces: dict[tuple[int, int], tuple[torch.Tensor, torch.Tensor]] = {}
-_GEMM_MAX_TILES = 1 << 16
 
 
 def _gemm_workspace(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
