@@ -88,7 +88,9 @@ def reference_logits(reference_root: str, cfg: dict, weights: dict[str, torch.Te
 
 
 def main() -> None:
-    reference_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/tokensprint")
+    reference_root = sys.argv[1]
     for tag, cfg in (("a", TINY_A), ("b", TINY_B)):
         if cfg.get("use_sliding_window"):
             raise SystemExit("golden configs must be full attention (the reference has no window)")
