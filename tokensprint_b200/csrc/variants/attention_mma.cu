@@ -187,6 +187,11 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   const int b = blockIdx.z, hk = blockIdx.y;
   const int row_tile = blockIdx.x % p.row_tiles, split = blockIdx.x / p.row_tiles;
   const int G = p.nq / p.nkv;
+  // In key-split mode a warp copies exactly the 16 rows of each key block that it then reads
+  // (thread t fills row t / 2), so the warps never wait for one another inside the loop.
+  auto tile_sync = [] {
+    if constexpr (SPLIT_KEYS) __syncwarp(); else __syncthreads();
+  };
 
   const int q_begin = p.cu_q[b];
   const int q_len = p.cu_q[b + 1] - q_begin;
@@ -231,6 +236,13 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     row_pos[h] = r < rows_total ? start_pos + r / G : -1;
     row_lo[h] = (p.window > 0 && row_pos[h] >= 0) ? max(0, row_pos[h] - p.window + 1) : 0;
   }
+  // Smallest position and largest window start among this warp's rows that exist: key blocks
+  // between them are seen in full by every such row.  (Rows that do not exist are never
+  // stored, so what an unmasked block leaves in them does not matter.)
+  const int warp_first_row = r0 + warp_row0;
+  const int warp_last_row = min(warp_first_row + 15, rows_total - 1);
+  const int warp_min_pos = warp_first_row < rows_total ? start_pos + warp_first_row / G : -1;
+  const int warp_max_lo = (p.window > 0 && warp_first_row < rows_total) ? max(0, start_pos + warp_last_row / G - p.window + 1) : 0;
 
   // Queries of the tile.
   for (int c = tid; c < BM * CH; c += NT) {
@@ -283,7 +295,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     } else {
       cp_async_wait<1>();
     }
-    __syncthreads();
+    tile_sync();
 
     // S = Q K^T over this warp's keys of the block
     float s[NTILES][4];
@@ -312,27 +324,39 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
       }
     }
 
-    // scale, mask, online softmax (log2 domain)
+    // mask, online softmax.  The running max is kept in raw score units (the scale is positive,
+    // so it commutes with max) and the scale is folded into the exponent's multiply-add:
+    // p = 2^(s * scale - max * scale).  Blocks that every valid row of this warp sees in full
+    // skip the mask; the output is rescaled only when some row's max moved.
     float m_new[2] = {m_run[0], m_run[1]};
+    const int wk0 = kbase + key0;  // first key this warp scores in this block
+    const bool unmasked = (wk0 + NTILES * 8 - 1 <= warp_min_pos) && (wk0 >= warp_max_lo);
+    if (unmasked) {
 #pragma unroll
-    for (int nt = 0; nt < NTILES; ++nt) {
+      for (int nt = 0; nt < NTILES; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int h = e >> 1;
-        const int j = kbase + key0 + nt * 8 + tq * 2 + (e & 1);
-        const bool ok = j <= row_pos[h] && j >= row_lo[h];
-        const float v = ok ? s[nt][e] * p.scale_log2 : -INFINITY;
-        s[nt][e] = v;
-        m_new[h] = fmaxf(m_new[h], v);
+        for (int e = 0; e < 4; ++e) m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < NTILES; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h = e >> 1;
+          const int j = wk0 + nt * 8 + tq * 2 + (e & 1);
+          const bool ok = j <= row_pos[h] && j >= row_lo[h];
+          const float v = ok ? s[nt][e] : -INFINITY;
+          s[nt][e] = v;
+          m_new[h] = fmaxf(m_new[h], v);
+        }
       }
     }
-    float corr[2], m_use[2];
+    float corr[2], m_off[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
       m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
-      m_use[h] = m_new[h] == -INFINITY ? 0.f : m_new[h];  // a row that has seen no key yet
-      corr[h] = exp2f(m_run[h] - m_use[h]);               // m_run = -inf gives 0
+      m_off[h] = m_new[h] == -INFINITY ? 0.f : m_new[h] * p.scale_log2;  // a row that has seen no key yet
+      corr[h] = fast_exp2(m_run[h] * p.scale_log2 - m_off[h]);           // m_run = -inf gives 0
       m_run[h] = m_new[h];
     }
     float l_add[2] = {0.f, 0.f};
@@ -340,20 +364,21 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     for (int nt = 0; nt < NTILES; ++nt) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int h = e >> 1;
-        const float pv = exp2f(s[nt][e] - m_use[h]);
+        const float pv = fast_exp2(fmaf(s[nt][e], p.scale_log2, -m_off[e >> 1]));
         s[nt][e] = pv;
-        l_add[h] += pv;
+        l_add[e >> 1] += pv;
       }
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * corr[h] + l_add[h];
+    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-      o_acc[i][0] *= corr[0];
-      o_acc[i][1] *= corr[0];
-      o_acc[i][2] *= corr[1];
-      o_acc[i][3] *= corr[1];
+      for (int i = 0; i < D / 8; ++i) {
+        o_acc[i][0] *= corr[0];
+        o_acc[i][1] *= corr[0];
+        o_acc[i][2] *= corr[1];
+        o_acc[i][3] *= corr[1];
+      }
     }
 
     if (more) {
@@ -361,7 +386,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     } else {
       cp_async_wait<0>();
     }
-    __syncthreads();
+    tile_sync();
 
     // O += P V
     const __nv_bfloat16* v_tile = v_s + stage * BN * LD + key0 * LD;
@@ -381,7 +406,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
         mma_bf16(o_acc[2 * np + 1], a, b2, b3);
       }
     }
-    __syncthreads();  // the next round's prefetch overwrites this stage
+    tile_sync();  // the next round's prefetch overwrites this stage
   }
 
   // Row sums live spread over the four threads of a quad.
@@ -393,7 +418,8 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
 
   if constexpr (SPLIT_KEYS) {
     // Merge the warps (each saw its own quarter of the keys) through shared memory, which
-    // is free now: the loop's last barrier is behind us and no copy is in flight.
+    // is free once every warp has left the loop and no copy is in flight.
+    __syncthreads();
     float* m_s = reinterpret_cast<float*>(k_s);        // [NWARPS][16]
     float* l_s = m_s + NWARPS * 16;                    // [NWARPS][16]
     float* o_s = l_s + NWARPS * 16;                    // [NWARPS][16][D]
@@ -401,7 +427,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     for (int h = 0; h < 2; ++h) {
       const int r = g + 8 * h;
       if (tq == 0) {
-        m_s[warp * 16 + r] = m_run[h];
+        m_s[warp * 16 + r] = m_run[h] * p.scale_log2;  // log2 units from here on (-inf stays -inf)
         l_s[warp * 16 + r] = l_run[h];
       }
 #pragma unroll
@@ -461,7 +487,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
         *reinterpret_cast<float2*>(dst + i * 8 + tq * 2) = make_float2(o_acc[i][2 * h], o_acc[i][2 * h + 1]);
       if (tq == 0) {
         float* ml = p.part_ml + (qrow * p.splits + split) * 2;
-        ml[0] = m_run[h];
+        ml[0] = m_run[h] * p.scale_log2;  // log2 units, as the merge expects
         ml[1] = l_run[h];
       }
     }
