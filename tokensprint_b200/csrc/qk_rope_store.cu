@@ -130,55 +130,78 @@ __global__ void qk_norm_rope_store_pairs_kernel(const TA* __restrict__ qkv, TA* 
     }
   }
 
-  for (int head = head0; head < head1; ++head) {
-    const TA* src = qkv + ((size_t)t * heads + head) * d;
-    const bool is_q = head < nq;
-    const bool is_k = !is_q && head < nq + nkv;
-    if (!is_q && slot < 0) continue;
-    if (!is_q && !is_k) {
-      TA* dst = v_dst + ((size_t)slot * nkv + (head - nq - nkv)) * d;
-      for (int i = 2 * lane; i < d; i += 64) {
-        const float2 v = ts_load2(src + i);
-        ts_store2(dst + i, v.x, v.y);
-      }
-      continue;
-    }
-    float2 lo[QKR_ROUNDS], hi[QKR_ROUNDS];
-    float ss = 0.f;
+  // Heads are taken four at a time: all loads of the four first, then the math and the stores,
+  // so four rows are in flight per warp instead of one.
+  constexpr int BATCH = 4;
+  for (int hb = head0; hb < head1; hb += BATCH) {
+    float2 lo[BATCH][QKR_ROUNDS], hi[BATCH][QKR_ROUNDS];
 #pragma unroll
-    for (int r = 0; r < QKR_ROUNDS; ++r) {
-      const int j = 2 * lane + 64 * r;
-      if (j < half) {
-        lo[r] = ts_load2(src + j);
-        hi[r] = ts_load2(src + half + j);
-        ss += lo[r].x * lo[r].x + lo[r].y * lo[r].y + hi[r].x * hi[r].x + hi[r].y * hi[r].y;
+    for (int u = 0; u < BATCH; ++u) {
+      const int head = hb + u;
+      if (head >= head1) continue;
+      if (head >= nq && slot < 0) continue;
+      const TA* src = qkv + ((size_t)t * heads + head) * d;
+#pragma unroll
+      for (int r = 0; r < QKR_ROUNDS; ++r) {
+        const int j = 2 * lane + 64 * r;
+        if (j < half) {
+          lo[u][r] = ts_load2(src + j);
+          hi[u][r] = ts_load2(src + half + j);
+        }
       }
     }
-    const float* w = is_q ? q_norm_w : k_norm_w;
-    float rstd = 1.f;
-    if (w) {
-      ss = ts_warp_sum(ss);
-      rstd = rsqrtf(ss / (float)d + eps);
-    }
-    TA* dst = is_q ? q_out + ((size_t)t * nq + head) * d : k_dst + ((size_t)slot * nkv + (head - nq)) * d;
 #pragma unroll
-    for (int r = 0; r < QKR_ROUNDS; ++r) {
-      const int j = 2 * lane + 64 * r;
-      if (j < half) {
-        float2 a = lo[r], b = hi[r];
-        if (w) {
-          const float2 wl = ts_load2(w + j), wh = ts_load2(w + half + j);
-          a.x *= rstd * wl.x; a.y *= rstd * wl.y;
-          b.x *= rstd * wh.x; b.y *= rstd * wh.y;
+    for (int u = 0; u < BATCH; ++u) {
+      const int head = hb + u;
+      if (head >= head1) continue;
+      const bool is_q = head < nq;
+      const bool is_k = !is_q && head < nq + nkv;
+      if (!is_q && slot < 0) continue;
+      if (!is_q && !is_k) {  // value head: plain copy
+        TA* dst = v_dst + ((size_t)slot * nkv + (head - nq - nkv)) * d;
+#pragma unroll
+        for (int r = 0; r < QKR_ROUNDS; ++r) {
+          const int j = 2 * lane + 64 * r;
+          if (j < half) {
+            ts_store2(dst + j, lo[u][r].x, lo[u][r].y);
+            ts_store2(dst + half + j, hi[u][r].x, hi[u][r].y);
+          }
         }
-        if (inv_freq) {
-          const float2 ra = make_float2(a.x * cs[r][0] - b.x * cs[r][1], a.y * cs[r][2] - b.y * cs[r][3]);
-          const float2 rb = make_float2(b.x * cs[r][0] + a.x * cs[r][1], b.y * cs[r][2] + a.y * cs[r][3]);
-          a = ra;
-          b = rb;
+        continue;
+      }
+      float ss = 0.f;
+#pragma unroll
+      for (int r = 0; r < QKR_ROUNDS; ++r) {
+        const int j = 2 * lane + 64 * r;
+        if (j < half)
+          ss += lo[u][r].x * lo[u][r].x + lo[u][r].y * lo[u][r].y + hi[u][r].x * hi[u][r].x + hi[u][r].y * hi[u][r].y;
+      }
+      const float* w = is_q ? q_norm_w : k_norm_w;
+      float rstd = 1.f;
+      if (w) {
+        ss = ts_warp_sum(ss);
+        rstd = rsqrtf(ss / (float)d + eps);
+      }
+      TA* dst = is_q ? q_out + ((size_t)t * nq + head) * d : k_dst + ((size_t)slot * nkv + (head - nq)) * d;
+#pragma unroll
+      for (int r = 0; r < QKR_ROUNDS; ++r) {
+        const int j = 2 * lane + 64 * r;
+        if (j < half) {
+          float2 a = lo[u][r], b = hi[u][r];
+          if (w) {
+            const float2 wl = ts_load2(w + j), wh = ts_load2(w + half + j);
+            a.x *= rstd * wl.x; a.y *= rstd * wl.y;
+            b.x *= rstd * wh.x; b.y *= rstd * wh.y;
+          }
+          if (inv_freq) {
+            const float2 ra = make_float2(a.x * cs[r][0] - b.x * cs[r][1], a.y * cs[r][2] - b.y * cs[r][3]);
+            const float2 rb = make_float2(b.x * cs[r][0] + a.x * cs[r][1], b.y * cs[r][2] + a.y * cs[r][3]);
+            a = ra;
+            b = rb;
+          }
+          ts_store2(dst + j, a.x, a.y);
+          ts_store2(dst + half + j, b.x, b.y);
         }
-        ts_store2(dst + j, a.x, a.y);
-        ts_store2(dst + half + j, b.x, b.y);
       }
     }
   }

@@ -34,8 +34,21 @@ def sample_key(seed: int, stream: int, position: int) -> int:
 
 
 class Sampler:
-    def __init__(self, device: torch.device | str) -> None:
+    """Temperatures and keys go to the device through pinned staging buffers that are reused
+    from step to step (two small asynchronous copies); the sampled ids come back in one."""
+
+    def __init__(self, device: torch.device | str, max_rows: int = 1024) -> None:
         self.device = torch.device(device)
+        self._alloc(max_rows)
+
+    def _alloc(self, rows: int) -> None:
+        self._rows = rows
+        pin = self.device.type == "cuda"
+        self._temps_host = torch.empty(rows, dtype=torch.float32, pin_memory=pin)
+        self._keys_host = torch.empty(rows, dtype=torch.int64, pin_memory=pin)
+        self._temps = torch.empty(rows, dtype=torch.float32, device=self.device)
+        self._keys = torch.empty(rows, dtype=torch.int64, device=self.device)
+        self._out = torch.empty(rows, dtype=torch.int32, device=self.device)
 
     @torch.inference_mode()
     def sample(self, logits: torch.Tensor, temperatures: Sequence[float], keys: Sequence[int]) -> list[int]:
@@ -45,8 +58,13 @@ class Sampler:
             raise ValueError(f"{R} rows of logits, {len(temperatures)} temperatures, {len(keys)} keys")
         if R == 0:
             return []
-        temps = torch.tensor(list(temperatures), dtype=torch.float32).to(self.device, non_blocking=True)
-        key_t = torch.tensor(list(keys), dtype=torch.int64).to(self.device, non_blocking=True)
-        out = torch.empty(R, dtype=torch.int32, device=self.device)
-        ops.sample(logits, temps, key_t, out)
+        if R > self._rows:
+            self._alloc(max(R, 2 * self._rows))
+        # The previous call ended with a synchronising copy of the ids, so the staging buffers are free.
+        self._temps_host[:R] = torch.tensor(temperatures, dtype=torch.float32)
+        self._keys_host[:R] = torch.tensor(keys, dtype=torch.int64)
+        self._temps[:R].copy_(self._temps_host[:R], non_blocking=True)
+        self._keys[:R].copy_(self._keys_host[:R], non_blocking=True)
+        out = self._out[:R]
+        ops.sample(logits, self._temps[:R], self._keys[:R], out)
         return out.tolist()
