@@ -342,6 +342,95 @@ def test_attention_ignores_pages_that_are_not_held():
 
 
 # ---------------------------------------------------------------------------
+# prompt attention on tcgen05 (head size 128)
+
+
+def run_tcgen05(case, window=0):
+    from tokensprint_b200 import ops
+
+    out = torch.full_like(case["q"], float("nan"))
+    max_q = max(ql for ql, _ in case["seqs"])
+    ops.attention_prefill_tcgen05(case["q"], case["kc"], case["vc"], out, case["cu"], case["ctxs"], case["table"],
+                                  case["page"], case["B"], max_q, case["nq"], case["nkv"], case["d"] ** -0.5, window)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    return out
+
+
+PROMPTS = [(1, 1), (1, 77), (5, 5), (3, 130), (64, 64), (37, 200), (2, 65), (1, 64), (130, 131), (300, 300), (129, 517), (33, 1000)]
+
+
+@pytest.mark.parametrize(
+    "nq,nkv,page,window",
+    [(32, 8, 16, 0), (4, 4, 16, 0), (8, 1, 8, 0), (16, 1, 64, 0), (2, 1, 32, 0), (6, 3, 16, 0), (128, 1, 16, 0),
+     (32, 8, 16, 100), (8, 2, 32, 7), (4, 1, 8, 64), (3, 3, 16, 300), (32, 8, 256, 0), (8, 2, 128, 90), (4, 1, 192, 0)],
+)
+def test_attention_tcgen05_mixed(nq, nkv, page, window):
+    """Prompt portions and single tokens of many lengths in one launch, every group size that
+    divides 128, pages of 8 to 256 slots in shuffled order, NaN in every slot nobody wrote."""
+    case = finish_case(paged_case(PROMPTS, nq, nkv, 128, page, torch.bfloat16, seed=nq + page))
+    got = run_tcgen05(case, window)
+    want = plain_attention(case, window)
+    assert rel_err(got, want) < 1e-2
+    assert torch.equal(run_tcgen05(case, window), got)
+
+
+def test_attention_tcgen05_says_what_it_takes():
+    from tokensprint_b200 import ops
+
+    assert ops.attention_tcgen05_supported(32, 8, 128, 16)
+    assert not ops.attention_tcgen05_supported(32, 8, 64, 16)  # head size
+    assert not ops.attention_tcgen05_supported(40, 8, 128, 16)  # groups of 5
+    assert not ops.attention_tcgen05_supported(32, 8, 128, 4)  # pages too small for one copy each
+    assert not ops.attention_tcgen05_supported(32, 8, 128, 96)  # pages that straddle the 64-key blocks
+    case = finish_case(paged_case([(5, 9)], 10, 2, 128, 16, torch.bfloat16))
+    with pytest.raises(ops.KernelError, match="group size"):
+        run_tcgen05(case)
+
+
+@pytest.mark.parametrize("target", ["first", "far", "page_edge_before", "page_edge_after", "block_edge", "own", "window_first", "window_out"])
+def test_attention_tcgen05_finds_one_key_that_stands_out(target):
+    """As for the other kernels, with a prompt portion: the query is token 650 of 700 and the
+    portion holds the last 100 tokens."""
+    nq, nkv, d, page, ctx, ql = 8, 2, 128, 16, 700, 100
+    qpos = 650
+    window = 0
+    where = {"first": 0, "far": 3, "page_edge_before": 16 * 20 - 1, "page_edge_after": 16 * 20, "block_edge": 64 * 7, "own": qpos}.get(target)
+    if target == "window_first":
+        window, where = 100, qpos - 99
+    if target == "window_out":
+        window, where = 100, qpos - 100
+    case = paged_case([(7, 40), (ql, ctx)], nq, nkv, d, page, torch.bfloat16, seed=5)
+    q, k, v = case["dense"][1]
+    k.mul_(0.05)
+    qi = qpos - (ctx - ql)
+    k[where, 1] = q[qi, 6] * 3.0  # head 6 (KV head 1) of that token finds itself at `where`
+    v[where, 1] = 10.0
+    case = finish_case(case)
+    got = run_tcgen05(case, window)
+    row = got.view(-1, nq, d)[7 + qi, 6].float()
+    if target == "window_out":
+        assert float(row.abs().max()) < 5.0, "a key outside the window was seen"
+    else:
+        assert float((row - 10.0).abs().max()) < 0.05, f"the key at {where} was not found"
+    assert rel_err(got, plain_attention(case, window)) < 1e-2
+
+
+def test_attention_tcgen05_ignores_pages_that_are_not_held():
+    nq, nkv, d, page, window = 8, 2, 128, 8, 40
+    case = finish_case(paged_case([(3, 200), (1, 90), (70, 400)], nq, nkv, d, page, torch.bfloat16, seed=9))
+    want = plain_attention(case, window)
+    for b, (ql, c) in enumerate(case["seqs"]):
+        first_needed = max(0, c - ql - window + 1) // page
+        for i in range(first_needed):
+            pg = int(case["table"][b, i])
+            case["kc"][pg] = float("nan")
+            case["vc"][pg] = float("nan")
+            case["table"][b, i] = -1
+    assert rel_err(run_tcgen05(case, window), want) < 1e-2
+
+
+# ---------------------------------------------------------------------------
 # sampling
 
 

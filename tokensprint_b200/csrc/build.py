@@ -231,6 +231,7 @@ def build_all() -> list[Path]:
     paths = [build()]
     with ThreadPoolExecutor(max_workers=min(os.cpu_count() or 2, 8)) as pool:
         paths += list(pool.map(lambda d: build_variant("attention_mma", {"TS_HEAD_DIM": d}), ATTENTION_HEAD_DIMS))
+    paths.append(build_variant("attention_tcgen05", {"TS_HEAD_DIM": 128}))
     return paths
 
 

@@ -1,0 +1,531 @@
+// Paged causal attention for prompt portions on the 5th-generation tensor cores
+// (tcgen05.mma, accumulators in tensor memory, operands brought by TMA): head size 128.
+//
+// What it computes is what attention_simple.cu computes (engine/nn/sdpa.py:56,85-102 of the
+// reference).  How: one CTA per (sequence, KV head, tile of 128 rows), a row being a (query
+// token, query head of the group) pair, so the heads that share a KV head share every key/value
+// block.  Keys are walked in blocks of 64:
+//   S = Q K^T      tcgen05.mma M=128 N=64 K=16 x 8, Q and K in shared memory (128-byte swizzle,
+//                  K-major), S in tensor memory;
+//   softmax        thread r owns row r: it reads its 64 scores from tensor memory, keeps the
+//                  running max and sum in registers (no shuffles), and writes P as bfloat16
+//                  into shared memory in the swizzled layout the next MMA reads;
+//   O_blk = P V    tcgen05.mma M=128 N=128 K=16 x 4, V read in its natural [key][dim] order
+//                  (an MN-major operand), O_blk in tensor memory;
+//   O = O c + O_blk in registers (c rescales to the new running max).
+// Q comes by one 4-d TMA box per half head; every page of K and V by one box per half head,
+// into a ring of two stages, one block ahead.  The S product of the next block is issued
+// before the rows of this block are folded into O, so the tensor core works while the
+// threads do.  One thread issues all TMA and MMA instructions.
+//
+// Every wait is on an mbarrier fed by this CTA's own copies and MMAs, bounded; a wait that
+// gives up raises the error word and the CTA frees its tensor memory and returns.
+//
+// Limits (the caller falls back to the mma.sync kernel otherwise): head size 128; the group
+// size (query heads per KV head) divides 128; the page size is at least 8 and divides 64 or is a
+// multiple of it.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "../common.cuh"
+
+#if TS_HEAD_DIM != 128
+#error "attention_tcgen05.cu is written for TS_HEAD_DIM=128"
+#endif
+
+namespace {
+
+constexpr int D = 128;
+constexpr int BM = 128;  // rows per tile
+constexpr int BN = 64;   // keys per block
+constexpr int STAGES = 2;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+constexpr uint32_t Q_BYTES = 2 * BM * 128;        // two half-head atoms of [128 rows x 128 B]
+constexpr uint32_t KV_HALF = BN * 128;            // [64 keys x 128 B]
+constexpr uint32_t KV_STAGE = 2 * KV_HALF;        // both halves of the head
+constexpr uint32_t P_BYTES = BM * 128;            // [128 rows x 64 keys] bfloat16
+constexpr uint32_t OFF_Q = 0;
+constexpr uint32_t OFF_K = OFF_Q + Q_BYTES;
+constexpr uint32_t OFF_V = OFF_K + STAGES * KV_STAGE;
+// P of a block lies where that block's K lay: K is dead once S is computed, P is dead once
+// O_blk is, and only then is the stage filled again.
+static_assert(P_BYTES == KV_STAGE, "P takes the place of one K stage");
+constexpr uint32_t SMEM_TILES = OFF_V + STAGES * KV_STAGE;  // 98,304 bytes: two CTAs per SM
+constexpr int MAX_TABLE = 1024;                   // block-table entries kept in shared memory
+constexpr uint32_t TMEM_COLS = 256;               // S: 64 columns, O_blk: 128 columns
+constexpr uint32_t TMEM_S = 0, TMEM_O = 64;
+
+struct Params {
+  __nv_bfloat16* out;     // [T, nq, D]
+  const int* cu_q;        // [B + 1]
+  const int* ctx_len;     // [B]
+  const int* block_table; // [B, max_blocks]
+  int* error;
+  int max_blocks, page, nq, nkv, window, total_slots;
+  float scale_log2;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+// K-major operand, 128-byte swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+  return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major operand (V as [key][dim]), 128-byte swizzle: rows of 64 dims (128 B), 8-key groups
+// 1024 bytes apart (stride offset), the second 64 dims `lbo` bytes further (leading offset).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t lbo) {
+  return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// idesc: float32 accumulate, bfloat16 operands, A K-major; B K-major or MN-major.
+__host__ __device__ constexpr uint32_t idesc(int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(BM >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                   const __grid_constant__ CUtensorMap map_k,
+                                                                   const __grid_constant__ CUtensorMap map_v,
+                                                                   const Params p) {
+  // Tensor memory is taken only after the kernels ahead are done, and the kernel behind may
+  // start only after every CTA of this one has its tensor memory: no CTA ever holds tensor
+  // memory while it waits for a kernel whose CTAs still need some.
+  ts_pdl_wait();
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t q_full, kv_full[STAGES], s_done, pv_done;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+  __shared__ int table_s[MAX_TABLE];
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int b = blockIdx.z, hk = blockIdx.y;
+  const int G = p.nq / p.nkv;
+  const int q_begin = p.cu_q[b];
+  const int q_len = p.cu_q[b + 1] - q_begin;
+  const int ctx = p.ctx_len[b];
+  const int start_pos = ctx - q_len;
+  const int rows_total = q_len * G;
+  const int seq_tiles = (rows_total + BM - 1) / BM;
+  const int row_tile = seq_tiles - 1 - (int)blockIdx.x;  // the tiles with the most keys first
+  if (q_len <= 0 || row_tile < 0) return;
+  const int r0 = row_tile * BM;
+
+  const int last_row = min(r0 + BM, rows_total) - 1;
+  const int hi = start_pos + last_row / G;          // last key any row of the tile sees
+  const int first_pos = start_pos + r0 / G;         // position of the tile's first row
+  const int lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+  const int kb0 = lo / BN, kb1 = hi / BN;
+  const int nblocks = kb1 - kb0 + 1;
+  const int box_rows = min(p.page, BN);  // keys per copy: a whole page, or 64 keys of a larger one
+  const int copies_per_block = BN / box_rows;
+
+  if (tid == 0) {
+    abort_s = 0;
+    mbar_init(smem_u32(&q_full), 1);
+    for (int s = 0; s < STAGES; ++s) mbar_init(smem_u32(&kv_full[s]), 1);
+    mbar_init(smem_u32(&s_done), 1);
+    mbar_init(smem_u32(&pv_done), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  // The block-table entries of the keys this tile walks, once, into shared memory.
+  const int first_entry = (kb0 * BN) / p.page;
+  {
+    const int n_entries = min(hi / p.page - first_entry + 1, MAX_TABLE);
+    const int* table = p.block_table + (size_t)b * p.max_blocks;
+    for (int i = tid; i < n_entries; i += 128) {
+      const int e = first_entry + i;
+      table_s[i] = e < p.max_blocks ? table[e] : -1;
+    }
+  }
+  if (warp == 0) {
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  ts_pdl_launch_dependents();
+  const uint32_t tmem_base = tmem_base_s;
+  volatile int* abort_flag = &abort_s;
+  const uint32_t sm = smem_u32(smem);
+
+  // One thread feeds the copy engine and the tensor core.
+  auto load_kv = [&](int blk) {  // keys of block kb0 + blk into stage blk % 2
+    const int stage = blk & 1;
+    const uint32_t bar = smem_u32(&kv_full[stage]);
+    mbar_expect_tx(bar, 2 * KV_STAGE);
+    for (int c = 0; c < copies_per_block; ++c) {
+      const int key0 = (kb0 + blk) * BN + c * box_rows;  // the first key of this copy
+      const int e = key0 / p.page;
+      int page_id = -1;
+      if (key0 <= hi && e < p.max_blocks)
+        page_id = e - first_entry < MAX_TABLE ? table_s[e - first_entry] : p.block_table[(size_t)b * p.max_blocks + e];
+      // a page that is not held is read from beyond the tensor's end: the copy engine fills zeros
+      const int slot = page_id >= 0 ? page_id * p.page + key0 % p.page : p.total_slots;
+      const uint32_t row_off = (uint32_t)(c * box_rows) * 128u;
+      for (int half = 0; half < 2; ++half) {
+        tma_load_3d(sm + OFF_K + stage * KV_STAGE + half * KV_HALF + row_off, &map_k, bar, half * 64, hk, slot);
+        tma_load_3d(sm + OFF_V + stage * KV_STAGE + half * KV_HALF + row_off, &map_v, bar, half * 64, hk, slot);
+      }
+    }
+  };
+  auto issue_s = [&](int blk) {  // S = Q K^T of block blk
+    const int stage = blk & 1;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const uint32_t half = ks >> 2, inner = (ks & 3) * 32;
+      umma_bf16(tmem_base + TMEM_S, desc_k_major(sm + OFF_Q + half * (BM * 128) + inner),
+                desc_k_major(sm + OFF_K + stage * KV_STAGE + half * KV_HALF + inner), idesc(BN, false), ks > 0 ? 1u : 0u);
+    }
+    umma_commit(smem_u32(&s_done));
+  };
+
+  if (tid == 0) {
+    mbar_expect_tx(smem_u32(&q_full), Q_BYTES);
+    for (int half = 0; half < 2; ++half)
+      tma_load_4d(sm + OFF_Q + half * (BM * 128), &map_q, smem_u32(&q_full), half * 64, 0, hk, q_begin + r0 / G);
+    load_kv(0);
+    if (nblocks > 1) load_kv(1);
+    bool ok = mbar_wait(smem_u32(&q_full), 0, abort_flag) && mbar_wait(smem_u32(&kv_full[0]), 0, abort_flag);
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      issue_s(0);
+    }
+  }
+
+  // Row state of this thread.
+  const int r = r0 + tid;
+  const int row_pos = r < rows_total ? start_pos + r / G : -1;
+  const int row_lo = (p.window > 0 && row_pos >= 0) ? max(0, row_pos - p.window + 1) : 0;
+  float o[D];
+#pragma unroll
+  for (int i = 0; i < D; ++i) o[i] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+  const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+
+  // A wait that gives up raises abort_s; the CTA leaves the loop together at the next barrier.
+
+  for (int blk = 0; blk < nblocks; ++blk) {
+    const int stage = blk & 1;
+    const int kbase = (kb0 + blk) * BN;
+    mbar_wait(smem_u32(&s_done), (uint32_t)blk & 1, abort_flag);
+    __syncwarp();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    unsigned char* p_row = smem + OFF_K + stage * KV_STAGE + tid * 128;
+
+    // scores of this row
+    float s[BN];
+#pragma unroll
+    for (int c = 0; c < BN / 16; ++c) {
+      uint32_t v[16];
+      tmem_ld16(lane_addr + TMEM_S + c * 16, v);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) s[c * 16 + i] = __uint_as_float(v[i]);
+    }
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+
+    const bool unmasked = (kbase + BN - 1 <= first_pos) && (r0 + BM <= rows_total) &&
+                          (p.window <= 0 || kbase >= start_pos + (r0 + BM - 1) / G - p.window + 1);
+    float m_new = m_run;
+    if (unmasked) {
+#pragma unroll
+      for (int j = 0; j < BN; ++j) m_new = fmaxf(m_new, s[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < BN; ++j) {
+        const int key = kbase + j;
+        s[j] = (key <= row_pos && key >= row_lo) ? s[j] : -INFINITY;
+        m_new = fmaxf(m_new, s[j]);
+      }
+    }
+    const float m_off = m_new == -INFINITY ? 0.f : m_new * p.scale_log2;
+    const float corr = fast_exp2(m_run * p.scale_log2 - m_off);
+    m_run = m_new;
+    float l_add = 0.f;
+    uint32_t packed[BN / 2];
+#pragma unroll
+    for (int j = 0; j < BN; j += 2) {
+      const float p0 = fast_exp2(fmaf(s[j], p.scale_log2, -m_off));
+      const float p1 = fast_exp2(fmaf(s[j + 1], p.scale_log2, -m_off));
+      l_add += p0 + p1;
+      packed[j >> 1] = pack_bf16(p0, p1);
+    }
+    l_run = l_run * corr + l_add;
+    // P row into shared memory, 16-byte chunk c at position c ^ (row % 8): the 128-byte swizzle
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint4 chunk = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+      *reinterpret_cast<uint4*>(p_row + ((c ^ (tid & 7)) << 4)) = chunk;
+    }
+    // The last block of a sequence may hold rows of V that no request has written: make them
+    // zeros (a masked key's weight is zero, but zero times garbage must stay zero).
+    if (kbase + BN - 1 > hi) {
+      mbar_wait(smem_u32(&kv_full[stage]), (uint32_t)(blk >> 1) & 1, abort_flag);
+      const int first_bad = hi - kbase + 1;  // 1..63
+      for (int i = tid; i < (BN - first_bad) * 16; i += 128) {
+        const int row = first_bad + i / 16, piece = i % 16;  // 16 pieces of 16 bytes: both halves of the head
+        *reinterpret_cast<uint4*>(smem + OFF_V + stage * KV_STAGE + (piece >> 3) * KV_HALF + row * 128 + ((piece & 7) << 4)) =
+            make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    if (__syncthreads_or(abort_s)) break;
+
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      bool ok = mbar_wait(smem_u32(&kv_full[stage]), (uint32_t)(blk >> 1) & 1, abort_flag);
+      if (ok) {
+        // O_blk = P V: V is read in its natural [key][dim] order as an MN-major operand
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          umma_bf16(tmem_base + TMEM_O, desc_k_major(sm + OFF_K + stage * KV_STAGE + kk * 32),
+                    desc_mn_major(sm + OFF_V + stage * KV_STAGE + kk * 2048, KV_HALF), idesc(D, true), kk > 0 ? 1u : 0u);
+        umma_commit(smem_u32(&pv_done));
+        // the next block's scores can be computed while the rows are folded into O
+        if (blk + 1 < nblocks && mbar_wait(smem_u32(&kv_full[stage ^ 1]), (uint32_t)((blk + 1) >> 1) & 1, abort_flag)) {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_s(blk + 1);
+        }
+      }
+    }
+    __syncwarp();
+
+    const bool pv_ok = mbar_wait(smem_u32(&pv_done), (uint32_t)blk & 1, abort_flag);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // this stage is free now: fetch the block after next into it
+    if (tid == 0 && pv_ok && blk + 2 < nblocks) load_kv(blk + 2);
+    __syncwarp();
+#pragma unroll
+    for (int c = 0; c < D / 16; ++c) {
+      uint32_t v[16];
+      tmem_ld16(lane_addr + TMEM_O + c * 16, v);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+      for (int i = 0; i < 16; ++i) o[c * 16 + i] = fmaf(o[c * 16 + i], corr, __uint_as_float(v[i]));
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
+
+  __syncthreads();
+  if (abort_s == 0 && r < rows_total) {
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    __nv_bfloat16* dst = p.out + ((size_t)(q_begin + r / G) * p.nq + hk * G + r % G) * D;
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c) {
+      uint4 chunk;
+      chunk.x = pack_bf16(o[8 * c] * inv, o[8 * c + 1] * inv);
+      chunk.y = pack_bf16(o[8 * c + 2] * inv, o[8 * c + 3] * inv);
+      chunk.z = pack_bf16(o[8 * c + 4] * inv, o[8 * c + 5] * inv);
+      chunk.w = pack_bf16(o[8 * c + 6] * inv, o[8 * c + 7] * inv);
+      *reinterpret_cast<uint4*>(dst + 8 * c) = chunk;
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (abort_s != 0 && tid == 0) *p.error = 1;
+  if (warp == 0) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  long long a, b, c;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && a == o.a && b == o.b && c == o.c; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.ptr) * 1000003u ^ std::hash<long long>()(k.a * 131 + k.b * 31 + k.c);
+  }
+};
+std::mutex map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> map_cache;
+
+// K or V pool [slots, nkv, D] as a 3-d tensor {D, nkv, slots}; boxes of {64, 1, page}.
+int cache_map(const void* ptr, long long slots, int nkv, int page, CUtensorMap* out) {
+  MapKey key{ptr, slots, nkv, page};
+  std::lock_guard<std::mutex> lock(map_mutex);
+  auto it = map_cache.find(key);
+  if (it != map_cache.end()) {
+    *out = it->second;
+    return 0;
+  }
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return TS_ERR_UNSUPPORTED_SIZE;
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)nkv, (cuuint64_t)slots};
+  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)nkv * D * 2};
+  cuuint32_t box[3] = {64, 1, (cuuint32_t)(page < BN ? page : BN)};
+  cuuint32_t estr[3] = {1, 1, 1};
+  if (fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return TS_ERR_BAD_ARGUMENT;
+  if (map_cache.size() > 4096) map_cache.clear();
+  map_cache.emplace(key, *out);
+  return 0;
+}
+
+// q [T, nq, D] as a 4-d tensor {D, G, nkv, T}; boxes of {64, G, 1, 128 / G}: the rows of a box
+// come out ordered (token, head of the group), which is the tile's row order.
+int query_map(const void* ptr, long long T, int nq, int nkv, CUtensorMap* out) {
+  MapKey key{ptr, T, nq, -(long long)nkv};
+  std::lock_guard<std::mutex> lock(map_mutex);
+  auto it = map_cache.find(key);
+  if (it != map_cache.end()) {
+    *out = it->second;
+    return 0;
+  }
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return TS_ERR_UNSUPPORTED_SIZE;
+  const int G = nq / nkv;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)G, (cuuint64_t)nkv, (cuuint64_t)T};
+  cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)G * D * 2, (cuuint64_t)nq * D * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)G, 1, (cuuint32_t)(BM / G)};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return TS_ERR_BAD_ARGUMENT;
+  if (map_cache.size() > 4096) map_cache.clear();
+  map_cache.emplace(key, *out);
+  return 0;
+}
+
+}  // namespace
+
+// Whether this kernel takes the sizes (the caller uses the mma.sync kernel otherwise).
+TS_EXPORT int ts_attention_tcgen05_supported(int nq, int nkv, int page) {
+  if (nq <= 0 || nkv <= 0 || nq % nkv) return 0;
+  const int G = nq / nkv;
+  if (G > BM || BM % G) return 0;
+  if (page < 8 || (BN % page && page % BN)) return 0;
+  return 1;
+}
+
+// q/out [T, nq, 128] bf16; caches [pages, page, nkv, 128] bf16 (`total_slots` = pages * page);
+// cu_q [B+1]; ctx_len [B]; block_table [B, max_blocks]; max_q: the most tokens of any sequence.
+// `error`: one int the kernel sets to 1 if one of its waits gave up.
+TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, const void* vcache, void* out,
+                                           const int* cu_q, const int* ctx_len, const int* block_table,
+                                           int max_blocks, int page, long long total_slots, int T, int B, int max_q,
+                                           int nq, int nkv, float scale, int window, int* error, void* stream_) {
+  if (T <= 0 || B <= 0) return 0;
+  if (!ts_attention_tcgen05_supported(nq, nkv, page) || max_blocks <= 0 || max_q <= 0 || error == nullptr)
+    return TS_ERR_BAD_ARGUMENT;
+  if (nkv > 65535 || B > 65535 || total_slots > 0x7fffffffLL - page) return TS_ERR_UNSUPPORTED_SIZE;
+  if (((uintptr_t)q | (uintptr_t)kcache | (uintptr_t)vcache | (uintptr_t)out) % 16) return TS_ERR_UNSUPPORTED_SIZE;
+  CUtensorMap mq, mk, mv;
+  int st = query_map(q, T, nq, nkv, &mq);
+  if (st) return st;
+  st = cache_map(kcache, total_slots, nkv, page, &mk);
+  if (st) return st;
+  st = cache_map(vcache, total_slots, nkv, page, &mv);
+  if (st) return st;
+  Params p;
+  p.out = (__nv_bfloat16*)out;
+  p.cu_q = cu_q;
+  p.ctx_len = ctx_len;
+  p.block_table = block_table;
+  p.error = error;
+  p.max_blocks = max_blocks;
+  p.page = page;
+  p.nq = nq;
+  p.nkv = nkv;
+  p.window = window;
+  p.total_slots = (int)total_slots;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const int G = nq / nkv;
+  const int row_tiles = (int)(((long long)max_q * G + BM - 1) / BM);
+  const size_t smem = SMEM_TILES + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  return ts_launch(attention_tcgen05_kernel, dim3(row_tiles, nkv, B), dim3(128), smem, (cudaStream_t)stream_, mq, mk, mv, p);
+}

@@ -492,6 +492,86 @@ def attention_scratch_floats(rows: int, splits: int, head_dim: int) -> int:
 
 
 # ---------------------------------------------------------------------------
+# prompt attention on tcgen05 tensor cores (head size 128)
+
+ATTENTION_TCGEN05_HEAD_DIM = 128
+_attention_tcgen05 = None
+_USE_ATTENTION_TCGEN05 = _os.environ.get("TS_ATTENTION_TCGEN05", "1") != "0"
+
+
+def _attention_tcgen05_fns():
+    global _attention_tcgen05
+    if _attention_tcgen05 is None:
+        lib = _build.load_variant("attention_tcgen05", {"TS_HEAD_DIM": ATTENTION_TCGEN05_HEAD_DIM})
+        run = lib.ts_attention_prefill_tcgen05
+        run.argtypes = [_c_void_p] * 7 + [_c_int, _c_int, _c_ll] + [_c_int] * 5 + [_c_float, _c_int, _c_void_p, _c_void_p]
+        run.restype = _c_int
+        ok = lib.ts_attention_tcgen05_supported
+        ok.argtypes = [_c_int, _c_int, _c_int]
+        ok.restype = _c_int
+        _attention_tcgen05 = (run, ok)
+    return _attention_tcgen05
+
+
+def attention_tcgen05_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Whether the tcgen05 prompt-attention kernel takes these sizes: head size 128, a group
+    size that divides 128, a page size of at least 8 that divides 64 or is a multiple of it."""
+    if not _USE_ATTENTION_TCGEN05 or head_dim != ATTENTION_TCGEN05_HEAD_DIM:
+        return False
+    if num_kv_heads <= 0 or num_heads % num_kv_heads or 128 % (num_heads // num_kv_heads):
+        return False
+    return page_size >= 8 and (64 % page_size == 0 or page_size % 64 == 0)
+
+
+def attention_prefill_tcgen05(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    out: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    context_lens: torch.Tensor,
+    block_table: torch.Tensor,
+    page_size: int,
+    num_seqs: int,
+    max_seqlen_q: int,
+    num_heads: int,
+    num_kv_heads: int,
+    scale: float,
+    window: int = 0,
+) -> None:
+    """Causal attention of prompt portions over the paged cache, tcgen05 tensor cores, head size 128.
+
+    Same arguments and meaning as attention_paged_mma (without seq_index, which it does not need).
+    """
+    run, ok = _attention_tcgen05_fns()
+    d = ATTENTION_TCGEN05_HEAD_DIM
+    for name, t in (("q", q), ("k_cache", k_cache), ("v_cache", v_cache), ("out", out)):
+        _cuda_contig(name, t, torch.bfloat16)
+    for name, t in (("cu_seqlens_q", cu_seqlens_q), ("context_lens", context_lens), ("block_table", block_table)):
+        _cuda_contig(name, t, torch.int32)
+    T = q.shape[0]
+    nq, nkv = num_heads, num_kv_heads
+    if not ok(nq, nkv, page_size):
+        raise KernelError(
+            f"attention_prefill_tcgen05: needs a group size that divides 128 and a page size of at least 8 that divides 64 or is a multiple of it; "
+            f"got {nq} query heads, {nkv} key/value heads, pages of {page_size}")
+    if q.numel() != T * nq * d or out.numel() != T * nq * d:
+        raise KernelError("attention_prefill_tcgen05: q/out do not match [T, heads*128]")
+    if tuple(k_cache.shape[-3:]) != (page_size, nkv, d) or k_cache.shape != v_cache.shape:
+        raise KernelError(f"attention_prefill_tcgen05: caches must be [pages,{page_size},{nkv},{d}], got {tuple(k_cache.shape)} and {tuple(v_cache.shape)}")
+    if block_table.dim() != 2 or block_table.shape[0] < num_seqs:
+        raise KernelError("attention_prefill_tcgen05: block_table must be [B,max_blocks]")
+    if cu_seqlens_q.numel() < num_seqs + 1 or context_lens.numel() < num_seqs:
+        raise KernelError("attention_prefill_tcgen05: cu_seqlens_q/context_lens are shorter than the batch")
+    _, error = _gemm_workspace(q.device)
+    _check("attention_prefill_tcgen05", run(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+        cu_seqlens_q.data_ptr(), context_lens.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], page_size, k_cache.shape[0] * page_size, T, num_seqs, max_seqlen_q, nq, nkv,
+        float(scale), int(window), error.data_ptr(), _stream()))
+
+
+# ---------------------------------------------------------------------------
 # skinny GEMM on tcgen05 tensor cores (decode steps)
 
 GEMM_SKINNY_MAX_ROWS = 128
@@ -560,4 +640,4 @@ def check_device_errors() -> None:
     for (dev, _), (_, error) in _gemm_workspaces.items():
         if int(error[0]) != 0:
             error[0] = 0
-            raise KernelError(f"gemm_skinny_bf16 on cuda:{dev}: a wait on an mbarrier gave up (the kernel returned early)")
+            raise KernelError(f"a tcgen05 kernel on cuda:{dev} (skinny GEMM or prompt attention): a wait on an mbarrier gave up (the kernel returned early)")

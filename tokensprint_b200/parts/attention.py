@@ -144,6 +144,12 @@ class AttentionMixer(Mixer):
                 if splits > 1:
                     scratch = torch.empty(ops.attention_scratch_floats(q.shape[0] * nq, splits, d),
                                           device=q.device, dtype=torch.float32)
+            elif ops.attention_tcgen05_supported(nq, nkv, d, step.page_size):
+                # prompt portions: the tcgen05 kernel, where it takes the sizes
+                ops.attention_prefill_tcgen05(
+                    q, cache.k_pages, cache.v_pages, out, step.cu_seqlens_q, step.context_lens, tables.block_table,
+                    step.page_size, step.num_seqs, step.max_seqlen_q, nq, nkv, self.scale, self.window)
+                return
             ops.attention_paged_mma(
                 q, cache.k_pages, cache.v_pages, out, step.cu_seqlens_q, step.context_lens, tables.block_table,
                 step.seq_index, step.page_size, step.num_seqs, step.max_seqlen_q, nq, nkv, d, self.scale,
