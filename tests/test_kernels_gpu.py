@@ -345,13 +345,13 @@ def test_attention_ignores_pages_that_are_not_held():
 # prompt attention on tcgen05 (head size 128)
 
 
-def run_tcgen05(case, window=0):
+def run_tcgen05(case, window=0, mode=0):
     from tokensprint_b200 import ops
 
     out = torch.full_like(case["q"], float("nan"))
     max_q = max(ql for ql, _ in case["seqs"])
     ops.attention_prefill_tcgen05(case["q"], case["kc"], case["vc"], out, case["cu"], case["ctxs"], case["table"],
-                                  case["page"], case["B"], max_q, case["nq"], case["nkv"], case["d"] ** -0.5, window)
+                                  case["page"], case["B"], max_q, case["nq"], case["nkv"], case["d"] ** -0.5, window, mode)
     torch.cuda.synchronize()
     ops.check_device_errors()
     return out
@@ -365,14 +365,15 @@ PROMPTS = [(1, 1), (1, 77), (5, 5), (3, 130), (64, 64), (37, 200), (2, 65), (1, 
     [(32, 8, 16, 0), (4, 4, 16, 0), (8, 1, 8, 0), (16, 1, 64, 0), (2, 1, 32, 0), (6, 3, 16, 0), (128, 1, 16, 0),
      (32, 8, 16, 100), (8, 2, 32, 7), (4, 1, 8, 64), (3, 3, 16, 300), (32, 8, 256, 0), (8, 2, 128, 90), (4, 1, 192, 0)],
 )
-def test_attention_tcgen05_mixed(nq, nkv, page, window):
+@pytest.mark.parametrize("mode", [1, 2])
+def test_attention_tcgen05_mixed(nq, nkv, page, window, mode):
     """Prompt portions and single tokens of many lengths in one launch, every group size that
     divides 128, pages of 8 to 256 slots in shuffled order, NaN in every slot nobody wrote."""
     case = finish_case(paged_case(PROMPTS, nq, nkv, 128, page, torch.bfloat16, seed=nq + page))
-    got = run_tcgen05(case, window)
+    got = run_tcgen05(case, window, mode)
     want = plain_attention(case, window)
     assert rel_err(got, want) < 1e-2
-    assert torch.equal(run_tcgen05(case, window), got)
+    assert torch.equal(run_tcgen05(case, window, mode), got)
 
 
 def test_attention_tcgen05_says_what_it_takes():
@@ -388,8 +389,9 @@ def test_attention_tcgen05_says_what_it_takes():
         run_tcgen05(case)
 
 
+@pytest.mark.parametrize("mode", [1, 2])
 @pytest.mark.parametrize("target", ["first", "far", "page_edge_before", "page_edge_after", "block_edge", "own", "window_first", "window_out"])
-def test_attention_tcgen05_finds_one_key_that_stands_out(target):
+def test_attention_tcgen05_finds_one_key_that_stands_out(target, mode):
     """As for the other kernels, with a prompt portion: the query is token 650 of 700 and the
     portion holds the last 100 tokens."""
     nq, nkv, d, page, ctx, ql = 8, 2, 128, 16, 700, 100
@@ -407,7 +409,7 @@ def test_attention_tcgen05_finds_one_key_that_stands_out(target):
     k[where, 1] = q[qi, 6] * 3.0  # head 6 (KV head 1) of that token finds itself at `where`
     v[where, 1] = 10.0
     case = finish_case(case)
-    got = run_tcgen05(case, window)
+    got = run_tcgen05(case, window, mode)
     row = got.view(-1, nq, d)[7 + qi, 6].float()
     if target == "window_out":
         assert float(row.abs().max()) < 5.0, "a key outside the window was seen"
@@ -427,7 +429,8 @@ def test_attention_tcgen05_ignores_pages_that_are_not_held():
             case["kc"][pg] = float("nan")
             case["vc"][pg] = float("nan")
             case["table"][b, i] = -1
-    assert rel_err(run_tcgen05(case, window), want) < 1e-2
+    for mode in (1, 2):
+        assert rel_err(run_tcgen05(case, window, mode), want) < 1e-2
 
 
 # ---------------------------------------------------------------------------

@@ -66,7 +66,15 @@ struct Params {
   int* error;
   int max_blocks, page, nq, nkv, window, total_slots;
   float scale_log2;
+  long long* probe;  // TS_ATT_PROBE builds: clock stamps of CTA 0's first softmax warp and of its MMA thread
 };
+
+#ifdef TS_ATT_PROBE
+#define PROBE(slot, blk, k) \
+  do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && p.probe && (blk) < 64) p.probe[((slot) * 64 + (blk)) * 8 + (k)] = clock64(); } while (0)
+#else
+#define PROBE(slot, blk, k) do { } while (0)
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -115,6 +123,46 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// the same with the accumulate flag known when compiling: D = A B, and D += A B
+__device__ __forceinline__ void umma_bf16_first(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_more(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
+}
+// A (here P, [128 rows x 16 keys], two bfloat16 per column) from tensor memory
+__device__ __forceinline__ void umma_bf16_tmem_a_first(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_tmem_a_more(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc) : "memory");
+}
+// one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+  uint32_t chosen;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(chosen));
+  return chosen != 0;
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -394,6 +442,420 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
 }
 
 // ---------------------------------------------------------------------------
+// Two tiles per CTA, roles in warps of their own (long prompt portions).
+//
+// A CTA owns 256 consecutive rows as two tiles of 128 and walks the keys once for both.
+//   warps 0-3, 4-7  softmax of tile 0 and of tile 1: thread r of a group owns row r;
+//   warp 8          one thread: TMA loads (Q once, then K and V blocks into rings of 3 stages);
+//   warp 9          one thread: every tcgen05.mma.
+// S has two buffers per tile in tensor memory, so S of block j+1 is computed while the threads
+// work on block j; O stays in tensor memory and P V accumulates into it.  The running max of a
+// row is only raised when the new max exceeds it by more than 2^8 (the weights then stay below
+// 2^8, well inside bfloat16 and float32 range, and the final division by the row sum, taken
+// with the same max, cancels it); only then is the row of O rescaled in tensor memory.
+// Synchronisation is by mbarriers alone; every wait is bounded.
+
+constexpr int KV_RING = 4;
+constexpr uint32_t P2_OFF_Q = 0;                                   // 2 tiles x 32 KB
+constexpr uint32_t P2_OFF_K = P2_OFF_Q + 2 * Q_BYTES;
+constexpr uint32_t P2_OFF_V = P2_OFF_K + KV_RING * KV_STAGE;
+constexpr uint32_t P2_SMEM = P2_OFF_V + KV_RING * KV_STAGE;        // 196,608 bytes
+constexpr uint32_t P2_TMEM_COLS = 512;
+// columns: S[tile][buffer] at tile * 128 + buffer * 64; O[tile] at 256 + tile * 128.  P of a
+// block (bfloat16, two keys per column) takes the first 32 columns of the S buffer it came from.
+constexpr float RESCALE_THRESHOLD = 8.f;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+__global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                        const __grid_constant__ CUtensorMap map_k,
+                                                                        const __grid_constant__ CUtensorMap map_v,
+                                                                        const Params p) {
+  ts_pdl_wait();  // see the other kernel: tensor memory is never held while waiting for another kernel
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t q_full, k_full[KV_RING], k_empty[KV_RING], v_full[KV_RING], v_empty[KV_RING];
+  __shared__ __align__(8) uint64_t s_done[2][2], p_ready[2], pv_done[2], all_done;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+  __shared__ int table_s[MAX_TABLE];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.z, hk = blockIdx.y;
+  const int G = p.nq / p.nkv;
+  const int q_begin = p.cu_q[b];
+  const int q_len = p.cu_q[b + 1] - q_begin;
+  const int ctx = p.ctx_len[b];
+  const int start_pos = ctx - q_len;
+  const int rows_total = q_len * G;
+  const int seq_pairs = (rows_total + 2 * BM - 1) / (2 * BM);
+  const int pair = seq_pairs - 1 - (int)blockIdx.x;  // the pairs with the most keys first
+  if (q_len <= 0 || pair < 0) return;
+  const int r0 = pair * 2 * BM;
+  const int ntiles = rows_total - r0 > BM ? 2 : 1;
+
+  // per tile: the last key any of its rows sees, and how many key blocks it walks
+  const int first_pos = start_pos + r0 / G;
+  const int lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+  const int kb0 = lo / BN;
+  int hi_t[2], n_t[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int last_row = min(r0 + (t + 1) * BM, rows_total) - 1;
+    hi_t[t] = start_pos + last_row / G;
+    n_t[t] = t < ntiles ? hi_t[t] / BN - kb0 + 1 : 0;
+  }
+  const int hi = hi_t[ntiles - 1];
+  const int nblocks = n_t[ntiles - 1];
+  const int box_rows = min(p.page, BN);
+  const int copies_per_block = BN / box_rows;
+
+  if (tid == 0) {
+    abort_s = 0;
+    mbar_init(smem_u32(&q_full), 1);
+    mbar_init(smem_u32(&all_done), 1);
+    for (int s = 0; s < KV_RING; ++s) {
+      mbar_init(smem_u32(&k_full[s]), 1);
+      mbar_init(smem_u32(&k_empty[s]), 1);
+      mbar_init(smem_u32(&v_full[s]), 1);
+      mbar_init(smem_u32(&v_empty[s]), 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(smem_u32(&s_done[t][i]), 1);
+      }
+      mbar_init(smem_u32(&p_ready[t]), 4);  // one arrival per softmax warp
+      mbar_init(smem_u32(&pv_done[t]), 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  const int first_entry = (kb0 * BN) / p.page;
+  {
+    const int n_entries = min(hi / p.page - first_entry + 1, MAX_TABLE);
+    const int* table = p.block_table + (size_t)b * p.max_blocks;
+    for (int i = tid; i < n_entries; i += blockDim.x) {
+      const int e = first_entry + i;
+      table_s[i] = e < p.max_blocks ? table[e] : -1;
+    }
+  }
+  if (warp == 0) {
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(P2_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  ts_pdl_launch_dependents();
+  const uint32_t tmem_base = tmem_base_s;
+  volatile int* abort_flag = &abort_s;
+  const uint32_t sm = smem_u32(smem);
+
+  if (warp == 8) {
+    // ---------------- copies: lane 0 announces the bytes, lanes 0..2*copies-1 each ask for one box ----------------
+    if (lane == 0) {
+      mbar_expect_tx(smem_u32(&q_full), (uint32_t)ntiles * Q_BYTES);
+      for (int t = 0; t < ntiles; ++t)
+        for (int half = 0; half < 2; ++half)
+          tma_load_4d(sm + P2_OFF_Q + t * Q_BYTES + half * (BM * 128), &map_q, smem_u32(&q_full), half * 64, 0, hk,
+                      q_begin + (r0 + t * BM) / G);
+    }
+    const int c = lane >> 1, half = lane & 1;  // this lane's copy within a block, and its half of the head
+    const bool copies = c < copies_per_block;
+    const uint32_t lane_off = (uint32_t)half * KV_HALF + (uint32_t)(c * box_rows) * 128u;
+    int issued[2] = {0, 0};  // K and V blocks asked for
+    bool ok = true;
+    for (int blk = 0; ok && blk < nblocks; ++blk) {
+      const int st = blk % KV_RING;
+      const uint32_t use = (uint32_t)(blk / KV_RING);
+      // where this lane's box starts in the cache
+      int slot = p.total_slots;  // beyond the end: the copy engine fills zeros (a page that is not held)
+      if (copies) {
+        const int key0 = (kb0 + blk) * BN + c * box_rows;
+        const int e = p.page < BN ? (kb0 + blk) * copies_per_block + c : key0 / p.page;
+        if (key0 <= hi && e < p.max_blocks) {
+          const int page_id = e - first_entry < MAX_TABLE ? table_s[e - first_entry] : p.block_table[(size_t)b * p.max_blocks + e];
+          if (page_id >= 0) slot = page_id * p.page + (key0 - e * p.page);
+        }
+      }
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {  // K first: S needs it first
+        const uint32_t full = smem_u32(which == 0 ? &k_full[st] : &v_full[st]);
+        const uint32_t empty = smem_u32(which == 0 ? &k_empty[st] : &v_empty[st]);
+        if (blk >= KV_RING) ok = mbar_wait(empty, (use - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane == 0) mbar_expect_tx(full, KV_STAGE);
+        __syncwarp();
+        if (copies)
+          tma_load_3d(sm + (which == 0 ? P2_OFF_K : P2_OFF_V) + st * KV_STAGE + lane_off, which == 0 ? &map_k : &map_v, full,
+                      half * 64, hk, slot);
+        issued[which] = blk + 1;
+      }
+    }
+    if (*abort_flag) {
+      // leave nothing in flight: wait (bounded, on a count of its own) for the copies already asked for
+      int patience = 0;
+      volatile int* own = &patience;
+      for (int which = 0; which < 2; ++which)
+        for (int blk = max(0, issued[which] - KV_RING); blk < issued[which]; ++blk)
+          mbar_wait(smem_u32(which == 0 ? &k_full[blk % KV_RING] : &v_full[blk % KV_RING]), (uint32_t)(blk / KV_RING) & 1, own);
+    }
+  } else if (warp == 9) {
+    // ---------------- tensor core: the warp runs together, one elected lane issues ----------------
+    {
+      // descriptors differ only in their address field (bytes / 16): prepared once, offsets added per instruction
+      const uint64_t q_desc = desc_k_major(sm + P2_OFF_Q), k_desc = desc_k_major(sm + P2_OFF_K);
+      const uint64_t v_desc = desc_mn_major(sm + P2_OFF_V, KV_HALF);
+      bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&q_full), 0, abort_flag));
+      for (int blk = 0; ok && blk <= nblocks; ++blk) {
+        if (blk < nblocks) {
+          const int st = blk % KV_RING;
+          if (lane == 0) PROBE(1, blk, 0);
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&k_full[st]), (uint32_t)(blk / KV_RING) & 1, abort_flag));
+          if (lane == 0) PROBE(1, blk, 1);
+          for (int t = ntiles - 1; ok && t >= 0; --t) {
+            if (blk >= n_t[t]) continue;
+            // This S buffer held S and then P of block blk - 2; P V of that block was issued before
+            // this point, and the tensor core runs what one thread issues in order.
+            const int buf = blk & 1;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t qd = q_desc + (uint64_t)((t * Q_BYTES) >> 4), kd = k_desc + (uint64_t)((st * KV_STAGE) >> 4);
+            const uint32_t s_addr = tmem_base + t * 128 + buf * 64;
+            if (elect_one()) {
+#pragma unroll
+              for (int ks = 0; ks < D / 16; ++ks) {
+                const uint32_t half = ks >> 2, inner = (ks & 3) * 32;
+                if (ks == 0)
+                  umma_bf16_first(s_addr, qd, kd, idesc(BN, false));
+                else
+                  umma_bf16_more(s_addr, qd + ((half * (BM * 128) + inner) >> 4), kd + ((half * KV_HALF + inner) >> 4), idesc(BN, false));
+              }
+              umma_commit(smem_u32(&s_done[t][buf]));
+            }
+            __syncwarp();
+          }
+          if (ok && elect_one()) umma_commit(smem_u32(&k_empty[st]));
+          __syncwarp();
+          if (lane == 0) PROBE(1, blk, 2);
+        }
+        if (blk >= 1 && ok) {
+          const int j = blk - 1;
+          const int st = j % KV_RING;
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&v_full[st]), (uint32_t)(j / KV_RING) & 1, abort_flag));
+          // the last tile first: in the last block its threads also clear the rows of V beyond the last key
+          for (int t = ntiles - 1; ok && t >= 0; --t) {
+            if (j >= n_t[t]) continue;
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&p_ready[t]), (uint32_t)j & 1, abort_flag));
+            if (lane == 0) PROBE(1, blk, 3 + t);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t vd = v_desc + (uint64_t)((st * KV_STAGE) >> 4);
+            const uint32_t o_addr = tmem_base + 256 + t * 128;
+            const uint32_t p_addr = tmem_base + t * 128 + (j & 1) * 64;  // 16 keys of P: 8 columns
+            if (elect_one()) {
+              if (j == 0)
+                umma_bf16_tmem_a_first(o_addr, p_addr, vd, idesc(D, true));
+              else
+                umma_bf16_tmem_a_more(o_addr, p_addr, vd, idesc(D, true));
+#pragma unroll
+              for (int kk = 1; kk < BN / 16; ++kk) umma_bf16_tmem_a_more(o_addr, p_addr + kk * 8, vd + ((kk * 2048) >> 4), idesc(D, true));
+              umma_commit(smem_u32(&pv_done[t]));
+            }
+            __syncwarp();
+          }
+          if (ok && elect_one()) umma_commit(smem_u32(&v_empty[st]));
+          __syncwarp();
+          if (lane == 0) PROBE(1, blk, 5);
+        }
+      }
+      // Everything this CTA asked of the tensor core is done when this arrives, the arrivals of
+      // the commits above included: nobody leaves before (an arrival after the CTA's end would
+      // land in the barriers of the next CTA on this SM).
+      if (elect_one()) umma_commit(smem_u32(&all_done));
+      __syncwarp();
+    }
+  } else if (warp < 4 * ntiles) {
+    // ---------------- softmax: thread `row` of tile t owns one row ----------------
+    const int t = warp >> 2;
+    const int row = tid & 127;
+    const int r = r0 + t * BM + row;
+    const int row_pos = r < rows_total ? start_pos + r / G : -1;
+    const int row_lo = (p.window > 0 && row_pos >= 0) ? max(0, row_pos - p.window + 1) : 0;
+    const int tile_first_pos = start_pos + (r0 + t * BM) / G;
+    const int tile_last_pos = start_pos + (r0 + t * BM + BM - 1) / G;
+    const bool tile_full = r0 + (t + 1) * BM <= rows_total;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t o_addr = lane_addr + 256 + t * 128;
+    const int n = n_t[t];
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+
+    for (int blk = 0; blk < n; ++blk) {
+      const int buf = blk & 1;
+      const int kbase = (kb0 + blk) * BN;
+      if (tid == 0) PROBE(0, blk, 0);
+      ok = mbar_wait(smem_u32(&s_done[t][buf]), (uint32_t)(blk >> 1) & 1, abort_flag);
+      if (!__all_sync(0xffffffffu, ok)) break;
+      if (tid == 0) PROBE(0, blk, 1);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      float s[BN];
+      {
+        uint32_t v0[32], v1[32];
+        tmem_ld32(lane_addr + t * 128 + buf * 64, v0);
+        tmem_ld32(lane_addr + t * 128 + buf * 64 + 32, v1);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          s[i] = __uint_as_float(v0[i]);
+          s[32 + i] = __uint_as_float(v1[i]);
+        }
+      }
+      if (tid == 0) PROBE(0, blk, 2);
+
+      const bool unmasked = tile_full && (kbase + BN - 1 <= tile_first_pos) &&
+                            (p.window <= 0 || kbase >= tile_last_pos - p.window + 1);
+      if (!unmasked) {
+#pragma unroll
+        for (int j = 0; j < BN; ++j) {
+          const int key = kbase + j;
+          s[j] = (key <= row_pos && key >= row_lo) ? s[j] : -INFINITY;
+        }
+      }
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: the warp has few others to hide latency behind
+#pragma unroll
+      for (int j = 0; j < BN; j += 4) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mx[i] = fmaxf(mx[i], s[j + i]);
+      }
+      const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      // raise the running max only when it is far behind
+      if (tid == 0) PROBE(0, blk, 3);
+      const bool raise = (m_blk - m_run) * p.scale_log2 > RESCALE_THRESHOLD;  // also true when m_run is -inf and m_blk is not
+      if (__any_sync(0xffffffffu, raise)) {
+        const float m_new = raise ? m_blk : m_run;
+        const float corr = m_new == -INFINITY ? 1.f : fast_exp2((m_run - m_new) * p.scale_log2);
+        m_run = m_new;
+        l_run *= corr;
+        if (blk > 0) {
+          ok = mbar_wait(smem_u32(&pv_done[t]), (uint32_t)(blk - 1) & 1, abort_flag);
+          if (!__all_sync(0xffffffffu, ok)) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld32(o_addr + c * 32, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+            tmem_st32(o_addr + c * 32, v);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+      }
+      const float m_off = m_run == -INFINITY ? 0.f : m_run * p.scale_log2;
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t packed[BN / 2];
+#pragma unroll
+      for (int j = 0; j < BN; j += 8) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float p0 = fast_exp2(fmaf(s[j + 2 * i], p.scale_log2, -m_off));
+          const float p1 = fast_exp2(fmaf(s[j + 2 * i + 1], p.scale_log2, -m_off));
+          sum[i] += p0 + p1;
+          packed[(j >> 1) + i] = pack_bf16(p0, p1);
+        }
+      }
+      l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+      if (tid == 0) PROBE(0, blk, 4);
+      if (tid == 0) PROBE(0, blk, 5);
+      // P over the first half of the S buffer it came from (this thread's own lane)
+      tmem_st32(lane_addr + t * 128 + buf * 64, packed);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      if (tid == 0) PROBE(0, blk, 6);
+      // rows of V that no request has written (beyond the last key): zeros, by the last tile
+      if (t == ntiles - 1 && kbase + BN - 1 > hi) {
+        const int st = blk % KV_RING;
+        ok = mbar_wait(smem_u32(&v_full[st]), (uint32_t)(blk / KV_RING) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) break;
+        const int first_bad = hi - kbase + 1;
+        for (int i = row; i < (BN - first_bad) * 16; i += BM) {
+          const int vrow = first_bad + i / 16, piece = i % 16;
+          *reinterpret_cast<uint4*>(smem + P2_OFF_V + st * KV_STAGE + (piece >> 3) * KV_HALF + vrow * 128 + ((piece & 7) << 4)) =
+              make_uint4(0u, 0u, 0u, 0u);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
+      // Every phase of pv_done is waited for, so that a later wait cannot take an older phase
+      // for the one it means; P V of the block before is long done by now.
+      if (blk > 0) {
+        ok = mbar_wait(smem_u32(&pv_done[t]), (uint32_t)(blk - 1) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) break;
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&p_ready[t]));
+      if (tid == 0) PROBE(0, blk, 7);
+    }
+
+    ok = mbar_wait(smem_u32(&all_done), 0, abort_flag);
+    if (__all_sync(0xffffffffu, ok) && *abort_flag == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* dst = p.out + ((size_t)(q_begin + r / G) * p.nq + hk * G + r % G) * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(o_addr + c * 32, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (r < rows_total) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 chunk;
+            chunk.x = pack_bf16(__uint_as_float(v[8 * i]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
+            chunk.y = pack_bf16(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
+            chunk.z = pack_bf16(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
+            chunk.w = pack_bf16(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + 8 * i) = chunk;
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (abort_s != 0 && tid == 0) *p.error = 1;
+  if (warp == 0) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(P2_TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
 // host side
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -477,6 +939,10 @@ int query_map(const void* ptr, long long T, int nq, int nkv, CUtensorMap* out) {
 
 }  // namespace
 
+// TS_ATT_PROBE builds only: where the next launches write their clock stamps (2 x 64 x 8 values).
+static long long* probe_buffer = nullptr;
+TS_EXPORT void ts_attention_tcgen05_set_probe(long long* buffer) { probe_buffer = buffer; }
+
 // Whether this kernel takes the sizes (the caller uses the mma.sync kernel otherwise).
 TS_EXPORT int ts_attention_tcgen05_supported(int nq, int nkv, int page) {
   if (nq <= 0 || nkv <= 0 || nq % nkv) return 0;
@@ -488,11 +954,13 @@ TS_EXPORT int ts_attention_tcgen05_supported(int nq, int nkv, int page) {
 
 // q/out [T, nq, 128] bf16; caches [pages, page, nkv, 128] bf16 (`total_slots` = pages * page);
 // cu_q [B+1]; ctx_len [B]; block_table [B, max_blocks]; max_q: the most tokens of any sequence.
+// `mode`: 0 chooses by the longest portion (two tiles per CTA when a sequence has more than 128
+// rows), 1 one tile per CTA, 2 two tiles per CTA.
 // `error`: one int the kernel sets to 1 if one of its waits gave up.
 TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, const void* vcache, void* out,
                                            const int* cu_q, const int* ctx_len, const int* block_table,
                                            int max_blocks, int page, long long total_slots, int T, int B, int max_q,
-                                           int nq, int nkv, float scale, int window, int* error, void* stream_) {
+                                           int nq, int nkv, float scale, int window, int mode, int* error, void* stream_) {
   if (T <= 0 || B <= 0) return 0;
   if (!ts_attention_tcgen05_supported(nq, nkv, page) || max_blocks <= 0 || max_q <= 0 || error == nullptr)
     return TS_ERR_BAD_ARGUMENT;
@@ -518,8 +986,21 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
   p.window = window;
   p.total_slots = (int)total_slots;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.probe = probe_buffer;
   const int G = nq / nkv;
-  const int row_tiles = (int)(((long long)max_q * G + BM - 1) / BM);
+  const long long rows = (long long)max_q * G;
+  const bool pairs = mode == 2 || (mode == 0 && rows > BM);
+  if (pairs) {
+    const size_t smem = P2_SMEM + 1024;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    return ts_launch(attention_tcgen05_pair_kernel, dim3((unsigned)((rows + 2 * BM - 1) / (2 * BM)), nkv, B), dim3(320), smem,
+                     (cudaStream_t)stream_, mq, mk, mv, p);
+  }
   const size_t smem = SMEM_TILES + 1024;
   static bool configured = false;
   if (!configured) {
@@ -527,5 +1008,6 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return ts_launch(attention_tcgen05_kernel, dim3(row_tiles, nkv, B), dim3(128), smem, (cudaStream_t)stream_, mq, mk, mv, p);
+  return ts_launch(attention_tcgen05_kernel, dim3((unsigned)((rows + BM - 1) / BM), nkv, B), dim3(128), smem, (cudaStream_t)stream_, mq, mk,
+                   mv, p);
 }

@@ -504,7 +504,7 @@ def _attention_tcgen05_fns():
     if _attention_tcgen05 is None:
         lib = _build.load_variant("attention_tcgen05", {"TS_HEAD_DIM": ATTENTION_TCGEN05_HEAD_DIM})
         run = lib.ts_attention_prefill_tcgen05
-        run.argtypes = [_c_void_p] * 7 + [_c_int, _c_int, _c_ll] + [_c_int] * 5 + [_c_float, _c_int, _c_void_p, _c_void_p]
+        run.argtypes = [_c_void_p] * 7 + [_c_int, _c_int, _c_ll] + [_c_int] * 5 + [_c_float, _c_int, _c_int, _c_void_p, _c_void_p]
         run.restype = _c_int
         ok = lib.ts_attention_tcgen05_supported
         ok.argtypes = [_c_int, _c_int, _c_int]
@@ -538,10 +538,13 @@ def attention_prefill_tcgen05(
     num_kv_heads: int,
     scale: float,
     window: int = 0,
+    mode: int = 0,
 ) -> None:
     """Causal attention of prompt portions over the paged cache, tcgen05 tensor cores, head size 128.
 
     Same arguments and meaning as attention_paged_mma (without seq_index, which it does not need).
+    `mode`: 1 one tile of 128 rows per CTA, 2 two tiles per CTA with the roles in warps of
+    their own, 0 chooses by the longest portion.
     """
     run, ok = _attention_tcgen05_fns()
     d = ATTENTION_TCGEN05_HEAD_DIM
@@ -568,7 +571,7 @@ def attention_prefill_tcgen05(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
         cu_seqlens_q.data_ptr(), context_lens.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], page_size, k_cache.shape[0] * page_size, T, num_seqs, max_seqlen_q, nq, nkv,
-        float(scale), int(window), error.data_ptr(), _stream()))
+        float(scale), int(window), int(mode), error.data_ptr(), _stream()))
 
 
 # ---------------------------------------------------------------------------
