@@ -64,14 +64,14 @@ struct Params {
   const int* ctx_len;     // [B]
   const int* block_table; // [B, max_blocks]
   int* error;
-  int max_blocks, page, nq, nkv, window, total_slots;
+  int max_blocks, page, nq, nkv, window, total_slots, num_seqs;
   float scale_log2;
   long long* probe;  // TS_ATT_PROBE builds: clock stamps of CTA 0's first softmax warp and of its MMA thread
 };
 
 #ifdef TS_ATT_PROBE
 #define PROBE(slot, blk, k) \
-  do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && p.probe && (blk) < 64) p.probe[((slot) * 64 + (blk)) * 8 + (k)] = clock64(); } while (0)
+  do { if (blockIdx.x == 0 && p.probe && (blk) < 64) p.probe[((slot) * 64 + (blk)) * 8 + (k)] = clock64(); } while (0)
 #else
 #define PROBE(slot, blk, k) do { } while (0)
 #endif
@@ -206,7 +206,9 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
   __shared__ int table_s[MAX_TABLE];
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int b = blockIdx.z, hk = blockIdx.y;
+  // CTAs are numbered so that those launched first have the most keys to walk: the last tile
+  // of every (sequence, KV head), then the tiles before them, and so on.
+  const int hk = blockIdx.x % p.nkv, b = (blockIdx.x / p.nkv) % p.num_seqs;
   const int G = p.nq / p.nkv;
   const int q_begin = p.cu_q[b];
   const int q_len = p.cu_q[b + 1] - q_begin;
@@ -214,7 +216,7 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
   const int start_pos = ctx - q_len;
   const int rows_total = q_len * G;
   const int seq_tiles = (rows_total + BM - 1) / BM;
-  const int row_tile = seq_tiles - 1 - (int)blockIdx.x;  // the tiles with the most keys first
+  const int row_tile = seq_tiles - 1 - (int)(blockIdx.x / (p.nkv * p.num_seqs));
   if (q_len <= 0 || row_tile < 0) return;
   const int r0 = row_tile * BM;
 
@@ -493,7 +495,9 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
                                                                         const __grid_constant__ CUtensorMap map_k,
                                                                         const __grid_constant__ CUtensorMap map_v,
                                                                         const Params p) {
+  if (threadIdx.x == 0) PROBE(1, 63, 6);
   ts_pdl_wait();  // see the other kernel: tensor memory is never held while waiting for another kernel
+  if (threadIdx.x == 0) PROBE(1, 62, 6);
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t q_full, k_full[KV_RING], k_empty[KV_RING], v_full[KV_RING], v_empty[KV_RING];
@@ -503,7 +507,8 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
   __shared__ int table_s[MAX_TABLE];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int b = blockIdx.z, hk = blockIdx.y;
+  // the CTAs with the most keys to walk are launched first (see the other kernel)
+  const int hk = blockIdx.x % p.nkv, b = (blockIdx.x / p.nkv) % p.num_seqs;
   const int G = p.nq / p.nkv;
   const int q_begin = p.cu_q[b];
   const int q_len = p.cu_q[b + 1] - q_begin;
@@ -511,7 +516,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
   const int start_pos = ctx - q_len;
   const int rows_total = q_len * G;
   const int seq_pairs = (rows_total + 2 * BM - 1) / (2 * BM);
-  const int pair = seq_pairs - 1 - (int)blockIdx.x;  // the pairs with the most keys first
+  const int pair = seq_pairs - 1 - (int)(blockIdx.x / (p.nkv * p.num_seqs));
   if (q_len <= 0 || pair < 0) return;
   const int r0 = pair * 2 * BM;
   const int ntiles = rows_total - r0 > BM ? 2 : 1;
@@ -573,6 +578,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
   const uint32_t tmem_base = tmem_base_s;
   volatile int* abort_flag = &abort_s;
   const uint32_t sm = smem_u32(smem);
+  if (tid == 0) PROBE(1, 61, 6);
 
   if (warp == 8) {
     // ---------------- copies: lane 0 announces the bytes, lanes 0..2*copies-1 each ask for one box ----------------
@@ -637,24 +643,36 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
           if (lane == 0) PROBE(1, blk, 0);
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&k_full[st]), (uint32_t)(blk / KV_RING) & 1, abort_flag));
           if (lane == 0) PROBE(1, blk, 1);
-          for (int t = ntiles - 1; ok && t >= 0; --t) {
-            if (blk >= n_t[t]) continue;
-            // This S buffer held S and then P of block blk - 2; P V of that block was issued before
-            // this point, and the tensor core runs what one thread issues in order.
+          // An S buffer held S and then P of block blk - 2; P V of that block was issued before
+          // this point, and the tensor core runs what one thread issues in order.  The products
+          // of the two tiles are issued in turns: neighbours in the queue then do not depend on
+          // each other's accumulator.
+          {
             const int buf = blk & 1;
+            const bool on0 = blk < n_t[0], on1 = ntiles > 1 && blk < n_t[1];
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t qd = q_desc + (uint64_t)((t * Q_BYTES) >> 4), kd = k_desc + (uint64_t)((st * KV_STAGE) >> 4);
-            const uint32_t s_addr = tmem_base + t * 128 + buf * 64;
+            const uint64_t kd = k_desc + (uint64_t)((st * KV_STAGE) >> 4);
+            const uint32_t s_addr = tmem_base + buf * 64;
             if (elect_one()) {
 #pragma unroll
               for (int ks = 0; ks < D / 16; ++ks) {
-                const uint32_t half = ks >> 2, inner = (ks & 3) * 32;
-                if (ks == 0)
-                  umma_bf16_first(s_addr, qd, kd, idesc(BN, false));
-                else
-                  umma_bf16_more(s_addr, qd + ((half * (BM * 128) + inner) >> 4), kd + ((half * KV_HALF + inner) >> 4), idesc(BN, false));
+                const uint32_t off_q = ((ks >> 2) * (BM * 128) + (ks & 3) * 32) >> 4, off_k = ((ks >> 2) * KV_HALF + (ks & 3) * 32) >> 4;
+                if (on1) {
+                  if (ks == 0)
+                    umma_bf16_first(s_addr + 128, q_desc + ((Q_BYTES >> 4) + off_q), kd + off_k, idesc(BN, false));
+                  else
+                    umma_bf16_more(s_addr + 128, q_desc + ((Q_BYTES >> 4) + off_q), kd + off_k, idesc(BN, false));
+                }
+                if (on0) {
+                  if (ks == 0)
+                    umma_bf16_first(s_addr, q_desc + off_q, kd + off_k, idesc(BN, false));
+                  else
+                    umma_bf16_more(s_addr, q_desc + off_q, kd + off_k, idesc(BN, false));
+                }
               }
-              umma_commit(smem_u32(&s_done[t][buf]));
+              PROBE(1, blk, 7);
+              if (on1) umma_commit(smem_u32(&s_done[1][buf]));
+              if (on0) umma_commit(smem_u32(&s_done[0][buf]));
             }
             __syncwarp();
           }
@@ -667,23 +685,35 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
           const int st = j % KV_RING;
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&v_full[st]), (uint32_t)(j / KV_RING) & 1, abort_flag));
           // the last tile first: in the last block its threads also clear the rows of V beyond the last key
-          for (int t = ntiles - 1; ok && t >= 0; --t) {
-            if (j >= n_t[t]) continue;
-            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&p_ready[t]), (uint32_t)j & 1, abort_flag));
-            if (lane == 0) PROBE(1, blk, 3 + t);
-            if (!ok) break;
+          if (lane == 0) PROBE(1, blk, 6);
+          const bool on0 = j < n_t[0], on1 = ntiles > 1 && j < n_t[1];
+          if (on1) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&p_ready[1]), (uint32_t)j & 1, abort_flag));
+          if (lane == 0) PROBE(1, blk, 4);
+          if (ok && on0) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&p_ready[0]), (uint32_t)j & 1, abort_flag));
+          if (lane == 0) PROBE(1, blk, 3);
+          if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint64_t vd = v_desc + (uint64_t)((st * KV_STAGE) >> 4);
-            const uint32_t o_addr = tmem_base + 256 + t * 128;
-            const uint32_t p_addr = tmem_base + t * 128 + (j & 1) * 64;  // 16 keys of P: 8 columns
+            const uint32_t o_addr = tmem_base + 256;
+            const uint32_t p_addr = tmem_base + (j & 1) * 64;  // 16 keys of P: 8 columns
             if (elect_one()) {
-              if (j == 0)
-                umma_bf16_tmem_a_first(o_addr, p_addr, vd, idesc(D, true));
-              else
-                umma_bf16_tmem_a_more(o_addr, p_addr, vd, idesc(D, true));
 #pragma unroll
-              for (int kk = 1; kk < BN / 16; ++kk) umma_bf16_tmem_a_more(o_addr, p_addr + kk * 8, vd + ((kk * 2048) >> 4), idesc(D, true));
-              umma_commit(smem_u32(&pv_done[t]));
+              for (int kk = 0; kk < BN / 16; ++kk) {
+                if (on1) {
+                  if (kk == 0 && j == 0)
+                    umma_bf16_tmem_a_first(o_addr + 128, p_addr + 128, vd, idesc(D, true));
+                  else
+                    umma_bf16_tmem_a_more(o_addr + 128, p_addr + 128 + kk * 8, vd + ((kk * 2048) >> 4), idesc(D, true));
+                }
+                if (on0) {
+                  if (kk == 0 && j == 0)
+                    umma_bf16_tmem_a_first(o_addr, p_addr, vd, idesc(D, true));
+                  else
+                    umma_bf16_tmem_a_more(o_addr, p_addr + kk * 8, vd + ((kk * 2048) >> 4), idesc(D, true));
+                }
+              }
+              if (on1) umma_commit(smem_u32(&pv_done[1]));
+              if (on0) umma_commit(smem_u32(&pv_done[0]));
             }
             __syncwarp();
           }
@@ -717,10 +747,10 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
     for (int blk = 0; blk < n; ++blk) {
       const int buf = blk & 1;
       const int kbase = (kb0 + blk) * BN;
-      if (tid == 0) PROBE(0, blk, 0);
+      if (row == 0) PROBE(t * 2, blk, 0);
       ok = mbar_wait(smem_u32(&s_done[t][buf]), (uint32_t)(blk >> 1) & 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) break;
-      if (tid == 0) PROBE(0, blk, 1);
+      if (row == 0) PROBE(t * 2, blk, 1);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float s[BN];
       {
@@ -734,7 +764,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
           s[32 + i] = __uint_as_float(v1[i]);
         }
       }
-      if (tid == 0) PROBE(0, blk, 2);
+      if (row == 0) PROBE(t * 2, blk, 2);
 
       const bool unmasked = tile_full && (kbase + BN - 1 <= tile_first_pos) &&
                             (p.window <= 0 || kbase >= tile_last_pos - p.window + 1);
@@ -753,7 +783,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
       }
       const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       // raise the running max only when it is far behind
-      if (tid == 0) PROBE(0, blk, 3);
+      if (row == 0) PROBE(t * 2, blk, 3);
       const bool raise = (m_blk - m_run) * p.scale_log2 > RESCALE_THRESHOLD;  // also true when m_run is -inf and m_blk is not
       if (__any_sync(0xffffffffu, raise)) {
         const float m_new = raise ? m_blk : m_run;
@@ -790,12 +820,12 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
         }
       }
       l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-      if (tid == 0) PROBE(0, blk, 4);
-      if (tid == 0) PROBE(0, blk, 5);
+      if (row == 0) PROBE(t * 2, blk, 4);
+      if (row == 0) PROBE(t * 2, blk, 5);
       // P over the first half of the S buffer it came from (this thread's own lane)
       tmem_st32(lane_addr + t * 128 + buf * 64, packed);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      if (tid == 0) PROBE(0, blk, 6);
+      if (row == 0) PROBE(t * 2, blk, 6);
       // rows of V that no request has written (beyond the last key): zeros, by the last tile
       if (t == ntiles - 1 && kbase + BN - 1 > hi) {
         const int st = blk % KV_RING;
@@ -818,34 +848,58 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&p_ready[t]));
-      if (tid == 0) PROBE(0, blk, 7);
+      if (row == 0) PROBE(t * 2, blk, 7);
     }
 
+    if (tid == 0) PROBE(1, 60, 6);
     ok = mbar_wait(smem_u32(&all_done), 0, abort_flag);
-    if (__all_sync(0xffffffffu, ok) && *abort_flag == 0) {
+    if (tid == 0) PROBE(1, 59, 6);
+    const bool good = __all_sync(0xffffffffu, ok) && *abort_flag == 0;
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    unsigned char* o_tile = smem + P2_OFF_Q + t * Q_BYTES;
+    const int g_shift = __ffs(G) - 1;
+    if (good) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = p.out + ((size_t)(q_begin + r / G) * p.nq + hk * G + r % G) * D;
+      // The tile goes through shared memory (where its Q lay: the tensor core is done with it), so
+      // that rows leave as whole 256-byte lines: row `row` at row * 256, its 16-byte piece c at
+      // position c ^ (row % 16), which spreads both the writes and the reads over the banks.
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t v[32];
         tmem_ld32(o_addr + c * 32, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (r < rows_total) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 chunk;
-            chunk.x = pack_bf16(__uint_as_float(v[8 * i]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
-            chunk.y = pack_bf16(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
-            chunk.z = pack_bf16(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
-            chunk.w = pack_bf16(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + 8 * i) = chunk;
-          }
+        for (int i = 0; i < 4; ++i) {
+          uint4 chunk;
+          chunk.x = pack_bf16(__uint_as_float(v[8 * i]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
+          chunk.y = pack_bf16(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
+          chunk.z = pack_bf16(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
+          chunk.w = pack_bf16(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+          *reinterpret_cast<uint4*>(o_tile + row * 256 + (((c * 4 + i) ^ (row & 15)) << 4)) = chunk;
+        }
+      }
+    }
+    // the four warps of this tile meet here whatever happened before
+    if (tid == 0) PROBE(1, 56, 6);
+    asm volatile("bar.sync %0, 128;" ::"r"(1 + t) : "memory");
+    if (tid == 0) PROBE(1, 55, 6);
+    if (good) {
+#pragma unroll 4
+      for (int it = 0; it < 16; ++it) {
+        const int idx = it * BM + row;
+        const int rr = idx >> 4, piece = idx & 15;
+        const int rg = r0 + t * BM + rr;
+        if (rg < rows_total) {
+          const uint4 chunk = *reinterpret_cast<const uint4*>(o_tile + rr * 256 + ((piece ^ (rr & 15)) << 4));
+          // the group size divides 128: a power of two
+          __nv_bfloat16* dst = p.out + ((size_t)(q_begin + (rg >> g_shift)) * p.nq + hk * G + (rg & (G - 1))) * D + piece * 8;
+          *reinterpret_cast<uint4*>(dst) = chunk;
         }
       }
     }
   }
 
+  if (tid == 0) PROBE(1, 58, 6);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (abort_s != 0 && tid == 0) *p.error = 1;
@@ -853,6 +907,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
     __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(P2_TMEM_COLS) : "memory");
   }
+  if (tid == 0) PROBE(1, 57, 6);
 }
 
 // ---------------------------------------------------------------------------
@@ -964,7 +1019,7 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
   if (T <= 0 || B <= 0) return 0;
   if (!ts_attention_tcgen05_supported(nq, nkv, page) || max_blocks <= 0 || max_q <= 0 || error == nullptr)
     return TS_ERR_BAD_ARGUMENT;
-  if (nkv > 65535 || B > 65535 || total_slots > 0x7fffffffLL - page) return TS_ERR_UNSUPPORTED_SIZE;
+  if (total_slots > 0x7fffffffLL - page || ((long long)max_q * (nq / nkv) / BM + 1) * nkv * B > 0x7fffffffLL) return TS_ERR_UNSUPPORTED_SIZE;
   if (((uintptr_t)q | (uintptr_t)kcache | (uintptr_t)vcache | (uintptr_t)out) % 16) return TS_ERR_UNSUPPORTED_SIZE;
   CUtensorMap mq, mk, mv;
   int st = query_map(q, T, nq, nkv, &mq);
@@ -985,6 +1040,7 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
   p.nkv = nkv;
   p.window = window;
   p.total_slots = (int)total_slots;
+  p.num_seqs = B;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.probe = probe_buffer;
   const int G = nq / nkv;
@@ -998,7 +1054,7 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    return ts_launch(attention_tcgen05_pair_kernel, dim3((unsigned)((rows + 2 * BM - 1) / (2 * BM)), nkv, B), dim3(320), smem,
+    return ts_launch(attention_tcgen05_pair_kernel, dim3((unsigned)(((rows + 2 * BM - 1) / (2 * BM)) * nkv * B)), dim3(320), smem,
                      (cudaStream_t)stream_, mq, mk, mv, p);
   }
   const size_t smem = SMEM_TILES + 1024;
@@ -1008,6 +1064,6 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return ts_launch(attention_tcgen05_kernel, dim3((unsigned)((rows + BM - 1) / BM), nkv, B), dim3(128), smem, (cudaStream_t)stream_, mq, mk,
+  return ts_launch(attention_tcgen05_kernel, dim3((unsigned)(((rows + BM - 1) / BM) * nkv * B)), dim3(128), smem, (cudaStream_t)stream_, mq, mk,
                    mv, p);
 }
