@@ -449,7 +449,8 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
 // A CTA owns 256 consecutive rows as two tiles of 128 and walks the keys once for both.
 //   warps 0-3, 4-7  softmax of tile 0 and of tile 1: thread r of a group owns row r;
 //   warp 8          one thread: TMA loads (Q once, then K and V blocks into rings of 3 stages);
-//   warp 9          one thread: every tcgen05.mma.
+//   warp 9          one thread: every tcgen05.mma;
+//   warp 10         a messenger between the copies and warp 9 (see there).
 // S has two buffers per tile in tensor memory, so S of block j+1 is computed while the threads
 // work on block j; O stays in tensor memory and P V accumulates into it.  The running max of a
 // row is only raised when the new max exceeds it by more than 2^8 (the weights then stay below
@@ -491,7 +492,7 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 
-__global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_q,
+__global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                         const __grid_constant__ CUtensorMap map_k,
                                                                         const __grid_constant__ CUtensorMap map_v,
                                                                         const Params p) {
@@ -501,7 +502,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t q_full, k_full[KV_RING], k_empty[KV_RING], v_full[KV_RING], v_empty[KV_RING];
-  __shared__ __align__(8) uint64_t s_done[2][2], p_ready[2], pv_done[2], all_done;
+  __shared__ __align__(8) uint64_t s_done[2], p_ready, pv_done, all_done;  // s_done per S buffer; all of them for both tiles
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   __shared__ int table_s[MAX_TABLE];
@@ -533,6 +534,8 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
     n_t[t] = t < ntiles ? hi_t[t] / BN - kb0 + 1 : 0;
   }
   const int hi = hi_t[ntiles - 1];
+  // Both tiles walk all blocks of the later one (its last block or two are fully masked for the
+  // earlier tile): one barrier then serves both.
   const int nblocks = n_t[ntiles - 1];
   const int box_rows = min(p.page, BN);
   const int copies_per_block = BN / box_rows;
@@ -547,13 +550,10 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
       mbar_init(smem_u32(&v_full[s]), 1);
       mbar_init(smem_u32(&v_empty[s]), 1);
     }
-    for (int t = 0; t < 2; ++t) {
-      for (int i = 0; i < 2; ++i) {
-        mbar_init(smem_u32(&s_done[t][i]), 1);
-      }
-      mbar_init(smem_u32(&p_ready[t]), 4);  // one arrival per softmax warp
-      mbar_init(smem_u32(&pv_done[t]), 1);
-    }
+    mbar_init(smem_u32(&s_done[0]), 1);
+    mbar_init(smem_u32(&s_done[1]), 1);
+    mbar_init(smem_u32(&p_ready), 4 * ntiles + 1);  // one arrival per softmax warp, one from the messenger warp
+    mbar_init(smem_u32(&pv_done), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -630,97 +630,95 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
         for (int blk = max(0, issued[which] - KV_RING); blk < issued[which]; ++blk)
           mbar_wait(smem_u32(which == 0 ? &k_full[blk % KV_RING] : &v_full[blk % KV_RING]), (uint32_t)(blk / KV_RING) & 1, own);
     }
+  } else if (warp == 10) {
+    // ---------------- messenger: tells the MMA warp that what a round needs has landed ----------------
+    // It arrives on p_ready for block j (beside the softmax warps) once V of j and K of j + 2 are
+    // there.  An arrival counts for the barrier's current phase, so it waits until the phase of
+    // block j - 1 is over; the copies it looks at landed long before that as a rule.
+    bool ok = true;
+    for (int j = 0; ok && j < nblocks; ++j) {
+      ok = mbar_wait(smem_u32(&v_full[j % KV_RING]), (uint32_t)(j / KV_RING) & 1, abort_flag);
+      if (ok && j + 2 < nblocks) ok = mbar_wait(smem_u32(&k_full[(j + 2) % KV_RING]), (uint32_t)((j + 2) / KV_RING) & 1, abort_flag);
+      if (ok && j >= 1) ok = mbar_wait(smem_u32(&p_ready), (uint32_t)(j - 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok && lane == 0) mbar_arrive(smem_u32(&p_ready));
+    }
   } else if (warp == 9) {
     // ---------------- tensor core: the warp runs together, one elected lane issues ----------------
+    // Order of issue: S(0), S(1), then for every block j: P V of j, S of j + 2.  S(j + 2) goes to
+    // the buffer that held S and then P of block j; the tensor core runs what one thread issues in
+    // order, so P V of j has read P before S(j + 2) overwrites it.  p_ready for block j gathers the
+    // softmax warps (P of j is written) and the messenger warp (V of j and K of j + 2 have landed), so
+    // that one wait a round is all this warp needs: each of its instructions is slow beside
+    // eight busy warps.
     {
       // descriptors differ only in their address field (bytes / 16): prepared once, offsets added per instruction
       const uint64_t q_desc = desc_k_major(sm + P2_OFF_Q), k_desc = desc_k_major(sm + P2_OFF_K);
       const uint64_t v_desc = desc_mn_major(sm + P2_OFF_V, KV_HALF);
+      const bool two = ntiles > 1;
+      auto issue_s = [&](int blk) {  // S of block blk for both tiles, in turns
+        const int st = blk % KV_RING, buf = blk & 1;
+        const uint64_t kd = k_desc + (uint64_t)((st * KV_STAGE) >> 4);
+        const uint32_t s_addr = tmem_base + buf * 64;
+        if (elect_one()) {
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t off_q = ((ks >> 2) * (BM * 128) + (ks & 3) * 32) >> 4, off_k = ((ks >> 2) * KV_HALF + (ks & 3) * 32) >> 4;
+            if (two) {
+              if (ks == 0)
+                umma_bf16_first(s_addr + 128, q_desc + ((Q_BYTES >> 4) + off_q), kd + off_k, idesc(BN, false));
+              else
+                umma_bf16_more(s_addr + 128, q_desc + ((Q_BYTES >> 4) + off_q), kd + off_k, idesc(BN, false));
+            }
+            if (ks == 0)
+              umma_bf16_first(s_addr, q_desc + off_q, kd + off_k, idesc(BN, false));
+            else
+              umma_bf16_more(s_addr, q_desc + off_q, kd + off_k, idesc(BN, false));
+          }
+          umma_commit(smem_u32(&s_done[buf]));  // the products of both tiles are done when this arrives
+          umma_commit(smem_u32(&k_empty[st]));
+        }
+        __syncwarp();
+      };
       bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&q_full), 0, abort_flag));
-      for (int blk = 0; ok && blk <= nblocks; ++blk) {
-        if (blk < nblocks) {
-          const int st = blk % KV_RING;
-          if (lane == 0) PROBE(1, blk, 0);
-          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&k_full[st]), (uint32_t)(blk / KV_RING) & 1, abort_flag));
-          if (lane == 0) PROBE(1, blk, 1);
-          // An S buffer held S and then P of block blk - 2; P V of that block was issued before
-          // this point, and the tensor core runs what one thread issues in order.  The products
-          // of the two tiles are issued in turns: neighbours in the queue then do not depend on
-          // each other's accumulator.
-          {
-            const int buf = blk & 1;
-            const bool on0 = blk < n_t[0], on1 = ntiles > 1 && blk < n_t[1];
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t kd = k_desc + (uint64_t)((st * KV_STAGE) >> 4);
-            const uint32_t s_addr = tmem_base + buf * 64;
-            if (elect_one()) {
-#pragma unroll
-              for (int ks = 0; ks < D / 16; ++ks) {
-                const uint32_t off_q = ((ks >> 2) * (BM * 128) + (ks & 3) * 32) >> 4, off_k = ((ks >> 2) * KV_HALF + (ks & 3) * 32) >> 4;
-                if (on1) {
-                  if (ks == 0)
-                    umma_bf16_first(s_addr + 128, q_desc + ((Q_BYTES >> 4) + off_q), kd + off_k, idesc(BN, false));
-                  else
-                    umma_bf16_more(s_addr + 128, q_desc + ((Q_BYTES >> 4) + off_q), kd + off_k, idesc(BN, false));
-                }
-                if (on0) {
-                  if (ks == 0)
-                    umma_bf16_first(s_addr, q_desc + off_q, kd + off_k, idesc(BN, false));
-                  else
-                    umma_bf16_more(s_addr, q_desc + off_q, kd + off_k, idesc(BN, false));
-                }
-              }
-              PROBE(1, blk, 7);
-              if (on1) umma_commit(smem_u32(&s_done[1][buf]));
-              if (on0) umma_commit(smem_u32(&s_done[0][buf]));
-            }
-            __syncwarp();
-          }
-          if (ok && elect_one()) umma_commit(smem_u32(&k_empty[st]));
-          __syncwarp();
-          if (lane == 0) PROBE(1, blk, 2);
+      for (int blk = 0; ok && blk < min(2, nblocks); ++blk) {
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&k_full[blk]), 0, abort_flag));
+        if (ok) {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_s(blk);
         }
-        if (blk >= 1 && ok) {
-          const int j = blk - 1;
-          const int st = j % KV_RING;
-          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&v_full[st]), (uint32_t)(j / KV_RING) & 1, abort_flag));
-          // the last tile first: in the last block its threads also clear the rows of V beyond the last key
-          if (lane == 0) PROBE(1, blk, 6);
-          const bool on0 = j < n_t[0], on1 = ntiles > 1 && j < n_t[1];
-          if (on1) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&p_ready[1]), (uint32_t)j & 1, abort_flag));
-          if (lane == 0) PROBE(1, blk, 4);
-          if (ok && on0) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&p_ready[0]), (uint32_t)j & 1, abort_flag));
-          if (lane == 0) PROBE(1, blk, 3);
-          if (ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t vd = v_desc + (uint64_t)((st * KV_STAGE) >> 4);
-            const uint32_t o_addr = tmem_base + 256;
-            const uint32_t p_addr = tmem_base + (j & 1) * 64;  // 16 keys of P: 8 columns
-            if (elect_one()) {
+      }
+      for (int j = 0; ok && j < nblocks; ++j) {
+        const int st = j % KV_RING;
+        if (lane == 0) PROBE(1, j, 0);
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&p_ready), (uint32_t)j & 1, abort_flag));
+        if (lane == 0) PROBE(1, j, 1);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t vd = v_desc + (uint64_t)((st * KV_STAGE) >> 4);
+        const uint32_t o_addr = tmem_base + 256;
+        const uint32_t p_addr = tmem_base + (j & 1) * 64;  // 16 keys of P: 8 columns
+        if (elect_one()) {
 #pragma unroll
-              for (int kk = 0; kk < BN / 16; ++kk) {
-                if (on1) {
-                  if (kk == 0 && j == 0)
-                    umma_bf16_tmem_a_first(o_addr + 128, p_addr + 128, vd, idesc(D, true));
-                  else
-                    umma_bf16_tmem_a_more(o_addr + 128, p_addr + 128 + kk * 8, vd + ((kk * 2048) >> 4), idesc(D, true));
-                }
-                if (on0) {
-                  if (kk == 0 && j == 0)
-                    umma_bf16_tmem_a_first(o_addr, p_addr, vd, idesc(D, true));
-                  else
-                    umma_bf16_tmem_a_more(o_addr, p_addr + kk * 8, vd + ((kk * 2048) >> 4), idesc(D, true));
-                }
-              }
-              if (on1) umma_commit(smem_u32(&pv_done[1]));
-              if (on0) umma_commit(smem_u32(&pv_done[0]));
+          for (int kk = 0; kk < BN / 16; ++kk) {
+            if (two) {
+              if (kk == 0 && j == 0)
+                umma_bf16_tmem_a_first(o_addr + 128, p_addr + 128, vd, idesc(D, true));
+              else
+                umma_bf16_tmem_a_more(o_addr + 128, p_addr + 128 + kk * 8, vd + ((kk * 2048) >> 4), idesc(D, true));
             }
-            __syncwarp();
+            if (kk == 0 && j == 0)
+              umma_bf16_tmem_a_first(o_addr, p_addr, vd, idesc(D, true));
+            else
+              umma_bf16_tmem_a_more(o_addr, p_addr + kk * 8, vd + ((kk * 2048) >> 4), idesc(D, true));
           }
-          if (ok && elect_one()) umma_commit(smem_u32(&v_empty[st]));
-          __syncwarp();
-          if (lane == 0) PROBE(1, blk, 5);
+          umma_commit(smem_u32(&pv_done));
+          umma_commit(smem_u32(&v_empty[st]));
         }
+        __syncwarp();
+        if (lane == 0) PROBE(1, j, 2);
+        if (j + 2 < nblocks) issue_s(j + 2);
+        if (lane == 0) PROBE(1, j, 3);
       }
       // Everything this CTA asked of the tensor core is done when this arrives, the arrivals of
       // the commits above included: nobody leaves before (an arrival after the CTA's end would
@@ -740,7 +738,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
     const bool tile_full = r0 + (t + 1) * BM <= rows_total;
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t o_addr = lane_addr + 256 + t * 128;
-    const int n = n_t[t];
+    const int n = nblocks;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
 
@@ -748,7 +746,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
       const int buf = blk & 1;
       const int kbase = (kb0 + blk) * BN;
       if (row == 0) PROBE(t * 2, blk, 0);
-      ok = mbar_wait(smem_u32(&s_done[t][buf]), (uint32_t)(blk >> 1) & 1, abort_flag);
+      ok = mbar_wait(smem_u32(&s_done[buf]), (uint32_t)(blk >> 1) & 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) break;
       if (row == 0) PROBE(t * 2, blk, 1);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -791,7 +789,7 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
         m_run = m_new;
         l_run *= corr;
         if (blk > 0) {
-          ok = mbar_wait(smem_u32(&pv_done[t]), (uint32_t)(blk - 1) & 1, abort_flag);
+          ok = mbar_wait(smem_u32(&pv_done), (uint32_t)(blk - 1) & 1, abort_flag);
           if (!__all_sync(0xffffffffu, ok)) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -842,12 +840,12 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_pair_kernel(const __
       // Every phase of pv_done is waited for, so that a later wait cannot take an older phase
       // for the one it means; P V of the block before is long done by now.
       if (blk > 0) {
-        ok = mbar_wait(smem_u32(&pv_done[t]), (uint32_t)(blk - 1) & 1, abort_flag);
+        ok = mbar_wait(smem_u32(&pv_done), (uint32_t)(blk - 1) & 1, abort_flag);
         if (!__all_sync(0xffffffffu, ok)) break;
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&p_ready[t]));
+      if (lane == 0) mbar_arrive(smem_u32(&p_ready));
       if (row == 0) PROBE(t * 2, blk, 7);
     }
 
@@ -1054,7 +1052,7 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    return ts_launch(attention_tcgen05_pair_kernel, dim3((unsigned)(((rows + 2 * BM - 1) / (2 * BM)) * nkv * B)), dim3(320), smem,
+    return ts_launch(attention_tcgen05_pair_kernel, dim3((unsigned)(((rows + 2 * BM - 1) / (2 * BM)) * nkv * B)), dim3(352), smem,
                      (cudaStream_t)stream_, mq, mk, mv, p);
   }
   const size_t smem = SMEM_TILES + 1024;
