@@ -207,6 +207,123 @@ __global__ void qk_norm_rope_store_pairs_kernel(const TA* __restrict__ qkv, TA* 
   }
 }
 
+// Prompt-sized batches, bfloat16, a head size that is a power of two: LPR = d / 16 lanes share
+// one head row (16-byte loads: 8 elements of the lower half and their 8 partners in the upper
+// half per lane), so a warp works on 32 / LPR heads of one token at a time; the sines and
+// cosines of the token's position are computed once per warp and serve all its heads.
+template <int LPR>
+__global__ void qk_norm_rope_store_vec8_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                                               __nv_bfloat16* __restrict__ k_dst, __nv_bfloat16* __restrict__ v_dst,
+                                               const int* __restrict__ slot_mapping, const int* __restrict__ positions,
+                                               const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w,
+                                               float eps, const float* __restrict__ inv_freq, int T, int nq, int nkv,
+                                               int warps_per_token) {
+  ts_pdl_prologue();
+  constexpr int D = LPR * 16, HALF = D / 2, ROWS = 32 / LPR;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * QKR_WARPS + warp;
+  if (item >= (long long)T * warps_per_token) return;
+  const int t = (int)(item / warps_per_token);
+  const int part = (int)(item - (long long)t * warps_per_token);
+  const int heads = nq + 2 * nkv;
+  const int per_part = (heads + warps_per_token - 1) / warps_per_token;
+  const int h0 = part * per_part, h1 = min(heads, h0 + per_part);
+  const int sub = lane / LPR, l = lane % LPR;
+  const int slot = slot_mapping ? slot_mapping[t] : t;
+
+  float cs[8], sn[8];
+  if (inv_freq && h0 < nq + nkv) {
+    const float pos = (float)positions[t];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sincosf(pos * inv_freq[8 * l + i], &sn[i], &cs[i]);
+  }
+
+  for (int base = h0; base < h1; base += ROWS) {
+    const int head = base + sub;
+    const bool is_q = head < nq;
+    const bool is_k = !is_q && head < nq + nkv;
+    const bool active = head < h1 && (is_q || slot >= 0);
+    uint4 raw_lo = make_uint4(0u, 0u, 0u, 0u), raw_hi = raw_lo;
+    if (active) {
+      const __nv_bfloat16* src = qkv + ((size_t)t * heads + head) * D + 8 * l;
+      raw_lo = *reinterpret_cast<const uint4*>(src);
+      raw_hi = *reinterpret_cast<const uint4*>(src + HALF);
+    }
+    __nv_bfloat16* dst = nullptr;
+    if (active)
+      dst = (is_q ? q_out + ((size_t)t * nq + head) * D
+                  : is_k ? k_dst + ((size_t)slot * nkv + (head - nq)) * D : v_dst + ((size_t)slot * nkv + (head - nq - nkv)) * D) + 8 * l;
+    float a[8], b[8];
+    {
+      const __nv_bfloat162* pl = reinterpret_cast<const __nv_bfloat162*>(&raw_lo);
+      const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&raw_hi);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 x = __bfloat1622float2(pl[i]), y = __bfloat1622float2(ph[i]);
+        a[2 * i] = x.x; a[2 * i + 1] = x.y;
+        b[2 * i] = y.x; b[2 * i + 1] = y.y;
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
+    // every lane takes part in the shuffles; the sums stay inside the LPR lanes of a row
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (!active) continue;
+    if (is_q || is_k) {
+      const float* w = is_q ? q_norm_w : k_norm_w;
+      if (w) {
+        const float rstd = rsqrtf(ss / (float)D + eps);
+        const float4 w0 = *reinterpret_cast<const float4*>(w + 8 * l), w1 = *reinterpret_cast<const float4*>(w + 8 * l + 4);
+        const float4 w2 = *reinterpret_cast<const float4*>(w + HALF + 8 * l), w3 = *reinterpret_cast<const float4*>(w + HALF + 8 * l + 4);
+        const float wl[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        const float wh[8] = {w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          a[i] *= rstd * wl[i];
+          b[i] *= rstd * wh[i];
+        }
+      }
+      if (inv_freq) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float ra = a[i] * cs[i] - b[i] * sn[i];
+          const float rb = b[i] * cs[i] + a[i] * sn[i];
+          a[i] = ra;
+          b[i] = rb;
+        }
+      }
+      uint4 out_lo, out_hi;
+      __nv_bfloat162* ol = reinterpret_cast<__nv_bfloat162*>(&out_lo);
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&out_hi);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        ol[i] = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
+        oh[i] = __floats2bfloat162_rn(b[2 * i], b[2 * i + 1]);
+      }
+      *reinterpret_cast<uint4*>(dst) = out_lo;
+      *reinterpret_cast<uint4*>(dst + HALF) = out_hi;
+    } else {  // value head: plain copy
+      *reinterpret_cast<uint4*>(dst) = raw_lo;
+      *reinterpret_cast<uint4*>(dst + HALF) = raw_hi;
+    }
+  }
+}
+
+template <int LPR>
+static int launch_vec8(const void* qkv, void* q_out, void* k_dst, void* v_dst, const int* slot_mapping, const int* positions,
+                       const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq, int T, int nq, int nkv,
+                       cudaStream_t s) {
+  // two warps per token where a token has enough heads for both
+  const int rows = 32 / LPR;
+  const int warps_per_token = (nq + 2 * nkv) >= 4 * rows ? 2 : 1;
+  const unsigned blocks = (unsigned)(((long long)T * warps_per_token + QKR_WARPS - 1) / QKR_WARPS);
+  return ts_launch(qk_norm_rope_store_vec8_kernel<LPR>, dim3(blocks), dim3(QKR_WARPS * 32), 0, s, (const __nv_bfloat16*)qkv,
+                   (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_dst, (__nv_bfloat16*)v_dst, slot_mapping, positions, q_norm_w, k_norm_w,
+                   eps, inv_freq, T, nq, nkv, warps_per_token);
+}
+
 TS_EXPORT int ts_qk_norm_rope_store(const void* qkv, int act_dtype, void* q_out, void* k_dst,
                                     void* v_dst, const int* slot_mapping, const int* positions,
                                     const float* q_norm_w, const float* k_norm_w, float eps,
@@ -227,6 +344,20 @@ TS_EXPORT int ts_qk_norm_rope_store(const void* qkv, int act_dtype, void* q_out,
   const int heads_per_warp = T >= 256 ? 8 : 1;
   const int groups = (nq + 2 * nkv + heads_per_warp - 1) / heads_per_warp;
   const unsigned pair_blocks = (unsigned)(((long long)T * groups + QKR_WARPS - 1) / QKR_WARPS);
+  // prompt-sized bfloat16 batches with a power-of-two head size: 16-byte accesses, several heads per warp
+  const bool vec8 = pairs && act_dtype == TS_DTYPE_BF16 && T >= 256 && d >= 16 && (d & (d - 1)) == 0 &&
+                    (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_dst | (uintptr_t)v_dst | (uintptr_t)q_norm_w |
+                      (uintptr_t)k_norm_w) % 16 == 0) && ((uintptr_t)inv_freq % 4 == 0);
+  if (vec8) {
+    switch (d) {
+      case 16: return launch_vec8<1>(qkv, q_out, k_dst, v_dst, slot_mapping, positions, q_norm_w, k_norm_w, eps, inv_freq, T, nq, nkv, s);
+      case 32: return launch_vec8<2>(qkv, q_out, k_dst, v_dst, slot_mapping, positions, q_norm_w, k_norm_w, eps, inv_freq, T, nq, nkv, s);
+      case 64: return launch_vec8<4>(qkv, q_out, k_dst, v_dst, slot_mapping, positions, q_norm_w, k_norm_w, eps, inv_freq, T, nq, nkv, s);
+      case 128: return launch_vec8<8>(qkv, q_out, k_dst, v_dst, slot_mapping, positions, q_norm_w, k_norm_w, eps, inv_freq, T, nq, nkv, s);
+      case 256: return launch_vec8<16>(qkv, q_out, k_dst, v_dst, slot_mapping, positions, q_norm_w, k_norm_w, eps, inv_freq, T, nq, nkv, s);
+      case 512: return launch_vec8<32>(qkv, q_out, k_dst, v_dst, slot_mapping, positions, q_norm_w, k_norm_w, eps, inv_freq, T, nq, nkv, s);
+    }
+  }
   if (pairs && act_dtype == TS_DTYPE_F32) {
     return ts_launch(qk_norm_rope_store_pairs_kernel<float>, dim3(pair_blocks), dim3(QKR_WARPS * 32), 0, s,
         (const float*)qkv, (float*)q_out, (float*)k_dst, (float*)v_dst, slot_mapping, positions, q_norm_w,
