@@ -17,27 +17,28 @@ __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, i
   out[idx] = ts_from_float<TA>(s * u);
 }
 
-// Eight bfloat16 per thread (16-byte loads) when the inner size allows it.
-__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I, size_t total8) {
+// Eight bfloat16 per thread (16-byte loads) when the inner size allows it; the row comes from
+// the grid (no division per thread), and the sigmoid uses the fast exponential and reciprocal:
+// their error (2 ulp of float32) disappears in the rounding to bfloat16.
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I, int T) {
   ts_pdl_prologue();
-  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= total8) return;
-  const int per_row = I >> 3;
-  const size_t t = idx / per_row;
-  const int i = (int)(idx - t * per_row) << 3;
-  const __nv_bfloat16* row = gu + t * (size_t)(2 * I);
-  const uint4 g4 = *reinterpret_cast<const uint4*>(row + i);
-  const uint4 u4 = *reinterpret_cast<const uint4*>(row + I + i);
-  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
-  const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
-  uint4 o4;
-  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) << 3;
+  if (i >= I) return;
+  for (int t = blockIdx.y; t < T; t += gridDim.y) {
+    const __nv_bfloat16* row = gu + (size_t)t * (size_t)(2 * I);
+    const uint4 g4 = *reinterpret_cast<const uint4*>(row + i);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(row + I + i);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
-    o2[k] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+    for (int k = 0; k < 4; ++k) {
+      const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+      o2[k] = __floats2bfloat162_rn(__fdividef(g.x, 1.f + __expf(-g.x)) * u.x, __fdividef(g.y, 1.f + __expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * (size_t)I + i) = o4;
   }
-  *reinterpret_cast<uint4*>(out + t * (size_t)I + i) = o4;
 }
 
 TS_EXPORT int ts_swiglu(const void* gu, void* out, int act_dtype, int T, int I, void* stream) {
@@ -49,8 +50,9 @@ TS_EXPORT int ts_swiglu(const void* gu, void* out, int act_dtype, int T, int I, 
   if (act_dtype == TS_DTYPE_F32)
     return ts_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)gu, (float*)out, I, total);
   else if (act_dtype == TS_DTYPE_BF16 && I % 8 == 0 && ((uintptr_t)gu | (uintptr_t)out) % 16 == 0) {
-    const size_t total8 = total >> 3;
-    return ts_launch(swiglu_bf16x8_kernel, dim3((unsigned)((total8 + 255) / 256)), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total8);
+    const int threads = I / 8 >= 256 ? 256 : 64;
+    return ts_launch(swiglu_bf16x8_kernel, dim3((unsigned)((I / 8 + threads - 1) / threads), (unsigned)(T < 65535 ? T : 65535)), dim3(threads), 0, s,
+                     (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, T);
   } else if (act_dtype == TS_DTYPE_BF16)
     return ts_launch(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, total);
   else
