@@ -334,3 +334,169 @@ def test_run_order_is_data_a_layer_twice_and_a_shared_cache(tmp_path):
         for (rid, position), row in got.items():
             assert abs(row - want[position].numpy()).max() < 1e-4 * float(want.abs().max()), f"position {position}"
     assert runner.cache_manager.pages_in_use() == 0
+
+
+# ---------------------------------------------------------------------------
+# two more toy parts defined here: a feed-forward with routing and a position encoding with a
+# table of its own (never a model of anyone's: they only show that the interfaces suffice)
+
+
+@dataclass(frozen=True)
+class ToyRoutedConfig:
+    vocab_size: int = 61
+    hidden_size: int = 40
+    num_hidden_layers: int = 2
+    num_experts: int = 3
+    expert_size: int = 24
+    max_positions: int = 96
+    rms_norm_eps: float = 1e-6
+    architectures: tuple = ("ToyRoutedForCausalLM",)
+
+    def to_dict(self):
+        d = asdict(self)
+        d["architectures"] = list(self.architectures)
+        return d
+
+    def save(self, folder):
+        import json
+        from pathlib import Path
+
+        Path(folder).mkdir(parents=True, exist_ok=True)
+        (Path(folder) / "config.json").write_text(json.dumps(self.to_dict()))
+
+
+def _register_routed_toy():
+    from tokensprint_b200.config.registry import register_architecture
+    from tokensprint_b200.models.spec import ModelSpec
+    from tokensprint_b200.parts.base import FeedForward, PartSpec, PositionEncoding, TensorSpec, register_part
+
+    @register_part("feed_forward", "toy_top1_experts", replace=True)
+    class Top1Experts(FeedForward):
+        """Each token goes to the expert its router row scores highest, y = p_e * W2_e relu(W1_e x),
+        p the softmax of the router scores (float32).  The tokens of an expert are gathered on the
+        host's say-so, so a step of it is not a fixed sequence of kernels: graph_safe stays False."""
+
+        def __init__(self, bctx, *, hidden_size, expert_size, num_experts, prefix):
+            self.H, self.I, self.E, self.prefix = hidden_size, expert_size, num_experts, prefix
+
+        def tensor_specs(self):
+            specs = [TensorSpec(self.prefix + "router", (self.E, self.H), "vector")]  # routing in float32
+            for e in range(self.E):
+                specs += [TensorSpec(f"{self.prefix}{e}.w1", (self.I, self.H)), TensorSpec(f"{self.prefix}{e}.w2", (self.H, self.I))]
+            return specs
+
+        def load(self, tensors):
+            self.router = tensors[self.prefix + "router"]
+            self.w1 = [tensors[f"{self.prefix}{e}.w1"] for e in range(self.E)]
+            self.w2 = [tensors[f"{self.prefix}{e}.w2"] for e in range(self.E)]
+
+        def forward(self, x, step):
+            probs = torch.softmax(x.float() @ self.router.t(), dim=-1)
+            top_p, top_e = probs.max(dim=-1)
+            out = torch.zeros_like(x)
+            for e in range(self.E):
+                rows = (top_e == e).nonzero().flatten()
+                if rows.numel():
+                    y = torch.relu(x[rows] @ self.w1[e].t()) @ self.w2[e].t()
+                    out[rows] = (y.float() * top_p[rows, None]).to(x.dtype)
+            return out
+
+    @register_part("position_encoding", "toy_learned_offsets", replace=True)
+    class LearnedOffsets(PositionEncoding):
+        """q and k get a learned row of a table added, by position: an encoding the fused kernel
+        does not know, so the attention mixer norms, calls `apply`, then stores."""
+
+        graph_safe = True  # one gather and two adds on device values
+
+        def __init__(self, bctx, *, dim, max_positions, table):
+            self.dim, self.max_positions, self.table_name = dim, max_positions, table
+
+        def tensor_specs(self):
+            return [TensorSpec(self.table_name, (self.max_positions, self.dim))]
+
+        def load(self, tensors):
+            self.table = tensors[self.table_name]
+
+        def apply(self, q, k, step):
+            rows = self.table[step.positions.long()]
+            q += rows[:, None, :]
+            k += rows[:, None, :]
+
+    @register_architecture("ToyRoutedForCausalLM", config_from_dict=lambda d: ToyRoutedConfig(**{k: (tuple(v) if isinstance(v, list) else v) for k, v in d.items()}))
+    def build(cfg: ToyRoutedConfig):
+        layers = []
+        for i in range(cfg.num_hidden_layers):
+            p = f"m.{i}."
+            mixer = PartSpec("attention", {"hidden_size": cfg.hidden_size, "num_heads": 4, "num_kv_heads": 2, "head_dim": 8,
+                                           "position": PartSpec("toy_learned_offsets", {"dim": 8, "max_positions": cfg.max_positions, "table": p + "pos"}),
+                                           "q": p + "q", "k": p + "k", "v": p + "v", "o": p + "o"})
+            norm = {"dim": cfg.hidden_size, "eps": cfg.rms_norm_eps}
+            layers.append(PartSpec("pre_norm", {
+                "mixer": mixer,
+                "feed_forward": PartSpec("toy_top1_experts", {"hidden_size": cfg.hidden_size, "expert_size": cfg.expert_size,
+                                                              "num_experts": cfg.num_experts, "prefix": p + "experts."}),
+                "mixer_norm": PartSpec("rmsnorm", {**norm, "weight": p + "n1"}),
+                "ffn_norm": PartSpec("rmsnorm", {**norm, "weight": p + "n2"})}))
+        return ModelSpec(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, embedding="m.embed", layers=layers,
+                         final_norm=PartSpec("rmsnorm", {"dim": cfg.hidden_size, "eps": cfg.rms_norm_eps, "weight": "m.norm"}),
+                         lm_head="m.head", max_positions=cfg.max_positions)
+
+
+def _plain_routed_toy(weights, cfg: ToyRoutedConfig, ids):
+    w = {k: v.double() for k, v in weights.items()}
+    T = len(ids)
+    h = plain.embedding(w["m.embed"], ids)
+    for i in range(cfg.num_hidden_layers):
+        p = f"m.{i}."
+        x = plain.rms_norm(h, w[p + "n1"], cfg.rms_norm_eps)
+        off = w[p + "pos"][:T]
+        q = (x @ w[p + "q"].T).view(T, 4, 8) + off[:, None, :]
+        k = (x @ w[p + "k"].T).view(T, 2, 8) + off[:, None, :]
+        v = (x @ w[p + "v"].T).view(T, 2, 8)
+        h = h + plain.causal_attention(q, k, v, scale=8**-0.5).reshape(T, 32) @ w[p + "o"].T
+        x = plain.rms_norm(h, w[p + "n2"], cfg.rms_norm_eps)
+        probs = torch.softmax(x @ w[p + "experts.router"].T, dim=-1)
+        y = torch.zeros_like(x)
+        for t in range(T):
+            e = int(probs[t].argmax())
+            y[t] = probs[t, e] * (torch.relu(x[t] @ w[f"{p}experts.{e}.w1"].T) @ w[f"{p}experts.{e}.w2"].T)
+        h = h + y
+    return plain.rms_norm(h, w["m.norm"], cfg.rms_norm_eps) @ w["m.head"].T
+
+
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding(tmp_path):
+    """Registered here, built from config.json and stepped in every way of cutting, without a
+    change to the framework's files; the model reports that its decode steps cannot be graphs."""
+    from tokensprint_b200.config.registry import unregister_architecture
+    from tokensprint_b200.engine.replay import TraceReplayer
+    from tokensprint_b200.parts.base import unregister_part
+    from tokensprint_b200.weights.loader import write_random_model
+    from tokensprint_b200.weights.safetensors_io import SafetensorsFolder
+
+    _register_routed_toy()
+    try:
+        cfg = ToyRoutedConfig()
+        folder = write_random_model(tmp_path / "routed", cfg, seed=11, dtype="float32", std=0.2)
+        files = SafetensorsFolder(folder)
+        weights = {n: files.tensor(n).clone() for n in files.keys()}
+        assert "m.0.experts.router" in weights and "m.1.pos" in weights and "m.0.experts.2.w2" in weights
+        g = torch.Generator().manual_seed(5)
+        requests = {f"r{i}": torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for i, n in enumerate((2, 17, 40, 70))}
+        want = {rid: _plain_routed_toy(weights, cfg, ids) for rid, ids in requests.items()}
+        # every expert is used by some token, so the routing is exercised
+        many = dict(requests)
+        many.update({k + "x": v for k, v in requests.items()})
+        for steps, reqs in ((trace_whole(requests), requests), (trace_decode_tail(requests, 16), requests),
+                            (trace_portions(requests), requests), (trace_mixed(many, 320, seed=6), many)):
+            replayer = TraceReplayer.from_folder(folder, "float32", 320)
+            assert not replayer.runner.model.graph_safe
+            assert replayer.runner.model.blocks[0].mixer.graph_safe  # the attention with the toy encoding alone could be
+            got = replay_in_process(replayer, steps)
+            for (rid, pos), row in got.items():
+                ref = want[rid.rstrip("x")][pos].numpy()
+                assert abs(row - ref).max() < 1e-4 * abs(want[rid.rstrip("x")]).max(), f"{rid} position {pos}"
+            assert len(got) == sum(len(v) for v in reqs.values())
+    finally:
+        unregister_architecture("ToyRoutedForCausalLM")
+        unregister_part("feed_forward", "toy_top1_experts")
+        unregister_part("position_encoding", "toy_learned_offsets")

@@ -138,8 +138,7 @@ class ModelRunner:
         # model_runner.py:310-390 of the reference); here the graph holds the whole step,
         # final norm and head included.
         self.max_model_len = max_model_len
-        self.use_graphs = (not enforce_eager) and all(
-            getattr(b.mixer, "graph_safe", False) for b in model.blocks)
+        self.use_graphs = (not enforce_eager) and model.graph_safe
         self.graph_buckets = [b for b in (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
                               if b <= max(1, min(max_graph_batch, num_slots))]
         self._graphs: dict[int, "_DecodeGraph"] = {}

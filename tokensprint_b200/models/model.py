@@ -38,6 +38,7 @@ class Model:
         ctx = BuildContext(device=self.device, dtype=dtype)
         self.blocks = [build_part("block", s, ctx) for s in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, ctx)
+        self.graph_safe = all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
 

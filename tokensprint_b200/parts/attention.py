@@ -35,8 +35,6 @@ class AttentionMixer(Mixer):
     into one [(nq + 2 nkv) d, H] matrix.
     """
 
-    graph_safe = True
-
     def __init__(
         self,
         ctx: BuildContext,
@@ -68,6 +66,9 @@ class AttentionMixer(Mixer):
         self.scale = float(scale) if scale is not None else float(head_dim) ** -0.5
         self.names = {"q": q, "k": k, "v": v, "o": o, "q_norm": q_norm, "k_norm": k_norm}
         self.position = build_part("position_encoding", position, ctx) if position is not None else None
+        # the kernels of this mixer read everything a step needs from device memory; a position
+        # encoding that rewrites q and k itself decides for itself
+        self.graph_safe = self.position is None or self.position.graph_safe
         self.dtype = ctx.dtype
         self.qkv_weight: Optional[torch.Tensor] = None
         self.o_weight: Optional[torch.Tensor] = None

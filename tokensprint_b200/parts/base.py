@@ -120,6 +120,11 @@ class LayerCache:
 class Part:
     """Base of all parts: declares its tensors and takes them once loaded."""
 
+    # True when a decode step of this part is a fixed sequence of kernels that read all
+    # per-step values from device memory (no host decisions, no shapes that depend on the
+    # data): only a model whose parts all say so has its decode steps captured in CUDA graphs.
+    graph_safe = False
+
     def first_weight(self) -> Optional[torch.Tensor]:
         """The first large weight this part reads in a step, for the part before it to prefetch."""
         return None
@@ -156,11 +161,6 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    # True when a decode step of this mixer is a fixed sequence of kernels that read all
-    # per-step values from device memory (no host decisions): such a step may be captured
-    # in a CUDA graph.
-    graph_safe = False
-
     def cache_need(self) -> CacheNeed:
         return CacheNeed()
 
@@ -174,7 +174,9 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    """An arrangement of mixer, feed-forward and norms around the residual stream."""
+    """An arrangement of mixer, feed-forward and norms around the residual stream.
+
+    A block sets `graph_safe` from the parts it holds."""
 
     mixer: Mixer
 

@@ -34,6 +34,7 @@ class PreNormBlock(Block):
         self.mixer_norm = build_part("norm", mixer_norm, ctx)
         self.ffn_norm = build_part("norm", ffn_norm, ctx)
         self._parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+        self.graph_safe = all(p.graph_safe for p in self._parts)
 
     def tensor_specs(self) -> list[TensorSpec]:
         return [s for p in self._parts for s in p.tensor_specs()]

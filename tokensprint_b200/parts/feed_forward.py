@@ -19,6 +19,8 @@ class SwiGLUFeedForward(FeedForward):
     gives both halves and the activation kernel reads them side by side.
     """
 
+    graph_safe = True
+
     def __init__(self, ctx: BuildContext, *, hidden_size: int, intermediate_size: int, gate: str, up: str, down: str) -> None:
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
         self.names = {"gate": gate, "up": up, "down": down}

@@ -17,6 +17,8 @@ class RMSNorm(Norm):
     Reference: engine/nn/base_layers.py:38-46 and engine/kernels/triton/rmsnorm.py:19-42.
     """
 
+    graph_safe = True
+
     def __init__(self, ctx: BuildContext, *, dim: int, eps: float, weight: str) -> None:
         self.dim, self.eps, self.weight_name = int(dim), float(eps), weight
         self.weight: Optional[torch.Tensor] = None

@@ -25,6 +25,8 @@ class RotaryEncoding(PositionEncoding):
     (engine/nn/rope.py:105-123, engine/kernels/triton/rope.py:22-65).  The rotation
     itself runs inside the fused q/k kernel; this part owns the frequencies."""
 
+    graph_safe = True
+
     def __init__(self, ctx: BuildContext, *, dim: int, theta: float) -> None:
         if dim % 2:
             raise ValueError(f"rotary width must be even, got {dim}")
