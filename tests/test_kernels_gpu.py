@@ -508,6 +508,91 @@ def test_gemm_skinny_tcgen05(M, N, K, out_dtype):
     assert torch.equal(out1[0], out[M - 1])
 
 
+@pytest.mark.parametrize("scaled", [False, True])
+@pytest.mark.parametrize("M,N,K", [(8, 384, 256), (5, 200, 520), (1, 4096, 4096), (32, 1000, 72), (17, 128, 12288)])
+def test_gemm_skinny_fused_row_scale(M, N, K, scaled):
+    """Plain output, every row multiplied by the 1/rms that the sums of squares give."""
+    from tokensprint_b200 import ops
+
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(DEV, torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(DEV, torch.bfloat16)
+    ssq = (torch.rand(3, M, generator=g) * 50 + 1).to(DEV)
+    width, eps = 96, 1e-3
+    for dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((M, N), float("nan"), device=DEV, dtype=dtype)
+        ops.gemm_skinny_fused(x, w, out=out, scale_ssq=ssq if scaled else None, scale_width=width, scale_eps=eps)
+        torch.cuda.synchronize()
+        ops.check_device_errors()
+        want = x.double() @ w.double().T
+        if scaled:
+            want = want * torch.rsqrt(ssq.double().sum(0) / width + eps)[:, None]
+        assert rel_err(out, want) < (1e-2 if dtype == torch.bfloat16 else 1e-5)
+        out2 = torch.full_like(out, float("nan"))
+        ops.gemm_skinny_fused(x, w, out=out2, scale_ssq=ssq if scaled else None, scale_width=width, scale_eps=eps)
+        assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("M,I,K", [(8, 192, 256), (3, 64, 1032), (32, 12288, 4096), (1, 1024, 4096)])
+def test_gemm_skinny_fused_swiglu(M, I, K):
+    """Gate and up rows stacked in blocks of 64 + 64: the activation comes out of the GEMM."""
+    from tokensprint_b200 import ops
+
+    g = torch.Generator().manual_seed(M + I)
+    x = torch.randn(M, K, generator=g).to(DEV, torch.bfloat16)
+    gate = (torch.randn(I, K, generator=g) * 0.05).to(torch.bfloat16)
+    up = (torch.randn(I, K, generator=g) * 0.05).to(torch.bfloat16)
+    stacked = torch.stack([gate.view(I // 64, 64, K), up.view(I // 64, 64, K)], dim=1).reshape(2 * I, K).contiguous().to(DEV)
+    ssq = (torch.rand(2, M, generator=g) * 5 + 1).to(DEV)
+    out = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.gemm_skinny_fused(x, stacked, out=out, mode=ops.GEMM_EPILOGUE_SWIGLU, scale_ssq=ssq, scale_width=K, scale_eps=1e-6)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    r = torch.rsqrt(ssq.double().sum(0) / K + 1e-6)[:, None].cpu()
+    gd, ud = (x.double().cpu() @ gate.double().T) * r, (x.double().cpu() @ up.double().T) * r
+    want = gd * torch.sigmoid(gd) * ud
+    assert rel_err(out, want) < 1e-2
+    out2 = torch.full_like(out, float("nan"))
+    ops.gemm_skinny_fused(x, stacked, out=out2, mode=ops.GEMM_EPILOGUE_SWIGLU, scale_ssq=ssq, scale_width=K, scale_eps=1e-6)
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 384, 256), (5, 200, 520), (2, 4096, 12288), (32, 4096, 4096), (7, 100, 64)])
+def test_gemm_skinny_fused_residual_and_norm_input(M, N, K):
+    """hidden += product, the next norm's input (without its 1/rms) and the sums of squares that
+    give the 1/rms, all from the GEMM; then a second GEMM uses them and matches norm + product."""
+    from tokensprint_b200 import ops
+
+    g = torch.Generator().manual_seed(N + K)
+    x = torch.randn(M, K, generator=g).to(DEV, torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(DEV, torch.bfloat16)
+    hidden0 = torch.randn(M, N, generator=g).to(DEV)
+    norm_w = (1 + 0.1 * torch.randn(N, generator=g)).to(DEV)
+    hidden = hidden0.clone()
+    xprime = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    tiles = -(-N // 128)
+    ssq = torch.full((tiles, M), float("nan"), device=DEV)
+    ops.gemm_skinny_fused(x, w, mode=ops.GEMM_EPILOGUE_RESIDUAL_NORM, hidden=hidden, norm_weight=norm_w, xprime=xprime, ssq_out=ssq)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    want_h = hidden0.double() + x.double() @ w.double().T
+    assert rel_err(hidden, want_h) < 1e-5
+    assert rel_err(xprime, want_h * norm_w.double()) < 1e-2
+    assert rel_err(ssq.sum(0), (want_h**2).sum(1)) < 1e-5
+    # the same again gives the same bits (one writer per tile, sums in a fixed order)
+    hidden_b, xprime_b, ssq_b = hidden0.clone(), torch.empty_like(xprime), torch.empty_like(ssq)
+    ops.gemm_skinny_fused(x, w, mode=ops.GEMM_EPILOGUE_RESIDUAL_NORM, hidden=hidden_b, norm_weight=norm_w, xprime=xprime_b, ssq_out=ssq_b)
+    assert torch.equal(hidden, hidden_b) and torch.equal(xprime, xprime_b) and torch.equal(ssq, ssq_b)
+    # consumer: a product with the normed rows
+    if N % 8 == 0:
+        eps = 1e-5
+        w2 = (torch.randn(136, N, generator=g) * 0.05).to(DEV, torch.bfloat16)
+        out = torch.empty((M, 136), device=DEV, dtype=torch.float32)
+        ops.gemm_skinny_fused(xprime, w2, out=out, scale_ssq=ssq, scale_width=N, scale_eps=eps)
+        normed = want_h * torch.rsqrt((want_h**2).mean(1, keepdim=True) + eps) * norm_w.double()
+        assert rel_err(out, normed @ w2.double().T) < 1e-2
+
+
 def test_gemm_skinny_refuses_what_it_cannot_take():
     from tokensprint_b200 import ops
 

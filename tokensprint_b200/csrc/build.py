@@ -34,6 +34,9 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fvisibility=hidden",
 ]
 
+# extra flags for tuning builds (for instance -DTS_GEMM_PROBE); they are part of the build's hash
+NVCC_FLAGS += os.environ.get("TS_NVCC_EXTRA_FLAGS", "").split()
+
 _lock = threading.Lock()
 _library: ctypes.CDLL | None = None
 

@@ -40,7 +40,7 @@
 // Optional timestamps for tuning (compile with -DTS_GEMM_PROBE): every CTA records the
 // nanosecond timer at a few points into args.probe[cta * 8 + i].
 #ifdef TS_GEMM_PROBE
-#define TS_PROBE(i) do { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); args.probe[blockIdx.x * 8 + (i)] = t_; } while (0)
+#define TS_PROBE(i) do { if (args.probe) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); args.probe[blockIdx.x * 8 + (i)] = t_; } } while (0)
 #else
 #define TS_PROBE(i) do { } while (0)
 #endif
@@ -52,6 +52,8 @@ constexpr int TILE_K = 64;    // bf16 per stage and row: one 128-byte swizzle at
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
 constexpr int MAX_CONTRIB = 8;   // most CTAs that may share one tile
+constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_RESIDUAL_NORM = 2;
+constexpr int FUSED_MAX_ROWS = 32;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 template <int MPAD>
@@ -73,6 +75,16 @@ struct GemmArgs {
   int tiles, chunks, units_per;  // chunks of K per tile; units (tile x chunk) per CTA
   const char* prefetch;          // weights of the GEMM that follows (may be null)
   unsigned long long prefetch_bytes;
+  // Fused epilogues (M <= 32), see ts_gemm_skinny_fused:
+  int mode;                      // EPI_PLAIN, EPI_SWIGLU or EPI_RESIDUAL_NORM
+  const float* scale_ssq;        // [scale_tiles, M] sums of squares of the rows of x's source, or null
+  int scale_tiles;
+  float scale_width, scale_eps;  // rstd[m] = rsqrt(sum / scale_width + scale_eps) multiplies row m of the product
+  float* hidden;                 // EPI_RESIDUAL_NORM: [M, ldh] float32 residual, += the product
+  const float* norm_w;           //   [N] weight of the norm that follows
+  __nv_bfloat16* xprime;         //   [M, ldh] bf16(hidden * norm_w)
+  float* ssq_out;                //   [tiles, M] sums of squares of the new hidden rows, per tile of 128 columns
+  long long ldh;
 #ifdef TS_GEMM_PROBE
   unsigned long long* probe;
 #endif
@@ -137,6 +149,68 @@ __device__ __forceinline__ Range cta_range(const GemmArgs& a, int cta) {
   return r;
 }
 
+// What the fused epilogues do with a finished tile (`tile`: [M][128] float32 sums of the
+// products, rows of W down the 128).  Called by the 128 epilogue threads together.
+//   EPI_PLAIN with a row scale: out = rstd[m] * sum.
+//   EPI_SWIGLU: the tile's first 64 rows of W are gate rows and the last 64 the up rows of the
+//     same 64 outputs: out[m][64 t + j] = silu(rstd g) * (rstd u).
+//   EPI_RESIDUAL_NORM: hidden[m][n] += sum; xprime = bf16(hidden * norm_w[n]); ssq_out[t][m] =
+//     the sum over the tile's columns of hidden^2 (a warp takes a whole row of the tile, so
+//     the sum needs shuffles only and is the same in every run).
+template <int MPAD>
+__device__ __forceinline__ void fused_epilogue(const GemmArgs& args, int t, int etid, int lane, const float* tile, const float* rstd) {
+  if (args.mode == EPI_SWIGLU) {
+    const int half_n = args.N >> 1;
+    for (int idx = etid; idx < args.M * 16; idx += 128) {
+      const int m = idx >> 4, j = (idx & 15) * 4;
+      const float4 g = *reinterpret_cast<const float4*>(tile + m * TILE_N + j);
+      const float4 u = *reinterpret_cast<const float4*>(tile + m * TILE_N + 64 + j);
+      const float r = rstd[m];
+      const float gs[4] = {g.x * r, g.y * r, g.z * r, g.w * r}, us[4] = {u.x * r, u.y * r, u.z * r, u.w * r};
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(args.out) + (size_t)m * args.ldo + t * 64 + j;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (t * 64 + j + i < half_n) dst[i] = __float2bfloat16_rn(gs[i] / (1.f + __expf(-gs[i])) * us[i]);
+    }
+  } else if (args.mode == EPI_RESIDUAL_NORM) {
+    for (int idx = etid; idx < args.M * 32; idx += 128) {
+      const int m = idx >> 5, nl = (idx & 31) * 4;  // the 32 lanes of a warp share m
+      const float4 v = *reinterpret_cast<const float4*>(tile + m * TILE_N + nl);
+      const float vals[4] = {v.x, v.y, v.z, v.w};
+      const int n0 = t * TILE_N + nl;
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (n0 + i < args.N) {
+          float* hp = args.hidden + (size_t)m * args.ldh + n0 + i;
+          const float h = *hp + vals[i] * rstd[m];
+          *hp = h;
+          args.xprime[(size_t)m * args.ldh + n0 + i] = __float2bfloat16_rn(h * args.norm_w[n0 + i]);
+          ss += h * h;
+        }
+      }
+      ss = ts_warp_sum(ss);
+      if (lane == 0) args.ssq_out[(size_t)t * args.M + m] = ss;
+    }
+  } else {
+    for (int idx = etid; idx < args.M * 32; idx += 128) {
+      const int m = idx >> 5, nl = (idx & 31) * 4;
+      const float4 v = *reinterpret_cast<const float4*>(tile + m * TILE_N + nl);
+      const float vals[4] = {v.x * rstd[m], v.y * rstd[m], v.z * rstd[m], v.w * rstd[m]};
+      const int n0 = t * TILE_N + nl;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (n0 + i < args.N) {
+          if (args.out_f32)
+            reinterpret_cast<float*>(args.out)[(size_t)m * args.ldo + n0 + i] = vals[i];
+          else
+            reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)m * args.ldo + n0 + i] = __float2bfloat16_rn(vals[i]);
+        }
+      }
+    }
+  }
+}
+
 template <int MPAD>
 __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                   const __grid_constant__ CUtensorMap map_x,
@@ -154,6 +228,8 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   __shared__ int last_s;
+  __shared__ __align__(16) float tile_s[(MPAD <= FUSED_MAX_ROWS ? MPAD : 1) * TILE_N];  // a finished tile, for the fused epilogues
+  __shared__ float rstd_s[FUSED_MAX_ROWS];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   ts_pdl_launch_dependents();  // the next kernel may begin its own set-up now
@@ -204,6 +280,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
         tma_load_2d(smem_u32(smem + (size_t)i * C::STAGE_BYTES), &map_w, bar, kc * TILE_K, t * TILE_N);
       }
       ts_pdl_wait();
+      TS_PROBE(6);
       for (int i = 0; i < early; ++i) {
         const int u = range.u0 + i;
         const int kc = u % chunks;
@@ -280,6 +357,17 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
     const int quarter = warp & 3;
     const int etid = (warp - 2) * 32 + lane;  // 0..127 among the epilogue threads
     ts_pdl_wait();  // nothing is stored before the kernels ahead in the stream are done
+    const bool fused = MPAD <= FUSED_MAX_ROWS && (args.mode != EPI_PLAIN || args.scale_ssq != nullptr);
+    if (fused) {
+      // rstd of every row of x's source, from the per-tile sums of squares the kernel before left
+      if (etid < args.M) {
+        float sum = 0.f;
+        if (args.scale_ssq != nullptr)
+          for (int j = 0; j < args.scale_tiles; ++j) sum += __ldcg(args.scale_ssq + (size_t)j * args.M + etid);
+        rstd_s[etid] = args.scale_ssq != nullptr ? rsqrtf(sum / args.scale_width + args.scale_eps) : 1.f;
+      }
+      epilogue_sync();
+    }
     int item = 0;
     for (int t = t_first; t <= t_last; ++t, ++item) {
       const int k0 = max(range.u0, t * chunks) - t * chunks;
@@ -319,6 +407,8 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
             const float v = __uint_as_float(r[c][i]);
             if (!whole)
               part[(size_t)m * TILE_N + n_local] = v;
+            else if (fused)
+              tile_s[(MPAD <= FUSED_MAX_ROWS ? m : 0) * TILE_N + n_local] = v;
             else if (n < args.N) {
               if (args.out_f32)
                 reinterpret_cast<float*>(args.out)[(size_t)m * args.ldo + n] = v;
@@ -328,6 +418,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
           }
         }
       }
+      bool last = false;
       if (!whole) {
         // Ticket: whoever arrives last for this tile adds the slots, in contributor order.
         const int c_first = (int)(((long long)t * chunks) / args.units_per);
@@ -339,7 +430,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
           last_s = (ticket == c_last - c_first) ? 1 : 0;
         }
         epilogue_sync();
-        const bool last = last_s != 0;
+        last = last_s != 0;
         epilogue_sync();  // everyone has read the flag before the next tile may rewrite it
         if (last) {
           __threadfence();
@@ -366,6 +457,10 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
               if (j < nc) { sum.x += v[j].x; sum.y += v[j].y; sum.z += v[j].z; sum.w += v[j].w; }
             const int nn = t * TILE_N + nl;
             const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+            if (fused) {
+              *reinterpret_cast<float4*>(&tile_s[(MPAD <= FUSED_MAX_ROWS ? m : 0) * TILE_N + nl]) = sum;
+              continue;
+            }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               if (nn + j < args.N) {
@@ -378,6 +473,11 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
           }
           if (etid == 0) args.counters[t] = 0;
         }
+      }
+      if (fused && (whole || last)) {  // the same for all epilogue threads
+        epilogue_sync();  // tile_s holds the tile's final sums
+        fused_epilogue<MPAD>(args, t, etid, lane, tile_s, rstd_s);
+        epilogue_sync();  // before the next tile overwrites tile_s
       }
     }
   }
@@ -499,6 +599,7 @@ void plan(int N, int K, int* tiles, int* chunks, int* units_per, int* ctas) {
 
 #ifdef TS_GEMM_PROBE
 unsigned long long* ts_gemm_probe_buffer = nullptr;
+TS_EXPORT void ts_gemm_set_probe(unsigned long long* buffer) { ts_gemm_probe_buffer = buffer; }
 #endif
 
 // Floats of scratch the caller brings for an [N, K] weight and M rows: two shared-tile slots
@@ -517,11 +618,45 @@ TS_EXPORT int ts_gemm_skinny_max_rows() { return 128; }
 // kernel sets to 1 if one of its waits gave up.
 // `prefetch` / `prefetch_bytes`: optionally the start of the weights the next GEMM will read (16-byte
 // aligned); the kernel asks for them to be brought into L2 once its own loads are issued.
+// The same product with work that would otherwise be kernels of their own done where the tile
+// is finished (M <= 32 rows):
+//   scale_ssq [scale_tiles, M] (or null): x holds rows of a source that still lack their
+//     norm's 1/rms; the sums of squares of the source rows, per 128 columns, come from the kernel
+//     that wrote it; every product row m is multiplied by rsqrt(sum_m / scale_width + scale_eps).
+//   mode 0: out as in ts_gemm_skinny_bf16.
+//   mode 1 (N even, rows of w in blocks of 128: 64 gate rows, then the 64 up rows of the same
+//     outputs): out [M, ldo] bf16 = silu(gate) * up, N / 2 columns.
+//   mode 2: hidden [M, ldh] float32 += product; xprime [M, ldh] bf16 = hidden * norm_w;
+//     ssq_out [ceil(N / 128), M] = sums of squares of the new hidden rows per 128 columns.
+TS_EXPORT int ts_gemm_skinny_fused(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
+                                   long long ldw, long long ldo, int out_f32, int mode, const float* scale_ssq,
+                                   int scale_tiles, float scale_width, float scale_eps, float* hidden, long long ldh,
+                                   const float* norm_w, void* xprime, float* ssq_out, float* partial, int* counters,
+                                   int* error, const void* prefetch, long long prefetch_bytes, void* stream_);
+
 TS_EXPORT int ts_gemm_skinny_bf16(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
                                   long long ldw, long long ldo, int out_f32, float* partial, int* counters,
                                   int* error, const void* prefetch, long long prefetch_bytes, void* stream_) {
+  return ts_gemm_skinny_fused(x, w, out, M, N, K, ldx, ldw, ldo, out_f32, 0, nullptr, 0, 1.f, 0.f, nullptr, 0, nullptr,
+                              nullptr, nullptr, partial, counters, error, prefetch, prefetch_bytes, stream_);
+}
+
+TS_EXPORT int ts_gemm_skinny_fused(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
+                                   long long ldw, long long ldo, int out_f32, int mode, const float* scale_ssq,
+                                   int scale_tiles, float scale_width, float scale_eps, float* hidden, long long ldh,
+                                   const float* norm_w, void* xprime, float* ssq_out, float* partial, int* counters,
+                                   int* error, const void* prefetch, long long prefetch_bytes, void* stream_) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || ldx < K || ldw < K || ldo < N || counters == nullptr || error == nullptr || partial == nullptr)
+  if (mode != EPI_PLAIN || scale_ssq != nullptr) {
+    if (M > FUSED_MAX_ROWS) return TS_ERR_UNSUPPORTED_SIZE;
+    if (scale_ssq != nullptr && (scale_tiles <= 0 || !(scale_width > 0.f))) return TS_ERR_BAD_ARGUMENT;
+    if (mode == EPI_SWIGLU && ((N & 1) || out_f32 || ldo < N / 2)) return TS_ERR_BAD_ARGUMENT;
+    if (mode == EPI_RESIDUAL_NORM && (hidden == nullptr || norm_w == nullptr || xprime == nullptr || ssq_out == nullptr || ldh < N))
+      return TS_ERR_BAD_ARGUMENT;
+    if (mode < 0 || mode > EPI_RESIDUAL_NORM) return TS_ERR_BAD_ARGUMENT;
+  }
+  if (mode == EPI_PLAIN && ldo < N) return TS_ERR_BAD_ARGUMENT;
+  if (K <= 0 || ldx < K || ldw < K || counters == nullptr || error == nullptr || partial == nullptr)
     return TS_ERR_BAD_ARGUMENT;
   if (M > 128 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)partial % 16))
     return TS_ERR_UNSUPPORTED_SIZE;
@@ -543,10 +678,22 @@ TS_EXPORT int ts_gemm_skinny_bf16(const void* x, const void* w, void* out, int M
   a.K = K;
   a.ldo = (int)ldo;
   a.out_f32 = out_f32;
+  a.mode = mode;
+  a.scale_ssq = scale_ssq;
+  a.scale_tiles = scale_tiles;
+  a.scale_width = scale_width;
+  a.scale_eps = scale_eps;
+  a.hidden = hidden;
+  a.norm_w = norm_w;
+  a.xprime = (__nv_bfloat16*)xprime;
+  a.ssq_out = ssq_out;
+  a.ldh = ldh;
   a.prefetch = (prefetch_bytes > 0 && ((uintptr_t)prefetch % 16) == 0) ? (const char*)prefetch : nullptr;
   a.prefetch_bytes = prefetch_bytes > 0 ? (unsigned long long)prefetch_bytes : 0ull;
 #ifdef TS_GEMM_PROBE
-  a.probe = ts_gemm_probe_buffer;
+  // every launch writes a region of its own (256 CTAs x 8 stamps), 512 regions in turn
+  static int probe_launch = 0;
+  a.probe = ts_gemm_probe_buffer ? ts_gemm_probe_buffer + (size_t)(probe_launch++ % 512) * 2048 : nullptr;
 #endif
   cudaStream_t stream = (cudaStream_t)stream_;
   switch (mpad) {

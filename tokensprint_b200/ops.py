@@ -637,6 +637,90 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, prefet
         _stream()))
 
 
+_SIGNATURES["ts_gemm_skinny_fused"] = [
+    _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_int,
+    _c_int, _c_void_p, _c_int, _c_float, _c_float, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p,
+    _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll, _c_void_p,
+]
+GEMM_FUSED_MAX_ROWS = 32
+GEMM_EPILOGUE_PLAIN, GEMM_EPILOGUE_SWIGLU, GEMM_EPILOGUE_RESIDUAL_NORM = 0, 1, 2
+
+
+def gemm_skinny_fused(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    *,
+    out: Optional[torch.Tensor] = None,
+    mode: int = GEMM_EPILOGUE_PLAIN,
+    scale_ssq: Optional[torch.Tensor] = None,
+    scale_width: int = 1,
+    scale_eps: float = 0.0,
+    hidden: Optional[torch.Tensor] = None,
+    norm_weight: Optional[torch.Tensor] = None,
+    xprime: Optional[torch.Tensor] = None,
+    ssq_out: Optional[torch.Tensor] = None,
+    prefetch: Optional[torch.Tensor] = None,
+) -> None:
+    """x[M,K] @ w[N,K]^T on the tcgen05 tensor cores (M <= 32) with the work of the neighbouring
+    small kernels done where each tile is finished.
+
+    scale_ssq [tiles, M] float32: x lacks its norm's 1/rms (x = source * norm weight); the sums
+    of squares of the source rows per 128 columns, as a GEMM in mode 2 leaves them; every row m of
+    the product is multiplied by rsqrt(sum_m / scale_width + scale_eps).
+    mode GEMM_EPILOGUE_PLAIN: out[M,N] bf16 or float32.
+    mode GEMM_EPILOGUE_SWIGLU: the rows of w come in blocks of 128, 64 gate rows and then the 64 up
+      rows of the same outputs; out[M,N/2] bf16 = silu(gate) * up.
+    mode GEMM_EPILOGUE_RESIDUAL_NORM: hidden[M,N] float32 += product; xprime[M,N] bf16 = hidden *
+      norm_weight; ssq_out[ceil(N/128), M] float32 = sums of squares of the new hidden rows.
+    """
+    if not gemm_skinny_supported(x, w) or x.shape[0] > GEMM_FUSED_MAX_ROWS:
+        raise KernelError(
+            f"gemm_skinny_fused: needs bfloat16, at most {GEMM_FUSED_MAX_ROWS} rows, K a multiple of 8 and 16-byte "
+            f"aligned rows; got x {tuple(x.shape)} {x.dtype} strides {x.stride()}, w {tuple(w.shape)} {w.dtype}")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"gemm_skinny_fused: shapes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    ldo, out_f32 = 0, 0
+    if mode in (GEMM_EPILOGUE_PLAIN, GEMM_EPILOGUE_SWIGLU):
+        cols = N if mode == GEMM_EPILOGUE_PLAIN else N // 2
+        if out is None or not out.is_cuda or tuple(out.shape) != (M, cols) or out.stride(1) != 1:
+            raise KernelError(f"gemm_skinny_fused: out must be [{M},{cols}]")
+        if out.dtype not in ((torch.bfloat16, torch.float32) if mode == GEMM_EPILOGUE_PLAIN else (torch.bfloat16,)):
+            raise KernelError(f"gemm_skinny_fused: out dtype {out.dtype} not taken in mode {mode}")
+        if mode == GEMM_EPILOGUE_SWIGLU and N % 128:
+            raise KernelError("gemm_skinny_fused: the gate/up blocks need N to be a multiple of 128")
+        ldo, out_f32 = out.stride(0), 1 if out.dtype == torch.float32 else 0
+    elif mode == GEMM_EPILOGUE_RESIDUAL_NORM:
+        tiles = -(-N // 128)
+        ok = (
+            hidden is not None and hidden.dtype == torch.float32 and tuple(hidden.shape) == (M, N) and hidden.is_contiguous()
+            and xprime is not None and xprime.dtype == torch.bfloat16 and tuple(xprime.shape) == (M, N) and xprime.is_contiguous()
+            and norm_weight is not None and norm_weight.dtype == torch.float32 and norm_weight.numel() == N and norm_weight.is_contiguous()
+            and ssq_out is not None and ssq_out.dtype == torch.float32 and ssq_out.numel() >= tiles * M and ssq_out.is_contiguous()
+        )
+        if not ok:
+            raise KernelError("gemm_skinny_fused: mode 2 needs hidden f32 [M,N], xprime bf16 [M,N], norm_weight f32 [N], ssq_out f32 [tiles,M]")
+    else:
+        raise KernelError(f"gemm_skinny_fused: no mode {mode}")
+    scale_tiles = 0
+    if scale_ssq is not None:
+        if scale_ssq.dtype != torch.float32 or not scale_ssq.is_contiguous() or scale_ssq.dim() != 2 or scale_ssq.shape[1] != M:
+            raise KernelError("gemm_skinny_fused: scale_ssq must be float32 [tiles, M]")
+        scale_tiles = scale_ssq.shape[0]
+    scratch_floats = library().ts_gemm_skinny_scratch_floats
+    scratch_floats.restype = _c_ll
+    partial = torch.empty(max(4, scratch_floats(M, N, K)), dtype=torch.float32, device=x.device)
+    counters, error = _gemm_workspace(x.device)
+    _check("gemm_skinny_fused", _fn("ts_gemm_skinny_fused")(
+        x.data_ptr(), w.data_ptr(), _ptr(out), M, N, K, x.stride(0), w.stride(0), ldo, out_f32,
+        int(mode), _ptr(scale_ssq), scale_tiles, float(scale_width), float(scale_eps),
+        _ptr(hidden), N, _ptr(norm_weight), _ptr(xprime), _ptr(ssq_out),
+        _ptr(partial), counters.data_ptr(), error.data_ptr(),
+        _ptr(prefetch), 0 if prefetch is None else min(prefetch.numel() * prefetch.element_size(), GEMM_PREFETCH_BYTES),
+        _stream()))
+
+
 def check_device_errors() -> None:
     """Raises if a kernel reported that one of its bounded waits gave up.  Cheap: reads
     pinned host words; call it wherever the host has just synchronised anyway."""
