@@ -500,3 +500,43 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding(tmp_path):
         unregister_architecture("ToyRoutedForCausalLM")
         unregister_part("feed_forward", "toy_top1_experts")
         unregister_part("position_encoding", "toy_learned_offsets")
+
+
+def test_norms_and_activation_folded_into_the_products_change_nothing_but_rounding(tmp_path, monkeypatch):
+    """Steps of few tokens fold the norms, the residual sums and the SwiGLU activation into the
+    epilogues of the engine's own GEMM (widths that are multiples of 64 allow it).  The same
+    trace with the folding switched off, and the float32 path, must give the same logits up to
+    bfloat16 rounding; and the folded path must really have run."""
+    from tests.tiny_configs import TINY_A, tiny_weights, write_model_folder
+    from tokensprint_b200 import ops
+    from tokensprint_b200.engine.replay import TraceReplayer
+    from tokensprint_b200.parts import linear as linear_module
+
+    cfg = dict(TINY_A)
+    cfg.update(hidden_size=192, intermediate_size=320, num_attention_heads=4, num_key_value_heads=2, head_dim=32, num_hidden_layers=3,
+               vocab_size=520, tie_word_embeddings=False)
+    weights = tiny_weights(cfg, 5, std=0.05)
+    folder = write_model_folder(tmp_path / "m", cfg, weights)
+    g = torch.Generator().manual_seed(1)
+    requests = {f"r{i}": torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for i, n in enumerate((40, 9, 77))}
+    steps = trace_decode_tail(requests, 24)
+
+    calls = []
+    real = ops.gemm_skinny_fused
+    monkeypatch.setattr(ops, "gemm_skinny_fused", lambda *a, **k: (calls.append(k.get("mode", 0)), real(*a, **k))[1])
+    folded = replay_in_process(TraceReplayer.from_folder(folder, "bfloat16", 512), steps)
+    assert {0, ops.GEMM_EPILOGUE_SWIGLU, ops.GEMM_EPILOGUE_RESIDUAL_NORM} <= set(calls), "the folded path did not run"
+    calls.clear()
+    monkeypatch.setattr(linear_module, "FOLD_NORMS", False)
+    plain_path = replay_in_process(TraceReplayer.from_folder(folder, "bfloat16", 512), steps)
+    assert not calls
+    exact = replay_in_process(TraceReplayer.from_folder(folder, "float32", 512), steps)
+    scale = max(float(abs(v).max()) for v in exact.values())
+    assert set(folded) == set(plain_path) == set(exact)
+    for key in exact:
+        assert float(abs(folded[key] - exact[key]).max()) < 4e-2 * scale, f"folded, {key}"
+        assert float(abs(plain_path[key] - exact[key]).max()) < 4e-2 * scale, f"unfolded, {key}"
+    # the folded path rounds less often than the unfolded one: on average it is no further from float32
+    err_f = sum(float(abs(folded[k] - exact[k]).mean()) for k in exact)
+    err_u = sum(float(abs(plain_path[k] - exact[k]).mean()) for k in exact)
+    assert err_f < 1.5 * err_u

@@ -211,6 +211,7 @@ class ModelRunner:
         step.host_seq_starts = [e.start for e in entries]
         step.host_seq_lens = lens
         step.host_state_slots = [e.cache.slot for e in entries]
+        step.rows_all = all(list(e.want) == list(range(n)) for e, n in zip(entries, lens))
         return step, layout.view(dev, "rows"), R
 
     def _fill(self, host, layout: _Layout, entries: Sequence[StepEntry], lens: Sequence[int]) -> None:
@@ -337,6 +338,7 @@ class ModelRunner:
         host.numpy()[layout.sections["rows"][0] : layout.sections["rows"][0] + bucket] = np.arange(bucket)
         dev.copy_(host)
         step = self._context(dev, layout, 1, self.max_model_len)
+        step.rows_all = True  # in a graph every lane's logits are computed
         rows = layout.view(dev, "rows")
         torch.cuda.synchronize(self.device)
         side = torch.cuda.Stream(self.device)

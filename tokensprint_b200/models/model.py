@@ -10,8 +10,8 @@ import torch
 import tokensprint_b200.parts  # noqa: F401  (registers the built-in parts)
 from tokensprint_b200 import ops
 from tokensprint_b200.models.spec import ModelSpec
-from tokensprint_b200.parts.base import BuildContext, CacheNeed, LayerCache, StepContext, TensorSpec, build_part
-from tokensprint_b200.parts.linear import linear_float32_out
+from tokensprint_b200.parts.base import BuildContext, CacheNeed, LayerCache, PreNormed, StepContext, TensorSpec, build_part
+from tokensprint_b200.parts.linear import folding_possible, linear_float32_out, linear_scaled
 from tokensprint_b200.weights.loader import LoadedTensors, WeightSource, check_tensors
 
 
@@ -115,15 +115,25 @@ class Model:
         ops.embed_gather(hidden, self.embedding, step.token_ids)
         pending = None
         order = self.spec.run_order
+        # the final norm may be prepared by the last block when every row's logits are wanted
+        # and the head product is one that applies the missing 1/rms
+        fold_final = step.rows_all and folding_possible(T, self.dtype, self.head)
         for i, run in enumerate(order):
-            # what is read after this block: the next block's first matrix, or the head
-            step.weight_after = self.blocks[order[i + 1].layer].first_weight() if i + 1 < len(order) else self.head
+            # what is read after this block: the next block's first matrix and first norm, or the head and the final norm
+            last = i + 1 == len(order)
+            step.weight_after = self.head if last else self.blocks[order[i + 1].layer].first_weight()
+            step.norm_after = (self.final_norm if fold_final else None) if last else self.blocks[order[i + 1].layer].entry_norm()
             pending = self.blocks[run.layer].forward(hidden, pending, step, caches[i])
-        step.weight_after = None
+        step.weight_after = step.norm_after = None
         return hidden, pending
 
-    def logits(self, hidden: torch.Tensor, pending: Optional[torch.Tensor], rows: torch.Tensor, num_rows: int) -> torch.Tensor:
-        """Final norm on the wanted rows only, then the head: float32 [R, V] (engine/model.py:75-86)."""
+    def logits(self, hidden: torch.Tensor, pending, rows: torch.Tensor, num_rows: int) -> torch.Tensor:
+        """Final norm on the wanted rows only, then the head: float32 [R, V] (engine/model.py:75-86).
+        `pending`: the last branch output not yet added, or a PreNormed of the final norm."""
+        if isinstance(pending, PreNormed):
+            if num_rows == hidden.shape[0] and folding_possible(num_rows, self.dtype, self.head):
+                return linear_scaled(pending, self.head, float32_out=True)
+            pending = None  # `hidden` is complete: norm it as usual
         normed = torch.empty((num_rows, self.spec.hidden_size), device=self.device, dtype=self.dtype)
         self.final_norm.forward(hidden, pending, normed, row_index=rows)
         return linear_float32_out(normed, self.head)

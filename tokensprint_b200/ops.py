@@ -27,7 +27,7 @@ _SIGNATURES = {
     "ts_embed_gather": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "ts_add_rmsnorm": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
     "ts_residual_add": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
-    "ts_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "ts_qk_norm_rope_store": [
         _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
         _c_float, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
@@ -166,14 +166,17 @@ def residual_add(hidden: torch.Tensor, delta: torch.Tensor) -> None:
         hidden.data_ptr(), delta.data_ptr(), _act_code("delta", delta), hidden.numel(), _stream()))
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t,i] = silu(gate_up[t,i]) * gate_up[t,I+i].  gate_up [T,2I], out [T,I]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
+    """out[t,i] = silu(gate[t,i]) * up[t,i].  gate_up [T,2I], out [T,I].  block 0: gate i at column
+    i, up at I + i; block 64: blocks of 128 columns, 64 gates and then their 64 ups."""
     _cuda_contig("gate_up", gate_up)
     _cuda_contig("out", out, gate_up.dtype)
     T, I = out.shape
     if gate_up.shape != (T, 2 * I):
         raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)} does not match out {tuple(out.shape)}")
-    _check("swiglu", _fn("ts_swiglu")(gate_up.data_ptr(), out.data_ptr(), _act_code("out", out), T, I, _stream()))
+    if block not in (0, 64) or (block and I % 64):
+        raise KernelError(f"swiglu: block must be 0 or 64 (and then divide the width), got {block} for width {I}")
+    _check("swiglu", _fn("ts_swiglu")(gate_up.data_ptr(), out.data_ptr(), _act_code("out", out), T, I, int(block), _stream()))
 
 
 QK_ROPE_MAX_HEAD_DIM = 512

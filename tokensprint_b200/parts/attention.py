@@ -18,7 +18,7 @@ from tokensprint_b200.parts.base import (
     build_part,
     register_part,
 )
-from tokensprint_b200.parts.linear import linear
+from tokensprint_b200.parts.linear import folding_possible, linear, linear_into_residual, linear_scaled
 
 
 @register_part("mixer", "attention")
@@ -107,14 +107,21 @@ class AttentionMixer(Mixer):
         if self.position is not None:
             self.position.load(tensors)
 
-    def forward(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
+    def can_fold(self, num_tokens: int, dtype: torch.dtype) -> bool:
+        return folding_possible(num_tokens, dtype, self.qkv_weight, self.o_weight)
+
+    def forward(self, x, step: StepContext, cache: LayerCache, fold: Optional[ResidualNorm] = None):
+        """x: [T, H], or a PreNormed (its missing 1/rms is applied by the q/k/v product).  With
+        `fold` the output projection adds its result into fold.hidden itself and the PreNormed of
+        the norm that follows is returned instead of the branch output."""
         if cache.k_pages is None or cache.group < 0:
             raise ops.KernelError("attention: this mixer needs cache pages (none were bound to its run)")
-        T = x.shape[0]
+        xt = x if isinstance(x, torch.Tensor) else x.x
+        T = xt.shape[0]
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         tables = step.groups[cache.group]
-        qkv = linear(x, self.qkv_weight, next_weight=self.o_weight)
-        q = torch.empty((T, nq * d), device=x.device, dtype=x.dtype)
+        qkv = linear_scaled(x, self.qkv_weight, next_weight=self.o_weight)
+        q = torch.empty((T, nq * d), device=xt.device, dtype=xt.dtype)
         inv_freq = self.position.rotary_inv_freq() if self.position is not None else None
         fused = self.position is None or inv_freq is not None
         if fused and cache.writes:
@@ -126,8 +133,10 @@ class AttentionMixer(Mixer):
             self._queries_only(qkv, q, step, inv_freq)
         else:
             self._unfused(qkv, q, step, cache, tables)
-        out = torch.empty((T, nq * d), device=x.device, dtype=x.dtype)
+        out = torch.empty((T, nq * d), device=xt.device, dtype=xt.dtype)
         self._attend(q, out, step, cache, tables)
+        if fold is not None:
+            return linear_into_residual(out, self.o_weight, fold, next_weight=step.weight_after)
         return linear(out, self.o_weight, next_weight=step.weight_after)
 
     # -- attention proper ---------------------------------------------------

@@ -97,9 +97,44 @@ class StepContext:
     host_seq_lens: list[int] = field(default_factory=list)
     host_state_slots: list[int] = field(default_factory=list)
     decode_only: bool = False
+    rows_all: bool = False  # the logits of every token are wanted, in the tokens' order
     # A hint, set by whoever calls a part: the first weight matrix that will be read after the
     # part returns (the part may hand it to its last product for prefetching; may be None).
     weight_after: Optional[torch.Tensor] = None
+    # Likewise the norm that will read the residual stream after the part returns (a block's
+    # last part may prepare that norm's input, see ResidualNorm).
+    norm_after: Optional["Norm"] = None
+
+
+@dataclass
+class NormParams:
+    """What a norm of the form x * rsqrt(mean(x^2) + eps) * weight is made of, for a part that
+    offers to fold it into its own kernels."""
+
+    weight: torch.Tensor  # [width] float32
+    eps: float
+    width: int
+
+
+@dataclass
+class ResidualNorm:
+    """A request to a part's last product: do not return the branch output, add it into the
+    float32 residual `hidden` yourself and prepare the input of the norm that follows."""
+
+    hidden: torch.Tensor  # [T, width] float32, updated in place
+    norm: NormParams
+
+
+@dataclass
+class PreNormed:
+    """Rows on which a norm is all but done: `x` = bf16(hidden * norm weight) and `ssq` the sums
+    of squares of the hidden rows per 128 columns ([tiles, T] float32); the 1/rms that is still
+    missing is a factor per row, which a product of x with a matrix can apply to its result."""
+
+    x: torch.Tensor
+    ssq: torch.Tensor
+    width: int
+    eps: float
 
 
 @dataclass
@@ -137,6 +172,11 @@ class Part:
 
 
 class Norm(Part):
+    def params(self) -> Optional[NormParams]:
+        """The norm's weight, eps and width if it is a plain RMS norm that other parts may fold
+        into their kernels; None keeps it a step of its own."""
+        return None
+
     def forward(
         self,
         hidden: torch.Tensor,
@@ -161,6 +201,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True if forward() also takes `x` as PreNormed and a keyword `fold: ResidualNorm`, and then
+    # may return a PreNormed instead of its output (see blocks.PreNormBlock); False: plain
+    # tensors in and out, the block does the norms and the residual sums around it.
+    folds_norms = False
+
     def cache_need(self) -> CacheNeed:
         return CacheNeed()
 
@@ -169,6 +214,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    folds_norms = False  # as for Mixer
+
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
@@ -180,17 +227,24 @@ class Block(Part):
 
     mixer: Mixer
 
+    def entry_norm(self) -> Optional["Norm"]:
+        """The norm that reads the residual stream first in this block, if the part before may
+        prepare its input (see ResidualNorm); None: nobody may."""
+        return None
+
     def forward(
         self,
         hidden: torch.Tensor,
-        pending: Optional[torch.Tensor],
+        pending,
         step: StepContext,
         cache: LayerCache,
-    ) -> Optional[torch.Tensor]:
+    ):
         """Runs the layer on the float32 residual `hidden` ([T,H], updated in place).
 
         `pending` is a branch output not yet added to `hidden` (the next norm adds it
-        in the same pass); the return value is this layer's own pending output.
+        in the same pass); the return value is this layer's own pending output.  A block that
+        names its entry_norm() may be handed a PreNormed for it instead, and a block may return
+        one made for `step.norm_after`.
         """
         raise NotImplementedError
 

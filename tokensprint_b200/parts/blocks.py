@@ -11,6 +11,8 @@ from tokensprint_b200.parts.base import (
     BuildContext,
     LayerCache,
     PartSpec,
+    PreNormed,
+    ResidualNorm,
     StepContext,
     TensorSpec,
     build_part,
@@ -43,15 +45,40 @@ class PreNormBlock(Block):
         for p in self._parts:
             p.load(tensors)
 
-    def forward(self, hidden, pending, step: StepContext, cache: LayerCache) -> Optional[torch.Tensor]:
-        normed = torch.empty(hidden.shape, device=hidden.device, dtype=self.dtype)
-        after_block = step.weight_after
-        self.mixer_norm.forward(hidden, pending, normed)
+    def entry_norm(self):
+        return self.mixer_norm
+
+    def forward(self, hidden, pending, step: StepContext, cache: LayerCache):
+        """`pending`: None, the last branch output not yet added to `hidden`, or a PreNormed that
+        stands for mixer_norm(hidden) (the part before prepared it; `hidden` is then complete).
+
+        Where mixer and feed-forward offer it (`folds_norms`, and `can_fold` for this step), the
+        norms and residual sums between them are folded into their products: the mixer's last
+        product adds into `hidden` and prepares the feed-forward's input, the feed-forward's last
+        product does the same for `step.norm_after`.  Otherwise every norm is a step of its own."""
+        T = hidden.shape[0]
+        after_block, norm_after = step.weight_after, step.norm_after
+        mixer_folds = self.mixer.folds_norms and self.mixer.can_fold(T, self.dtype)
+        ffn_folds = self.feed_forward.folds_norms and self.feed_forward.can_fold(T, self.dtype)
+
+        if isinstance(pending, PreNormed) and mixer_folds:
+            x = pending
+        else:
+            x = torch.empty(hidden.shape, device=hidden.device, dtype=self.dtype)
+            self.mixer_norm.forward(hidden, None if isinstance(pending, PreNormed) else pending, x)
         step.weight_after = self.feed_forward.first_weight()
-        mixed = self.mixer.forward(normed, step, cache)
-        self.ffn_norm.forward(hidden, mixed, normed)
+        ffn_norm = self.ffn_norm.params()
+        if mixer_folds and ffn_folds and ffn_norm is not None:
+            x = self.mixer.forward(x, step, cache, fold=ResidualNorm(hidden, ffn_norm))
+        else:
+            mixed = self.mixer.forward(x, step, cache)
+            x = torch.empty(hidden.shape, device=hidden.device, dtype=self.dtype)
+            self.ffn_norm.forward(hidden, mixed, x)
         step.weight_after = after_block
-        return self.feed_forward.forward(normed, step)
+        next_norm = norm_after.params() if norm_after is not None else None
+        if ffn_folds and next_norm is not None:
+            return self.feed_forward.forward(x, step, fold=ResidualNorm(hidden, next_norm))
+        return self.feed_forward.forward(x, step)
 
     def first_weight(self):
         return self.mixer.first_weight()

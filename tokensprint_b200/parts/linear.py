@@ -10,6 +10,7 @@ path whatever torch's global switches say.
 
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -46,6 +47,56 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
     else:
         raise ops.KernelError(f"linear: unsupported dtype {x.dtype}")
     return out
+
+
+FOLD_NORMS = os.environ.get("TS_FOLD_NORMS", "1") != "0"  # 0: every norm and activation stays a kernel of its own
+
+
+def folding_possible(num_tokens: int, dtype: torch.dtype, *weights: torch.Tensor) -> bool:
+    """Whether the products of a step of `num_tokens` rows with these weights run through the
+    engine's own GEMM with fused epilogues (so norms, residual sums and the activation can be
+    folded into them): bfloat16, few rows, shapes the kernel takes."""
+    if not FOLD_NORMS or dtype != torch.bfloat16 or not 0 < num_tokens <= min(SKINNY_ROWS, ops.GEMM_FUSED_MAX_ROWS):
+        return False
+    return all(w is not None and w.is_cuda and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.stride(1) == 1
+               and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0 for w in weights)
+
+
+def linear_scaled(x: "PreNormed | torch.Tensor", weight: torch.Tensor, next_weight: Optional[torch.Tensor] = None,
+                  float32_out: bool = False) -> torch.Tensor:
+    """linear() for an input whose norm still lacks its 1/rms (a PreNormed): the factor is applied
+    to the rows of the product.  A plain tensor is passed on to linear()."""
+    if isinstance(x, torch.Tensor):
+        return linear_float32_out(x, weight) if float32_out else linear(x, weight, next_weight=next_weight)
+    out = torch.empty((x.x.shape[0], weight.shape[0]), device=x.x.device, dtype=torch.float32 if float32_out else x.x.dtype)
+    ops.gemm_skinny_fused(x.x, weight, out=out, scale_ssq=x.ssq, scale_width=x.width, scale_eps=x.eps, prefetch=next_weight)
+    return out
+
+
+def linear_swiglu(x: "PreNormed | torch.Tensor", gate_up_blocks: torch.Tensor, next_weight: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) in one kernel; the rows of `gate_up_blocks` come in blocks of 64
+    gate rows and the 64 up rows of the same outputs."""
+    xt = x if isinstance(x, torch.Tensor) else x.x
+    out = torch.empty((xt.shape[0], gate_up_blocks.shape[0] // 2), device=xt.device, dtype=xt.dtype)
+    if isinstance(x, torch.Tensor):
+        ops.gemm_skinny_fused(x, gate_up_blocks, out=out, mode=ops.GEMM_EPILOGUE_SWIGLU, prefetch=next_weight)
+    else:
+        ops.gemm_skinny_fused(x.x, gate_up_blocks, out=out, mode=ops.GEMM_EPILOGUE_SWIGLU, scale_ssq=x.ssq, scale_width=x.width,
+                              scale_eps=x.eps, prefetch=next_weight)
+    return out
+
+
+def linear_into_residual(x: torch.Tensor, weight: torch.Tensor, fold: "ResidualNorm", next_weight: Optional[torch.Tensor] = None) -> "PreNormed":
+    """fold.hidden += x @ weight^T, and the input of the norm that follows, all in the product's
+    kernel.  Returns the PreNormed that stands for norm(hidden)."""
+    from tokensprint_b200.parts.base import PreNormed
+
+    T, N = x.shape[0], weight.shape[0]
+    xprime = torch.empty((T, N), device=x.device, dtype=x.dtype)
+    ssq = torch.empty((-(-N // 128), T), device=x.device, dtype=torch.float32)
+    ops.gemm_skinny_fused(x, weight, mode=ops.GEMM_EPILOGUE_RESIDUAL_NORM, hidden=fold.hidden, norm_weight=fold.norm.weight,
+                          xprime=xprime, ssq_out=ssq, prefetch=next_weight)
+    return PreNormed(xprime, ssq, fold.norm.width, fold.norm.eps)
 
 
 def linear_float32_out(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

@@ -7,7 +7,7 @@ from typing import Mapping, Optional
 import torch
 
 from tokensprint_b200 import ops
-from tokensprint_b200.parts.base import BuildContext, Norm, TensorSpec, register_part
+from tokensprint_b200.parts.base import NormParams, BuildContext, Norm, TensorSpec, register_part
 
 
 @register_part("norm", "rmsnorm")
@@ -28,6 +28,9 @@ class RMSNorm(Norm):
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = tensors[self.weight_name]
+
+    def params(self) -> Optional[NormParams]:
+        return NormParams(self.weight, self.eps, self.dim)
 
     def forward(self, hidden, delta, out, row_index=None) -> None:
         ops.add_rmsnorm(hidden, delta, self.weight, out, self.eps, row_index)
