@@ -262,7 +262,7 @@ def test_attention_mma_mixed(nq, nkv, d, page, window):
     assert rel_err(got, want) < 1e-2
 
 
-@pytest.mark.parametrize("splits", [1, 2, 5, 32])
+@pytest.mark.parametrize("splits", [1, 2, 5, 8, 32])
 @pytest.mark.parametrize("nq,nkv,d,page,window", [(32, 8, 128, 16, 0), (4, 2, 16, 16, 0), (16, 1, 64, 32, 0), (5, 1, 48, 4, 90), (40, 2, 80, 16, 0)])
 def test_attention_mma_decode_with_key_splits(splits, nq, nkv, d, page, window):
     case = finish_case(paged_case(DECODE, nq, nkv, d, page, torch.bfloat16, seed=3 * d))
@@ -272,6 +272,16 @@ def test_attention_mma_decode_with_key_splits(splits, nq, nkv, d, page, window):
     # the merge as a kernel of its own gives the same, and twice in a row (the tickets reset)
     assert rel_err(run_mma(case, window, splits, fuse_merge=False), want) < 1e-2
     assert torch.equal(run_mma(case, window, splits), got)
+    # 2..8 splits merge inside a thread-block cluster by default; through scratch and a second kernel it is the same
+    from tokensprint_b200 import ops
+
+    lib = ops._build.load_variant("attention_mma", {"TS_HEAD_DIM": d})
+    assert lib.ts_attention_mma_cluster_merge() == 1
+    lib.ts_attention_mma_set_cluster_merge(0)
+    try:
+        assert rel_err(run_mma(case, window, splits), want) < 1e-2
+    finally:
+        lib.ts_attention_mma_set_cluster_merge(1)
 
 
 @pytest.mark.parametrize("splits,chunk", [(16, 64), (8, 128), (4, 256), (2, 512), (64, 64)])

@@ -47,6 +47,7 @@ struct AttnParams {
   int max_blocks, page, nq, nkv, window, splits, row_tiles;
   int* counters;                  // [B * nkv] tickets of the key splits (zero between launches), or null: merge in a kernel of its own
   int keys_per_split;             // > 0: split s covers this many keys (a multiple of BN); 0: the range is divided evenly
+  int cluster;                    // 1: the key splits of a (sequence, KV head) pair are one thread-block cluster and merge through its shared memory
   float scale_log2;               // scale * log2(e)
 };
 
@@ -213,8 +214,9 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   }
   const int nblocks = kb1 - kb0 + 1;  // may be <= 0 for a split without work
   const int* table = p.block_table + (size_t)b * p.max_blocks;
-  if (nblocks <= 0 && p.splits > 1) {
-    // A split beyond this sequence's keys: mark its partial as empty and leave.
+  if (nblocks <= 0 && p.splits > 1 && !p.cluster) {
+    // A split beyond this sequence's keys: mark its partial as empty and leave.  (In a cluster it
+    // stays for the barriers and brings an empty partial: no key seen, sum 0.)
     for (int r = tid; r < min(BM, rows_total - r0); r += NT) {
       const int row = r0 + r;
       const size_t qrow = (size_t)(q_begin + row / G) * p.nq + hk * G + row % G;
@@ -450,22 +452,80 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
       }
       const size_t qrow = (size_t)(q_begin + row / G) * p.nq + hk * G + row % G;
       const float inv = (p.splits == 1) ? (l > 0.f ? 1.f / l : 0.f) : 1.f;
+      float* cta_part = o_s + NWARPS * 16 * D + r * (D + 2);  // cluster mode: this CTA's partial of row r
       for (int d = lane; d < D; d += 32) {
         float acc = 0.f;
 #pragma unroll
         for (int w = 0; w < NWARPS; ++w) acc += wgt[w] * o_s[(w * 16 + r) * D + d];
         if (p.splits == 1)
           p.out[qrow * D + d] = __float2bfloat16_rn(acc * inv);
+        else if (p.cluster)
+          cta_part[d] = acc;
         else
           p.part_o[(qrow * p.splits + split) * D + d] = acc;
       }
       if (p.splits > 1 && lane == 0) {
-        float* ml = p.part_ml + (qrow * p.splits + split) * 2;
+        float* ml = p.cluster ? cta_part + D : p.part_ml + (qrow * p.splits + split) * 2;
         ml[0] = m;
         ml[1] = l;
       }
     }
-    if (p.splits > 1 && p.counters != nullptr) merge_splits_by_last_arriver<NT>(p, b, hk, q_begin, rows_total, G, &last_flag);
+    if (p.splits > 1 && p.cluster) {
+      // The splits of this (sequence, KV head) pair are the CTAs of one cluster: each has left its
+      // partial (weighted sum, max, sum of weights per row) in its own shared memory; after a
+      // cluster barrier CTA r % splits merges row r from all of them through distributed shared
+      // memory, in rank order, and a second barrier keeps every CTA's memory alive until then.
+      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+      unsigned rank, nranks;
+      asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+      asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(nranks));
+      const int rows_here = min(16, rows_total - r0);
+      for (int r = (int)rank + (int)nranks * warp; r < rows_here; r += (int)nranks * NWARPS) {  // a warp per row
+        const int row = r0 + r;
+        const unsigned local = (unsigned)__cvta_generic_to_shared(o_s + NWARPS * 16 * D + r * (D + 2));
+        float m = -INFINITY;
+        for (unsigned c = 0; c < nranks; ++c) {
+          unsigned remote;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(c));
+          float mc, lc;
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(mc) : "r"(remote + D * 4));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(lc) : "r"(remote + D * 4 + 4));
+          if (lc > 0.f) m = fmaxf(m, mc);
+        }
+        float l = 0.f, acc[(D + 31) / 32];
+#pragma unroll
+        for (int i = 0; i < (D + 31) / 32; ++i) acc[i] = 0.f;
+        for (unsigned c = 0; c < nranks; ++c) {
+          unsigned remote;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(c));
+          float mc, lc;
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(mc) : "r"(remote + D * 4));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(lc) : "r"(remote + D * 4 + 4));
+          const float wgt = lc > 0.f ? exp2f(mc - m) : 0.f;
+          l += wgt * lc;
+#pragma unroll
+          for (int i = 0; i < (D + 31) / 32; ++i) {
+            const int d = lane + 32 * i;
+            if (d < D) {
+              float v;
+              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote + d * 4));
+              acc[i] += wgt * v;
+            }
+          }
+        }
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const size_t qrow = (size_t)(q_begin + row / G) * p.nq + hk * G + row % G;
+#pragma unroll
+        for (int i = 0; i < (D + 31) / 32; ++i) {
+          const int d = lane + 32 * i;
+          if (d < D) p.out[qrow * D + d] = __float2bfloat16_rn(acc[i] * inv);
+        }
+      }
+      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+    if (p.splits > 1 && !p.cluster && p.counters != nullptr) merge_splits_by_last_arriver<NT>(p, b, hk, q_begin, rows_total, G, &last_flag);
   } else {
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -798,6 +858,8 @@ int launch(const AttnParams& p, int B, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid(p.row_tiles * p.splits, p.nkv, B);
+  if (p.cluster)  // the grid's x dimension is the key splits of one pair: one cluster
+    return ts_launch_cluster(attention_mma_kernel<NWARPS, SPLIT_KEYS>, grid, dim3(NWARPS * 32), smem, stream, p.splits, p);
   return ts_launch(attention_mma_kernel<NWARPS, SPLIT_KEYS>, grid, dim3(NWARPS * 32), smem, stream, p);
 }
 
@@ -822,6 +884,26 @@ TS_EXPORT int ts_attention_mma_head_dim() { return D; }
 // last CTA of every (sequence, KV head) pair merges the pair's splits itself and no second kernel
 // runs; only for decode steps (at most 16 query rows per pair).  Null: the merge is a kernel of
 // its own.
+// How many CTAs of the decode kernel the GPU runs at once.
+static long long decode_slots() {
+  static long long slots = 0;
+  if (slots == 0) {
+    int dev = 0, sms = 0, per_sm = 0;
+    const size_t smem = (size_t)(16 + 2 * STAGES * BN) * LD * sizeof(__nv_bfloat16);
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
+    cudaFuncSetAttribute(attention_mma_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_mma_kernel<4, true>, 128, smem) != cudaSuccess || per_sm <= 0) per_sm = 1;
+    slots = (long long)sms * per_sm;
+  }
+  return slots;
+}
+
+// Whether decode steps with 2..8 key splits merge the splits inside a thread-block cluster
+// (through distributed shared memory) instead of through scratch and a second kernel.
+static int ts_attention_cluster_merge = 1;
+TS_EXPORT void ts_attention_mma_set_cluster_merge(int on) { ts_attention_cluster_merge = on ? 1 : 0; }
+TS_EXPORT int ts_attention_mma_cluster_merge(void) { return ts_attention_cluster_merge; }
+
 TS_EXPORT int ts_attention_paged_mma_fused(const void* q, const void* kcache, const void* vcache, void* out,
                                            float* scratch, const int* cu_q, const int* ctx_len,
                                            const int* block_table, const int* seq_index, int max_blocks,
@@ -853,6 +935,11 @@ TS_EXPORT int ts_attention_paged_mma_fused(const void* q, const void* kcache, co
   p.splits = splits;
   p.keys_per_split = keys_per_split;
   p.counters = (counters != nullptr && splits > 1 && (long long)max_q * (nq / nkv) <= 16) ? counters : nullptr;
+  // merge inside a cluster: decode steps (one row tile) with 2..8 splits, the splits dividing each sequence's keys evenly
+  // (and only while all CTAs run at once: clusters are placed as wholes, which costs occupancy as soon as CTAs queue)
+  p.cluster = (ts_attention_cluster_merge && splits > 1 && splits <= 8 && (long long)max_q * (nq / nkv) <= 16 && keys_per_split == 0 &&
+               (long long)B * nkv * splits <= decode_slots()) ? 1 : 0;
+  if (p.cluster) p.counters = nullptr;
   p.scale_log2 = scale * 1.4426950408889634f;
   const long long rows = (long long)max_q * G;
   int status;
@@ -867,7 +954,7 @@ TS_EXPORT int ts_attention_paged_mma_fused(const void* q, const void* kcache, co
       status = launch<8, false>(p, B, stream);
   }
   if (status != 0) return status;
-  if (splits > 1 && p.counters == nullptr) {
+  if (splits > 1 && p.counters == nullptr && !p.cluster) {
     const int total = T * nq;
     status = ts_launch(attention_combine_kernel, dim3((total + 3) / 4), dim3(128), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, seq_index, total, nq, splits);
   }

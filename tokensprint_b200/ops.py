@@ -337,6 +337,9 @@ def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 # ---------------------------------------------------------------------------
 # tensor-core attention (one library per head size)
 
+# Decode steps with 2..8 key splits: the splits of a (sequence, KV head) pair form a thread-block
+# cluster and merge through its shared memory (TS_ATTENTION_CLUSTER=0: scratch and a second kernel).
+ATTENTION_CLUSTER_MERGE = _os.environ.get("TS_ATTENTION_CLUSTER", "1") != "0"
 ATTENTION_MMA_MAX_HEAD_DIM = 256
 ATTENTION_MMA_MAX_SPLITS = 64
 _attention_mma: dict[int, tuple] = {}
@@ -361,9 +364,17 @@ def _attention_mma_fns(head_dim: int):
         scratch.restype = _c_ll
         if lib.ts_attention_mma_head_dim() != head_dim:
             raise KernelError("attention_paged_mma: the loaded library was built for another head size")
+        lib.ts_attention_mma_set_cluster_merge.argtypes = [_c_int]
+        lib.ts_attention_mma_set_cluster_merge(1 if ATTENTION_CLUSTER_MERGE else 0)
         fns = (run, scratch)
         _attention_mma[head_dim] = fns
     return fns
+
+
+def _decode_slots(head_dim: int) -> int:
+    """CTAs of the decode attention kernel that run at once (shared memory allows a few per SM)."""
+    smem = (16 + 4 * 64) * (head_dim + 8) * 2
+    return max(1, (227 * 1024) // smem) * 148
 
 
 def attention_decode_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: int = 128) -> int:
@@ -375,8 +386,7 @@ def attention_decode_splits(num_seqs: int, num_kv_heads: int, max_context: int, 
     share, so the count is chosen to fill whole waves: one wave for small batches, and for
     batches with more pairs than slots a count that makes the last wave nearly full.
     """
-    smem = (16 + 4 * 64) * (head_dim + 8) * 2
-    slots = max(1, (227 * 1024) // smem) * 148
+    slots = _decode_slots(head_dim)
     pairs = max(1, num_seqs * num_kv_heads)
     blocks = max(1, -(-max_context // 64))
     if _os.environ.get("TS_DECODE_SPLITS"):
@@ -384,8 +394,12 @@ def attention_decode_splits(num_seqs: int, num_kv_heads: int, max_context: int, 
     best, best_cost = 1, None
     for s in range(1, min(blocks, 16) + 1):
         waves = -(-pairs * s // slots)
-        # per CTA: start and merge (about 3 us) + 2.5 us per 64-key block; + the combine kernel
-        cost = waves * (3.0 + 2.5 * -(-blocks // s)) + (0.3 * s if s > 1 else 0.0)
+        # per CTA: start and merge (about 3 us) + 2.5 us per 64-key block; merging the splits costs
+        # little inside a thread-block cluster (up to 8 CTAs, all running at once), more through
+        # scratch and a kernel of its own
+        in_cluster = ATTENTION_CLUSTER_MERGE and s <= 8 and pairs * s <= slots
+        merge = 0.0 if s == 1 else (0.8 if in_cluster else 1.5 + 0.15 * s)
+        cost = waves * (3.0 + 2.5 * -(-blocks // s)) + merge
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best
@@ -472,7 +486,9 @@ def attention_paged_mma(
         cu_seqlens_q.data_ptr(), context_lens.data_ptr(), block_table.data_ptr(), seq_index.data_ptr(),
         block_table.shape[1], page_size, T, num_seqs, max_seqlen_q, nq, nkv, float(scale), int(window), int(splits),
         int(keys_per_split), counters, _stream()))
-    if splits > 1 and counters is None:
+    in_cluster = (1 < splits <= 8 and max_seqlen_q * (nq // nkv) <= 16 and keys_per_split == 0 and ATTENTION_CLUSTER_MERGE
+                  and num_seqs * nkv * splits <= _decode_slots(d))
+    if splits > 1 and counters is None and not in_cluster:
         global launch_count
         launch_count += 1  # the combine kernel
 
