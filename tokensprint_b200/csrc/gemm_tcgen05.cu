@@ -48,7 +48,14 @@
 namespace {
 
 constexpr int TILE_N = 128;   // W rows per tile (the MMA's M)
-constexpr int TILE_K = 64;    // bf16 per stage and row: one 128-byte swizzle atom
+// Boxes side by side per stage.  Two (256 contiguous bytes of every W row asked for at once, half
+// as many stages of twice the size) measured the same alone and 4 % slower inside the decode step.
+#ifndef TS_GEMM_KATOMS
+#define TS_GEMM_KATOMS 1
+#endif
+constexpr int ATOM_K = 64;                       // bf16 per row of one TMA box: one 128-byte swizzle atom
+constexpr int KATOMS = TS_GEMM_KATOMS;
+constexpr int TILE_K = ATOM_K * KATOMS;          // bf16 per stage and row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
 constexpr int MAX_CONTRIB = 8;   // most CTAs that may share one tile
@@ -61,7 +68,9 @@ struct Cfg {
   static constexpr uint32_t A_BYTES = TILE_N * TILE_K * 2;
   static constexpr uint32_t B_BYTES = MPAD * TILE_K * 2;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + ((B_BYTES + 1023) / 1024) * 1024;
-  static constexpr int STAGES = MPAD <= 16 ? 10 : (MPAD <= 32 ? 9 : (MPAD <= 64 ? 8 : 6));
+  static constexpr int STAGES = (MPAD <= 16 ? 10 : (MPAD <= 32 ? 9 : (MPAD <= 64 ? 8 : 6))) / KATOMS;
+  static constexpr uint32_t A_ATOM = TILE_N * ATOM_K * 2;  // one box of W
+  static constexpr uint32_t B_ATOM = MPAD * ATOM_K * 2;    // one box of X
   static constexpr uint32_t TMEM_COLS = 2 * MPAD < 32 ? 32 : 2 * MPAD;
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;
 };
@@ -277,14 +286,19 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
         const int t = u / chunks, kc = u - t * chunks;
         const uint32_t bar = smem_u32(&full_bar[i]);
         mbar_expect_tx(bar, C::A_BYTES + C::B_BYTES);
-        tma_load_2d(smem_u32(smem + (size_t)i * C::STAGE_BYTES), &map_w, bar, kc * TILE_K, t * TILE_N);
+#pragma unroll
+        for (int a = 0; a < KATOMS; ++a)
+          tma_load_2d(smem_u32(smem + (size_t)i * C::STAGE_BYTES) + a * C::A_ATOM, &map_w, bar, kc * TILE_K + a * ATOM_K, t * TILE_N);
       }
       ts_pdl_wait();
       TS_PROBE(6);
       for (int i = 0; i < early; ++i) {
         const int u = range.u0 + i;
         const int kc = u % chunks;
-        tma_load_2d(smem_u32(smem + (size_t)i * C::STAGE_BYTES) + C::A_BYTES, &map_x, smem_u32(&full_bar[i]), kc * TILE_K, 0);
+#pragma unroll
+        for (int a = 0; a < KATOMS; ++a)
+          tma_load_2d(smem_u32(smem + (size_t)i * C::STAGE_BYTES) + C::A_BYTES + a * C::B_ATOM, &map_x, smem_u32(&full_bar[i]),
+                      kc * TILE_K + a * ATOM_K, 0);
       }
       int it = early;
       for (; it < n_units; ++it) {
@@ -296,8 +310,10 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
         const uint32_t bar = smem_u32(&full_bar[s]);
         const uint32_t dst = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
         mbar_expect_tx(bar, C::A_BYTES + C::B_BYTES);
-        tma_load_2d(dst, &map_w, bar, kc * TILE_K, t * TILE_N);
-        tma_load_2d(dst + C::A_BYTES, &map_x, bar, kc * TILE_K, 0);
+#pragma unroll
+        for (int a = 0; a < KATOMS; ++a) tma_load_2d(dst + a * C::A_ATOM, &map_w, bar, kc * TILE_K + a * ATOM_K, t * TILE_N);
+#pragma unroll
+        for (int a = 0; a < KATOMS; ++a) tma_load_2d(dst + C::A_BYTES + a * C::B_ATOM, &map_x, bar, kc * TILE_K + a * ATOM_K, 0);
       }
       // All loads of this GEMM are on their way.  While its last tiles are multiplied and stored
       // (and while the small kernels after it run) HBM would idle: ask for this CTA's share of the
@@ -343,8 +359,11 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
           const uint64_t bdesc = umma_desc_sw128(a_addr + C::A_BYTES);
 #pragma unroll
           for (int k = 0; k < TILE_K / UMMA_K; ++k) {
-            // 16 bf16 = 32 bytes further along K inside the swizzle atom: +2 in the address field
-            umma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, IDESC, (kc > k0 || k > 0) ? 1u : 0u);
+            // 16 bf16 = 32 bytes further along K inside the swizzle atom: +2 in the address field;
+            // the next atom (box) of the stage starts A_ATOM / B_ATOM bytes further
+            const int atom = k / (ATOM_K / UMMA_K), kk = k % (ATOM_K / UMMA_K);
+            umma_bf16(tmem_d, adesc + (uint64_t)(atom * (C::A_ATOM >> 4) + 2 * kk), bdesc + (uint64_t)(atom * (C::B_ATOM >> 4) + 2 * kk), IDESC,
+                      (kc > k0 || k > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&empty_bar[s]));  // arrives when these MMAs have read the stage
         }
@@ -546,7 +565,7 @@ int tensor_map(const void* ptr, long long rows, long long cols, long long ld, in
   if (!fn) return TS_ERR_UNSUPPORTED_SIZE;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)ATOM_K, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
