@@ -13,6 +13,7 @@ from tokensprint_b200.parts.base import (
     LayerCache,
     Mixer,
     PartSpec,
+    ResidualNorm,
     StepContext,
     TensorSpec,
     build_part,
@@ -34,6 +35,8 @@ class AttentionMixer(Mixer):
     None) and the checkpoint names of the tensors.  q, k, v weights are stacked at load
     into one [(nq + 2 nkv) d, H] matrix.
     """
+
+    folds_norms = True
 
     def __init__(
         self,
