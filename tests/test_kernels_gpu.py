@@ -603,6 +603,58 @@ def test_gemm_skinny_fused_residual_and_norm_input(M, N, K):
         assert rel_err(out, normed @ w2.double().T) < 1e-2
 
 
+@pytest.mark.parametrize("M,nq,nkv,K,rope,norm", [(8, 32, 8, 4096, True, True), (3, 4, 2, 256, True, False), (32, 2, 1, 520, False, True), (5, 8, 8, 1024, True, True)])
+def test_gemm_skinny_qk_rope_store(M, nq, nkv, K, rope, norm):
+    """The q/k/v projection with per-head norm, rotation and the cache store in its epilogue,
+    against the projection followed by the kernel that does the same on its own."""
+    from tokensprint_b200 import ops
+
+    d = 128
+    g = torch.Generator().manual_seed(M + nq + K)
+    x = torch.randn(M, K, generator=g).to(DEV, torch.bfloat16)
+    w = (torch.randn((nq + 2 * nkv) * d, K, generator=g) * 0.05).to(DEV, torch.bfloat16)
+    qw = (1 + 0.2 * torch.randn(d, generator=g)).to(DEV) if norm else None
+    kw = (1 + 0.2 * torch.randn(d, generator=g)).to(DEV) if norm else None
+    inv_freq = (1.0 / (1e4 ** (torch.arange(0, d, 2).float() / d))).to(DEV) if rope else None
+    positions = torch.randint(0, 3000, (M,), generator=g).to(DEV, torch.int32)
+    slots = torch.randperm(M + 7, generator=g)[:M].to(DEV, torch.int32)
+    slots[M // 2] = -1  # a row whose key and value are not stored
+    ssq = (torch.rand(2, M, generator=g) * 5 + 1).to(DEV)
+
+    def caches():
+        return torch.full((M + 7, nkv, d), 7.0, device=DEV, dtype=torch.bfloat16), torch.full((M + 7, nkv, d), 7.0, device=DEV, dtype=torch.bfloat16)
+
+    # reference: float64 product with the row scale, then the plain functions
+    r = torch.rsqrt(ssq.double().sum(0) / K + 1e-6)[:, None].cpu()
+    qkv = (x.double().cpu() @ w.double().cpu().T) * r
+    heads = qkv.view(M, nq + 2 * nkv, d)
+    qh, kh, vh = heads[:, :nq], heads[:, nq : nq + nkv], heads[:, nq + nkv :]
+    if norm:
+        qh = plain.rms_norm(qh, qw.double().cpu(), 1e-5)
+        kh = plain.rms_norm(kh, kw.double().cpu(), 1e-5)
+    if rope:
+        ang = plain.rope_angles(positions.tolist(), d, 1e4)
+        qh, kh = plain.apply_rope(qh, ang), plain.apply_rope(kh, ang)
+
+    q = torch.full((M, nq * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    kc, vc = caches()
+    ops.gemm_qk_rope_store(x, w, q, kc, vc, slots, positions, qw, kw, 1e-5, inv_freq, nq, nkv, scale_ssq=ssq, scale_width=K, scale_eps=1e-6)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    assert rel_err(q.view(M, nq, d), qh) < 1e-2
+    for m in range(M):
+        s_ = int(slots[m])
+        if s_ >= 0:
+            assert rel_err(kc[s_], kh[m]) < 1e-2 and rel_err(vc[s_], vh[m]) < 1e-2
+    used = {int(v) for v in slots.tolist() if v >= 0}
+    for s_ in range(M + 7):
+        if s_ not in used:
+            assert bool((kc[s_] == 7.0).all()) and bool((vc[s_] == 7.0).all()), "a slot nobody owns was written"
+    q2, (kc2, vc2) = torch.empty_like(q), caches()
+    ops.gemm_qk_rope_store(x, w, q2, kc2, vc2, slots, positions, qw, kw, 1e-5, inv_freq, nq, nkv, scale_ssq=ssq, scale_width=K, scale_eps=1e-6)
+    assert torch.equal(q, q2) and torch.equal(kc, kc2) and torch.equal(vc, vc2)
+
+
 def test_gemm_skinny_refuses_what_it_cannot_take():
     from tokensprint_b200 import ops
 

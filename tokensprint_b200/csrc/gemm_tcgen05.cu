@@ -59,7 +59,7 @@ constexpr int TILE_K = ATOM_K * KATOMS;          // bf16 per stage and row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
 constexpr int MAX_CONTRIB = 8;   // most CTAs that may share one tile
-constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_RESIDUAL_NORM = 2;
+constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_RESIDUAL_NORM = 2, EPI_QK_ROPE = 3;
 constexpr int FUSED_MAX_ROWS = 32;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
@@ -97,6 +97,17 @@ struct GemmArgs {
   __nv_bfloat16* xprime;         //   [M, ldh] bf16(hidden * norm_w)
   float* ssq_out;                //   [tiles, M] sums of squares of the new hidden rows, per tile of 128 columns
   long long ldh;
+  // EPI_QK_ROPE (head size 128 = one tile per head; rows of W: nq query heads, nkv key heads, nkv value heads):
+  __nv_bfloat16* q_out;          //   [M, nq * 128]
+  __nv_bfloat16* k_cache;        //   [slots, nkv, 128]
+  __nv_bfloat16* v_cache;
+  const int* slot_mapping;       //   [M] cache slot of every row, -1: no store
+  const int* positions;          //   [M]
+  const float* q_norm_w;         //   [128] or null
+  const float* k_norm_w;
+  const float* inv_freq;         //   [64] or null (no rotation)
+  float qk_eps;
+  int nq, nkv;
 #ifdef TS_GEMM_PROBE
   unsigned long long* probe;
 #endif
@@ -203,6 +214,47 @@ __device__ __forceinline__ void fused_epilogue(const GemmArgs& args, int t, int 
       }
       ss = ts_warp_sum(ss);
       if (lane == 0) args.ssq_out[(size_t)t * args.M + m] = ss;
+    }
+  } else if (args.mode == EPI_QK_ROPE) {
+    // Tile t is head t: per-head RMS norm over the tile's 128 columns, rotate-half rotation of
+    // the pairs (j, j + 64) (the partner sits 16 lanes away), then queries to q_out, keys and
+    // values to their cache slot (engine/nn/attention.py:171-188 of the reference; angles and
+    // trigonometry in float32).
+    const bool is_q = t < args.nq, is_k = !is_q && t < args.nq + args.nkv;
+    const float* w = is_q ? args.q_norm_w : (is_k ? args.k_norm_w : nullptr);
+    for (int idx = etid; idx < args.M * 32; idx += 128) {
+      const int m = idx >> 5, nl = (idx & 31) * 4;  // the 32 lanes of a warp share m
+      const float4 v4 = *reinterpret_cast<const float4*>(tile + m * TILE_N + nl);
+      float v[4] = {v4.x * rstd[m], v4.y * rstd[m], v4.z * rstd[m], v4.w * rstd[m]};
+      if (is_q || is_k) {
+        if (w != nullptr) {
+          const float ss = ts_warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
+          const float r = rsqrtf(ss / (float)TILE_N + args.qk_eps);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) v[i] *= r * w[nl + i];
+        }
+        if (args.inv_freq != nullptr) {
+          const float pos = (float)args.positions[m];
+          const bool upper = nl >= 64;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float partner = __shfl_xor_sync(0xffffffffu, v[i], 16);
+            float sn, cs;
+            sincosf(pos * args.inv_freq[(nl & 63) + i], &sn, &cs);
+            v[i] = upper ? v[i] * cs + partner * sn : v[i] * cs - partner * sn;
+          }
+        }
+      }
+      const int slot = is_q ? 0 : args.slot_mapping[m];
+      if (slot < 0) continue;
+      __nv_bfloat16* dst = is_q ? args.q_out + ((size_t)m * args.nq + t) * TILE_N
+                                : (is_k ? args.k_cache + ((size_t)slot * args.nkv + (t - args.nq)) * TILE_N
+                                        : args.v_cache + ((size_t)slot * args.nkv + (t - args.nq - args.nkv)) * TILE_N);
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+      uint2 packed;
+      packed.x = *reinterpret_cast<unsigned*>(&lo);
+      packed.y = *reinterpret_cast<unsigned*>(&hi);
+      *reinterpret_cast<uint2*>(dst + nl) = packed;
     }
   } else {
     for (int idx = etid; idx < args.M * 32; idx += 128) {
@@ -656,6 +708,19 @@ TS_EXPORT int ts_gemm_skinny_fused(const void* x, const void* w, void* out, int 
                                    const float* norm_w, void* xprime, float* ssq_out, float* partial, int* counters,
                                    int* error, const void* prefetch, long long prefetch_bytes, void* stream_);
 
+// The q/k/v projection of an attention layer with head size 128 (w: nq query heads, then nkv key
+// heads, then nkv value heads, 128 rows each), with what follows it done where each head's tile is
+// finished: per-head RMS norm of queries and keys (weights [128] or null), rotate-half rotation
+// with angle = position * inv_freq[j] (inv_freq [64] or null), queries to q_out [M, nq * 128], keys
+// and values to slot slot_mapping[m] of the caches [slots, nkv, 128] (-1: not stored).
+// scale_ssq as in ts_gemm_skinny_fused.
+TS_EXPORT int ts_gemm_skinny_qk_rope(const void* x, const void* w, int M, int K, long long ldx, long long ldw, int nq, int nkv,
+                                     void* q_out, void* k_cache, void* v_cache, const int* slot_mapping, const int* positions,
+                                     const float* q_norm_w, const float* k_norm_w, float qk_eps, const float* inv_freq,
+                                     const float* scale_ssq, int scale_tiles, float scale_width, float scale_eps,
+                                     float* partial, int* counters, int* error, const void* prefetch, long long prefetch_bytes,
+                                     void* stream_);
+
 TS_EXPORT int ts_gemm_skinny_bf16(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
                                   long long ldw, long long ldo, int out_f32, float* partial, int* counters,
                                   int* error, const void* prefetch, long long prefetch_bytes, void* stream_) {
@@ -663,27 +728,17 @@ TS_EXPORT int ts_gemm_skinny_bf16(const void* x, const void* w, void* out, int M
                               nullptr, nullptr, partial, counters, error, prefetch, prefetch_bytes, stream_);
 }
 
-TS_EXPORT int ts_gemm_skinny_fused(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
-                                   long long ldw, long long ldo, int out_f32, int mode, const float* scale_ssq,
-                                   int scale_tiles, float scale_width, float scale_eps, float* hidden, long long ldh,
-                                   const float* norm_w, void* xprime, float* ssq_out, float* partial, int* counters,
-                                   int* error, const void* prefetch, long long prefetch_bytes, void* stream_) {
-  if (M <= 0 || N <= 0) return 0;
-  if (mode != EPI_PLAIN || scale_ssq != nullptr) {
-    if (M > FUSED_MAX_ROWS) return TS_ERR_UNSUPPORTED_SIZE;
-    if (scale_ssq != nullptr && (scale_tiles <= 0 || !(scale_width > 0.f))) return TS_ERR_BAD_ARGUMENT;
-    if (mode == EPI_SWIGLU && ((N & 1) || out_f32 || ldo < N / 2)) return TS_ERR_BAD_ARGUMENT;
-    if (mode == EPI_RESIDUAL_NORM && (hidden == nullptr || norm_w == nullptr || xprime == nullptr || ssq_out == nullptr || ldh < N))
-      return TS_ERR_BAD_ARGUMENT;
-    if (mode < 0 || mode > EPI_RESIDUAL_NORM) return TS_ERR_BAD_ARGUMENT;
-  }
-  if (mode == EPI_PLAIN && ldo < N) return TS_ERR_BAD_ARGUMENT;
+// What every entry point shares: checks, the split of the work, tensor maps, launch.  `a` comes
+// with its epilogue fields set.
+static int run_gemm(const void* x, const void* w, int M, int N, int K, long long ldx, long long ldw, GemmArgs& a, float* partial,
+                    int* counters, int* error, const void* prefetch, long long prefetch_bytes, void* stream_) {
   if (K <= 0 || ldx < K || ldw < K || counters == nullptr || error == nullptr || partial == nullptr)
     return TS_ERR_BAD_ARGUMENT;
   if (M > 128 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)partial % 16))
     return TS_ERR_UNSUPPORTED_SIZE;
+  if ((a.mode != EPI_PLAIN || a.scale_ssq != nullptr) && M > FUSED_MAX_ROWS) return TS_ERR_UNSUPPORTED_SIZE;
+  if (a.scale_ssq != nullptr && (a.scale_tiles <= 0 || !(a.scale_width > 0.f))) return TS_ERR_BAD_ARGUMENT;
   const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
-  GemmArgs a;
   int ctas;
   plan(N, K, &a.tiles, &a.chunks, &a.units_per, &ctas);
   CUtensorMap mw, mx;
@@ -691,25 +746,12 @@ TS_EXPORT int ts_gemm_skinny_fused(const void* x, const void* w, void* out, int 
   if (st != 0) return st;
   st = tensor_map(x, M, K, ldx, mpad, &mx);
   if (st != 0) return st;
-  a.out = out;
   a.partial = partial;
   a.counters = counters;
   a.error = error;
   a.M = M;
   a.N = N;
   a.K = K;
-  a.ldo = (int)ldo;
-  a.out_f32 = out_f32;
-  a.mode = mode;
-  a.scale_ssq = scale_ssq;
-  a.scale_tiles = scale_tiles;
-  a.scale_width = scale_width;
-  a.scale_eps = scale_eps;
-  a.hidden = hidden;
-  a.norm_w = norm_w;
-  a.xprime = (__nv_bfloat16*)xprime;
-  a.ssq_out = ssq_out;
-  a.ldh = ldh;
   a.prefetch = (prefetch_bytes > 0 && ((uintptr_t)prefetch % 16) == 0) ? (const char*)prefetch : nullptr;
   a.prefetch_bytes = prefetch_bytes > 0 ? (unsigned long long)prefetch_bytes : 0ull;
 #ifdef TS_GEMM_PROBE
@@ -724,4 +766,63 @@ TS_EXPORT int ts_gemm_skinny_fused(const void* x, const void* w, void* out, int 
     case 64: return launch_skinny<64>(mw, mx, a, ctas, stream);
     default: return launch_skinny<128>(mw, mx, a, ctas, stream);
   }
+}
+
+TS_EXPORT int ts_gemm_skinny_fused(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
+                                   long long ldw, long long ldo, int out_f32, int mode, const float* scale_ssq,
+                                   int scale_tiles, float scale_width, float scale_eps, float* hidden, long long ldh,
+                                   const float* norm_w, void* xprime, float* ssq_out, float* partial, int* counters,
+                                   int* error, const void* prefetch, long long prefetch_bytes, void* stream_) {
+  if (M <= 0 || N <= 0) return 0;
+  if (mode < 0 || mode > EPI_RESIDUAL_NORM) return TS_ERR_BAD_ARGUMENT;
+  if (mode == EPI_SWIGLU && ((N & 1) || out_f32 || ldo < N / 2)) return TS_ERR_BAD_ARGUMENT;
+  if (mode == EPI_RESIDUAL_NORM && (hidden == nullptr || norm_w == nullptr || xprime == nullptr || ssq_out == nullptr || ldh < N))
+    return TS_ERR_BAD_ARGUMENT;
+  if (mode == EPI_PLAIN && ldo < N) return TS_ERR_BAD_ARGUMENT;
+  GemmArgs a = {};
+  a.out = out;
+  a.ldo = (int)ldo;
+  a.out_f32 = out_f32;
+  a.mode = mode;
+  a.scale_ssq = scale_ssq;
+  a.scale_tiles = scale_tiles;
+  a.scale_width = scale_width;
+  a.scale_eps = scale_eps;
+  a.hidden = hidden;
+  a.norm_w = norm_w;
+  a.xprime = (__nv_bfloat16*)xprime;
+  a.ssq_out = ssq_out;
+  a.ldh = ldh;
+  return run_gemm(x, w, M, N, K, ldx, ldw, a, partial, counters, error, prefetch, prefetch_bytes, stream_);
+}
+
+TS_EXPORT int ts_gemm_skinny_qk_rope(const void* x, const void* w, int M, int K, long long ldx, long long ldw, int nq, int nkv,
+                                     void* q_out, void* k_cache, void* v_cache, const int* slot_mapping, const int* positions,
+                                     const float* q_norm_w, const float* k_norm_w, float qk_eps, const float* inv_freq,
+                                     const float* scale_ssq, int scale_tiles, float scale_width, float scale_eps,
+                                     float* partial, int* counters, int* error, const void* prefetch, long long prefetch_bytes,
+                                     void* stream_) {
+  if (M <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || q_out == nullptr || k_cache == nullptr || v_cache == nullptr || slot_mapping == nullptr ||
+      (inv_freq != nullptr && positions == nullptr))
+    return TS_ERR_BAD_ARGUMENT;
+  if (((uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) % 8) return TS_ERR_UNSUPPORTED_SIZE;
+  GemmArgs a = {};
+  a.mode = EPI_QK_ROPE;
+  a.scale_ssq = scale_ssq;
+  a.scale_tiles = scale_tiles;
+  a.scale_width = scale_width;
+  a.scale_eps = scale_eps;
+  a.q_out = (__nv_bfloat16*)q_out;
+  a.k_cache = (__nv_bfloat16*)k_cache;
+  a.v_cache = (__nv_bfloat16*)v_cache;
+  a.slot_mapping = slot_mapping;
+  a.positions = positions;
+  a.q_norm_w = q_norm_w;
+  a.k_norm_w = k_norm_w;
+  a.inv_freq = inv_freq;
+  a.qk_eps = qk_eps;
+  a.nq = nq;
+  a.nkv = nkv;
+  return run_gemm(x, w, M, (nq + 2 * nkv) * TILE_N, K, ldx, ldw, a, partial, counters, error, prefetch, prefetch_bytes, stream_);
 }

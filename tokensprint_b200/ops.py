@@ -740,6 +740,77 @@ def gemm_skinny_fused(
         _stream()))
 
 
+_SIGNATURES["ts_gemm_skinny_qk_rope"] = [
+    _c_void_p, _c_void_p, _c_int, _c_int, _c_ll, _c_ll, _c_int, _c_int,
+    _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+    _c_void_p, _c_void_p, _c_float, _c_void_p,
+    _c_void_p, _c_int, _c_float, _c_float,
+    _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll, _c_void_p,
+]
+GEMM_QK_ROPE_HEAD_DIM = 128
+
+
+def gemm_qk_rope_store(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    q_out: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    slot_mapping: torch.Tensor,
+    positions: torch.Tensor,
+    q_norm_weight: Optional[torch.Tensor],
+    k_norm_weight: Optional[torch.Tensor],
+    eps: float,
+    inv_freq: Optional[torch.Tensor],
+    num_heads: int,
+    num_kv_heads: int,
+    *,
+    scale_ssq: Optional[torch.Tensor] = None,
+    scale_width: int = 1,
+    scale_eps: float = 0.0,
+    prefetch: Optional[torch.Tensor] = None,
+) -> None:
+    """The q/k/v projection (w [(nq + 2 nkv) * 128, K], heads of 128) with qk_norm_rope_store's work
+    done in the product's epilogue: per-head RMS norm of q and k, rotate-half rotation over the
+    whole head (inv_freq [64]) or none, q to q_out [M, nq * 128], k and v to their cache slots.
+    At most 32 rows.  scale_ssq as in gemm_skinny_fused."""
+    nq, nkv, d = num_heads, num_kv_heads, GEMM_QK_ROPE_HEAD_DIM
+    if not gemm_skinny_supported(x, w) or x.shape[0] > GEMM_FUSED_MAX_ROWS:
+        raise KernelError(f"gemm_qk_rope_store: needs bfloat16, at most {GEMM_FUSED_MAX_ROWS} rows and 16-byte aligned rows")
+    M, K = x.shape
+    if tuple(w.shape) != ((nq + 2 * nkv) * d, K):
+        raise KernelError(f"gemm_qk_rope_store: w must be [{(nq + 2 * nkv) * d},{K}], got {tuple(w.shape)}")
+    _cuda_contig("q_out", q_out, torch.bfloat16)
+    _cuda_contig("k_cache", k_cache, torch.bfloat16)
+    _cuda_contig("v_cache", v_cache, torch.bfloat16)
+    _cuda_contig("slot_mapping", slot_mapping, torch.int32)
+    _cuda_contig("positions", positions, torch.int32)
+    if q_out.numel() != M * nq * d or tuple(k_cache.shape[-2:]) != (nkv, d) or k_cache.shape != v_cache.shape:
+        raise KernelError("gemm_qk_rope_store: q_out must hold [M, nq*128], the caches [.., nkv, 128]")
+    if slot_mapping.numel() < M or positions.numel() < M:
+        raise KernelError("gemm_qk_rope_store: slot_mapping/positions are shorter than the rows")
+    for name, t, n in (("q_norm_weight", q_norm_weight, d), ("k_norm_weight", k_norm_weight, d), ("inv_freq", inv_freq, d // 2)):
+        if t is not None and (t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous() or t.numel() != n):
+            raise KernelError(f"gemm_qk_rope_store: {name} must be {n} float32 on the device")
+    scale_tiles = 0
+    if scale_ssq is not None:
+        if scale_ssq.dtype != torch.float32 or not scale_ssq.is_contiguous() or scale_ssq.dim() != 2 or scale_ssq.shape[1] != M:
+            raise KernelError("gemm_qk_rope_store: scale_ssq must be float32 [tiles, M]")
+        scale_tiles = scale_ssq.shape[0]
+    scratch_floats = library().ts_gemm_skinny_scratch_floats
+    scratch_floats.restype = _c_ll
+    partial = torch.empty(max(4, scratch_floats(M, w.shape[0], K)), dtype=torch.float32, device=x.device)
+    counters, error = _gemm_workspace(x.device)
+    _check("gemm_qk_rope_store", _fn("ts_gemm_skinny_qk_rope")(
+        x.data_ptr(), w.data_ptr(), M, K, x.stride(0), w.stride(0), nq, nkv,
+        q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), slot_mapping.data_ptr(), positions.data_ptr(),
+        _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps), _ptr(inv_freq),
+        _ptr(scale_ssq), scale_tiles, float(scale_width), float(scale_eps),
+        _ptr(partial), counters.data_ptr(), error.data_ptr(),
+        _ptr(prefetch), 0 if prefetch is None else min(prefetch.numel() * prefetch.element_size(), GEMM_PREFETCH_BYTES),
+        _stream()))
+
+
 def check_device_errors() -> None:
     """Raises if a kernel reported that one of its bounded waits gave up.  Cheap: reads
     pinned host words; call it wherever the host has just synchronised anyway."""

@@ -123,10 +123,24 @@ class AttentionMixer(Mixer):
         T = xt.shape[0]
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         tables = step.groups[cache.group]
-        qkv = linear_scaled(x, self.qkv_weight, next_weight=self.o_weight)
         q = torch.empty((T, nq * d), device=xt.device, dtype=xt.dtype)
         inv_freq = self.position.rotary_inv_freq() if self.position is not None else None
         fused = self.position is None or inv_freq is not None
+        if (fused and cache.writes and d == ops.GEMM_QK_ROPE_HEAD_DIM and (inv_freq is None or inv_freq.numel() == d // 2)
+                and folding_possible(T, xt.dtype, self.qkv_weight)):
+            # few tokens, heads of 128: norm, rotation and the store are the projection's own epilogue
+            pre = None if isinstance(x, torch.Tensor) else x
+            ops.gemm_qk_rope_store(
+                xt, self.qkv_weight, q, cache.k_pages, cache.v_pages, tables.slot_mapping, step.positions,
+                self.q_norm_weight, self.k_norm_weight, self.qk_norm_eps, inv_freq, nq, nkv,
+                scale_ssq=None if pre is None else pre.ssq, scale_width=1 if pre is None else pre.width,
+                scale_eps=0.0 if pre is None else pre.eps, prefetch=self.o_weight)
+            out = torch.empty((T, nq * d), device=xt.device, dtype=xt.dtype)
+            self._attend(q, out, step, cache, tables)
+            if fold is not None:
+                return linear_into_residual(out, self.o_weight, fold, next_weight=step.weight_after)
+            return linear(out, self.o_weight, next_weight=step.weight_after)
+        qkv = linear_scaled(x, self.qkv_weight, next_weight=self.o_weight)
         if fused and cache.writes:
             ops.qk_norm_rope_store(
                 qkv, q, cache.k_pages, cache.v_pages, tables.slot_mapping, step.positions,
