@@ -48,8 +48,15 @@ struct AttnParams {
   int* counters;                  // [B * nkv] tickets of the key splits (zero between launches), or null: merge in a kernel of its own
   int keys_per_split;             // > 0: split s covers this many keys (a multiple of BN); 0: the range is divided evenly
   int cluster;                    // 1: the key splits of a (sequence, KV head) pair are one thread-block cluster and merge through its shared memory
+  long long* probe;               // TS_ATT_PROBE builds: clock stamps of a few CTAs of the decode kernel
   float scale_log2;               // scale * log2(e)
 };
+
+#ifdef TS_ATT_PROBE
+#define APROBE(k) do { if (p.probe && threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) p.probe[blockIdx.x * 16 + (k)] = clock64(); } while (0)
+#else
+#define APROBE(k) do { } while (0)
+#endif
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -175,7 +182,13 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   constexpr int NT = NWARPS * 32;
   constexpr int BM = SPLIT_KEYS ? 16 : NWARPS * 16;
   constexpr int NTILES = SPLIT_KEYS ? 2 : BN / 8;  // 8-key score tiles per warp and block
-  ts_pdl_prologue();
+  APROBE(0);
+  // Decode (key-split mode): everything that does not depend on the kernel before is done before
+  // waiting for it: the step's index arrays (copied from the host before the step's first kernel)
+  // and the keys and values of earlier steps.  Only the queries and the keys and values of
+  // this step's own tokens (written by the projection just before) are fetched after the wait.
+  ts_pdl_launch_dependents();
+  if constexpr (!SPLIT_KEYS) ts_pdl_wait();
   static_assert(!SPLIT_KEYS || NWARPS * 16 == BN, "key-split mode: the warps must cover one key block");
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [BM][LD]
@@ -216,7 +229,9 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   const int* table = p.block_table + (size_t)b * p.max_blocks;
   if (nblocks <= 0 && p.splits > 1 && !p.cluster) {
     // A split beyond this sequence's keys: mark its partial as empty and leave.  (In a cluster it
-    // stays for the barriers and brings an empty partial: no key seen, sum 0.)
+    // stays for the barriers and brings an empty partial: no key seen, sum 0.)  Nothing is written
+    // before the kernels ahead are done: the scratch may be memory they still read.
+    if constexpr (SPLIT_KEYS) ts_pdl_wait();
     for (int r = tid; r < min(BM, rows_total - r0); r += NT) {
       const int row = r0 + r;
       const size_t qrow = (size_t)(q_begin + row / G) * p.nq + hk * G + row % G;
@@ -246,6 +261,26 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   const int warp_min_pos = warp_first_row < rows_total ? start_pos + warp_first_row / G : -1;
   const int warp_max_lo = (p.window > 0 && warp_first_row < rows_total) ? max(0, start_pos + warp_last_row / G - p.window + 1) : 0;
 
+  // Keys and values of the first two blocks (in decode: before the wait, see above).
+  int pg_first[2] = {-1, -1}, pg_next = -1;
+  if (nblocks > 0) {
+    pg_first[0] = lookup_page<NT>(table, p.page, kb0 * BN, hi, tid);
+    if (nblocks > 1) pg_first[1] = lookup_page<NT>(table, p.page, (kb0 + 1) * BN, hi, tid);
+    if constexpr (SPLIT_KEYS) {
+      load_kv_tiles<NT>(k_s, v_s, p.kcache, p.vcache, pg_first[0], p.page, p.nkv, hk, kb0 * BN, tid, false);
+      if (nblocks > 1)
+        load_kv_tiles<NT>(k_s + BN * LD, v_s + BN * LD, p.kcache, p.vcache, pg_first[1], p.page, p.nkv, hk, (kb0 + 1) * BN, tid, false);
+      if (nblocks > 2) pg_next = lookup_page<NT>(table, p.page, (kb0 + 2) * BN, hi, tid);
+    }
+  }
+  if constexpr (SPLIT_KEYS) {
+    ts_pdl_wait();
+    APROBE(1);
+    // what was asked for above has landed before rows of it are fetched again
+    cp_async_wait<0>();
+    __syncwarp();
+  }
+
   // Queries of the tile.
   for (int c = tid; c < BM * CH; c += NT) {
     const int row = c / CH, ch = c - row * CH;
@@ -255,14 +290,32 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     if (valid) src = p.q + ((size_t)(q_begin + r / G) * p.nq + hk * G + r % G) * D + ch * 8;
     cp_async16(q_s + row * LD + ch * 8, src, valid);
   }
-  cp_async_commit();
-  int pg_next = -1;
-  if (nblocks > 0) {
-    const int pg0 = lookup_page<NT>(table, p.page, kb0 * BN, hi, tid);
-    if (nblocks > 1) pg_next = lookup_page<NT>(table, p.page, (kb0 + 1) * BN, hi, tid);
-    load_kv_tiles<NT>(k_s, v_s, p.kcache, p.vcache, pg0, p.page, p.nkv, hk, kb0 * BN, tid, false);
+  if constexpr (SPLIT_KEYS) {
+    // this step's own keys and values (positions from start_pos on), where they lie in the two blocks already fetched
+    constexpr int TPR = NT / BN;
+    const int row = tid / TPR;
+#pragma unroll
+    for (int sblk = 0; sblk < 2; ++sblk) {
+      const int j = (kb0 + sblk) * BN + row;
+      if (sblk < nblocks && j >= start_pos && j <= hi && pg_first[sblk] >= 0) {
+        const size_t off = (((size_t)pg_first[sblk] * p.page + (j % p.page)) * p.nkv + hk) * D;
+#pragma unroll
+        for (int ch = tid % TPR; ch < CH; ch += TPR) {
+          cp_async16(k_s + (sblk * BN + row) * LD + ch * 8, p.kcache + off + ch * 8, true);
+          cp_async16(v_s + (sblk * BN + row) * LD + ch * 8, p.vcache + off + ch * 8, true);
+        }
+      }
+    }
+    cp_async_commit();
+  } else {
+    cp_async_commit();
+    if (nblocks > 0) {
+      if (nblocks > 1) pg_next = pg_first[1];
+      load_kv_tiles<NT>(k_s, v_s, p.kcache, p.vcache, pg_first[0], p.page, p.nkv, hk, kb0 * BN, tid, false);
+    }
   }
 
+  APROBE(2);
   float o_acc[D / 8][4];
 #pragma unroll
   for (int i = 0; i < D / 8; ++i)
@@ -272,10 +325,10 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
 
   unsigned q_frag[Q_IN_REGS ? D / 16 : 1][4];
   const __nv_bfloat16* q_warp = q_s + warp_row0 * LD;
-  if (nblocks > 0) {
+  if (nblocks > 0 && !SPLIT_KEYS) {
     cp_async_wait<2>();  // the queries have landed (K and V of block 0 may still fly)
   } else {
-    cp_async_wait<0>();
+    cp_async_wait<0>();  // decode: the queries and this step's own keys and values; the rest landed before
   }
   __syncthreads();
   if constexpr (Q_IN_REGS) {
@@ -289,15 +342,18 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     const int stage = it & 1;
     const int kbase = (kb0 + it) * BN;
     const bool more = it + 1 < nblocks;
-    if (more) {
+    // decode: blocks 0 and 1 are there already, so the first round has nothing to ask or wait for
+    const bool ask = more && !(SPLIT_KEYS && it == 0);
+    if (ask) {
       load_kv_tiles<NT>(k_s + (stage ^ 1) * BN * LD, v_s + (stage ^ 1) * BN * LD, p.kcache, p.vcache, pg_next, p.page,
                         p.nkv, hk, kbase + BN, tid, false);
       if (it + 2 < nblocks) pg_next = lookup_page<NT>(table, p.page, kbase + 2 * BN, hi, tid);
-      cp_async_wait<3>();
-    } else {
-      cp_async_wait<1>();
+      if constexpr (SPLIT_KEYS) cp_async_wait<2>(); else cp_async_wait<3>();
+    } else if (!more) {
+      if constexpr (SPLIT_KEYS) cp_async_wait<0>(); else cp_async_wait<1>();
     }
     tile_sync();
+    APROBE(3 + min(it, 3) * 2);
 
     // S = Q K^T over this warp's keys of the block
     float s[NTILES][4];
@@ -383,9 +439,9 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
       }
     }
 
-    if (more) {
+    if (ask) {
       cp_async_wait<2>();
-    } else {
+    } else if (!more) {
       cp_async_wait<0>();
     }
     tile_sync();
@@ -409,7 +465,9 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
       }
     }
     tile_sync();  // the next round's prefetch overwrites this stage
+    APROBE(4 + min(it, 3) * 2);
   }
+  APROBE(11);
 
   // Row sums live spread over the four threads of a quad.
 #pragma unroll
@@ -470,6 +528,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
         ml[1] = l;
       }
     }
+    APROBE(12);
     if (p.splits > 1 && p.cluster) {
       // The splits of this (sequence, KV head) pair are the CTAs of one cluster: each has left its
       // partial (weighted sum, max, sum of weights per row) in its own shared memory; after a
@@ -477,6 +536,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
       // memory, in rank order, and a second barrier keeps every CTA's memory alive until then.
       asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
       asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+      APROBE(13);
       unsigned rank, nranks;
       asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
       asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(nranks));
@@ -522,8 +582,10 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
           if (d < D) p.out[qrow * D + d] = __float2bfloat16_rn(acc[i] * inv);
         }
       }
+      APROBE(14);
       asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
       asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+      APROBE(15);
     }
     if (p.splits > 1 && !p.cluster && p.counters != nullptr) merge_splits_by_last_arriver<NT>(p, b, hk, q_begin, rows_total, G, &last_flag);
   } else {
@@ -898,6 +960,10 @@ static long long decode_slots() {
   return slots;
 }
 
+// TS_ATT_PROBE builds: where the decode kernel's first CTAs leave their clock stamps (16 per CTA).
+static long long* ts_attention_probe = nullptr;
+TS_EXPORT void ts_attention_mma_set_probe(long long* buffer) { ts_attention_probe = buffer; }
+
 // Whether decode steps with 2..8 key splits merge the splits inside a thread-block cluster
 // (through distributed shared memory) instead of through scratch and a second kernel.
 static int ts_attention_cluster_merge = 1;
@@ -941,6 +1007,7 @@ TS_EXPORT int ts_attention_paged_mma_fused(const void* q, const void* kcache, co
                (long long)B * nkv * splits <= decode_slots()) ? 1 : 0;
   if (p.cluster) p.counters = nullptr;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.probe = ts_attention_probe;
   const long long rows = (long long)max_q * G;
   int status;
   if (rows <= 16) {
