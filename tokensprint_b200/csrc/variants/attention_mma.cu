@@ -544,35 +544,45 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
       for (int r = (int)rank + (int)nranks * warp; r < rows_here; r += (int)nranks * NWARPS) {  // a warp per row
         const int row = r0 + r;
         const unsigned local = (unsigned)__cvta_generic_to_shared(o_s + NWARPS * 16 * D + r * (D + 2));
-        float m = -INFINITY;
-        for (unsigned c = 0; c < nranks; ++c) {
-          unsigned remote;
-          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(c));
-          float mc, lc;
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(mc) : "r"(remote + D * 4));
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(lc) : "r"(remote + D * 4 + 4));
-          if (lc > 0.f) m = fmaxf(m, mc);
-        }
-        float l = 0.f, acc[(D + 31) / 32];
+        // all loads of a kind are issued before the first is used: two round trips through the
+        // cluster's shared memory instead of two per rank
+        constexpr int MAXR = 8;  // a cluster has at most 8 CTAs
+        unsigned remote[MAXR];
+        float mc[MAXR], lc[MAXR];
 #pragma unroll
-        for (int i = 0; i < (D + 31) / 32; ++i) acc[i] = 0.f;
-        for (unsigned c = 0; c < nranks; ++c) {
-          unsigned remote;
-          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(c));
-          float mc, lc;
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(mc) : "r"(remote + D * 4));
-          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(lc) : "r"(remote + D * 4 + 4));
-          const float wgt = lc > 0.f ? exp2f(mc - m) : 0.f;
-          l += wgt * lc;
+        for (unsigned c = 0; c < MAXR; ++c) {
+          remote[c] = 0;
+          mc[c] = -INFINITY;
+          lc[c] = 0.f;
+          if (c < nranks) {
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[c]) : "r"(local), "r"(c));
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(mc[c]) : "r"(remote[c] + D * 4));
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(lc[c]) : "r"(remote[c] + D * 4 + 4));
+          }
+        }
+        float v[MAXR][(D + 31) / 32];
+#pragma unroll
+        for (unsigned c = 0; c < MAXR; ++c) {
 #pragma unroll
           for (int i = 0; i < (D + 31) / 32; ++i) {
             const int d = lane + 32 * i;
-            if (d < D) {
-              float v;
-              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote + d * 4));
-              acc[i] += wgt * v;
-            }
+            v[c][i] = 0.f;
+            if (c < nranks && d < D) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[c][i]) : "r"(remote[c] + d * 4));
           }
+        }
+        float m = -INFINITY;
+#pragma unroll
+        for (unsigned c = 0; c < MAXR; ++c)
+          if (lc[c] > 0.f) m = fmaxf(m, mc[c]);
+        float l = 0.f, acc[(D + 31) / 32];
+#pragma unroll
+        for (int i = 0; i < (D + 31) / 32; ++i) acc[i] = 0.f;
+#pragma unroll
+        for (unsigned c = 0; c < MAXR; ++c) {  // in rank order
+          const float wgt = lc[c] > 0.f ? exp2f(mc[c] - m) : 0.f;
+          l += wgt * lc[c];
+#pragma unroll
+          for (int i = 0; i < (D + 31) / 32; ++i) acc[i] += wgt * v[c][i];
         }
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const size_t qrow = (size_t)(q_begin + row / G) * p.nq + hk * G + row % G;
