@@ -386,6 +386,15 @@ def test_attention_tcgen05_mixed(nq, nkv, page, window, mode):
     assert torch.equal(run_tcgen05(case, window, mode), got)
 
 
+@pytest.mark.parametrize("mode", [1, 2])
+def test_attention_tcgen05_long_context_with_small_pages(mode):
+    """More block-table entries than the kernel keeps in shared memory (1,024): the entries
+    beyond come straight from the table.  9,000 keys in pages of 8; one portion starts deep inside."""
+    case = finish_case(paged_case([(260, 9000), (3, 8300)], 4, 1, 128, 8, torch.bfloat16, seed=21))
+    got = run_tcgen05(case, 0, mode)
+    assert rel_err(got, plain_attention(case, 0)) < 1e-2
+
+
 def test_attention_tcgen05_says_what_it_takes():
     from tokensprint_b200 import ops
 
