@@ -263,7 +263,8 @@ def test_attention_mma_mixed(nq, nkv, d, page, window):
 
 
 @pytest.mark.parametrize("splits", [1, 2, 5, 8, 32])
-@pytest.mark.parametrize("nq,nkv,d,page,window", [(32, 8, 128, 16, 0), (4, 2, 16, 16, 0), (16, 1, 64, 32, 0), (5, 1, 48, 4, 90), (40, 2, 80, 16, 0)])
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(32, 8, 128, 16, 0), (4, 2, 16, 16, 0), (16, 1, 64, 32, 0), (5, 1, 48, 4, 90), (40, 2, 80, 16, 0),
+                                                  (8, 2, 128, 8, 200), (4, 1, 128, 256, 0), (6, 2, 192, 64, 0), (2, 1, 256, 16, 300), (8, 8, 64, 128, 0)])
 def test_attention_mma_decode_with_key_splits(splits, nq, nkv, d, page, window):
     case = finish_case(paged_case(DECODE, nq, nkv, d, page, torch.bfloat16, seed=3 * d))
     got = run_mma(case, window, splits)
@@ -282,6 +283,14 @@ def test_attention_mma_decode_with_key_splits(splits, nq, nkv, d, page, window):
         assert rel_err(run_mma(case, window, splits), want) < 1e-2
     finally:
         lib.ts_attention_mma_set_cluster_merge(1)
+    # keys and values come by the copy engine where head and page sizes allow it; by the threads' own copies it is the same
+    lib.ts_attention_mma_set_decode_tma(0)
+    try:
+        assert rel_err(run_mma(case, window, splits), want) < 1e-2
+    finally:
+        lib.ts_attention_mma_set_decode_tma(1)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
 
 
 @pytest.mark.parametrize("splits,chunk", [(16, 64), (8, 128), (4, 256), (2, 512), (64, 64)])

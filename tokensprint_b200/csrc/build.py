@@ -182,7 +182,7 @@ def variant_path(name: str, defines: dict[str, int]) -> Path:
     h.update(" ".join(NVCC_FLAGS).encode())
     h.update(repr(sorted(defines.items())).encode())
     h.update(src.read_bytes())
-    for p in sorted(CSRC.glob("*.cuh")):
+    for p in sorted(list(CSRC.glob("*.cuh")) + list(VARIANTS.glob("*.cuh")) + list(VARIANTS.glob("*.h"))):
         h.update(p.read_bytes())
     tag = "_".join(f"{k.lower()}{v}" for k, v in sorted(defines.items()))
     rel = Path(h.hexdigest()[:16]) / f"libtokensprint_b200_{name}_{tag}.so"

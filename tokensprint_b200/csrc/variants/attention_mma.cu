@@ -16,7 +16,10 @@
 //
 // The order of the sums for one query row depends on its own keys and on the number of
 // splits only, never on what else is in the batch.
+#include <string.h>
+
 #include "../common.cuh"
+#include "kv_tensor_map.cuh"
 
 #ifndef TS_HEAD_DIM
 #error "compile with -DTS_HEAD_DIM=<head size>"
@@ -33,6 +36,12 @@ constexpr int LD = D + 8;         // padded row of a shared-memory tile (odd cou
 constexpr int CH = D / 8;         // 16-byte chunks per row
 constexpr int STAGES = 2;
 constexpr bool Q_IN_REGS = D <= 128;
+// Decode with the copy engine (TMA): head sizes that are multiples of 64 (a box is 64 wide).
+constexpr bool TMA_HEAD = (D % 64) == 0;
+constexpr int HALVES = TMA_HEAD ? D / 64 : 1;           // 64-wide boxes per head row
+constexpr unsigned KV_TILE = HALVES * BN * 128;         // bytes of the K (or V) rows of one block: [HALVES][64 keys][128 B], swizzled
+constexpr long long SLOT_BOUND = 1ll << 30;             // slots the maps declare; coordinate SLOT_BOUND is out of bounds: zeros, no access
+constexpr unsigned TMA_SPIN_LIMIT = 1u << 22;
 
 struct AttnParams {
   const __nv_bfloat16* q;         // [T, nq, D]
@@ -49,6 +58,7 @@ struct AttnParams {
   int keys_per_split;             // > 0: split s covers this many keys (a multiple of BN); 0: the range is divided evenly
   int cluster;                    // 1: the key splits of a (sequence, KV head) pair are one thread-block cluster and merge through its shared memory
   long long* probe;               // TS_ATT_PROBE builds: clock stamps of a few CTAs of the decode kernel
+  int* error;                     // set to 1 when a bounded wait of the copy-engine path gave up
   float scale_log2;               // scale * log2(e)
 };
 
@@ -57,6 +67,42 @@ struct AttnParams {
 #else
 #define APROBE(k) do { } while (0)
 #endif
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded: gives up after TMA_SPIN_LIMIT tries or when another thread of the CTA has.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag) {
+  for (unsigned i = 0; i < TMA_SPIN_LIMIT; ++i) {
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+// Address of the 16-byte piece that holds elements [col, col + 8) of row `row` in a swizzled tile
+// [HALVES][64 rows][128 B]: piece c of a row sits at position c ^ (row % 8).
+__device__ __forceinline__ const unsigned char* swizzled(const unsigned char* tile, int row, int col) {
+  return tile + (col >> 6) * (BN * 128) + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4);
+}
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -177,8 +223,14 @@ __device__ __forceinline__ void merge_splits_by_last_arriver(const AttnParams& p
 // SPLIT_KEYS = false (prefill): the CTA's warps own 16 query rows each and all walk every key.
 // SPLIT_KEYS = true (decode, at most 16 rows): the warps share the rows and own 16 keys each of
 // every 64-key block, with running max/sum/output of their own, merged when the keys are done.
-template <int NWARPS, bool SPLIT_KEYS>
-__global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnParams p) {
+// USE_TMA (decode only): the copy engine brings whole pages into swizzled tiles, one instruction
+// per box of [page rows x 64 elements] instead of one 16-byte copy per thread and piece (at
+// large batches the 16-byte copies, not the memory, bound the kernel); warp 0 asks, a pair of
+// mbarriers per stage says "landed" and "all four warps are done with it".
+template <int NWARPS, bool SPLIT_KEYS, bool USE_TMA>
+__global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnParams p, const __grid_constant__ CUtensorMap map_k,
+                                                                    const __grid_constant__ CUtensorMap map_v) {
+  static_assert(!USE_TMA || (SPLIT_KEYS && TMA_HEAD), "the copy-engine path is the decode path, for head sizes that are multiples of 64");
   constexpr int NT = NWARPS * 32;
   constexpr int BM = SPLIT_KEYS ? 16 : NWARPS * 16;
   constexpr int NTILES = SPLIT_KEYS ? 2 : BN / 8;  // 8-key score tiles per warp and block
@@ -194,7 +246,16 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [BM][LD]
   __nv_bfloat16* k_s = q_s + BM * LD;                                        // [STAGES][BN][LD]
   __nv_bfloat16* v_s = k_s + STAGES * BN * LD;                               // [STAGES][BN][LD]
+  // copy-engine path: swizzled tiles on a 1,024-byte boundary, K of both stages, then V of both stages
+  unsigned char* kv_tma = reinterpret_cast<unsigned char*>(((uintptr_t)(q_s + BM * LD) + 1023) & ~(uintptr_t)1023);
+  if constexpr (USE_TMA) {
+    k_s = reinterpret_cast<__nv_bfloat16*>(kv_tma);  // the merge at the end reuses this region through k_s
+    v_s = reinterpret_cast<__nv_bfloat16*>(kv_tma + STAGES * KV_TILE);
+  }
   __shared__ int last_flag;
+  __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES];
+  __shared__ int abort_s;
+  volatile int* abort_flag = &abort_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
@@ -261,9 +322,55 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   const int warp_min_pos = warp_first_row < rows_total ? start_pos + warp_first_row / G : -1;
   const int warp_max_lo = (p.window > 0 && warp_first_row < rows_total) ? max(0, start_pos + warp_last_row / G - p.window + 1) : 0;
 
+  // Copy-engine path: warp 0 asks for block `blk` (all its lanes together: every lane one box of
+  // [page rows x 64 elements] of K or V), waiting first until the four warps are done with what
+  // the stage held.  A page that is not held is asked for at a coordinate beyond the declared
+  // pool: the copy engine then writes zeros and touches no memory.
+  const int box_rows = min(p.page, BN), copies = BN / box_rows;
+  auto tma_ask = [&](int blk) -> bool {
+    const int stage = blk & 1;
+    bool ok = true;
+    if (blk >= STAGES) ok = mbar_wait(smem_u32(&empty_bar[stage]), (unsigned)((blk >> 1) - 1) & 1, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) return false;
+    if (lane == 0) mbar_expect_tx(smem_u32(&full_bar[stage]), 2 * KV_TILE);
+    __syncwarp();
+    for (int item = lane; item < copies * 2 * HALVES; item += 32) {
+      const int c = item / (2 * HALVES), which = (item / HALVES) & 1, half = item % HALVES;
+      const int key0 = (kb0 + blk) * BN + c * box_rows;
+      const int e = key0 / p.page;
+      int page_id = -1;
+      if (key0 <= hi && e < p.max_blocks) page_id = table[e];
+      const long long slot = page_id >= 0 ? (long long)page_id * p.page + key0 % p.page : SLOT_BOUND;
+      unsigned char* dst = kv_tma + (which * STAGES + stage) * KV_TILE + half * (BN * 128) + c * box_rows * 128;
+      tma_load_3d(smem_u32(dst), which ? &map_v : &map_k, smem_u32(&full_bar[stage]), half * 64, hk, (int)slot);
+    }
+    return true;
+  };
+  int asked = 0;  // blocks asked for so far (warp 0 keeps count; the other warps do not use it)
+  if constexpr (USE_TMA) {
+    if (tid == 0) {
+      abort_s = 0;
+      for (int i = 0; i < STAGES; ++i) {
+        mbar_init(smem_u32(&full_bar[i]), 1);
+        mbar_init(smem_u32(&empty_bar[i]), NWARPS);
+      }
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    // before the wait: blocks that hold only keys of earlier steps
+    if (warp == 0)
+      while (asked < min(nblocks, STAGES) && (kb0 + asked) * BN + BN - 1 < start_pos && tma_ask(asked)) ++asked;
+    ts_pdl_wait();
+    APROBE(1);
+    if (warp == 0)
+      while (asked < min(nblocks, STAGES) && tma_ask(asked)) ++asked;
+  }
+
   // Keys and values of the first two blocks (in decode: before the wait, see above).
   int pg_first[2] = {-1, -1}, pg_next = -1;
-  if (nblocks > 0) {
+  if (nblocks > 0 && !USE_TMA) {
     pg_first[0] = lookup_page<NT>(table, p.page, kb0 * BN, hi, tid);
     if (nblocks > 1) pg_first[1] = lookup_page<NT>(table, p.page, (kb0 + 1) * BN, hi, tid);
     if constexpr (SPLIT_KEYS) {
@@ -273,7 +380,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
       if (nblocks > 2) pg_next = lookup_page<NT>(table, p.page, (kb0 + 2) * BN, hi, tid);
     }
   }
-  if constexpr (SPLIT_KEYS) {
+  if constexpr (SPLIT_KEYS && !USE_TMA) {
     ts_pdl_wait();
     APROBE(1);
     // what was asked for above has landed before rows of it are fetched again
@@ -290,7 +397,9 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     if (valid) src = p.q + ((size_t)(q_begin + r / G) * p.nq + hk * G + r % G) * D + ch * 8;
     cp_async16(q_s + row * LD + ch * 8, src, valid);
   }
-  if constexpr (SPLIT_KEYS) {
+  if constexpr (USE_TMA) {
+    cp_async_commit();  // the queries
+  } else if constexpr (SPLIT_KEYS) {
     // this step's own keys and values (positions from start_pos on), where they lie in the two blocks already fetched
     constexpr int TPR = NT / BN;
     const int row = tid / TPR;
@@ -343,8 +452,21 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     const int kbase = (kb0 + it) * BN;
     const bool more = it + 1 < nblocks;
     // decode: blocks 0 and 1 are there already, so the first round has nothing to ask or wait for
-    const bool ask = more && !(SPLIT_KEYS && it == 0);
-    if (ask) {
+    const bool ask = !USE_TMA && more && !(SPLIT_KEYS && it == 0);
+    if constexpr (USE_TMA) {
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[stage]), (unsigned)(it >> 1) & 1, abort_flag))) break;
+      // rows of V beyond the last key hold whatever was in the cache: zeros instead (their weights
+      // are zero, but zero times garbage must stay zero); each warp clears its own 16 rows
+      if (kbase + BN - 1 > hi) {
+        unsigned char* v_tile = kv_tma + (STAGES + stage) * KV_TILE;
+        for (int i = lane; i < 16 * HALVES * 8; i += 32) {
+          const int row = warp * 16 + i / (HALVES * 8), piece = i % (HALVES * 8);
+          if (kbase + row > hi)
+            *reinterpret_cast<uint4*>(v_tile + (piece >> 3) * (BN * 128) + row * 128 + ((piece & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        __syncwarp();
+      }
+    } else if (ask) {
       load_kv_tiles<NT>(k_s + (stage ^ 1) * BN * LD, v_s + (stage ^ 1) * BN * LD, p.kcache, p.vcache, pg_next, p.page,
                         p.nkv, hk, kbase + BN, tid, false);
       if (it + 2 < nblocks) pg_next = lookup_page<NT>(table, p.page, kbase + 2 * BN, hi, tid);
@@ -352,7 +474,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     } else if (!more) {
       if constexpr (SPLIT_KEYS) cp_async_wait<0>(); else cp_async_wait<1>();
     }
-    tile_sync();
+    if constexpr (!USE_TMA) tile_sync();
     APROBE(3 + min(it, 3) * 2);
 
     // S = Q K^T over this warp's keys of the block
@@ -375,8 +497,12 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
 #pragma unroll
       for (int np = 0; np < NTILES / 2; ++np) {
         unsigned b0, b1, b2, b3;
-        ldmatrix_x4(b0, b1, b2, b3,
-                    k_tile + (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
+        if constexpr (USE_TMA)
+          ldmatrix_x4(b0, b1, b2, b3, swizzled(kv_tma + stage * KV_TILE, key0 + np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8,
+                                               ks * 16 + ((lane >> 3) & 1) * 8));
+        else
+          ldmatrix_x4(b0, b1, b2, b3,
+                      k_tile + (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
         mma_bf16(s[2 * np], a, b0, b1);
         mma_bf16(s[2 * np + 1], a, b2, b3);
       }
@@ -439,12 +565,14 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
       }
     }
 
-    if (ask) {
-      cp_async_wait<2>();
-    } else if (!more) {
-      cp_async_wait<0>();
+    if constexpr (!USE_TMA) {
+      if (ask) {
+        cp_async_wait<2>();
+      } else if (!more) {
+        cp_async_wait<0>();
+      }
+      tile_sync();
     }
-    tile_sync();
 
     // O += P V
     const __nv_bfloat16* v_tile = v_s + stage * BN * LD + key0 * LD;
@@ -458,14 +586,31 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
 #pragma unroll
       for (int np = 0; np < D / 16; ++np) {
         unsigned b0, b1, b2, b3;
-        ldmatrix_x4_trans(b0, b1, b2, b3,
-                          v_tile + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + np * 16 + ((lane >> 4) & 1) * 8);
+        if constexpr (USE_TMA)
+          ldmatrix_x4_trans(b0, b1, b2, b3, swizzled(kv_tma + (STAGES + stage) * KV_TILE, key0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
+                                                     np * 16 + ((lane >> 4) & 1) * 8));
+        else
+          ldmatrix_x4_trans(b0, b1, b2, b3,
+                            v_tile + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + np * 16 + ((lane >> 4) & 1) * 8);
         mma_bf16(o_acc[2 * np], a, b0, b1);
         mma_bf16(o_acc[2 * np + 1], a, b2, b3);
       }
     }
-    tile_sync();  // the next round's prefetch overwrites this stage
+    if constexpr (USE_TMA) {
+      // this warp is done with the stage; warp 0 asks for the block after next once all are
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
+      if (warp == 0 && asked < nblocks && asked == it + STAGES) {
+        if (!tma_ask(asked)) break;
+        ++asked;
+      }
+    } else {
+      tile_sync();  // the next round's prefetch overwrites this stage
+    }
     APROBE(4 + min(it, 3) * 2);
+  }
+  if constexpr (USE_TMA) {
+    if (abort_s != 0 && tid == 0 && p.error != nullptr) *p.error = 1;
   }
   APROBE(11);
 
@@ -924,15 +1069,48 @@ int launch(const AttnParams& p, int B, cudaStream_t stream) {
   const size_t smem = (size_t)(BM + 2 * STAGES * BN) * LD * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<NWARPS, SPLIT_KEYS>,
+    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<NWARPS, SPLIT_KEYS, false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
+  CUtensorMap none;
+  memset(&none, 0, sizeof(none));
   dim3 grid(p.row_tiles * p.splits, p.nkv, B);
   if (p.cluster)  // the grid's x dimension is the key splits of one pair: one cluster
-    return ts_launch_cluster(attention_mma_kernel<NWARPS, SPLIT_KEYS>, grid, dim3(NWARPS * 32), smem, stream, p.splits, p);
-  return ts_launch(attention_mma_kernel<NWARPS, SPLIT_KEYS>, grid, dim3(NWARPS * 32), smem, stream, p);
+    return ts_launch_cluster(attention_mma_kernel<NWARPS, SPLIT_KEYS, false>, grid, dim3(NWARPS * 32), smem, stream, p.splits, p, none, none);
+  return ts_launch(attention_mma_kernel<NWARPS, SPLIT_KEYS, false>, grid, dim3(NWARPS * 32), smem, stream, p, none, none);
+}
+
+// Whether the decode kernel's copy-engine path takes these sizes.
+bool decode_tma_ok(const AttnParams& p) {
+  return TMA_HEAD && p.page >= 8 && (BN % p.page == 0 || p.page % BN == 0) &&
+         ((uintptr_t)p.kcache | (uintptr_t)p.vcache) % 16 == 0 && ((long long)p.nkv * D * 2) % 16 == 0;
+}
+
+// Decode with the copy engine: the same kernel, its K/V tiles swizzled and brought by TMA.
+int launch_decode_tma(const AttnParams& p, int B, cudaStream_t stream) {
+  if constexpr (!TMA_HEAD) {
+    return TS_ERR_UNSUPPORTED_SIZE;
+  } else {
+    const size_t smem = (size_t)16 * LD * sizeof(__nv_bfloat16) + 1024 + (size_t)2 * STAGES * KV_TILE;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<4, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    CUtensorMap mk, mv;
+    const int box_rows = p.page < BN ? p.page : BN;
+    int st = ts_kv_cache_map(p.kcache, SLOT_BOUND, p.nkv, D, box_rows, &mk);
+    if (st != 0) return st;
+    st = ts_kv_cache_map(p.vcache, SLOT_BOUND, p.nkv, D, box_rows, &mv);
+    if (st != 0) return st;
+    dim3 grid(p.row_tiles * p.splits, p.nkv, B);
+    if (p.cluster)
+      return ts_launch_cluster(attention_mma_kernel<4, true, true>, grid, dim3(128), smem, stream, p.splits, p, mk, mv);
+    return ts_launch(attention_mma_kernel<4, true, true>, grid, dim3(128), smem, stream, p, mk, mv);
+  }
 }
 
 }  // namespace
@@ -963,8 +1141,8 @@ static long long decode_slots() {
     int dev = 0, sms = 0, per_sm = 0;
     const size_t smem = (size_t)(16 + 2 * STAGES * BN) * LD * sizeof(__nv_bfloat16);
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
-    cudaFuncSetAttribute(attention_mma_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_mma_kernel<4, true>, 128, smem) != cudaSuccess || per_sm <= 0) per_sm = 1;
+    cudaFuncSetAttribute(attention_mma_kernel<4, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_mma_kernel<4, true, false>, 128, smem) != cudaSuccess || per_sm <= 0) per_sm = 1;
     slots = (long long)sms * per_sm;
   }
   return slots;
@@ -973,6 +1151,13 @@ static long long decode_slots() {
 // TS_ATT_PROBE builds: where the decode kernel's first CTAs leave their clock stamps (16 per CTA).
 static long long* ts_attention_probe = nullptr;
 TS_EXPORT void ts_attention_mma_set_probe(long long* buffer) { ts_attention_probe = buffer; }
+
+// Whether decode steps fetch keys and values with the copy engine where the sizes allow it, and the
+// word (in memory the host can read) that a kernel sets when one of its bounded waits gave up.
+static int ts_attention_decode_tma = 1;
+static int* ts_attention_error_word = nullptr;
+TS_EXPORT void ts_attention_mma_set_decode_tma(int on) { ts_attention_decode_tma = on ? 1 : 0; }
+TS_EXPORT void ts_attention_mma_set_error_word(int* word) { ts_attention_error_word = word; }
 
 // Whether decode steps with 2..8 key splits merge the splits inside a thread-block cluster
 // (through distributed shared memory) instead of through scratch and a second kernel.
@@ -1018,11 +1203,12 @@ TS_EXPORT int ts_attention_paged_mma_fused(const void* q, const void* kcache, co
   if (p.cluster) p.counters = nullptr;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.probe = ts_attention_probe;
+  p.error = ts_attention_error_word;
   const long long rows = (long long)max_q * G;
   int status;
   if (rows <= 16) {
     p.row_tiles = 1;
-    status = launch<4, true>(p, B, stream);
+    status = (ts_attention_decode_tma && decode_tma_ok(p)) ? launch_decode_tma(p, B, stream) : launch<4, true>(p, B, stream);
   } else {
     p.row_tiles = (int)((rows + 127) / 128);
     if (D <= 128 && splits == 1)

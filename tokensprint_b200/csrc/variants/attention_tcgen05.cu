@@ -24,12 +24,8 @@
 // Limits (the caller falls back to the mma.sync kernel otherwise): head size 128; the group
 // size (query heads per KV head) divides 128; the page size is at least 8 and divides 64 or is a
 // multiple of it.
-#include <cuda.h>
-
-#include <mutex>
-#include <unordered_map>
-
 #include "../common.cuh"
+#include "kv_tensor_map.cuh"
 
 #if TS_HEAD_DIM != 128
 #error "attention_tcgen05.cu is written for TS_HEAD_DIM=128"
@@ -965,71 +961,18 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
 // ---------------------------------------------------------------------------
 // host side
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)ptr;
-  }
-  return fn;
-}
-
-struct MapKey {
-  const void* ptr;
-  long long a, b, c;
-  bool operator==(const MapKey& o) const { return ptr == o.ptr && a == o.a && b == o.b && c == o.c; }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& k) const {
-    return std::hash<const void*>()(k.ptr) * 1000003u ^ std::hash<long long>()(k.a * 131 + k.b * 31 + k.c);
-  }
-};
-std::mutex map_mutex;
-std::unordered_map<MapKey, CUtensorMap, MapKeyHash> map_cache;
-
-// K or V pool [slots, nkv, D] as a 3-d tensor {D, nkv, slots}; boxes of {64, 1, page}.
-int cache_map(const void* ptr, long long slots, int nkv, int page, CUtensorMap* out) {
-  MapKey key{ptr, slots, nkv, page};
-  std::lock_guard<std::mutex> lock(map_mutex);
-  auto it = map_cache.find(key);
-  if (it != map_cache.end()) {
-    *out = it->second;
-    return 0;
-  }
-  EncodeTiledFn fn = encode_tiled();
-  if (!fn) return TS_ERR_UNSUPPORTED_SIZE;
-  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)nkv, (cuuint64_t)slots};
-  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)nkv * D * 2};
-  cuuint32_t box[3] = {64, 1, (cuuint32_t)(page < BN ? page : BN)};
-  cuuint32_t estr[3] = {1, 1, 1};
-  if (fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return TS_ERR_BAD_ARGUMENT;
-  if (map_cache.size() > 4096) map_cache.clear();
-  map_cache.emplace(key, *out);
-  return 0;
-}
-
 // q [T, nq, D] as a 4-d tensor {D, G, nkv, T}; boxes of {64, G, 1, 128 / G}: the rows of a box
 // come out ordered (token, head of the group), which is the tile's row order.
 int query_map(const void* ptr, long long T, int nq, int nkv, CUtensorMap* out) {
-  MapKey key{ptr, T, nq, -(long long)nkv};
-  std::lock_guard<std::mutex> lock(map_mutex);
+  TsMapKey key{ptr, T, nq, -(long long)nkv};
+  std::lock_guard<std::mutex> lock(ts_map_mutex());
+  auto& map_cache = ts_map_cache();
   auto it = map_cache.find(key);
   if (it != map_cache.end()) {
     *out = it->second;
     return 0;
   }
-  EncodeTiledFn fn = encode_tiled();
+  TsEncodeTiledFn fn = ts_encode_tiled();
   if (!fn) return TS_ERR_UNSUPPORTED_SIZE;
   const int G = nq / nkv;
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)G, (cuuint64_t)nkv, (cuuint64_t)T};
@@ -1076,9 +1019,9 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
   CUtensorMap mq, mk, mv;
   int st = query_map(q, T, nq, nkv, &mq);
   if (st) return st;
-  st = cache_map(kcache, total_slots, nkv, page, &mk);
+  st = ts_kv_cache_map(kcache, total_slots, nkv, D, page < BN ? page : BN, &mk);
   if (st) return st;
-  st = cache_map(vcache, total_slots, nkv, page, &mv);
+  st = ts_kv_cache_map(vcache, total_slots, nkv, D, page < BN ? page : BN, &mv);
   if (st) return st;
   Params p;
   p.out = (__nv_bfloat16*)out;

@@ -340,6 +340,21 @@ def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 # Decode steps with 2..8 key splits: the splits of a (sequence, KV head) pair form a thread-block
 # cluster and merge through its shared memory (TS_ATTENTION_CLUSTER=0: scratch and a second kernel).
 ATTENTION_CLUSTER_MERGE = _os.environ.get("TS_ATTENTION_CLUSTER", "1") != "0"
+# Decode steps fetch keys and values with the copy engine (TMA) where the sizes allow it: head sizes
+# that are multiples of 64, pages of at least 8 slots that divide 64 or are multiples of it
+# (TS_ATTENTION_TMA=0: 16-byte asynchronous copies by the threads, which take every size).
+ATTENTION_DECODE_TMA = _os.environ.get("TS_ATTENTION_TMA", "1") != "0"
+_attention_error: Optional[torch.Tensor] = None
+
+
+def _attention_error_word() -> torch.Tensor:
+    """One int in pinned host memory that the decode attention sets when a bounded wait gave up."""
+    global _attention_error
+    if _attention_error is None:
+        _attention_error = torch.zeros(1, dtype=torch.int32).pin_memory()
+    return _attention_error
+
+
 ATTENTION_MMA_MAX_HEAD_DIM = 256
 ATTENTION_MMA_MAX_SPLITS = 64
 _attention_mma: dict[int, tuple] = {}
@@ -366,6 +381,10 @@ def _attention_mma_fns(head_dim: int):
             raise KernelError("attention_paged_mma: the loaded library was built for another head size")
         lib.ts_attention_mma_set_cluster_merge.argtypes = [_c_int]
         lib.ts_attention_mma_set_cluster_merge(1 if ATTENTION_CLUSTER_MERGE else 0)
+        lib.ts_attention_mma_set_decode_tma.argtypes = [_c_int]
+        lib.ts_attention_mma_set_decode_tma(1 if ATTENTION_DECODE_TMA else 0)
+        lib.ts_attention_mma_set_error_word.argtypes = [_c_void_p]
+        lib.ts_attention_mma_set_error_word(_attention_error_word().data_ptr())
         fns = (run, scratch)
         _attention_mma[head_dim] = fns
     return fns
@@ -814,6 +833,9 @@ def gemm_qk_rope_store(
 def check_device_errors() -> None:
     """Raises if a kernel reported that one of its bounded waits gave up.  Cheap: reads
     pinned host words; call it wherever the host has just synchronised anyway."""
+    if _attention_error is not None and int(_attention_error[0]) != 0:
+        _attention_error[0] = 0
+        raise KernelError("decode attention: a wait on an mbarrier gave up (the kernel returned early)")
     for (dev, _), (_, error) in _gemm_workspaces.items():
         if int(error[0]) != 0:
             error[0] = 0
