@@ -42,6 +42,10 @@ constexpr int HALVES = TMA_HEAD ? D / 64 : 1;           // 64-wide boxes per hea
 constexpr unsigned KV_TILE = HALVES * BN * 128;         // bytes of the K (or V) rows of one block: [HALVES][64 keys][128 B], swizzled
 constexpr long long SLOT_BOUND = 1ll << 30;             // slots the maps declare; coordinate SLOT_BOUND is out of bounds: zeros, no access
 constexpr unsigned TMA_SPIN_LIMIT = 1u << 22;
+#ifndef TS_DECODE_TMA_STAGES
+#define TS_DECODE_TMA_STAGES 2
+#endif
+constexpr int TSTAGES = TS_DECODE_TMA_STAGES;           // key blocks in flight per CTA on the copy-engine path
 
 struct AttnParams {
   const __nv_bfloat16* q;         // [T, nq, D]
@@ -250,10 +254,10 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   unsigned char* kv_tma = reinterpret_cast<unsigned char*>(((uintptr_t)(q_s + BM * LD) + 1023) & ~(uintptr_t)1023);
   if constexpr (USE_TMA) {
     k_s = reinterpret_cast<__nv_bfloat16*>(kv_tma);  // the merge at the end reuses this region through k_s
-    v_s = reinterpret_cast<__nv_bfloat16*>(kv_tma + STAGES * KV_TILE);
+    v_s = reinterpret_cast<__nv_bfloat16*>(kv_tma + TSTAGES * KV_TILE);
   }
   __shared__ int last_flag;
-  __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES];
+  __shared__ __align__(8) unsigned long long full_bar[TSTAGES], empty_bar[TSTAGES];
   __shared__ int abort_s;
   volatile int* abort_flag = &abort_s;
 
@@ -328,9 +332,9 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   // pool: the copy engine then writes zeros and touches no memory.
   const int box_rows = min(p.page, BN), copies = BN / box_rows;
   auto tma_ask = [&](int blk) -> bool {
-    const int stage = blk & 1;
+    const int stage = blk % TSTAGES;
     bool ok = true;
-    if (blk >= STAGES) ok = mbar_wait(smem_u32(&empty_bar[stage]), (unsigned)((blk >> 1) - 1) & 1, abort_flag);
+    if (blk >= TSTAGES) ok = mbar_wait(smem_u32(&empty_bar[stage]), (unsigned)(blk / TSTAGES - 1) & 1, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) return false;
     if (lane == 0) mbar_expect_tx(smem_u32(&full_bar[stage]), 2 * KV_TILE);
@@ -342,7 +346,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
       int page_id = -1;
       if (key0 <= hi && e < p.max_blocks) page_id = table[e];
       const long long slot = page_id >= 0 ? (long long)page_id * p.page + key0 % p.page : SLOT_BOUND;
-      unsigned char* dst = kv_tma + (which * STAGES + stage) * KV_TILE + half * (BN * 128) + c * box_rows * 128;
+      unsigned char* dst = kv_tma + (which * TSTAGES + stage) * KV_TILE + half * (BN * 128) + c * box_rows * 128;
       tma_load_3d(smem_u32(dst), which ? &map_v : &map_k, smem_u32(&full_bar[stage]), half * 64, hk, (int)slot);
     }
     return true;
@@ -351,7 +355,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   if constexpr (USE_TMA) {
     if (tid == 0) {
       abort_s = 0;
-      for (int i = 0; i < STAGES; ++i) {
+      for (int i = 0; i < TSTAGES; ++i) {
         mbar_init(smem_u32(&full_bar[i]), 1);
         mbar_init(smem_u32(&empty_bar[i]), NWARPS);
       }
@@ -361,11 +365,11 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     __syncthreads();
     // before the wait: blocks that hold only keys of earlier steps
     if (warp == 0)
-      while (asked < min(nblocks, STAGES) && (kb0 + asked) * BN + BN - 1 < start_pos && tma_ask(asked)) ++asked;
+      while (asked < min(nblocks, TSTAGES) && (kb0 + asked) * BN + BN - 1 < start_pos && tma_ask(asked)) ++asked;
     ts_pdl_wait();
     APROBE(1);
     if (warp == 0)
-      while (asked < min(nblocks, STAGES) && tma_ask(asked)) ++asked;
+      while (asked < min(nblocks, TSTAGES) && tma_ask(asked)) ++asked;
   }
 
   // Keys and values of the first two blocks (in decode: before the wait, see above).
@@ -448,17 +452,17 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   }
 
   for (int it = 0; it < nblocks; ++it) {
-    const int stage = it & 1;
+    const int stage = USE_TMA ? it % TSTAGES : (it & 1);
     const int kbase = (kb0 + it) * BN;
     const bool more = it + 1 < nblocks;
     // decode: blocks 0 and 1 are there already, so the first round has nothing to ask or wait for
     const bool ask = !USE_TMA && more && !(SPLIT_KEYS && it == 0);
     if constexpr (USE_TMA) {
-      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[stage]), (unsigned)(it >> 1) & 1, abort_flag))) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&full_bar[stage]), (unsigned)(it / TSTAGES) & 1, abort_flag))) break;
       // rows of V beyond the last key hold whatever was in the cache: zeros instead (their weights
       // are zero, but zero times garbage must stay zero); each warp clears its own 16 rows
       if (kbase + BN - 1 > hi) {
-        unsigned char* v_tile = kv_tma + (STAGES + stage) * KV_TILE;
+        unsigned char* v_tile = kv_tma + (TSTAGES + stage) * KV_TILE;
         for (int i = lane; i < 16 * HALVES * 8; i += 32) {
           const int row = warp * 16 + i / (HALVES * 8), piece = i % (HALVES * 8);
           if (kbase + row > hi)
@@ -587,7 +591,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
       for (int np = 0; np < D / 16; ++np) {
         unsigned b0, b1, b2, b3;
         if constexpr (USE_TMA)
-          ldmatrix_x4_trans(b0, b1, b2, b3, swizzled(kv_tma + (STAGES + stage) * KV_TILE, key0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
+          ldmatrix_x4_trans(b0, b1, b2, b3, swizzled(kv_tma + (TSTAGES + stage) * KV_TILE, key0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
                                                      np * 16 + ((lane >> 4) & 1) * 8));
         else
           ldmatrix_x4_trans(b0, b1, b2, b3,
@@ -600,7 +604,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
       // this warp is done with the stage; warp 0 asks for the block after next once all are
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
-      if (warp == 0 && asked < nblocks && asked == it + STAGES) {
+      if (warp == 0 && asked < nblocks && asked == it + TSTAGES) {
         if (!tma_ask(asked)) break;
         ++asked;
       }
@@ -1093,7 +1097,7 @@ int launch_decode_tma(const AttnParams& p, int B, cudaStream_t stream) {
   if constexpr (!TMA_HEAD) {
     return TS_ERR_UNSUPPORTED_SIZE;
   } else {
-    const size_t smem = (size_t)16 * LD * sizeof(__nv_bfloat16) + 1024 + (size_t)2 * STAGES * KV_TILE;
+    const size_t smem = (size_t)16 * LD * sizeof(__nv_bfloat16) + 1024 + (size_t)2 * TSTAGES * KV_TILE;
     static bool configured = false;
     if (!configured) {
       cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<4, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
