@@ -11,13 +11,15 @@ from tests.replay_helpers import random_tokens, replay_in_process, trace_decode_
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def folder(tmp_path_factory):
+@pytest.fixture(scope="module", params=["qwen3-8b", "qwen3-32b", "qwen3-0.6b"])
+def folder(request, tmp_path_factory):
+    """8B: four query heads per KV head; 32B: eight, width 5120, intermediate 25600; 0.6B: two,
+    width 1024 with heads of 128 (heads * head size is twice the width) and a tied head."""
     from tokensprint_b200.config.model_config import Qwen3Config
     from tokensprint_b200.config.registry import get_preset_dict
     from tokensprint_b200.weights.loader import write_random_model
 
-    d = get_preset_dict("qwen3-8b")
+    d = get_preset_dict(request.param)
     d["num_hidden_layers"] = 2
     cfg = Qwen3Config.from_dict(d)
     path = write_random_model(tmp_path_factory.mktemp("wide") / "m", cfg, seed=3, dtype="bfloat16", std=0.02)
