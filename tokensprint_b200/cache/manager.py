@@ -105,6 +105,7 @@ class CacheManager:
         if len(groups) != len(pages_per_group):
             raise ValueError("one page count per group is needed")
         self.groups = list(groups)
+        self._any_window = any(g.kind == "window" for g in self.groups)
         self.page_size = page_size
         self.pools = [PagePool(n) for n in pages_per_group]
         self.num_slots = num_slots
@@ -166,8 +167,18 @@ class CacheManager:
             plan.append((droppable, max(0, total - len(table))))
         return plan
 
+    def _fits_as_is(self, rc: RequestCache, new_len: int) -> bool:
+        """The common case of a decode step: no group has a window and the pages held already
+        cover new_len positions, so nothing is taken and nothing given back."""
+        if self._any_window or rc.released or new_len < rc.num_tokens:
+            return False
+        total = -(-new_len // self.page_size)
+        return all(len(t) >= total for t in rc.tables)
+
     def can_extend(self, rc: RequestCache, start: int, new_len: int) -> bool:
         """Whether `extend` would succeed right now."""
+        if self._fits_as_is(rc, new_len) and start <= new_len:
+            return True
         for pool, (drop, take) in zip(self.pools, self._plan(rc, start, new_len)):
             if take > pool.num_free + drop:
                 return False
@@ -181,6 +192,9 @@ class CacheManager:
         """
         if rc.released:
             raise CacheError(f"request {rc.request!r} was freed")
+        if self._fits_as_is(rc, new_len) and start <= new_len:
+            rc.num_tokens = new_len
+            return
         plan = self._plan(rc, start, new_len)
         for pool, (drop, take) in zip(self.pools, plan):
             if take > pool.num_free + drop:

@@ -48,6 +48,8 @@ class _DecodeGraph:
     logits: torch.Tensor  # [bucket, vocab] float32, rewritten by every replay
     kernels: int  # kernels of this library inside the graph
     event: Optional["torch.cuda.Event"] = None
+    # per cache group: row of the batch -> (request cache, table entries written, first entry still held)
+    row_marks: list = None
 
 
 def _round4(n: int) -> int:
@@ -214,7 +216,7 @@ class ModelRunner:
         step.rows_all = all(list(e.want) == list(range(n)) for e, n in zip(entries, lens))
         return step, layout.view(dev, "rows"), R
 
-    def _fill(self, host, layout: _Layout, entries: Sequence[StepEntry], lens: Sequence[int]) -> None:
+    def _fill(self, host, layout: _Layout, entries: Sequence[StepEntry], lens: Sequence[int], row_marks=None) -> None:
         """Writes the step's index arrays into `host` (a numpy view of pinned memory).  A
         layout larger than the step (a graph bucket) is padded with lanes that belong to no
         request: sequence index -1, no cache slot, no tokens in their sequence."""
@@ -243,12 +245,20 @@ class ModelRunner:
                 raise ValueError(
                     f"request {rc.request!r}: tokens {e.start}..{e.start + n - 1} have no place in the cache "
                     f"({rc.num_tokens} positions were given one)")
-            ids = np.asarray(e.tokens, dtype=np.int64)
-            if ids.min() < 0 or ids.max() >= self.vocab_size:
-                raise ValueError(f"request {rc.request!r}: token id outside 0..{self.vocab_size - 1}")
-            tok[t0 : t0 + n] = ids
-            pos[t0 : t0 + n] = np.arange(e.start, e.start + n)
-            sidx[t0 : t0 + n] = b
+            if n == 1:  # a decoded token: plain numbers instead of array operations
+                token = e.tokens[0]
+                if not 0 <= token < self.vocab_size:
+                    raise ValueError(f"request {rc.request!r}: token id outside 0..{self.vocab_size - 1}")
+                tok[t0] = token
+                pos[t0] = e.start
+                sidx[t0] = b
+            else:
+                ids = np.asarray(e.tokens, dtype=np.int64)
+                if ids.min() < 0 or ids.max() >= self.vocab_size:
+                    raise ValueError(f"request {rc.request!r}: token id outside 0..{self.vocab_size - 1}")
+                tok[t0 : t0 + n] = ids
+                pos[t0 : t0 + n] = np.arange(e.start, e.start + n)
+                sidx[t0 : t0 + n] = b
             cu[b + 1] = t0 + n
             ctx_lens[b] = e.start + n
             slots[b] = rc.slot
@@ -258,10 +268,29 @@ class ModelRunner:
                 rows[r0] = t0 + w
                 r0 += 1
             for g in range(len(self.groups)):
-                slot_maps[g][t0 : t0 + n] = self.cache_manager.slots_for(rc, g, e.start, n)
-                have = rc.tables[g][: widths[g]]
-                tables[g][b, : len(have)] = have
-                tables[g][b, len(have) :] = -1
+                table = rc.tables[g]
+                if n == 1:
+                    page = table[e.start // self.page_size]
+                    if page < 0:
+                        raise ValueError(f"request {rc.request!r}: position {e.start} lies in a page that was given back")
+                    slot_maps[g][t0] = page * self.page_size + e.start % self.page_size
+                else:
+                    slot_maps[g][t0 : t0 + n] = self.cache_manager.slots_for(rc, g, e.start, n)
+                count = min(len(table), widths[g])
+                # A buffer that is filled step after step (a decode graph's) remembers what each
+                # row holds: the same request in the same row only gets its new entries written
+                # (and the entries a window gave back), not its whole table again.
+                mark = None if row_marks is None else row_marks[g].get(b)
+                if mark is not None and mark[0] is rc and mark[1] <= count and mark[2] <= rc.first_held[g]:
+                    if mark[1] < count:
+                        tables[g][b, mark[1] : count] = table[mark[1] : count]
+                    if mark[2] < rc.first_held[g]:
+                        tables[g][b, mark[2] : min(rc.first_held[g], count)] = -1
+                else:
+                    tables[g][b, :count] = table[:count]
+                    tables[g][b, count:] = -1
+                if row_marks is not None:
+                    row_marks[g][b] = (rc, count, rc.first_held[g])
             if rc.fresh_slot:
                 self.cache_tensors.zero_slot(rc.slot)
                 rc.fresh_slot = False
@@ -280,6 +309,9 @@ class ModelRunner:
             slots[nb:] = 0
             for g in range(len(self.groups)):
                 tables[g][nb:] = -1
+                if row_marks is not None:
+                    for b in range(nb, B):
+                        row_marks[g].pop(b, None)
         if r0 < layout.R:
             rows[r0:] = 0
 
@@ -355,7 +387,7 @@ class ModelRunner:
         kernels = ops.launch_count - before
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
-        return _DecodeGraph(bucket, layout, dev, host, graph, logits, kernels)
+        return _DecodeGraph(bucket, layout, dev, host, graph, logits, kernels, row_marks=[{} for _ in self.groups])
 
     def _step_graph(self, bucket: int, entries: Sequence[StepEntry]) -> torch.Tensor:
         g = self._graphs.get(bucket)
@@ -363,7 +395,7 @@ class ModelRunner:
             g = self._graphs[bucket] = self._capture(bucket)
         if g.event is not None:
             g.event.synchronize()
-        self._fill(g.host.numpy(), g.layout, entries, [1] * len(entries))
+        self._fill(g.host.numpy(), g.layout, entries, [1] * len(entries), g.row_marks)
         # in a graph every lane's logits are computed; the wanted ones are picked afterwards
         rows_off = g.layout.sections["rows"][0]
         g.host.numpy()[rows_off : rows_off + bucket] = np.arange(bucket)
