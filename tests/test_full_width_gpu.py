@@ -38,7 +38,7 @@ def _logits(folder, dtype, steps, graphs=False):
     return got
 
 
-def test_full_width_cuttings(folder):
+def test_full_width_cuttings(folder, monkeypatch):
     path, cfg = folder
     requests = {"a": random_tokens(cfg, 150, 1), "b": random_tokens(cfg, 70, 2), "c": random_tokens(cfg, 33, 3)}
     ref = _logits(path, "float32", trace_whole(requests))
@@ -66,3 +66,23 @@ def test_full_width_cuttings(folder):
         assert len(got) == len(ref)
         worst = max(float(abs(got[k] - ref[k]).max()) for k in ref)
         assert worst < 4e-2 * scale, f"{name}: bfloat16 strays {worst / scale:.3g} from float32"
+
+    # decode steps through the kernel that gives every CTA an even share of all key blocks (the
+    # engine takes it for batches whose (sequence, KV head) pairs do not all run at once)
+    from tokensprint_b200 import ops
+
+    calls = []
+    flat = ops.attention_decode_flat
+    monkeypatch.setattr(ops, "attention_decode_prefers_flat", lambda *a: True)
+    monkeypatch.setattr(ops, "attention_decode_flat", lambda *a, **k: (calls.append(1), flat(*a, **k))[1])
+    for name, steps, graphs in (
+        ("tail, even shares", trace_decode_tail(requests), False),
+        ("tail in graphs, even shares", trace_decode_tail(requests), True),
+        ("mixed with graphs, even shares", trace_mixed(requests, 512, seed=2), True),
+    ):
+        calls.clear()
+        got = _logits(path, "bfloat16", steps, graphs)
+        assert calls, f"{name}: the even-share kernel did not run"
+        worst = max(float(abs(got[k] - ref[k]).max()) for k in ref)
+        assert worst < 4e-2 * scale, f"{name}: bfloat16 strays {worst / scale:.3g} from float32"
+    ops.check_device_errors()

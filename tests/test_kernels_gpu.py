@@ -293,6 +293,111 @@ def test_attention_mma_decode_with_key_splits(splits, nq, nkv, d, page, window):
     ops.check_device_errors()
 
 
+def run_flat(case, window=0, ctas=0):
+    from tokensprint_b200 import ops
+
+    out = torch.full_like(case["q"], float("nan"))
+    max_q = max(ql for ql, _ in case["seqs"])
+    ops.attention_decode_flat(case["q"], case["kc"], case["vc"], out, case["cu"], case["ctxs"], case["table"], case["seq_index"],
+                              case["page"], case["B"], max_q, case["nq"], case["nkv"], case["d"], case["d"] ** -0.5, window, ctas)
+    return out
+
+
+@pytest.mark.parametrize("ctas", [0, 1, 2, 7, 23, 150])
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(32, 8, 128, 16, 0), (16, 1, 64, 32, 0), (8, 2, 128, 8, 200), (4, 1, 128, 256, 0),
+                                                  (6, 2, 192, 64, 0), (2, 1, 256, 16, 300), (8, 8, 64, 128, 0), (12, 3, 128, 16, 90)])
+def test_attention_decode_flat(ctas, nq, nkv, d, page, window):
+    """The even-share decode kernel: the key blocks of all (sequence, KV head) pairs are one list that
+    `ctas` CTAs divide evenly.  One CTA walks every pair; a few walk several pairs each and share some;
+    many take a block or two each (and some nothing)."""
+    from tokensprint_b200 import ops
+
+    case = finish_case(paged_case(DECODE, nq, nkv, d, page, torch.bfloat16, seed=7 * d + nq))
+    want = plain_attention(case, window)
+    got = run_flat(case, window, ctas)
+    assert rel_err(got, want) < 1e-2
+    assert torch.equal(run_flat(case, window, ctas), got)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+
+
+@pytest.mark.parametrize("ctas", [0, 5])
+def test_attention_decode_flat_rows_of_several_tokens_and_lanes_without_a_sequence(ctas):
+    """Sequences that bring up to four tokens (16 rows with four heads per KV head), sequences of a
+    fixed-size batch that bring none, and token lanes that belong to no sequence (their output is zero)."""
+    from tokensprint_b200 import ops
+
+    nq, nkv, d, page = 8, 2, 128, 16
+    seqs = [(4, 4), (2, 65), (1, 64), (3, 500), (4, 129), (1, 1)]
+    case = finish_case(paged_case(seqs, nq, nkv, d, page, torch.bfloat16, seed=11))
+    want = plain_attention(case, 0)
+    T = case["q"].shape[0]
+    # two more sequences without tokens, three more token lanes without a sequence
+    B = case["B"] + 2
+    cu = torch.cat([case["cu"], case["cu"][-1:].repeat(2)])
+    ctxs = torch.cat([case["ctxs"], torch.zeros(2, dtype=torch.int32, device=DEV)])
+    table = torch.cat([case["table"], torch.full((2, case["table"].shape[1]), -1, dtype=torch.int32, device=DEV)])
+    q = torch.cat([case["q"], torch.randn(3, nq * d, device=DEV).bfloat16()])
+    seq_index = torch.cat([case["seq_index"], torch.full((3,), -1, dtype=torch.int32, device=DEV)])
+    out = torch.full_like(q, float("nan"))
+    ops.attention_decode_flat(q, case["kc"], case["vc"], out, cu, ctxs, table, seq_index, page, B, 4, nq, nkv, d, d ** -0.5, 0, ctas)
+    assert rel_err(out[:T], want) < 1e-2
+    assert float(out[T:].float().abs().max()) == 0.0
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+
+
+@pytest.mark.parametrize("ctas", [0, 3])
+@pytest.mark.parametrize("target", ["first", "far", "page_edge_before", "page_edge_after", "block_edge", "last", "window_first", "window_out"])
+def test_attention_decode_flat_finds_one_key_that_stands_out(target, ctas):
+    nq, nkv, d, page, ctx = 4, 1, 64, 16, 700
+    window = 0
+    where = {"first": 0, "far": 3, "page_edge_before": 16 * 20 - 1, "page_edge_after": 16 * 20, "block_edge": 64 * 7,
+             "last": ctx - 1}.get(target)
+    if target == "window_first":
+        window, where = 100, ctx - 100
+    if target == "window_out":
+        window, where = 100, ctx - 101
+    case = paged_case([(1, 90), (1, ctx), (1, 200)], nq, nkv, d, page, torch.bfloat16, seed=5)
+    q, k, v = case["dense"][1]
+    k.mul_(0.05)
+    k[where, 0] = q[0, 2] * 3.0  # head 2's query finds itself at `where`
+    v[where, 0] = 10.0
+    case = finish_case(case)
+    got = run_flat(case, window, ctas)
+    head2 = got.view(3, nq, d)[1, 2].float()
+    if target == "window_out":
+        assert float(head2.abs().max()) < 5.0, "a key outside the window was seen"
+    else:
+        assert float((head2 - 10.0).abs().max()) < 0.05, f"the key at {where} was not found"
+    assert rel_err(got, plain_attention(case, window)) < 1e-2
+
+
+def test_attention_decode_flat_long_and_short_sequences_together():
+    """One sequence of 20,000 keys beside short ones: the long one is shared by nearly all CTAs,
+    the short ones lie inside single CTAs."""
+    from tokensprint_b200 import ops
+
+    nq, nkv, d, page = 8, 2, 128, 16
+    case = finish_case(paged_case([(1, 30), (1, 20000), (1, 70), (1, 3000), (1, 64)], nq, nkv, d, page, torch.bfloat16, seed=13))
+    assert rel_err(run_flat(case, 0, 0), plain_attention(case, 0)) < 1e-2
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+
+
+def test_attention_decode_flat_says_what_it_takes():
+    from tokensprint_b200 import ops
+
+    assert ops.attention_decode_flat_supported(32, 8, 128, 16, 64, 1)
+    assert not ops.attention_decode_flat_supported(32, 8, 80, 16, 64, 1)    # head size no multiple of 64
+    assert not ops.attention_decode_flat_supported(32, 8, 128, 4, 64, 1)    # pages too small for the copy engine
+    assert not ops.attention_decode_flat_supported(32, 8, 128, 16, 64, 5)   # 20 rows per pair
+    assert not ops.attention_decode_flat_supported(32, 8, 128, 16, 600, 1)  # too many sequences
+    case = finish_case(paged_case([(5, 70)], 32, 8, 128, 16, torch.bfloat16, seed=1))
+    with pytest.raises(ops.KernelError, match="at most 16 rows"):
+        run_flat(case)
+
+
 @pytest.mark.parametrize("splits,chunk", [(16, 64), (8, 128), (4, 256), (2, 512), (64, 64)])
 @pytest.mark.parametrize("nq,nkv,d,page,window", [(32, 8, 128, 16, 0), (4, 2, 16, 16, 0), (5, 1, 48, 4, 90), (16, 1, 64, 32, 700)])
 def test_attention_mma_decode_with_fixed_key_chunks(splits, chunk, nq, nkv, d, page, window):

@@ -81,9 +81,10 @@ def _build_root() -> Path:
     in_tree = CSRC / "_build"
     try:
         in_tree.mkdir(exist_ok=True)
-        probe = in_tree / f".w{os.getpid()}"
-        probe.write_bytes(b"")
-        probe.unlink()
+        # a name of its own for every caller: variants are built from several threads at once
+        fd, probe = tempfile.mkstemp(prefix=".w", dir=in_tree)
+        os.close(fd)
+        os.unlink(probe)
         return in_tree
     except OSError:
         root = Path(tempfile.gettempdir()) / f"tokensprint_b200-build-{os.getuid()}"

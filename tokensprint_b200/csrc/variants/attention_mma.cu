@@ -64,6 +64,8 @@ struct AttnParams {
   long long* probe;               // TS_ATT_PROBE builds: clock stamps of a few CTAs of the decode kernel
   int* error;                     // set to 1 when a bounded wait of the copy-engine path gave up
   float scale_log2;               // scale * log2(e)
+  int num_seqs;                   // B
+  int* flat_prefix;               // even-share kernel: [B + 1] key blocks of the sequences before each one, left for its combine kernel
 };
 
 #ifdef TS_ATT_PROBE
@@ -1067,6 +1069,529 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
   }
 }
 
+#if (TS_HEAD_DIM % 64) == 0
+// ---------------------------------------------------------------------------
+// Decode with an even share of key blocks per CTA.
+//
+// The kernel above gives every (sequence, KV head) pair the same number of CTAs, chosen before the
+// launch; with many pairs the CTAs queue in waves whose last is nearly empty, and with few pairs
+// and long contexts the fixed count is too small.  Here the key blocks of all pairs form one list
+// (sequence-major, then KV head, then block), and CTA c of C takes blocks [c * total / C,
+// (c + 1) * total / C) of it, whatever the lengths are: every CTA walks the same number of blocks
+// (to within one), through as many pairs as its range meets.  The copy engine runs ahead across
+// the pairs, so the start of a pair costs no memory latency.  A pair that lies inside one CTA's
+// range gets its output from that CTA; a pair that several CTAs share gets partial results (a CTA
+// has at most two such pairs: its first and its last) and attention_flat_combine_kernel, which
+// derives the same ranges, merges them.  All of it is computed on the device from the step's
+// lengths, so one captured launch serves every step.
+constexpr int FLAT_MAX_SEQS = 512;   // sequences whose block counts fit the shared-memory prefix
+constexpr int FLAT_ROWS = 16;        // rows of a pair (tokens x heads of the group) at most
+
+struct FlatSeq {
+  int q_begin, rows_total, start_pos, hi, kb0, n;  // n: key blocks of each of its pairs
+};
+
+__device__ __forceinline__ FlatSeq flat_seq(const AttnParams& p, int b, int G) {
+  FlatSeq s;
+  s.q_begin = p.cu_q[b];
+  const int q_len = p.cu_q[b + 1] - s.q_begin;
+  const int ctx = p.ctx_len[b];
+  s.start_pos = ctx - q_len;
+  s.rows_total = min(q_len * G, FLAT_ROWS);
+  s.hi = ctx - 1;
+  const int lo = p.window > 0 ? max(0, s.start_pos - p.window + 1) : 0;
+  s.kb0 = lo / BN;
+  s.n = (q_len > 0 && ctx > 0 && s.start_pos >= 0) ? s.hi / BN - s.kb0 + 1 : 0;
+  return s;
+}
+
+struct FlatCursor {
+  int b, hk, blk;
+  FlatSeq s;
+};
+
+// The cursor of block f of the list (f < total).
+__device__ __forceinline__ void flat_seek(const AttnParams& p, const int* prefix, int G, int f, FlatCursor& c) {
+  int lo = 0, hi = p.num_seqs - 1;
+  while (lo < hi) {  // the last sequence whose first block is at or before f (sequences without blocks share their successor's start)
+    const int mid = (lo + hi + 1) >> 1;
+    if (p.nkv * prefix[mid] <= f) lo = mid; else hi = mid - 1;
+  }
+  c.b = lo;
+  c.s = flat_seq(p, lo, G);
+  const int rem = f - p.nkv * prefix[lo];
+  const int n = max(c.s.n, 1);
+  c.hk = rem / n;
+  c.blk = rem - c.hk * n;
+}
+
+__device__ __forceinline__ void flat_next(const AttnParams& p, int G, FlatCursor& c) {
+  if (++c.blk < c.s.n) return;
+  c.blk = 0;
+  if (++c.hk < p.nkv) return;
+  c.hk = 0;
+  do {
+    if (++c.b >= p.num_seqs) {
+      c.b = p.num_seqs - 1;
+      c.s.n = 0;
+      return;
+    }
+    c.s = flat_seq(p, c.b, G);
+  } while (c.s.n == 0);
+}
+
+// CTAs that take part: all that run at once, but no more than leaves each FLAT_MIN_BLOCKS blocks
+// (a CTA that walks one block costs more in starting and merging than it saves).
+constexpr int FLAT_MIN_BLOCKS = 2;
+__device__ __forceinline__ int flat_ctas_used(int total, int grid) { return max(1, min(grid, total / FLAT_MIN_BLOCKS)); }
+
+// First block of CTA c: floor(c * total / ctas), in 32-bit steps (total < 2^31, ctas < 2^15).
+__device__ __forceinline__ int flat_start(int total, int ctas, int c) {
+  const int per = total / ctas, rest = total - per * ctas;
+  return c * per + (c * rest) / ctas;
+}
+
+// The CTA whose range holds block f.
+__device__ __forceinline__ int flat_owner(int total, int ctas, int f) {
+  int c = (int)((long long)f * ctas / total);
+  while (c + 1 < ctas && flat_start(total, ctas, c + 1) <= f) ++c;
+  return c;
+}
+
+__global__ void __launch_bounds__(128) attention_decode_flat_kernel(const AttnParams p, const __grid_constant__ CUtensorMap map_k,
+                                                                    const __grid_constant__ CUtensorMap map_v) {
+  constexpr int NWARPS = 4, NT = 128, NTILES = 2;
+  static_assert(2 * 4 * D * sizeof(float) <= FLAT_ROWS * LD * sizeof(__nv_bfloat16), "the merge buffer is the query tile");
+  ts_pdl_launch_dependents();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [16][LD]
+  // swizzled tiles on a 1,024-byte boundary: per stage the K tile, then the V tile
+  unsigned char* kv = reinterpret_cast<unsigned char*>(((uintptr_t)(q_s + FLAT_ROWS * LD) + 1023) & ~(uintptr_t)1023);
+  __shared__ int prefix_s[FLAT_MAX_SEQS + 1];
+  __shared__ float mb_s[8], lb_s[8];
+  __shared__ __align__(8) unsigned long long full_bar[TSTAGES], empty_bar[TSTAGES];
+  __shared__ int abort_s;
+  volatile int* abort_flag = &abort_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, tq = lane & 3;
+  const int G = p.nq / p.nkv;
+  const int key0 = warp * 16;  // first key of every block that this warp scores
+
+  // Before the wait for the kernel ahead: what depends only on the step's index arrays (copied
+  // from the host before the step's first kernel) and on keys and values of earlier steps.
+  if (warp == 0) {
+    int carry = 0;
+    for (int base = 0; base < p.num_seqs; base += 32) {
+      const int b = base + lane;
+      const int n = b < p.num_seqs ? flat_seq(p, b, G).n : 0;
+      int incl = n;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      if (b < p.num_seqs) prefix_s[b] = carry + incl - n;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) {
+      prefix_s[p.num_seqs] = carry;
+      abort_s = 0;
+      for (int i = 0; i < TSTAGES; ++i) {
+        mbar_init(smem_u32(&full_bar[i]), 1);
+        mbar_init(smem_u32(&empty_bar[i]), NWARPS);
+      }
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+  }
+  __syncthreads();
+  const int total = p.nkv * prefix_s[p.num_seqs];
+  const int ctas = flat_ctas_used(total, (int)gridDim.x), cta = (int)blockIdx.x;
+  const int f0 = cta < ctas ? flat_start(total, ctas, cta) : 0, f1 = cta < ctas ? flat_start(total, ctas, cta + 1) : 0;
+  const int nblk = f1 - f0;  // blocks of this CTA
+
+  // Warp 0 asks for the blocks, all its lanes together (every lane one box of [page rows x 64
+  // elements] of K or V), in list order, each into the stage that its number names, waiting first
+  // until the four warps are done with what the stage held.  A page that is not held is asked for
+  // at a coordinate beyond the declared pool: the copy engine then writes zeros and touches no memory.
+  const int box_rows = min(p.page, BN), copies = BN / box_rows;
+  FlatCursor pc;  // the next block to ask for (warp 0 only)
+  int asked = 0;
+  auto ask = [&]() -> bool {
+    const int stage = asked % TSTAGES;
+    bool ok = true;
+    if (asked >= TSTAGES) ok = mbar_wait(smem_u32(&empty_bar[stage]), (unsigned)(asked / TSTAGES - 1) & 1, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      if (lane == 0) mbar_expect_tx(smem_u32(&full_bar[stage]), 2 * KV_TILE);
+      __syncwarp();
+      const int* table = p.block_table + (size_t)pc.b * p.max_blocks;
+      for (int item = lane; item < copies * 2 * HALVES; item += 32) {
+        const int c = item / (2 * HALVES), which = (item / HALVES) & 1, half = item % HALVES;
+        const int k0 = (pc.s.kb0 + pc.blk) * BN + c * box_rows;
+        const int e = k0 / p.page;
+        int page_id = -1;
+        if (k0 <= pc.s.hi && e < p.max_blocks) page_id = table[e];
+        const long long slot = page_id >= 0 ? (long long)page_id * p.page + k0 % p.page : SLOT_BOUND;
+        unsigned char* dst = kv + (stage * 2 + which) * KV_TILE + half * (BN * 128) + c * box_rows * 128;
+        tma_load_3d(smem_u32(dst), which ? &map_v : &map_k, smem_u32(&full_bar[stage]), half * 64, pc.hk, (int)slot);
+      }
+    }
+    // after a wait that gave up nothing more is asked for; the count goes on so that every warp
+    // leaves the loops at the same place (their waits give up at once)
+    ++asked;
+    flat_next(p, G, pc);
+    return ok;
+  };
+  if (warp == 0 && nblk > 0) {
+    flat_seek(p, prefix_s, G, f0, pc);
+    while (asked < min(nblk, TSTAGES) && (pc.s.kb0 + pc.blk) * BN + BN - 1 < pc.s.start_pos) ask();
+  }
+  ts_pdl_wait();
+  if (cta == 0 && p.flat_prefix != nullptr)
+    for (int i = tid; i <= p.num_seqs; i += NT) p.flat_prefix[i] = prefix_s[i];
+  if (nblk <= 0) return;
+  if (warp == 0)
+    while (asked < min(nblk, TSTAGES)) ask();
+
+  auto load_queries = [&](const FlatSeq& s, int hk) {
+    for (int c = tid; c < FLAT_ROWS * CH; c += NT) {
+      const int row = c / CH, ch = c - row * CH;
+      const bool valid = row < s.rows_total;
+      const __nv_bfloat16* src = p.q;
+      if (valid) src = p.q + ((size_t)(s.q_begin + row / G) * p.nq + hk * G + row % G) * D + ch * 8;
+      cp_async16(q_s + row * LD + ch * 8, src, valid);
+    }
+    cp_async_commit();
+  };
+  FlatCursor cc;
+  flat_seek(p, prefix_s, G, f0, cc);
+  int done = 0;  // blocks walked so far
+  for (int seg = 0; done < nblk; ++seg) {
+    // One pair: blocks [blk0, blk0 + cnt) of sequence b, KV head hk.
+    const FlatSeq s = cc.s;
+    const int b = cc.b, hk = cc.hk, blk0 = cc.blk;
+    const int cnt = min(s.n - blk0, nblk - done);
+    const bool whole = blk0 == 0 && cnt == s.n;
+    (void)b;
+
+    // The pair after this one: its queries are asked for while this pair's warps merge.
+    FlatCursor nc = cc;
+    nc.blk = blk0 + cnt - 1;
+    flat_next(p, G, nc);
+    if (seg == 0) load_queries(s, hk);  // the first pair's queries: nothing could ask for them earlier
+    int row_pos[2], row_lo[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = g + 8 * h;
+      row_pos[h] = r < s.rows_total ? s.start_pos + r / G : -1;
+      row_lo[h] = (p.window > 0 && row_pos[h] >= 0) ? max(0, row_pos[h] - p.window + 1) : 0;
+    }
+    const int warp_min_pos = s.start_pos;
+    const int warp_max_lo = p.window > 0 ? max(0, s.start_pos + (s.rows_total - 1) / G - p.window + 1) : 0;
+
+    float o_acc[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    cp_async_wait<0>();
+    __syncthreads();
+    unsigned q_frag[Q_IN_REGS ? D / 16 : 1][4];
+    if constexpr (Q_IN_REGS) {
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks)
+        ldmatrix_x4(q_frag[ks][0], q_frag[ks][1], q_frag[ks][2], q_frag[ks][3],
+                    q_s + ((lane & 7) + ((lane >> 3) & 1) * 8) * LD + ks * 16 + (lane >> 4) * 8);
+    }
+
+    for (int it = 0; it < cnt; ++it, ++done) {
+      const int stage = done % TSTAGES;
+      const int kbase = (s.kb0 + blk0 + it) * BN;
+      unsigned char* k_tile = kv + (stage * 2) * KV_TILE;
+      unsigned char* v_tile = k_tile + KV_TILE;
+      mbar_wait(smem_u32(&full_bar[stage]), (unsigned)(done / TSTAGES) & 1, abort_flag);
+      __syncwarp();
+      // rows of V beyond the last key hold whatever was in the cache: zeros instead (their weights
+      // are zero, but zero times garbage must stay zero); each warp clears its own 16 rows
+      if (kbase + BN - 1 > s.hi) {
+        for (int i = lane; i < 16 * HALVES * 8; i += 32) {
+          const int row = key0 + i / (HALVES * 8), piece = i % (HALVES * 8);
+          if (kbase + row > s.hi)
+            *reinterpret_cast<uint4*>(v_tile + (piece >> 3) * (BN * 128) + row * 128 + ((piece & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        __syncwarp();
+      }
+
+      // S = Q K^T over this warp's 16 keys of the block
+      float sc[NTILES][4];
+#pragma unroll
+      for (int i = 0; i < NTILES; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sc[i][j] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        unsigned a[4];
+        if constexpr (Q_IN_REGS) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) a[j] = q_frag[ks][j];
+        } else {
+          ldmatrix_x4(a[0], a[1], a[2], a[3], q_s + ((lane & 7) + ((lane >> 3) & 1) * 8) * LD + ks * 16 + (lane >> 4) * 8);
+        }
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3, swizzled(k_tile, key0 + (lane & 7) + ((lane >> 4) & 1) * 8, ks * 16 + ((lane >> 3) & 1) * 8));
+        mma_bf16(sc[0], a, b0, b1);
+        mma_bf16(sc[1], a, b2, b3);
+      }
+
+      // mask and online softmax, as in the kernel above
+      float m_new[2] = {m_run[0], m_run[1]};
+      const int wk0 = kbase + key0;
+      const bool unmasked = (wk0 + NTILES * 8 - 1 <= warp_min_pos) && (wk0 >= warp_max_lo);
+      if (unmasked) {
+#pragma unroll
+        for (int nt = 0; nt < NTILES; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) m_new[e >> 1] = fmaxf(m_new[e >> 1], sc[nt][e]);
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < NTILES; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int h = e >> 1;
+            const int j = wk0 + nt * 8 + tq * 2 + (e & 1);
+            const bool ok = j <= row_pos[h] && j >= row_lo[h];
+            const float v = ok ? sc[nt][e] : -INFINITY;
+            sc[nt][e] = v;
+            m_new[h] = fmaxf(m_new[h], v);
+          }
+        }
+      }
+      float corr[2], m_off[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
+        m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
+        m_off[h] = m_new[h] == -INFINITY ? 0.f : m_new[h] * p.scale_log2;
+        corr[h] = fast_exp2(m_run[h] * p.scale_log2 - m_off[h]);
+        m_run[h] = m_new[h];
+      }
+      float l_add[2] = {0.f, 0.f};
+#pragma unroll
+      for (int nt = 0; nt < NTILES; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pv = fast_exp2(fmaf(sc[nt][e], p.scale_log2, -m_off[e >> 1]));
+          sc[nt][e] = pv;
+          l_add[e >> 1] += pv;
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * corr[h] + l_add[h];
+      if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+          o_acc[i][0] *= corr[0];
+          o_acc[i][1] *= corr[0];
+          o_acc[i][2] *= corr[1];
+          o_acc[i][3] *= corr[1];
+        }
+      }
+
+      // O += P V
+      {
+        unsigned a[4];
+        a[0] = pack_bf16(sc[0][0], sc[0][1]);
+        a[1] = pack_bf16(sc[0][2], sc[0][3]);
+        a[2] = pack_bf16(sc[1][0], sc[1][1]);
+        a[3] = pack_bf16(sc[1][2], sc[1][3]);
+#pragma unroll
+        for (int np = 0; np < D / 16; ++np) {
+          unsigned b0, b1, b2, b3;
+          ldmatrix_x4_trans(b0, b1, b2, b3, swizzled(v_tile, key0 + (lane & 7) + ((lane >> 3) & 1) * 8, np * 16 + ((lane >> 4) & 1) * 8));
+          mma_bf16(o_acc[2 * np], a, b0, b1);
+          mma_bf16(o_acc[2 * np + 1], a, b2, b3);
+        }
+      }
+
+      // this warp is done with the stage; warp 0 asks for the block that takes it next once all are
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
+      if (warp == 0 && asked < nblk && asked == done + TSTAGES) ask();
+    }
+
+    // The pair's blocks of this CTA are walked: the four warps (each saw a quarter of the keys)
+    // merge.  No stage of the pipeline is held for it (the copy engine goes on fetching the next
+    // pair's blocks): the warps fold in pairs through the small tile that held the queries, four
+    // rows at a time, each thread merging the elements it holds itself with the same elements of
+    // its partner (warps 2 and 3 into 0 and 1, then 1 into 0), and warp 0 writes the rows.
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+      l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+    float* buf = reinterpret_cast<float*>(q_s);  // [2][4][D]
+    __syncthreads();  // the queries are in registers (or read for the last time) in every warp
+#pragma unroll
+    for (int chunk = 0; chunk < 4; ++chunk) {
+      if (chunk * 4 >= s.rows_total) continue;  // the same for every thread
+      // rows g + 8 * hs with g / 4 == gs: 0..3, 4..7, 8..11, 12..15
+      constexpr int hs_of[4] = {0, 0, 1, 1};
+      const int hs = hs_of[chunk], gs = chunk & 1;
+      const bool mine = (g >> 2) == gs;
+      const int slot = g & 3;
+      auto put = [&](int which) {
+        if (tq == 0) {
+          mb_s[which * 4 + slot] = m_run[hs];
+          lb_s[which * 4 + slot] = l_run[hs];
+        }
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i)
+          *reinterpret_cast<float2*>(buf + (which * 4 + slot) * D + i * 8 + tq * 2) = make_float2(o_acc[i][2 * hs], o_acc[i][2 * hs + 1]);
+      };
+      auto fold = [&](int which) {
+        const float m_b = mb_s[which * 4 + slot], l_b = lb_s[which * 4 + slot];
+        const float m = fmaxf(m_run[hs], m_b);
+        const float m_off = m == -INFINITY ? 0.f : m * p.scale_log2;
+        const float wa = fast_exp2(m_run[hs] * p.scale_log2 - m_off), wb = fast_exp2(m_b * p.scale_log2 - m_off);
+        m_run[hs] = m;
+        l_run[hs] = wa * l_run[hs] + wb * l_b;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+          const float2 o_b = *reinterpret_cast<const float2*>(buf + (which * 4 + slot) * D + i * 8 + tq * 2);
+          o_acc[i][2 * hs] = wa * o_acc[i][2 * hs] + wb * o_b.x;
+          o_acc[i][2 * hs + 1] = wa * o_acc[i][2 * hs + 1] + wb * o_b.y;
+        }
+      };
+      if (warp >= 2 && mine) put(warp - 2);
+      __syncthreads();
+      if (warp < 2 && mine) fold(warp);
+      if (warp == 1) {
+        __syncwarp();  // the quad has read the partner's max and sum before one of it overwrites them
+        if (mine) put(1);  // of the rows, every thread overwrites only what it has just read itself
+      }
+      __syncthreads();
+      if (warp == 0 && mine) {
+        fold(1);
+        const int r = g + 8 * hs;
+        if (r < s.rows_total) {
+          const size_t qrow = (size_t)(s.q_begin + r / G) * p.nq + hk * G + r % G;
+          if (whole) {
+            const float inv = l_run[hs] > 0.f ? 1.f / l_run[hs] : 0.f;
+            __nv_bfloat16* dst = p.out + qrow * D;
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i)
+              *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + tq * 2) = __floats2bfloat162_rn(o_acc[i][2 * hs] * inv, o_acc[i][2 * hs + 1] * inv);
+          } else {
+            // a shared pair: slot 0 of this CTA if the pair is its first, else slot 1 (then it is its last)
+            float* part = p.part_o + ((size_t)(cta * 2 + (seg == 0 ? 0 : 1)) * FLAT_ROWS + r) * (D + 2);
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i)
+              *reinterpret_cast<float2*>(part + i * 8 + tq * 2) = make_float2(o_acc[i][2 * hs], o_acc[i][2 * hs + 1]);
+            if (tq == 0) {
+              part[D] = m_run[hs] * p.scale_log2;  // log2 units, as the combine kernel expects (-inf stays -inf)
+              part[D + 1] = l_run[hs];
+            }
+          }
+        }
+      }
+      __syncthreads();
+    }
+    if (done < nblk) load_queries(nc.s, nc.hk);
+    cc = nc;
+  }
+  if (abort_s != 0) {
+    // A wait gave up: say so, and let the copies that were asked for land before the CTA leaves
+    // (bounded again), so that none writes into the shared memory of the CTA that comes next.
+    if (tid == 0) {
+      if (p.error != nullptr) *p.error = 1;
+      volatile int never = 0;
+      for (int i = max(0, asked - TSTAGES); i < asked; ++i) mbar_wait(smem_u32(&full_bar[i % TSTAGES]), (unsigned)(i / TSTAGES) & 1, &never);
+    }
+    __syncthreads();
+  }
+}
+
+// Merges the partial results of the pairs that several CTAs of attention_decode_flat_kernel shared:
+// one warp per (token, head); pairs that one CTA held whole already have their output.  The lanes
+// fetch the maxima and sums of up to 32 CTAs at once; the weighted sum then runs over the CTAs
+// in list order, a few rows in flight at a time.
+__global__ void attention_flat_combine_kernel(const float* __restrict__ part, const int* __restrict__ prefix,
+                                              __nv_bfloat16* __restrict__ out, const int* __restrict__ seq_index,
+                                              const int* __restrict__ cu_q, int rows, int nq, int nkv, int num_seqs, int grid) {
+  ts_pdl_prologue();
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int t = row / nq, h = row - t * nq;
+  __nv_bfloat16* dst = out + (size_t)row * D;
+  const int b = seq_index[t];
+  if (b < 0) {  // a padded lane of a fixed-size batch
+    for (int d = lane; d < D; d += 32) dst[d] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const int G = nq / nkv, hk = h / G;
+  const int n = prefix[b + 1] - prefix[b];
+  const int total = nkv * prefix[num_seqs];
+  if (n <= 0 || total <= 0) return;
+  const int ctas = flat_ctas_used(total, grid);
+  const int off = nkv * prefix[b] + hk * n;
+  const int c_first = flat_owner(total, ctas, off), c_last = flat_owner(total, ctas, off + n - 1);
+  if (c_first == c_last) return;  // held whole by one CTA
+  const int r = (t - cu_q[b]) * G + h % G;
+  if (r >= FLAT_ROWS) return;
+  // Only the first CTA can have begun before the pair (the pair is then its last, slot 1); every
+  // other one begins inside it (the pair is its first, slot 0).
+  const int first_slot = flat_start(total, ctas, c_first) < off ? 1 : 0;
+  auto rows_of = [&](int c) { return part + ((size_t)(c * 2 + (c == c_first ? first_slot : 0)) * FLAT_ROWS + r) * (D + 2); };
+  float m = -INFINITY;
+  for (int c = c_first + lane; c <= c_last; c += 32) {
+    const float* src = rows_of(c);
+    if (src[D + 1] > 0.f) m = fmaxf(m, src[D]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  float l = 0.f;
+  float acc[(D + 31) / 32];
+#pragma unroll
+  for (int i = 0; i < (D + 31) / 32; ++i) acc[i] = 0.f;
+  for (int base = c_first; base <= c_last; base += 32) {
+    const int mine = base + lane;
+    float w_mine = 0.f;
+    if (mine <= c_last) {
+      const float* src = rows_of(mine);
+      const float ls = src[D + 1];
+      if (ls > 0.f) {
+        w_mine = exp2f(src[D] - m);
+        l += w_mine * ls;
+      }
+    }
+    const int here = min(32, c_last - base + 1);
+#pragma unroll 4
+    for (int j = 0; j < here; ++j) {  // in list order
+      const float w = __shfl_sync(0xffffffffu, w_mine, j);
+      const float* src = rows_of(base + j);
+#pragma unroll
+      for (int i = 0; i < (D + 31) / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < D) acc[i] += w * src[d];
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+  for (int i = 0; i < (D + 31) / 32; ++i) {
+    const int d = lane + 32 * i;
+    if (d < D) dst[d] = __float2bfloat16_rn(acc[i] * inv);
+  }
+}
+
+#endif  // head sizes that the copy engine takes
+
 template <int NWARPS, bool SPLIT_KEYS>
 int launch(const AttnParams& p, int B, cudaStream_t stream) {
   constexpr int BM = SPLIT_KEYS ? 16 : NWARPS * 16;
@@ -1116,6 +1641,24 @@ int launch_decode_tma(const AttnParams& p, int B, cudaStream_t stream) {
     return ts_launch(attention_mma_kernel<4, true, true>, grid, dim3(128), smem, stream, p, mk, mv);
   }
 }
+
+
+#if (TS_HEAD_DIM % 64) == 0
+size_t flat_smem() { return (size_t)FLAT_ROWS * LD * sizeof(__nv_bfloat16) + 1024 + (size_t)2 * TSTAGES * KV_TILE; }
+
+// How many CTAs of the even-share decode kernel the GPU runs at once: its grid.
+int flat_ctas() {
+  static int ctas = 0;
+  if (ctas == 0) {
+    int dev = 0, sms = 0, per_sm = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
+    cudaFuncSetAttribute(attention_decode_flat_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)flat_smem());
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_flat_kernel, 128, flat_smem()) != cudaSuccess || per_sm <= 0) per_sm = 1;
+    ctas = sms * per_sm;
+  }
+  return ctas;
+}
+#endif
 
 }  // namespace
 
@@ -1206,6 +1749,8 @@ TS_EXPORT int ts_attention_paged_mma_fused(const void* q, const void* kcache, co
                (long long)B * nkv * splits <= decode_slots()) ? 1 : 0;
   if (p.cluster) p.counters = nullptr;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.num_seqs = B;
+  p.flat_prefix = nullptr;
   p.probe = ts_attention_probe;
   p.error = ts_attention_error_word;
   const long long rows = (long long)max_q * G;
@@ -1245,6 +1790,79 @@ TS_EXPORT int ts_attention_paged_mma(const void* q, const void* kcache, const vo
                                      int window, int splits, void* stream_) {
   return ts_attention_paged_mma_fused(q, kcache, vcache, out, scratch, cu_q, ctx_len, block_table, seq_index,
                                       max_blocks, page, T, B, max_q, nq, nkv, scale, window, splits, 0, nullptr, stream_);
+}
+
+// ---------------------------------------------------------------------------
+// Decode with an even share of key blocks per CTA (see attention_decode_flat_kernel): decode steps
+// only (at most 16 rows per sequence and KV head), head sizes that are multiples of 64, at most 512
+// sequences, pages the copy engine takes.  `ctas`: the grid, at most ts_attention_decode_flat_ctas();
+// `scratch`: ts_attention_decode_flat_scratch_floats(B, ctas) floats.
+TS_EXPORT int ts_attention_decode_flat_ctas(void) {
+#if (TS_HEAD_DIM % 64) == 0
+  return flat_ctas();
+#else
+  return 0;
+#endif
+}
+
+TS_EXPORT long long ts_attention_decode_flat_scratch_floats(int B, int ctas) {
+#if (TS_HEAD_DIM % 64) == 0
+  return (long long)ctas * 2 * FLAT_ROWS * (D + 2) + B + 1;
+#else
+  (void)B;
+  (void)ctas;
+  return 0;
+#endif
+}
+
+TS_EXPORT int ts_attention_decode_flat(const void* q, const void* kcache, const void* vcache, void* out, float* scratch,
+                                       const int* cu_q, const int* ctx_len, const int* block_table, const int* seq_index,
+                                       int max_blocks, int page, int T, int B, int max_q, int nq, int nkv, float scale,
+                                       int window, int ctas, void* stream_) {
+#if (TS_HEAD_DIM % 64) == 0
+  if (T <= 0 || B <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page <= 0 || max_blocks <= 0 || max_q <= 0 || scratch == nullptr || seq_index == nullptr)
+    return TS_ERR_BAD_ARGUMENT;
+  if ((long long)max_q * (nq / nkv) > FLAT_ROWS || B > FLAT_MAX_SEQS || ctas < 1 || ctas > flat_ctas()) return TS_ERR_UNSUPPORTED_SIZE;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  AttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = (const __nv_bfloat16*)q;
+  p.kcache = (const __nv_bfloat16*)kcache;
+  p.vcache = (const __nv_bfloat16*)vcache;
+  p.out = (__nv_bfloat16*)out;
+  p.part_o = scratch;
+  p.flat_prefix = reinterpret_cast<int*>(scratch + (size_t)ctas * 2 * FLAT_ROWS * (D + 2));
+  p.cu_q = cu_q;
+  p.ctx_len = ctx_len;
+  p.block_table = block_table;
+  p.max_blocks = max_blocks;
+  p.page = page;
+  p.nq = nq;
+  p.nkv = nkv;
+  p.window = window;
+  p.splits = 1;
+  p.row_tiles = 1;
+  p.num_seqs = B;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.probe = ts_attention_probe;
+  p.error = ts_attention_error_word;
+  if (!decode_tma_ok(p)) return TS_ERR_UNSUPPORTED_SIZE;
+  CUtensorMap mk, mv;
+  const int box_rows = page < BN ? page : BN;
+  int st = ts_kv_cache_map(p.kcache, SLOT_BOUND, nkv, D, box_rows, &mk);
+  if (st != 0) return st;
+  st = ts_kv_cache_map(p.vcache, SLOT_BOUND, nkv, D, box_rows, &mv);
+  if (st != 0) return st;
+  (void)flat_ctas();  // sets the kernel's shared-memory limit
+  st = ts_launch(attention_decode_flat_kernel, dim3(ctas), dim3(128), flat_smem(), stream, p, mk, mv);
+  if (st != 0) return st;
+  const int total = T * nq;
+  return ts_launch(attention_flat_combine_kernel, dim3((total + 3) / 4), dim3(128), 0, stream, (const float*)p.part_o,
+                   (const int*)p.flat_prefix, p.out, seq_index, cu_q, total, nq, nkv, B, ctas);
+#else
+  return TS_ERR_UNSUPPORTED_SIZE;
+#endif
 }
 
 // ---------------------------------------------------------------------------

@@ -385,6 +385,12 @@ def _attention_mma_fns(head_dim: int):
         lib.ts_attention_mma_set_decode_tma(1 if ATTENTION_DECODE_TMA else 0)
         lib.ts_attention_mma_set_error_word.argtypes = [_c_void_p]
         lib.ts_attention_mma_set_error_word(_attention_error_word().data_ptr())
+        lib.ts_attention_decode_flat.argtypes = [_c_void_p] * 9 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_void_p]
+        lib.ts_attention_decode_flat.restype = _c_int
+        lib.ts_attention_decode_flat_ctas.restype = _c_int
+        lib.ts_attention_decode_flat_scratch_floats.argtypes = [_c_int, _c_int]
+        lib.ts_attention_decode_flat_scratch_floats.restype = _c_ll
+        _attention_flat[head_dim] = lib
         fns = (run, scratch)
         _attention_mma[head_dim] = fns
     return fns
@@ -510,6 +516,100 @@ def attention_paged_mma(
     if splits > 1 and counters is None and not in_cluster:
         global launch_count
         launch_count += 1  # the combine kernel
+
+
+# Decode steps whose (sequence, KV head) pairs times key splits do not all run at once go to the
+# kernel that gives every CTA an even share of all key blocks instead (TS_ATTENTION_FLAT=0: never).
+ATTENTION_DECODE_FLAT = _os.environ.get("TS_ATTENTION_FLAT", "1") != "0"
+ATTENTION_FLAT_MAX_SEQS = 512
+ATTENTION_FLAT_MAX_ROWS = 16
+_attention_flat: dict[int, ctypes.CDLL] = {}
+_flat_ctas: dict[int, int] = {}
+
+
+def attention_decode_flat_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, num_seqs: int, max_seqlen_q: int) -> bool:
+    """Whether the even-share decode kernel takes these sizes: head sizes that are multiples of 64,
+    pages the copy engine can fetch (8 or more slots; 64 a multiple of the page or the page of 64),
+    at most 16 rows (tokens x heads of a group) per sequence and KV head, at most 512 sequences."""
+    return (head_dim % 64 == 0 and attention_mma_supported(head_dim) and num_kv_heads > 0 and num_heads % num_kv_heads == 0
+            and page_size >= 8 and (64 % page_size == 0 or page_size % 64 == 0)
+            and max_seqlen_q * (num_heads // num_kv_heads) <= ATTENTION_FLAT_MAX_ROWS and 0 < num_seqs <= ATTENTION_FLAT_MAX_SEQS
+            and (num_kv_heads * head_dim * 2) % 16 == 0)
+
+
+def attention_decode_prefers_flat(num_seqs: int, num_kv_heads: int, splits: int, head_dim: int) -> bool:
+    """Whether a decode step of this many sequences is better served by the even-share kernel:
+    when the CTAs of the split kernel would queue (measured at 8 KV heads of 128: equal at 32
+    sequences, 19 % faster at 64, 10 % at 128; with fewer sequences the split kernel, whose
+    splits merge inside a cluster, is faster)."""
+    return ATTENTION_DECODE_FLAT and num_seqs * num_kv_heads * splits > _decode_slots(head_dim)
+
+
+def attention_decode_flat_ctas(head_dim: int) -> int:
+    """CTAs of the even-share decode kernel that the GPU runs at once: its grid."""
+    n = _flat_ctas.get(head_dim)
+    if n is None:
+        _attention_mma_fns(head_dim)
+        n = int(_attention_flat[head_dim].ts_attention_decode_flat_ctas())
+        _flat_ctas[head_dim] = n
+    return n
+
+
+def attention_decode_flat(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    out: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    context_lens: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_index: torch.Tensor,
+    page_size: int,
+    num_seqs: int,
+    max_seqlen_q: int,
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    scale: float,
+    window: int = 0,
+    ctas: int = 0,
+) -> None:
+    """Decode attention over the paged cache with an even share of key blocks per CTA (bfloat16).
+
+    Arguments as attention_paged_mma.  The key blocks (64 keys) of all (sequence, KV head) pairs
+    form one list that the CTAs of a fixed grid divide evenly on the device, whatever the lengths
+    are; pairs that several CTAs share are merged by a second kernel.  `ctas` (0: as many as run
+    at once) sets the grid."""
+    _attention_mma_fns(head_dim)
+    lib = _attention_flat[head_dim]
+    for name, t in (("q", q), ("k_cache", k_cache), ("v_cache", v_cache), ("out", out)):
+        _cuda_contig(name, t, torch.bfloat16)
+    for name, t in (("cu_seqlens_q", cu_seqlens_q), ("context_lens", context_lens), ("block_table", block_table), ("seq_index", seq_index)):
+        _cuda_contig(name, t, torch.int32)
+    T = q.shape[0]
+    nq, nkv, d = num_heads, num_kv_heads, head_dim
+    if not attention_decode_flat_supported(nq, nkv, d, page_size, num_seqs, max_seqlen_q):
+        raise KernelError(
+            f"attention_decode_flat: takes head sizes that are multiples of 64, pages of 8 or more slots that divide 64 or are multiples of it, "
+            f"at most {ATTENTION_FLAT_MAX_ROWS} rows per sequence and KV head and at most {ATTENTION_FLAT_MAX_SEQS} sequences; got "
+            f"heads {nq}/{nkv} of {d}, page {page_size}, {num_seqs} sequences of up to {max_seqlen_q} tokens")
+    if q.numel() != T * nq * d or out.numel() != T * nq * d:
+        raise KernelError("attention_decode_flat: q/out do not match [T, heads*head_dim]")
+    if tuple(k_cache.shape[-3:]) != (page_size, nkv, d) or k_cache.shape != v_cache.shape:
+        raise KernelError(f"attention_decode_flat: caches must be [pages,{page_size},{nkv},{d}], got {tuple(k_cache.shape)} and {tuple(v_cache.shape)}")
+    if block_table.dim() != 2 or block_table.shape[0] < num_seqs:
+        raise KernelError("attention_decode_flat: block_table must be [B,max_blocks]")
+    if cu_seqlens_q.numel() < num_seqs + 1 or context_lens.numel() < num_seqs or seq_index.numel() < T:
+        raise KernelError("attention_decode_flat: cu_seqlens_q/context_lens/seq_index are shorter than the batch")
+    most = attention_decode_flat_ctas(d)
+    ctas = most if ctas <= 0 else min(int(ctas), most)
+    scratch = torch.empty(int(lib.ts_attention_decode_flat_scratch_floats(num_seqs, ctas)), device=q.device, dtype=torch.float32)
+    _check("attention_decode_flat", lib.ts_attention_decode_flat(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), scratch.data_ptr(),
+        cu_seqlens_q.data_ptr(), context_lens.data_ptr(), block_table.data_ptr(), seq_index.data_ptr(),
+        block_table.shape[1], page_size, T, num_seqs, max_seqlen_q, nq, nkv, float(scale), int(window), ctas, _stream()))
+    global launch_count
+    launch_count += 1  # the combine kernel
 
 
 _FUSE_ATTENTION_MERGE = _os.environ.get("TS_FUSE_ATTENTION_MERGE", "0") != "0"  # measured: the separate merge kernel is a little faster

@@ -168,6 +168,13 @@ class AttentionMixer(Mixer):
                 # divides its own keys evenly.
                 context = min(step.max_context_len, 2048) if self.window <= 0 else min(step.max_context_len, self.window + 64)
                 splits = ops.attention_decode_splits(step.num_seqs, nkv, context, d)
+                if (ops.attention_decode_prefers_flat(step.num_seqs, nkv, splits, d)
+                        and ops.attention_decode_flat_supported(nq, nkv, d, step.page_size, step.num_seqs, step.max_seqlen_q)):
+                    # more (sequence, KV head) pairs than CTAs run at once: an even share of all key blocks per CTA
+                    ops.attention_decode_flat(
+                        q, cache.k_pages, cache.v_pages, out, step.cu_seqlens_q, step.context_lens, tables.block_table,
+                        step.seq_index, step.page_size, step.num_seqs, step.max_seqlen_q, nq, nkv, d, self.scale, self.window)
+                    return
                 if splits > 1:
                     scratch = torch.empty(ops.attention_scratch_floats(q.shape[0] * nq, splits, d),
                                           device=q.device, dtype=torch.float32)
