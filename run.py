@@ -10,7 +10,8 @@ FlagConversionOff.  The model folder is `cache_dir/<last part of the repo id>` u
 folder from the registered config and a seed when none is there), --prompt-ids (token ids
 instead of text; without tokenizer files in the folder this is the only way),
 --dtype, --kvcache-block-size, --num-kvcache-blocks, --max-num-batched-tokens,
---chunked-prefill, --seed.
+--chunked-prefill, --seed, --overlap-steps (launch a step before the host has read the ids
+of the step before; default True).
 """
 
 from __future__ import annotations
@@ -49,6 +50,7 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--max-num-batched-tokens", type=int, default=16384)
     p.add_argument("--chunked-prefill", type=_bool, default=False)
     p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--overlap-steps", type=_bool, default=True)
     return p.parse_args(argv)
 
 
@@ -95,6 +97,7 @@ def main(args: argparse.Namespace) -> None:
         num_kvcache_blocks=args.num_kvcache_blocks,
         max_num_batched_tokens=args.max_num_batched_tokens,
         chunked_prefill=args.chunked_prefill,
+        overlap_steps=args.overlap_steps,
     )
     engine = LLMEngine(model=model, config=config, tokenizer=tokenizer)
     sampling_params = SamplingParams(temperature=args.temperature, max_tokens=args.max_tokens, seed=args.seed)

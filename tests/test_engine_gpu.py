@@ -84,6 +84,32 @@ def test_preemption_and_recompute_do_not_change_the_tokens(tmp_path):
     assert tight.model_runner.cache_manager.pages_in_use() == 0
 
 
+@pytest.mark.parametrize("eager", [True, False])
+def test_overlapping_steps_change_no_token(tmp_path, eager):
+    """Steps launched before the host has read the ids of the step before (their tokens are fed on
+    the device), against steps one by one: the same completions, with an end-of-sequence token that
+    random weights do sample (so ends are seen one step late and the extra token is dropped) and
+    with so few pages that requests are preempted while a step of theirs is in flight."""
+    from tokensprint_b200.config.engine_config import SamplingParams
+
+    folder, _ = make_folder(tmp_path, TINY_B, 6, sharp=2.0)
+    prompts = [random_tokens(TINY_B, n, 40 + n) for n in (1, 9, 31, 100, 150, 200, 3, 60)]
+    sps = [SamplingParams(temperature=0.9, max_tokens=40 - 3 * i, ignore_eos=(i % 3 == 0), seed=21) for i in range(len(prompts))]
+    runs = {}
+    for overlap in (False, True):
+        kw = dict(kvcache_block_size=32, num_kvcache_blocks=14, max_num_batched_tokens=64, eos=7, enforce_eager=eager,
+                  overlap_steps=overlap)
+        engine = make_engine(folder, "float32", **kw)
+        assert engine.overlap == overlap
+        runs[overlap] = engine.generate(prompts, sps, use_tqdm=False)
+        assert engine.scheduler.num_preemptions >= 1
+        assert engine.model_runner.cache_manager.pages_in_use() == 0
+        engine.model_runner.cache_manager.check_invariants()
+    assert runs[True] == runs[False]
+    ended_early = [c for c, sp in zip(runs[True], sps) if len(c) < sp.max_tokens]
+    assert ended_early and all(c[-1] == 7 for c in ended_early), "no request ended with the end-of-sequence token"
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding(tmp_path, dtype):
     """Several hundred single-token steps across many pages, in graphs, against the plain model."""

@@ -194,3 +194,89 @@ def test_random_workloads_finish_with_nothing_held(tmp_path, seed):
         assert steps < 5000
     assert all(x.is_finished for x in seqs)
     assert s.cache_manager.pages_in_use() == 0 and len(s.cache_manager.free_slots) == s.cache_manager.num_slots
+
+
+# -- steps that overlap: advance right after a launch, resolve one step later ------------------
+
+
+def test_advance_counts_and_resolve_fills_in(tmp_path):
+    from tokensprint_b200.engine.sequence import UNKNOWN_TOKEN
+
+    s = make_scheduler(tmp_path, eos=9)
+    a, b = seq(10, max_tokens=2), seq(10)
+    s.add_sequence(a)
+    s.add_sequence(b)
+    out0 = s.schedule()
+    pos0 = s.advance(out0, [0, 1])
+    assert pos0 == [10, 10] and a.token_ids[-1] == UNKNOWN_TOKEN and len(a) == 11 and a.num_cached_tokens == 10
+    assert (a.sample_row, b.sample_row) == (0, 1)
+    # the next step is scheduled (and launched) before the first one's tokens are known
+    out1 = s.schedule()
+    assert out1 == [a, b] and a.num_new_tokens == 1 and a.token_ids[a.num_cached_tokens] == UNKNOWN_TOKEN
+    pos1 = s.advance(out1, [0, 1])
+    assert a.is_finished and a.cache is None and s.running == [b]  # max_tokens needs no token
+    assert s.resolve(out0, [0, 1], pos0, [5, 6]) == []  # a is finished but its last token is not there yet
+    assert a.token_ids[10] == 5 and b.token_ids[10] == 6
+    done = s.resolve(out1, [0, 1], pos1, [7, 8])
+    assert done == [a] and a.completion_token_ids == [5, 7] and b.completion_token_ids == [6, 8]
+    check_queues(s)
+
+
+def test_end_of_sequence_is_seen_one_step_late_and_the_extra_token_dropped(tmp_path):
+    s = make_scheduler(tmp_path, eos=9)
+    a, b = seq(10), seq(10)
+    s.add_sequence(a)
+    s.add_sequence(b)
+    out0 = s.schedule()
+    pos0 = s.advance(out0, [0, 1])
+    out1 = s.schedule()
+    pos1 = s.advance(out1, [0, 1])
+    done = s.resolve(out0, [0, 1], pos0, [9, 4])  # a's first token ends it; it is in flight once more
+    assert done == [a] and a.completion_token_ids == [9] and a.cache is None and s.running == [b]
+    assert s.resolve(out1, [0, 1], pos1, [3, 2]) == []  # what the second step sampled for a is dropped
+    assert a.completion_token_ids == [9] and b.completion_token_ids == [4, 2]
+    assert s.cache_manager.pages_in_use() == 1
+    check_queues(s)
+
+
+def test_overlapping_steps_give_the_same_tokens_as_steps_one_by_one(tmp_path):
+    """Random requests under a tight page pool (so that some are preempted), once with
+    postprocess after every step and once with advance/resolve one step apart: the same
+    completions, token by token.  The 'model' is a function of (request, position)."""
+    def token_for(x, position):
+        return (x.seq_id_base * 31 + position * 7) % 13  # 9 is the end-of-sequence token
+
+    def run(overlap):
+        rng = random.Random(5)
+        s = make_scheduler(tmp_path, num_pages=12, budget=64, chunked=True, eos=9, max_num_seqs=4)
+        reqs = []
+        for i in range(12):
+            x = seq(rng.randint(1, 60), max_tokens=rng.randint(1, 40), ignore_eos=rng.random() < 0.3)
+            x.seq_id_base = i
+            reqs.append(x)
+            s.add_sequence(x)
+        inflight = None
+        steps = 0
+        while not s.is_finished() or inflight is not None:
+            launched = None
+            if not s.is_finished():
+                out = s.schedule()
+                need = [i for i, x in enumerate(out) if x.num_cached_tokens + x.num_new_tokens == len(x)]
+                tokens = [token_for(out[i], len(out[i])) for i in need]
+                if overlap:
+                    launched = (out, need, s.advance(out, need), tokens)
+                else:
+                    s.postprocess(out, tokens, need)
+            if inflight is not None:
+                o, n, p, t = inflight
+                s.resolve(o, n, p, t)
+            inflight = launched
+            check_queues(s)
+            steps += 1
+            assert steps < 5000
+        assert s.cache_manager.pages_in_use() == 0
+        return [x.completion_token_ids for x in reqs], s.num_preemptions
+
+    plain, preempted = run(False)
+    assert preempted > 0
+    assert run(True)[0] == plain

@@ -60,6 +60,10 @@ class Config:
     num_kvcache_blocks: int = -1
     chunked_prefill: bool = False
     dtype: str = "bfloat16"
+    # Launch a step before the host has read the ids that the step before sampled (they are fed
+    # on the device), so that the device does not wait for the host between steps.  A request's
+    # end is then seen one step later; what that step computed for it is dropped.
+    overlap_steps: bool = True
 
     def __post_init__(self) -> None:
         if not os.path.isdir(self.model):

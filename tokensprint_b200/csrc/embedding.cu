@@ -21,7 +21,6 @@ __global__ void embed_gather_kernel(float* __restrict__ hidden, const TW* __rest
 __global__ void embed_gather_bf16x8_kernel(float* __restrict__ hidden, const __nv_bfloat16* __restrict__ table,
                                            const int* __restrict__ ids, int H, int V) {
   ts_pdl_prologue();
-  ts_pdl_prologue();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* dst = hidden + (size_t)t * H;
@@ -60,4 +59,18 @@ TS_EXPORT int ts_embed_gather(float* hidden, const void* table, int table_dtype,
   else
     return TS_ERR_BAD_ARGUMENT;
   return ts_launch_status();
+}
+
+// Token ids that an earlier kernel left on the device (the ids the step before sampled): lane
+// lanes[i] of `ids` takes source[rows[i]].  The other lanes of `ids` come from the host.
+__global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ source, const int* __restrict__ lanes,
+                                   const int* __restrict__ rows, int n) {
+  ts_pdl_prologue();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) ids[lanes[i]] = source[rows[i]];
+}
+
+TS_EXPORT int ts_feed_tokens(int* ids, const int* source, const int* lanes, const int* rows, int n, void* stream) {
+  if (n <= 0) return 0;
+  return ts_launch(feed_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, ids, (const int*)source, lanes, rows, n);
 }

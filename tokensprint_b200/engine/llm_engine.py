@@ -19,7 +19,7 @@ from tokensprint_b200 import ops
 from tokensprint_b200.config.engine_config import Config, SamplingParams
 from tokensprint_b200.engine.runner import ModelRunner, StepEntry
 from tokensprint_b200.engine.scheduler import Scheduler
-from tokensprint_b200.engine.sequence import Sequence
+from tokensprint_b200.engine.sequence import UNKNOWN_TOKEN, Sequence
 from tokensprint_b200.models.model import Model
 from tokensprint_b200.sampling.sampler import Sampler, sample_key
 
@@ -44,6 +44,11 @@ class LLMEngine:
         self.sampler = Sampler(model.device)
         self.tokenizer = tokenizer
         self._next_stream = 0
+        # Steps overlap (config.overlap_steps): a step is launched before the host has read what
+        # the step before sampled; its decoded tokens are fed on the device.  What is in flight:
+        # (sequences, which of them are sampled for, the positions of their tokens, the ids' ticket).
+        self.overlap = bool(getattr(config, "overlap_steps", True))
+        self._inflight = None
 
     def _tokenize_prompt(self, prompt: str) -> list[int]:
         if self.tokenizer is None:
@@ -54,7 +59,7 @@ class LLMEngine:
         return token_ids
 
     def is_finished(self) -> bool:
-        return self.scheduler.is_finished()
+        return self.scheduler.is_finished() and self._inflight is None
 
     def add_request(self, prompt: str | list[int], sampling_params: SamplingParams) -> Sequence:
         if isinstance(prompt, str):
@@ -68,23 +73,54 @@ class LLMEngine:
         self.scheduler.add_sequence(sequence)
         return sequence
 
-    def step(self) -> tuple[list[tuple[int, list[int]]], int]:
+    def _launch(self):
+        """Schedules and launches one step; returns what `_inflight` holds."""
         seqs = self.scheduler.schedule()
         entries, need, temps, keys = [], [], [], []
         for i, seq in enumerate(seqs):
             start, n = seq.num_cached_tokens, seq.num_new_tokens
             reaches_end = start + n == len(seq)
-            entries.append(StepEntry(seq.cache, seq.token_ids[start : start + n], start, [n - 1] if reaches_end else []))
+            tokens = seq.token_ids[start : start + n]
+            feed = -1
+            if tokens[-1] == UNKNOWN_TOKEN:
+                # sampled by the step before and not read yet: the device has it
+                if n != 1 or seq.sample_row < 0:
+                    raise RuntimeError(f"Sequence {seq.seq_id} is scheduled with a token that is not known yet.")
+                feed = seq.sample_row
+            entries.append(StepEntry(seq.cache, tokens, start, [n - 1] if reaches_end else [], feed))
             if reaches_end:
                 need.append(i)
                 temps.append(seq.temperature)
                 keys.append(sample_key(seq.seed, seq.sample_stream, len(seq)))
-        logits = self.model_runner.step(entries)
-        token_ids = self.sampler.sample(logits, temps, keys)
-        ops.check_device_errors()  # the copy of the sampled ids has just synchronised
-        self.scheduler.postprocess(seqs, token_ids, need)
-        outputs = [(seq.seq_id, seq.completion_token_ids) for seq in seqs if seq.is_finished]
-        num_total_tokens = sum(len(seq) for seq in seqs if seq.is_finished)
+        logits = self.model_runner.step(entries, self.sampler.device_ids)
+        return seqs, need, logits, temps, keys
+
+    def step(self) -> tuple[list[tuple[int, list[int]]], int]:
+        """One step.  Returns the requests that finished, as (id, completion token ids), and the
+        number of their tokens.  With overlapping steps a call launches the next step and then
+        reads the ids of the step before, so a request's end is reported one call later."""
+        if not self.overlap:
+            seqs, need, logits, temps, keys = self._launch()
+            token_ids = self.sampler.sample(logits, temps, keys)
+            ops.check_device_errors()  # the copy of the sampled ids has just synchronised
+            self.scheduler.postprocess(seqs, token_ids, need)
+            finished = [seq for seq in seqs if seq.is_finished]
+        else:
+            launched = None
+            if not self.scheduler.is_finished():
+                seqs, need, logits, temps, keys = self._launch()
+                ticket = self.sampler.sample_async(logits, temps, keys)
+                positions = self.scheduler.advance(seqs, need)
+                launched = (seqs, need, positions, ticket)
+            finished = []
+            if self._inflight is not None:
+                seqs, need, positions, ticket = self._inflight
+                token_ids = ticket.result()
+                ops.check_device_errors()  # the copy of the sampled ids has just synchronised
+                finished = self.scheduler.resolve(seqs, need, positions, token_ids)
+            self._inflight = launched
+        outputs = [(seq.seq_id, seq.completion_token_ids) for seq in finished]
+        num_total_tokens = sum(len(seq) for seq in finished)
         return outputs, num_total_tokens
 
     def generate(

@@ -36,6 +36,9 @@ class StepEntry:
     tokens: Sequence[int]
     start: int  # absolute position of tokens[0]
     want: Sequence[int] = ()  # places among `tokens` whose logits are asked for
+    # A single token that the host does not know yet: row `feed` of the ids that the step's
+    # caller names (what an earlier step sampled, still on the device) takes the place of tokens[0].
+    feed: int = -1
 
 
 @dataclass
@@ -76,6 +79,8 @@ class _Layout:
         add("context_lens", B)
         add("state_slots", B)
         add("rows", R)
+        add("feed_lanes", B)
+        add("feed_rows", B)
         for g, w in enumerate(self.widths):
             add(f"slots{g}", T)
             add(f"table{g}", B * w)
@@ -183,7 +188,17 @@ class ModelRunner:
             self._pinned[i] = torch.empty(n, dtype=torch.int32, pin_memory=True)
         return self._pinned[i], i
 
-    def build_context(self, entries: Sequence[StepEntry]) -> tuple[StepContext, torch.Tensor, int]:
+    def _feed(self, dev: torch.Tensor, layout: _Layout, feeds: int, fed_ids: Optional[torch.Tensor]) -> None:
+        """Tokens that only the device knows go from `fed_ids` into the step's token lanes."""
+        if feeds == 0:
+            return
+        from tokensprint_b200 import ops
+
+        if fed_ids is None:
+            raise ValueError("an entry names a row of fed ids, but the step was given none")
+        ops.feed_tokens(layout.view(dev, "token_ids"), fed_ids, layout.view(dev, "feed_lanes"), layout.view(dev, "feed_rows"), feeds)
+
+    def build_context(self, entries: Sequence[StepEntry], fed_ids: Optional[torch.Tensor] = None) -> tuple[StepContext, torch.Tensor, int]:
         """Packs the step's index arrays, copies them to the device once and returns the
         context, the rows whose logits are wanted and their number."""
         if not entries:
@@ -201,11 +216,12 @@ class ModelRunner:
         layout = _Layout(T, B, R, widths)
         pinned, slot_i = self._pinned_buffer(layout.total)
         host = pinned.numpy()[: layout.total]
-        self._fill(host, layout, entries, lens)
+        feeds = self._fill(host, layout, entries, lens)
 
         dev = torch.empty(layout.total, dtype=torch.int32, device=self.device)
         dev.copy_(pinned[: layout.total], non_blocking=True)
         self.h2d_bytes += layout.total * 4
+        self._feed(dev, layout, feeds, fed_ids)
         ev = torch.cuda.Event()
         ev.record()
         self._pinned_events[slot_i] = ev
@@ -216,10 +232,11 @@ class ModelRunner:
         step.rows_all = all(list(e.want) == list(range(n)) for e, n in zip(entries, lens))
         return step, layout.view(dev, "rows"), R
 
-    def _fill(self, host, layout: _Layout, entries: Sequence[StepEntry], lens: Sequence[int], row_marks=None) -> None:
+    def _fill(self, host, layout: _Layout, entries: Sequence[StepEntry], lens: Sequence[int], row_marks=None) -> int:
         """Writes the step's index arrays into `host` (a numpy view of pinned memory).  A
         layout larger than the step (a graph bucket) is padded with lanes that belong to no
-        request: sequence index -1, no cache slot, no tokens in their sequence."""
+        request: sequence index -1, no cache slot, no tokens in their sequence.  Returns how
+        many token lanes are to be fed on the device (entries with `feed`)."""
         B, widths = layout.B, layout.widths
         tok = layout.view(host, "token_ids")
         pos = layout.view(host, "positions")
@@ -228,6 +245,9 @@ class ModelRunner:
         ctx_lens = layout.view(host, "context_lens")
         slots = layout.view(host, "state_slots")
         rows = layout.view(host, "rows")
+        feed_lanes = layout.view(host, "feed_lanes")
+        feed_rows = layout.view(host, "feed_rows")
+        feeds = 0
         cu[0] = 0
         t0 = 0
         r0 = 0
@@ -245,7 +265,16 @@ class ModelRunner:
                 raise ValueError(
                     f"request {rc.request!r}: tokens {e.start}..{e.start + n - 1} have no place in the cache "
                     f"({rc.num_tokens} positions were given one)")
-            if n == 1:  # a decoded token: plain numbers instead of array operations
+            if e.feed >= 0:
+                if n != 1:
+                    raise ValueError(f"request {rc.request!r}: only a single token can be fed on the device")
+                tok[t0] = 0
+                feed_lanes[feeds] = t0
+                feed_rows[feeds] = e.feed
+                feeds += 1
+                pos[t0] = e.start
+                sidx[t0] = b
+            elif n == 1:  # a decoded token: plain numbers instead of array operations
                 token = e.tokens[0]
                 if not 0 <= token < self.vocab_size:
                     raise ValueError(f"request {rc.request!r}: token id outside 0..{self.vocab_size - 1}")
@@ -314,6 +343,7 @@ class ModelRunner:
                         row_marks[g].pop(b, None)
         if r0 < layout.R:
             rows[r0:] = 0
+        return feeds
 
     def _context(self, dev: torch.Tensor, layout: _Layout, max_q: int, max_context: int) -> StepContext:
         B = layout.B
@@ -389,13 +419,13 @@ class ModelRunner:
             self._graph_pool = graph.pool()
         return _DecodeGraph(bucket, layout, dev, host, graph, logits, kernels, row_marks=[{} for _ in self.groups])
 
-    def _step_graph(self, bucket: int, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def _step_graph(self, bucket: int, entries: Sequence[StepEntry], fed_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
         g = self._graphs.get(bucket)
         if g is None:
             g = self._graphs[bucket] = self._capture(bucket)
         if g.event is not None:
             g.event.synchronize()
-        self._fill(g.host.numpy(), g.layout, entries, [1] * len(entries), g.row_marks)
+        feeds = self._fill(g.host.numpy(), g.layout, entries, [1] * len(entries), g.row_marks)
         # in a graph every lane's logits are computed; the wanted ones are picked afterwards
         rows_off = g.layout.sections["rows"][0]
         g.host.numpy()[rows_off : rows_off + bucket] = np.arange(bucket)
@@ -404,6 +434,7 @@ class ModelRunner:
         if g.event is None:
             g.event = torch.cuda.Event()
         g.event.record()
+        self._feed(g.dev, g.layout, feeds, fed_ids)
         g.graph.replay()
         self.graph_launches += g.kernels
         wanted = [b for b, e in enumerate(entries) if len(e.want)]
@@ -414,18 +445,19 @@ class ModelRunner:
         return g.logits.index_select(0, torch.tensor(wanted, device=self.device))
 
     @torch.inference_mode()
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Float32 logits [wanted, vocab], in the order of the entries and of their `want`."""
+    def step(self, entries: Sequence[StepEntry], fed_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Float32 logits [wanted, vocab], in the order of the entries and of their `want`.
+        `fed_ids` (int32, on the device): where entries with `feed` take their token from."""
         self.steps_run += 1
         bucket = self._graph_bucket(entries)
         if bucket is not None:
             for e in entries:
-                if e.cache.released or e.start + 1 > e.cache.num_tokens or not (0 <= e.tokens[0] < self.vocab_size):
+                if e.cache.released or e.start + 1 > e.cache.num_tokens or not (e.feed >= 0 or 0 <= e.tokens[0] < self.vocab_size):
                     raise ValueError(f"request {e.cache.request!r}: bad decode entry")
                 if any(w != 0 for w in e.want):
                     raise ValueError(f"request {e.cache.request!r}: wanted place outside its 1 token")
-            return self._step_graph(bucket, entries)
-        step, rows, R = self.build_context(entries)
+            return self._step_graph(bucket, entries, fed_ids)
+        step, rows, R = self.build_context(entries, fed_ids)
         hidden, pending = self.model.forward_hidden(step, self.layer_caches)
         if R == 0:
             return torch.empty((0, self.vocab_size), device=self.device, dtype=torch.float32)

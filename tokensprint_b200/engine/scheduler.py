@@ -28,7 +28,7 @@ from collections import deque
 
 from tokensprint_b200.cache.manager import CacheManager, OutOfSlots
 from tokensprint_b200.config.engine_config import Config
-from tokensprint_b200.engine.sequence import Sequence, SequenceStatus
+from tokensprint_b200.engine.sequence import UNKNOWN_TOKEN, Sequence, SequenceStatus
 
 log = logging.getLogger(__name__)
 
@@ -175,6 +175,67 @@ class Scheduler:
             if seq.status != SequenceStatus.FINISHED:
                 seq.num_cached_tokens += seq.num_new_tokens
                 seq.num_new_tokens = 0
+
+    # -- steps that overlap ------------------------------------------------------------------
+    #
+    # A step can be launched before the host has read what the step before sampled: the new
+    # token of every sequence is then on the device only.  `advance` does, right after the
+    # launch, what `postprocess` does without looking at the tokens: the sequences grow by a
+    # token that is not known yet, and the ends that only depend on counts (max_tokens, the
+    # model's length) are decided.  `resolve` fills the tokens in when they have arrived, one
+    # step later, and ends a sequence whose token was the end-of-sequence token; what the step
+    # in flight has meanwhile computed for that sequence is dropped.
+
+    def advance(self, seqs: list[Sequence], seq_need_compute_logits: list[int]) -> list[int]:
+        """Returns, for every sequence that the step samples for, the position its token will have."""
+        positions = []
+        for row, seq_index in enumerate(seq_need_compute_logits):
+            seq = seqs[seq_index]
+            positions.append(len(seq))
+            seq.append_token(UNKNOWN_TOKEN)
+            seq.unresolved += 1
+            seq.sample_row = row
+            if seq.num_completion_tokens == seq.max_tokens or len(seq) >= self.max_model_len:
+                if len(seq) >= self.max_model_len:
+                    log.info("Sequence %s reached max_model_len %s.", seq.seq_id, self.max_model_len)
+                seq.status = SequenceStatus.FINISHED
+                self._release(seq)
+                self.running.remove(seq)
+        for seq in seqs:
+            if seq.status != SequenceStatus.FINISHED:
+                seq.num_cached_tokens += seq.num_new_tokens
+                seq.num_new_tokens = 0
+        return positions
+
+    def resolve(self, seqs: list[Sequence], seq_need_compute_logits: list[int], positions: list[int],
+                token_ids: list[int]) -> list[Sequence]:
+        """Fills in the tokens of a step that `advance` has accounted for.  Returns the sequences
+        that are finished and complete (each once)."""
+        if not (len(token_ids) == len(seq_need_compute_logits) == len(positions)):
+            raise ValueError(
+                "token_ids, seq_need_compute_logits and positions must have equal length, "
+                f"got {len(token_ids)}, {len(seq_need_compute_logits)} and {len(positions)}.")
+        done = []
+        for seq_index, position, token_id in zip(seq_need_compute_logits, positions, token_ids):
+            seq = seqs[seq_index]
+            if 0 <= seq.ended_at < position:
+                continue  # sampled after the sequence's end: dropped with the sequence's tail
+            seq.set_token(position, token_id)
+            seq.unresolved -= 1
+            if not seq.ignore_eos and token_id == self.eos:
+                seq.ended_at = position
+                seq.truncate(position + 1)
+                seq.unresolved = 0
+                if seq.status == SequenceStatus.RUNNING:
+                    self.running.remove(seq)
+                elif seq.status == SequenceStatus.WAITING:  # preempted in the meantime
+                    self.waiting.remove(seq)
+                seq.status = SequenceStatus.FINISHED
+                self._release(seq)
+            if seq.status == SequenceStatus.FINISHED and seq.unresolved == 0 and not seq.reported:
+                seq.reported = True
+                done.append(seq)
+        return done
 
     def abort(self, seq: Sequence) -> None:
         """Drops a request wherever it is."""

@@ -11,6 +11,9 @@ from tokensprint_b200.cache.manager import RequestCache
 from tokensprint_b200.config.engine_config import SamplingParams
 
 
+UNKNOWN_TOKEN = -1  # stands in a sequence for a token that has been sampled but not yet read by the host
+
+
 class SequenceStatus(Enum):
     WAITING = auto()
     RUNNING = auto()
@@ -46,6 +49,13 @@ class Sequence:
         self.sample_stream = 0  # which noise stream this request draws from (set by the engine)
         self.cache: Optional[RequestCache] = None
         self.num_preemptions = 0
+        # Steps that overlap: tokens appended as UNKNOWN_TOKEN and not yet filled in; the row that
+        # holds this sequence's newest id among the ids the last step sampled; the position of an
+        # end-of-sequence token once one was seen (what later steps sampled for it is dropped).
+        self.unresolved = 0
+        self.sample_row = -1
+        self.ended_at = -1
+        self.reported = False
 
     def __len__(self) -> int:
         return self.num_tokens
@@ -57,6 +67,17 @@ class Sequence:
         self.token_ids.append(token_id)
         self.last_token = token_id
         self.num_tokens += 1
+
+    def set_token(self, position: int, token_id: int) -> None:
+        """Fills in a token that was appended before the host knew it."""
+        self.token_ids[position] = token_id
+        if position == self.num_tokens - 1:
+            self.last_token = token_id
+
+    def truncate(self, num_tokens: int) -> None:
+        del self.token_ids[num_tokens:]
+        self.num_tokens = len(self.token_ids)
+        self.last_token = self.token_ids[-1]
 
     @property
     def is_finished(self) -> bool:

@@ -25,6 +25,7 @@ _c_ll = ctypes.c_longlong
 
 _SIGNATURES = {
     "ts_embed_gather": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_feed_tokens": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p],
     "ts_add_rmsnorm": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
     "ts_residual_add": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
     "ts_swiglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
@@ -119,6 +120,16 @@ def embed_gather(hidden: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -
         raise KernelError(f"embed_gather: shapes disagree: hidden {tuple(hidden.shape)}, table {tuple(table.shape)}, ids {tuple(ids.shape)}")
     _check("embed_gather", _fn("ts_embed_gather")(
         hidden.data_ptr(), table.data_ptr(), _act_code("table", table), ids.data_ptr(), T, H, V, _stream()))
+
+
+def feed_tokens(ids: torch.Tensor, source: torch.Tensor, lanes: torch.Tensor, rows: torch.Tensor, n: int) -> None:
+    """ids[lanes[i]] = source[rows[i]] for i < n (all int32, on the device): token ids that an
+    earlier kernel produced go into a step's inputs without passing through the host."""
+    for name, t in (("ids", ids), ("source", source), ("lanes", lanes), ("rows", rows)):
+        _cuda_contig(name, t, torch.int32)
+    if n > lanes.numel() or n > rows.numel():
+        raise KernelError(f"feed_tokens: {n} lanes, but the index arrays hold {lanes.numel()} and {rows.numel()}")
+    _check("feed_tokens", _fn("ts_feed_tokens")(ids.data_ptr(), source.data_ptr(), lanes.data_ptr(), rows.data_ptr(), int(n), _stream()))
 
 
 def add_rmsnorm(
