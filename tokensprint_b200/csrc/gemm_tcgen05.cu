@@ -430,6 +430,20 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
     // Epilogue warps 2..5: TMEM lanes 32 * (warp % 4) .. + 31.
     const int quarter = warp & 3;
     const int etid = (warp - 2) * 32 + lane;  // 0..127 among the epilogue threads
+    if (MPAD <= FUSED_MAX_ROWS && args.mode == EPI_QK_ROPE) {
+      // the step's positions and cache slots and the small weight vectors of the rotation epilogue
+      // (none of them written by a kernel of the step) go to the L1 ahead of their use
+      if (etid < args.M) {
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(args.positions + etid));
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(args.slot_mapping + etid));
+      } else if (etid < 64) {
+        if (args.inv_freq != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.inv_freq + (etid & 7) * 8));
+      } else if (etid < 96) {
+        if (args.q_norm_w != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.q_norm_w + (etid & 15) * 8));
+      } else {
+        if (args.k_norm_w != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.k_norm_w + (etid & 15) * 8));
+      }
+    }
     ts_pdl_wait();  // nothing is stored before the kernels ahead in the stream are done
     const bool fused = MPAD <= FUSED_MAX_ROWS && (args.mode != EPI_PLAIN || args.scale_ssq != nullptr);
     if (fused) {
@@ -452,6 +466,15 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       __syncwarp();
       if (etid == 0 && t == t_last) TS_PROBE(4);
+      if (fused && args.mode == EPI_RESIDUAL_NORM) {
+        // whoever finishes this tile adds it to the residual stream: ask for those values now,
+        // so that they are in the L1 when the partial sums and the ticket have made their trips
+        for (int idx = etid; idx < args.M * 32; idx += 128) {
+          const int pn = t * TILE_N + (idx & 31) * 4;
+          if (pn < args.N) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.hidden + (size_t)(idx >> 5) * args.ldh + pn));
+        }
+        if (etid < 32 && t * TILE_N + etid * 4 < args.N) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.norm_w + t * TILE_N + etid * 4));
+      }
       const int n_local = quarter * 32 + lane;
       const int n = t * TILE_N + n_local;
       const int slot = (t == t_first) ? 0 : 1;
@@ -517,31 +540,45 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
             const int c_t_first = (int)(((long long)c * args.units_per) / chunks);
             src[j] = args.partial + (size_t)(c * 2 + ((t == c_t_first) ? 0 : 1)) * args.M * TILE_N;
           }
-          for (int idx = etid; idx < args.M * (TILE_N / 4); idx += 128) {
-            const int m = idx / (TILE_N / 4), nl = (idx % (TILE_N / 4)) * 4;
-            const size_t off = (size_t)m * TILE_N + nl;
-            // all loads first (they are independent), then the sum in contributor order
-            float4 v[MAX_CONTRIB];
+          // Two pieces of four columns per thread and pass, all their loads first (they are
+          // independent: one trip to the L2 per pass, not one per piece), then the sums in contributor order.
+          constexpr int PIECES = 2;
+          const int total = args.M * (TILE_N / 4);
+          for (int base = etid; base < total; base += 128 * PIECES) {
+            float4 v[PIECES][MAX_CONTRIB];
 #pragma unroll
-            for (int j = 0; j < MAX_CONTRIB; ++j)
-              if (j < nc) v[j] = __ldcg(reinterpret_cast<const float4*>(src[j] + off));
-            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int u = 0; u < PIECES; ++u) {
+              const int idx = base + u * 128;
+              if (idx < total) {
+                const size_t off = (size_t)(idx / (TILE_N / 4)) * TILE_N + (idx % (TILE_N / 4)) * 4;
 #pragma unroll
-            for (int j = 0; j < MAX_CONTRIB; ++j)
-              if (j < nc) { sum.x += v[j].x; sum.y += v[j].y; sum.z += v[j].z; sum.w += v[j].w; }
-            const int nn = t * TILE_N + nl;
-            const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
-            if (fused) {
-              *reinterpret_cast<float4*>(&tile_s[(MPAD <= FUSED_MAX_ROWS ? m : 0) * TILE_N + nl]) = sum;
-              continue;
+                for (int j = 0; j < MAX_CONTRIB; ++j)
+                  if (j < nc) v[u][j] = __ldcg(reinterpret_cast<const float4*>(src[j] + off));
+              }
             }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (nn + j < args.N) {
-                if (args.out_f32)
-                  reinterpret_cast<float*>(args.out)[(size_t)m * args.ldo + nn + j] = vals[j];
-                else
-                  reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)m * args.ldo + nn + j] = __float2bfloat16_rn(vals[j]);
+            for (int u = 0; u < PIECES; ++u) {
+              const int idx = base + u * 128;
+              if (idx >= total) continue;
+              const int m = idx / (TILE_N / 4), nl = (idx % (TILE_N / 4)) * 4;
+              float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+              for (int j = 0; j < MAX_CONTRIB; ++j)
+                if (j < nc) { sum.x += v[u][j].x; sum.y += v[u][j].y; sum.z += v[u][j].z; sum.w += v[u][j].w; }
+              const int nn = t * TILE_N + nl;
+              const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+              if (fused) {
+                *reinterpret_cast<float4*>(&tile_s[(MPAD <= FUSED_MAX_ROWS ? m : 0) * TILE_N + nl]) = sum;
+                continue;
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (nn + j < args.N) {
+                  if (args.out_f32)
+                    reinterpret_cast<float*>(args.out)[(size_t)m * args.ldo + nn + j] = vals[j];
+                  else
+                    reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)m * args.ldo + nn + j] = __float2bfloat16_rn(vals[j]);
+                }
               }
             }
           }
