@@ -144,6 +144,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
+// The same with a cache policy for the L2 (weights pass through once per step: "evict first"
+// leaves the L2 to what is read again, the activations and what was asked ahead).
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "l"(policy) : "memory");
+}
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
   // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart; descriptor version 1 (sm_100).
   return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
@@ -335,6 +342,8 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
       const int n_units = range.u1 - range.u0;
       // The weights are written by no kernel, so the first ring of W tiles is requested before
       // the kernels ahead in the stream have finished; X (their output) only after the wait.
+      uint64_t w_policy;
+      asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(w_policy));
       const int early = min(n_units, STAGES);
       for (int i = 0; i < early; ++i) {
         const int u = range.u0 + i;
@@ -343,7 +352,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
         mbar_expect_tx(bar, C::A_BYTES + C::B_BYTES);
 #pragma unroll
         for (int a = 0; a < KATOMS; ++a)
-          tma_load_2d(smem_u32(smem + (size_t)i * C::STAGE_BYTES) + a * C::A_ATOM, &map_w, bar, kc * TILE_K + a * ATOM_K, t * TILE_N);
+          tma_load_2d_hint(smem_u32(smem + (size_t)i * C::STAGE_BYTES) + a * C::A_ATOM, &map_w, bar, kc * TILE_K + a * ATOM_K, t * TILE_N, w_policy);
       }
       ts_pdl_wait();
       TS_PROBE(6);
@@ -366,7 +375,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
         const uint32_t dst = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
         mbar_expect_tx(bar, C::A_BYTES + C::B_BYTES);
 #pragma unroll
-        for (int a = 0; a < KATOMS; ++a) tma_load_2d(dst + a * C::A_ATOM, &map_w, bar, kc * TILE_K + a * ATOM_K, t * TILE_N);
+        for (int a = 0; a < KATOMS; ++a) tma_load_2d_hint(dst + a * C::A_ATOM, &map_w, bar, kc * TILE_K + a * ATOM_K, t * TILE_N, w_policy);
 #pragma unroll
         for (int a = 0; a < KATOMS; ++a) tma_load_2d(dst + C::A_BYTES + a * C::B_ATOM, &map_x, bar, kc * TILE_K + a * ATOM_K, 0);
       }

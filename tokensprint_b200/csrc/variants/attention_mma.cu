@@ -99,10 +99,14 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
   *abort_flag = 1;
   return false;
 }
+// In a decode step every key and value is read once: the copies say "evict first", which leaves
+// the L2 to what is read again (activations, the next weights asked ahead).
 __device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1, int c2) {
+  unsigned long long policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy) : "memory");
 }
 // Address of the 16-byte piece that holds elements [col, col + 8) of row `row` in a swizzled tile
 // [HALVES][64 rows][128 B]: piece c of a row sits at position c ^ (row % 8).

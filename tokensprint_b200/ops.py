@@ -732,10 +732,11 @@ _SIGNATURES["ts_gemm_skinny_bf16"] = [
     _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll, _c_void_p,
 ]
 # How much of the next GEMM's weights a GEMM asks into L2 while its own last tiles are finished.
-# Measured on the decode step at batch 8 (ms per step): none 4.03, 8 MB 3.98, 16 to 32 MB 3.96,
-# 48 MB 3.98, 64 MB and more 4.02 to 4.06 (the requests then compete with the kernel's own tail).
-# TS_GEMM_PREFETCH_MB overrides it for measurements.
-GEMM_PREFETCH_BYTES = int(_os.environ.get("TS_GEMM_PREFETCH_MB", "24")) << 20
+# Measured on the decode step at batch 8 (ms per step, the weights themselves passing through the
+# L2 as "evict first"): none 3.87, 8 MB 3.83, 16 MB 3.80, 24 MB 3.82, 32 MB 3.84, 48 MB 3.86,
+# 96 MB 3.94 (the requests then compete with the kernel's own tail).  TS_GEMM_PREFETCH_MB
+# overrides it for measurements.
+GEMM_PREFETCH_BYTES = int(_os.environ.get("TS_GEMM_PREFETCH_MB", "16")) << 20
 _gemm_workspaces: dict[tuple[int, int], tuple[torch.Tensor, torch.Tensor]] = {}
 
 
