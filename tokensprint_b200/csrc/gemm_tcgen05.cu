@@ -50,6 +50,11 @@ namespace {
 constexpr int TILE_N = 128;   // W rows per tile (the MMA's M)
 // Boxes side by side per stage.  Two (256 contiguous bytes of every W row asked for at once, half
 // as many stages of twice the size) measured the same alone and 4 % slower inside the decode step.
+// Tiles of W and X in flight per CTA, for up to 64 rows (a build option for measurements: 6, 10
+// and 12 were measured no better than 8).
+#ifndef TS_GEMM_STAGES
+#define TS_GEMM_STAGES 8
+#endif
 #ifndef TS_GEMM_KATOMS
 #define TS_GEMM_KATOMS 1
 #endif
@@ -71,7 +76,7 @@ struct Cfg {
   // Stages of the ring.  Measured inside the decode step (8 rows, Qwen3-8B sizes): 6 stages
   // 4.52 ms, 8 4.39 ms, 10 4.40 ms, 12 4.47 ms per step: more bytes in flight than the memory
   // system turns around only queue up.
-  static constexpr int STAGES = (MPAD <= 64 ? 8 : 6) / KATOMS;
+  static constexpr int STAGES = (MPAD <= 64 ? TS_GEMM_STAGES : 6) / KATOMS;
   static constexpr uint32_t A_ATOM = TILE_N * ATOM_K * 2;  // one box of W
   static constexpr uint32_t B_ATOM = MPAD * ATOM_K * 2;    // one box of X
   static constexpr uint32_t TMEM_COLS = 2 * MPAD < 32 ? 32 : 2 * MPAD;
