@@ -21,7 +21,7 @@ from tokensprint_b200 import ops
 # Up to this many rows the engine's own weight-streaming kernel is used; above it the
 # library GEMM is (measured on B200 at Qwen3-8B sizes: the own kernel wins while the step is
 # bound by reading the weights).
-SKINNY_ROWS = 32
+SKINNY_ROWS = int(os.environ.get("TS_SKINNY_ROWS", "32"))  # the variable is for measurements
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
