@@ -66,7 +66,16 @@ def _fn(name: str):
     return f
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> int:
+    """The current CUDA stream's handle.  (torch.cuda.current_stream() builds a Python object and
+    resolves the device by name every time: a third of the host's time in a step launched kernel by
+    kernel; the raw call is a hundred times cheaper.)"""
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
     return torch.cuda.current_stream().cuda_stream
 
 
