@@ -787,3 +787,16 @@ def test_gemm_skinny_refuses_what_it_cannot_take():
         ops.gemm_skinny_bf16(x, w, torch.empty(129, 128, device=DEV, dtype=torch.bfloat16))
     with pytest.raises(ops.KernelError):
         ops.gemm_skinny_bf16(x[:4, :60], w[:, :60], torch.empty(4, 128, device=DEV, dtype=torch.bfloat16))
+
+
+def test_kernel_bench_runs_a_small_case(capsys):
+    """The kernel table's program, on its smallest decode-attention case: one line per kernel with a
+    time and a share of the roofline."""
+    import json
+
+    from tokensprint_b200 import kernel_bench
+
+    assert kernel_bench.main(["--only", "decode", "--batches", "2", "--contexts", "256", "--json"]) == 0
+    rows = [json.loads(line) for line in capsys.readouterr().out.strip().splitlines()]
+    assert [r["kernel"] for r in rows] == ["attention, decode", "attention, decode, even shares"]
+    assert all(r["us"] > 0 and 0 < r["frac"] < 1.5 and r["unit"] == "GB/s" for r in rows)
