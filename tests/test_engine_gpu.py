@@ -110,6 +110,41 @@ def test_overlapping_steps_change_no_token(tmp_path, eager):
     assert ended_early and all(c[-1] == 7 for c in ended_early), "no request ended with the end-of-sequence token"
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+def test_a_step_takes_tokens_that_only_the_device_knows(tmp_path, graphs):
+    """`StepEntry.feed`: a decoded token that lies in a device tensor (what the step before sampled)
+    gives the same logits as the same token given by the host, beside entries of both kinds."""
+    from tokensprint_b200.engine.runner import ModelRunner, StepEntry
+    from tokensprint_b200.models.api import load_model
+
+    cfg = TINY_A
+    folder, _ = make_folder(tmp_path, cfg, 9, sharp=2.0)
+    model, _ = load_model(folder, device="cuda", dtype="float32")
+    results = []
+    for fed in (False, True):
+        runner = ModelRunner(model, page_size=16, num_pages=32, num_slots=4, enforce_eager=not graphs, max_model_len=128)
+        cm = runner.cache_manager
+        prompts = [random_tokens(cfg, n, 60 + n) for n in (5, 17, 9)]
+        caches = []
+        for i, p in enumerate(prompts):
+            rc = cm.admit(i)
+            cm.extend(rc, 0, len(p))
+            caches.append(rc)
+        runner.step([StepEntry(rc, p, 0, []) for rc, p in zip(caches, prompts)])
+        nxt = [11, 22, 33]
+        device_ids = torch.tensor([99, nxt[2], 99, nxt[0]], dtype=torch.int32, device="cuda")  # rows 1 and 3 are used
+        entries = []
+        for i, (rc, p) in enumerate(zip(caches, prompts)):
+            cm.extend(rc, len(p), len(p) + 1)
+            feed = {0: 3, 2: 1}.get(i, -1) if fed else -1
+            entries.append(StepEntry(rc, [0 if feed >= 0 else nxt[i]], len(p), [0], feed))
+        results.append(runner.step(entries, device_ids).clone())
+        assert bool(runner._graphs) == graphs
+    assert torch.equal(results[0], results[1])
+    with pytest.raises(ValueError, match="given none"):
+        runner.step([StepEntry(caches[0], [0], len(prompts[0]), [0], 0)])
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding(tmp_path, dtype):
     """Several hundred single-token steps across many pages, in graphs, against the plain model."""

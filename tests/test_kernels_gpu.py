@@ -800,3 +800,20 @@ def test_kernel_bench_runs_a_small_case(capsys):
     rows = [json.loads(line) for line in capsys.readouterr().out.strip().splitlines()]
     assert [r["kernel"] for r in rows] == ["attention, decode", "attention, decode, even shares"]
     assert all(r["us"] > 0 and 0 < r["frac"] < 1.5 and r["unit"] == "GB/s" for r in rows)
+
+
+def test_feed_tokens():
+    from tokensprint_b200 import ops
+
+    ids = torch.arange(100, 120, dtype=torch.int32, device=DEV)
+    source = torch.tensor([7, 8, 9, 10], dtype=torch.int32, device=DEV)
+    lanes = torch.tensor([3, 0, 19, 5, 5, 5], dtype=torch.int32, device=DEV)
+    rows = torch.tensor([2, 0, 3, 1, 1, 1], dtype=torch.int32, device=DEV)
+    ops.feed_tokens(ids, source, lanes, rows, 3)  # only the first three pairs
+    want = list(range(100, 120))
+    want[3], want[0], want[19] = 9, 7, 10
+    assert ids.tolist() == want
+    ops.feed_tokens(ids, source, lanes, rows, 0)
+    assert ids.tolist() == want
+    with pytest.raises(ops.KernelError, match="index arrays hold"):
+        ops.feed_tokens(ids, source, lanes, rows, 7)
