@@ -86,3 +86,52 @@ def test_full_width_cuttings(folder, monkeypatch):
         worst = max(float(abs(got[k] - ref[k]).max()) for k in ref)
         assert worst < 4e-2 * scale, f"{name}: bfloat16 strays {worst / scale:.3g} from float32"
     ops.check_device_errors()
+
+
+def test_many_sequences_decode_through_the_even_share_kernel(tmp_path):
+    """Sixty sequences of different lengths decoding together at Qwen3-0.6B layer sizes (8 KV heads
+    of 128): more (sequence, KV head) pairs than CTAs run at once, so the engine itself picks the
+    even-share decode kernel, in a graph whose batch bucket has lanes without a sequence.  bfloat16
+    against the float32 path, the same trace."""
+    from tokensprint_b200 import ops
+    from tokensprint_b200.config.model_config import Qwen3Config
+    from tokensprint_b200.config.registry import get_preset_dict
+    from tokensprint_b200.engine.replay import TraceReplayer
+    from tokensprint_b200.engine.runner import ModelRunner
+    from tokensprint_b200.models.api import load_model
+    from tokensprint_b200.weights.loader import write_random_model
+
+    d = get_preset_dict("qwen3-0.6b")
+    d["num_hidden_layers"] = 2
+    cfg = Qwen3Config.from_dict(d)
+    path = write_random_model(tmp_path / "m", cfg, seed=5, dtype="bfloat16", std=0.02)
+    lengths = [3 + (37 * i) % 150 for i in range(60)]
+    requests = {f"r{i}": random_tokens(d, n + 6, 100 + i) for i, n in enumerate(lengths)}
+    steps = []
+    for i, (rid, ids) in enumerate(requests.items()):
+        steps.append({"step": i, "entries": [{"id": rid, "tokens": ids[:-6], "want": [len(ids) - 7]}], "end": []})
+    for k in range(6):
+        steps.append({"step": 60 + k, "entries": [{"id": rid, "tokens": [ids[len(ids) - 6 + k]], "want": [0]} for rid, ids in requests.items()],
+                      "end": list(requests) if k == 5 else []})
+
+    calls = []
+    flat = ops.attention_decode_flat
+    got = {}
+    for dtype, graphs in (("float32", False), ("bfloat16", False), ("bfloat16", True)):
+        model, _ = load_model(path, device="cuda", dtype=dtype)
+        runner = ModelRunner(model, page_size=16, num_pages=60 * 11, num_slots=64, enforce_eager=not graphs, max_model_len=256)
+        calls.clear()
+        ops.attention_decode_flat = lambda *a, **k: (calls.append(1), flat(*a, **k))[1]
+        try:
+            got[dtype, graphs] = replay_in_process(TraceReplayer(runner), steps)
+        finally:
+            ops.attention_decode_flat = flat
+        assert bool(calls) == (dtype == "bfloat16"), "the even-share kernel is the bfloat16 path's, for batches like this one"
+        assert not graphs or runner._graphs
+    ref = got["float32", False]
+    scale = max(float(abs(v).max()) for v in ref.values())
+    for key in (("bfloat16", False), ("bfloat16", True)):
+        assert len(got[key]) == len(ref) == 60 * 7
+        worst = max(float(abs(got[key][k] - ref[k]).max()) for k in ref)
+        assert worst < 4e-2 * scale, f"{key}: bfloat16 strays {worst / scale:.3g} from float32"
+    ops.check_device_errors()
