@@ -762,6 +762,26 @@ def _gemm_workspace(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
     return ws
 
 
+_gemm_partials: dict[tuple[int, int], torch.Tensor] = {}
+_gemm_scratch_need: dict[tuple[int, int, int], int] = {}
+
+
+def _gemm_partial(device: torch.device, M: int, N: int, K: int) -> torch.Tensor:
+    """Per (device, stream): the float32 scratch in which CTAs that share a tile meet.  One buffer
+    serves every launch on the stream (it only grows): a GEMM stores nothing before the kernels
+    ahead of it are done, so two launches never use it at once."""
+    need = _gemm_scratch_need.get((M, N, K))
+    if need is None:
+        scratch_floats = library().ts_gemm_skinny_scratch_floats
+        scratch_floats.restype = _c_ll
+        need = _gemm_scratch_need[(M, N, K)] = max(4, int(scratch_floats(M, N, K)))
+    key = (device.index or 0, _stream())
+    buf = _gemm_partials.get(key)
+    if buf is None or buf.numel() < need:
+        buf = _gemm_partials[key] = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=device)
+    return buf
+
+
 def gemm_skinny_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
     M, K = x.shape
     return (
@@ -789,9 +809,7 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, prefet
     N = w.shape[0]
     if w.shape[1] != K or tuple(out.shape) != (M, N) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"gemm_skinny_bf16: shapes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
-    scratch_floats = library().ts_gemm_skinny_scratch_floats
-    scratch_floats.restype = _c_ll
-    partial = torch.empty(max(4, scratch_floats(M, N, K)), dtype=torch.float32, device=x.device)
+    partial = _gemm_partial(x.device, M, N, K)
     counters, error = _gemm_workspace(x.device)
     _check("gemm_skinny_bf16", _fn("ts_gemm_skinny_bf16")(
         x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0), out.stride(0),
@@ -871,9 +889,7 @@ def gemm_skinny_fused(
         if scale_ssq.dtype != torch.float32 or not scale_ssq.is_contiguous() or scale_ssq.dim() != 2 or scale_ssq.shape[1] != M:
             raise KernelError("gemm_skinny_fused: scale_ssq must be float32 [tiles, M]")
         scale_tiles = scale_ssq.shape[0]
-    scratch_floats = library().ts_gemm_skinny_scratch_floats
-    scratch_floats.restype = _c_ll
-    partial = torch.empty(max(4, scratch_floats(M, N, K)), dtype=torch.float32, device=x.device)
+    partial = _gemm_partial(x.device, M, N, K)
     counters, error = _gemm_workspace(x.device)
     _check("gemm_skinny_fused", _fn("ts_gemm_skinny_fused")(
         x.data_ptr(), w.data_ptr(), _ptr(out), M, N, K, x.stride(0), w.stride(0), ldo, out_f32,
@@ -941,9 +957,7 @@ def gemm_qk_rope_store(
         if scale_ssq.dtype != torch.float32 or not scale_ssq.is_contiguous() or scale_ssq.dim() != 2 or scale_ssq.shape[1] != M:
             raise KernelError("gemm_qk_rope_store: scale_ssq must be float32 [tiles, M]")
         scale_tiles = scale_ssq.shape[0]
-    scratch_floats = library().ts_gemm_skinny_scratch_floats
-    scratch_floats.restype = _c_ll
-    partial = torch.empty(max(4, scratch_floats(M, w.shape[0], K)), dtype=torch.float32, device=x.device)
+    partial = _gemm_partial(x.device, M, w.shape[0], K)
     counters, error = _gemm_workspace(x.device)
     _check("gemm_qk_rope_store", _fn("ts_gemm_skinny_qk_rope")(
         x.data_ptr(), w.data_ptr(), M, K, x.stride(0), w.stride(0), nq, nkv,
