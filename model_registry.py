@@ -1,25 +1,21 @@
-"""Prints the registered models grouped by family (the reference's model_registry.py:8-22)."""
+"""Lists the registered models, family by family, each with its repo id (the output format
+of the reference's model_registry.py)."""
 
 from __future__ import annotations
 
-from collections import defaultdict
-
-from tokensprint_b200.config.registry import all_registered_models, get_model_family, get_model_repo_id
+from tokensprint_b200.config.registry import registered_families
 
 
-def main() -> None:
-    families: dict[str, list[str]] = defaultdict(list)
-    for model in all_registered_models(newest_first=False):
-        families[get_model_family(model)].append(model)
+def listing() -> str:
+    families = registered_families()
     if not families:
-        print("No models are currently registered.")
-        return
-    print("Registered models:")
-    for family in sorted(families):
-        print(f"\n{family}:")
-        for model in families[family]:
-            print(f"  - {model} ({get_model_repo_id(model)})")
+        return "No models are currently registered."
+    lines = ["Registered models:"]
+    for family, presets in families.items():
+        lines += ["", f"{family}:"]
+        lines += [f"  - {p.name} ({p.repo_id})" for p in presets]
+    return "\n".join(lines)
 
 
 if __name__ == "__main__":
-    main()
+    print(listing())

@@ -104,13 +104,16 @@ def test_duplicate_registration_is_refused():
         registry.register_preset("qwen", "qwen3-8b", registry.PRESET_DIR / "qwen3-8b.json")
 
 
-def test_listing_script(capsys):
+def test_listing_script():
     import model_registry
 
-    model_registry.main()
-    out = capsys.readouterr().out
+    out = model_registry.listing()
     assert out.startswith("Registered models:\n\nqwen:\n")
     assert "  - qwen3-0.6b (qwen/qwen3-0.6b)" in out
+    for name in ("qwen3-1.7b", "qwen3-4b", "qwen3-8b", "qwen3-14b", "qwen3-32b"):
+        assert f"  - {name} (qwen/{name})" in out
+    assert registry.get_models_from_family("qwen", newest_first=False)[0] == "qwen3-0.6b"
+    assert registry.get_models_from_family("nobody") == []
 
 
 def test_engine_config_and_sampling_params(tmp_path):

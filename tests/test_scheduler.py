@@ -280,3 +280,41 @@ def test_overlapping_steps_give_the_same_tokens_as_steps_one_by_one(tmp_path):
     plain, preempted = run(False)
     assert preempted > 0
     assert run(True)[0] == plain
+
+
+def test_abort_with_a_token_in_flight_is_never_reported(tmp_path):
+    s = make_scheduler(tmp_path, eos=9)
+    a, b = seq(10), seq(10)
+    s.add_sequence(a)
+    s.add_sequence(b)
+    out0 = s.schedule()
+    pos0 = s.advance(out0, [0, 1])
+    s.abort(a)  # its first token is still on the device
+    assert a.is_finished and a.cache is None and s.running == [b]
+    done = s.resolve(out0, [0, 1], pos0, [5, 6])
+    assert done == [] and b.completion_token_ids == [6]
+    assert s.schedule() == [b]
+    check_queues(s)
+
+
+def test_a_prompt_beyond_a_window_groups_pool_is_refused_when_added(tmp_path):
+    groups = [GroupSpec("full"), GroupSpec("window", 32)]
+    # whole prompts only: a window group holds every page of the prompt during its one step
+    config = Config(model=str(tmp_path), num_kvcache_blocks=8, kvcache_block_size=16, max_num_batched_tokens=512,
+                    max_num_seqs=4, chunked_prefill=False)
+    s = Scheduler(config, CacheManager(groups, 16, [64, 8], 4))
+    with pytest.raises(ValueError, match="group 1 .window.*could never be scheduled"):
+        s.add_sequence(seq(200))
+    s.add_sequence(seq(100))
+    assert len(s.schedule()) == 1
+    # in portions the group needs the window and one portion only
+    config = Config(model=str(tmp_path), num_kvcache_blocks=8, kvcache_block_size=16, max_num_batched_tokens=48,
+                    max_num_seqs=4, chunked_prefill=True)
+    s = Scheduler(config, CacheManager(groups, 16, [64, 8], 4))
+    long = seq(200)
+    s.add_sequence(long)
+    while long.num_cached_tokens < 200:
+        out = s.schedule()
+        need = [0] if long.num_cached_tokens + long.num_new_tokens == len(long) else []
+        s.postprocess(out, [1] * len(need), need)
+    check_queues(s)

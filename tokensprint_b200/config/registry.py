@@ -35,9 +35,6 @@ class Architecture:
 ARCHITECTURES: dict[str, Architecture] = {}
 _MODEL_TYPE_TO_ARCH: dict[str, str] = {}
 
-MODEL_REGISTRY: dict[str, Path] = {}
-MODEL_FAMILY_REGISTRY: dict[str, str] = {}
-FAMILY_MODEL_REGISTRY: dict[str, list[str]] = {}
 
 
 def register_architecture(
@@ -106,64 +103,98 @@ def load_model_config(model_dir: str | Path) -> tuple[Architecture, Any]:
 # model names and presets
 
 
+@dataclass(frozen=True)
+class Preset:
+    """A named model: `family/name` is its repo id, `path` its config.json."""
+
+    name: str
+    family: str
+    path: Path
+
+    @property
+    def repo_id(self) -> str:
+        return f"{self.family}/{self.name}"
+
+
+# short name -> preset, in registration order (oldest first)
+PRESETS: dict[str, Preset] = {}
+
+
 def register_preset(family: str, name: str, path: Path) -> None:
-    if name in MODEL_REGISTRY:
+    if name in PRESETS:
         raise ValueError(f"Model {name} already registered.")
-    MODEL_REGISTRY[name] = Path(path)
-    MODEL_FAMILY_REGISTRY[name] = family
-    FAMILY_MODEL_REGISTRY.setdefault(family, []).append(name)
+    PRESETS[name] = Preset(name, family, Path(path))
+
+
+def _find_preset(spelling: str) -> Preset | None:
+    """A preset by its short name or by `family/short`; None if neither is known."""
+    _ensure_registered()
+    family, _, short = spelling.rpartition("/")
+    preset = PRESETS.get(short)
+    if preset is None or (family and family != preset.family):
+        return None
+    return preset
+
+
+def _preset(spelling: str) -> Preset:
+    preset = _find_preset(spelling)
+    if preset is None:
+        known = ", ".join(sorted(p.repo_id for p in PRESETS.values()))
+        raise ValueError(f"Unsupported model_name '{spelling}'. Available models: [{known}]")
+    return preset
+
+
+def _ordered(presets, newest_first: bool) -> list[Preset]:
+    presets = list(presets)
+    if newest_first:
+        presets.reverse()
+    return presets
 
 
 def resolve_model_name(model_name: str) -> str:
-    _ensure_registered()
-    if model_name in MODEL_REGISTRY:
-        return model_name
-    if "/" in model_name:
-        family, short_name = model_name.split("/", 1)
-        if short_name in MODEL_REGISTRY and MODEL_FAMILY_REGISTRY.get(short_name) == family:
-            return short_name
-    available = ", ".join(sorted(all_registered_repo_ids()))
-    raise ValueError(f"Unsupported model_name '{model_name}'. Available models: [{available}]")
+    """The short name of either spelling (engine/models/_registry.py:194-215 of the reference)."""
+    return _preset(model_name).name
 
 
 def model_is_registered(model_name: str) -> bool:
-    _ensure_registered()
-    if model_name in MODEL_REGISTRY:
-        return True
-    if "/" not in model_name:
-        return False
-    family, short_name = model_name.split("/", 1)
-    return short_name in MODEL_REGISTRY and MODEL_FAMILY_REGISTRY.get(short_name) == family
+    return _find_preset(model_name) is not None
 
 
 def get_model_family(model: str) -> str:
-    return MODEL_FAMILY_REGISTRY[resolve_model_name(model)]
+    return _preset(model).family
 
 
 def get_model_repo_id(model: str) -> str:
-    name = resolve_model_name(model)
-    return f"{MODEL_FAMILY_REGISTRY[name]}/{name}"
+    return _preset(model).repo_id
 
 
 def all_registered_models(newest_first: bool = True) -> list[str]:
     _ensure_registered()
-    models = list(MODEL_REGISTRY)
-    return models[::-1] if newest_first else models
+    return [p.name for p in _ordered(PRESETS.values(), newest_first)]
 
 
 def get_models_from_family(family: str, newest_first: bool = True) -> list[str]:
     _ensure_registered()
-    models = list(FAMILY_MODEL_REGISTRY.get(family, []))
-    return models[::-1] if newest_first else models
+    return [p.name for p in _ordered((p for p in PRESETS.values() if p.family == family), newest_first)]
 
 
 def all_registered_repo_ids(newest_first: bool = True) -> list[str]:
-    return [get_model_repo_id(name) for name in all_registered_models(newest_first)]
+    _ensure_registered()
+    return [p.repo_id for p in _ordered(PRESETS.values(), newest_first)]
+
+
+def registered_families() -> dict[str, list[Preset]]:
+    """family -> its presets, oldest first; families in alphabetical order."""
+    _ensure_registered()
+    out: dict[str, list[Preset]] = {}
+    for preset in sorted(PRESETS.values(), key=lambda p: p.family):
+        out.setdefault(preset.family, []).append(preset)
+    return out
 
 
 def get_preset_dict(model_name: str) -> dict[str, Any]:
     """The config.json content of a registered model name."""
-    with open(MODEL_REGISTRY[resolve_model_name(model_name)], "r", encoding="utf-8") as f:
+    with open(_preset(model_name).path, "r", encoding="utf-8") as f:
         return json.load(f)
 
 

@@ -50,20 +50,22 @@ class LLMEngine:
         self.overlap = bool(getattr(config, "overlap_steps", True))
         self._inflight = None
 
-    def _tokenize_prompt(self, prompt: str) -> list[int]:
+    def _token_ids(self, prompt: str | list[int]) -> list[int]:
+        """Token ids of a request: a list is taken as it is, text goes through the tokenizer."""
+        if not isinstance(prompt, str):
+            return list(prompt)
         if self.tokenizer is None:
             raise ValueError("a text prompt needs a tokenizer; pass token ids instead")
-        token_ids = self.tokenizer.encode(prompt, add_special_tokens=True)
-        if not isinstance(token_ids, list):
-            raise TypeError("Expected tokenizer.encode(...) to return list[int].")
-        return token_ids
+        ids = self.tokenizer.encode(prompt, add_special_tokens=True)
+        if not isinstance(ids, list):
+            raise TypeError(f"the tokenizer's encode() must return a list of ids, got {type(ids).__name__}")
+        return ids
 
     def is_finished(self) -> bool:
         return self.scheduler.is_finished() and self._inflight is None
 
     def add_request(self, prompt: str | list[int], sampling_params: SamplingParams) -> Sequence:
-        if isinstance(prompt, str):
-            prompt = self._tokenize_prompt(prompt)
+        prompt = self._token_ids(prompt)
         vocab = self.model_runner.vocab_size
         if any((t < 0 or t >= vocab) for t in prompt):
             raise ValueError(f"prompt holds a token id outside 0..{vocab - 1}")
@@ -123,38 +125,50 @@ class LLMEngine:
         num_total_tokens = sum(len(seq) for seq in finished)
         return outputs, num_total_tokens
 
+    def finished_requests(self):
+        """Runs steps until nothing is left; yields (request id, completion token ids) as requests end."""
+        while not self.is_finished():
+            outputs, _ = self.step()
+            yield from outputs
+
     def generate(
         self,
         prompts: Seq[str] | Seq[list[int]],
         sampling_params: SamplingParams | list[SamplingParams],
         use_tqdm: bool = True,
     ) -> list[list[int]]:
-        """Completions (token ids) in the order of the prompts."""
-        if not isinstance(sampling_params, list):
-            sampling_params = [sampling_params] * len(prompts)
-        if len(sampling_params) != len(prompts):
-            raise ValueError(
-                f"sampling_params length must match prompts length, got {len(sampling_params)} and {len(prompts)}.")
-        pbar = None
-        if use_tqdm:
-            from tqdm.auto import tqdm
+        """Completions (token ids) in the order of the prompts (engine/generation/llm_engine.py:67-114
+        of the reference: same arguments, same result)."""
+        per_prompt = sampling_params if isinstance(sampling_params, list) else [sampling_params] * len(prompts)
+        if len(per_prompt) != len(prompts):
+            raise ValueError(f"{len(prompts)} prompts but {len(per_prompt)} sampling_params: one per prompt, or one for all.")
+        order = [self.add_request(prompt, sp).seq_id for prompt, sp in zip(prompts, per_prompt)]
+        progress = _Progress(len(order)) if use_tqdm else None
+        completions: dict[int, list[int]] = {}
+        for seq_id, token_ids in self.finished_requests():
+            completions[seq_id] = token_ids
+            if progress is not None:
+                progress.request_done(len(token_ids))
+        if progress is not None:
+            progress.close()
+        return [completions[seq_id] for seq_id in order]
 
-            pbar = tqdm(total=len(prompts), desc="Generating", dynamic_ncols=True)
-        for prompt, sp in zip(prompts, sampling_params):
-            self.add_request(prompt, sp)
-        outputs: dict[int, list[int]] = {}
-        num_total_tokens = 0
-        t = time.perf_counter()
-        while not self.is_finished():
-            output, num_step_tokens = self.step()
-            num_total_tokens += num_step_tokens
-            if pbar is not None:
-                throughput = num_total_tokens / max(time.perf_counter() - t, 1e-9)
-                pbar.set_postfix({"total_throughput": f"{int(throughput)}tok/s"})
-            for seq_id, token_ids in output:
-                outputs[seq_id] = token_ids
-                if pbar is not None:
-                    pbar.update(1)
-        if pbar is not None:
-            pbar.close()
-        return [outputs[seq_id] for seq_id in sorted(outputs)]
+
+class _Progress:
+    """A tqdm bar over finished requests with the throughput of generated tokens so far."""
+
+    def __init__(self, total: int) -> None:
+        from tqdm.auto import tqdm
+
+        self.bar = tqdm(total=total, desc="Generating", dynamic_ncols=True)
+        self.started = time.perf_counter()
+        self.tokens = 0
+
+    def request_done(self, completion_tokens: int) -> None:
+        self.tokens += completion_tokens
+        rate = self.tokens / max(time.perf_counter() - self.started, 1e-9)
+        self.bar.set_postfix({"generated": f"{int(rate)}tok/s"})
+        self.bar.update(1)
+
+    def close(self) -> None:
+        self.bar.close()

@@ -57,89 +57,105 @@ class Scheduler:
             raise ValueError(
                 f"Prompt of {len(seq)} tokens exceeds max_num_batched_tokens={self.max_num_batched_tokens} "
                 "and chunked_prefill is off: it could never be scheduled.")
-        page = self.cache_manager.page_size
-        need = -(-(len(seq) + 1) // page)
-        for g, pool in enumerate(self.cache_manager.pools):
-            if self.cache_manager.groups[g].kind == "full" and need > pool.num_pages:
+        cm = self.cache_manager
+        # The most pages the request holds at once: all of them in a group that keeps every key;
+        # in a window group all of them too when the prompt comes in one portion (pages are given
+        # back between steps only), else the window plus the largest portion.
+        for g, pool in enumerate(cm.pools):
+            spec = cm.groups[g]
+            tokens = len(seq) + 1
+            if spec.kind == "window" and self.enable_chunked:
+                tokens = min(tokens, spec.window + self.max_num_batched_tokens + cm.page_size)
+            need = -(-tokens // cm.page_size)
+            if need > pool.num_pages:
                 raise ValueError(
-                    f"Prompt of {len(seq)} tokens needs {need} cache pages, the pool holds {pool.num_pages}: "
-                    "it could never be scheduled.")
+                    f"Prompt of {len(seq)} tokens needs {need} cache pages of group {g} ({spec.kind}), the pool holds "
+                    f"{pool.num_pages}: it could never be scheduled.")
         self.waiting.append(seq)
 
     # -- one step ---------------------------------------------------------------------
 
-    def schedule(self) -> list[Sequence]:
-        scheduled_running: list[Sequence] = []
-        scheduled_new: list[Sequence] = []
-        preempted: list[Sequence] = []
-        token_budget = self.max_num_batched_tokens
+    def _share(self, seq: Sequence, budget: int) -> int:
+        """How many of the tokens it has not cached yet `seq` runs in a step with `budget` left:
+        all of them, cut to the budget where portions are allowed, and never past the model's length."""
+        share = len(seq) - seq.num_cached_tokens
+        if self.enable_chunked:
+            share = min(share, budget)
+        return min(share, self.max_model_len - 1 - seq.num_cached_tokens)
+
+    def _reserve(self, seq: Sequence, share: int) -> bool:
+        """Pages for the next `share` tokens of a sequence that has a cache; False: not now."""
+        first = seq.num_cached_tokens
+        if not self.cache_manager.can_extend(seq.cache, first, first + share):
+            return False
+        self.cache_manager.extend(seq.cache, first, first + share)
+        seq.num_new_tokens = share
+        return True
+
+    def _continue_running(self, budget: int, step: list[Sequence]) -> tuple[int, bool]:
+        """Running requests in their order while the budget lasts.  One that finds no pages takes
+        them from the tail of the running list, request by request, itself last.  Returns the
+        budget left and whether anybody lost its place."""
+        evicted = False
+        place = 0
+        while place < len(self.running) and budget > 0:
+            seq = self.running[place]
+            share = self._share(seq, budget)
+            if share < 1:
+                raise RuntimeError(f"Running sequence {seq.seq_id} has nothing to compute (share {share}).")
+            while seq.status == SequenceStatus.RUNNING and not self._reserve(seq, share):
+                self.preempt(self.running[-1])
+                evicted = True
+            if seq.status != SequenceStatus.RUNNING:
+                break  # it gave up its own place; it was the last one
+            step.append(seq)
+            budget -= share
+            place += 1
+        return budget, evicted
+
+    def _admit_waiting(self, budget: int, step: list[Sequence]) -> None:
+        """Waiting requests, first come first served, while budget, slots and pages allow."""
         cm = self.cache_manager
+        while self.waiting and budget > 0 and len(self.running) < self.max_num_seqs:
+            seq = self.waiting[0]
+            if seq.cache is not None:
+                raise RuntimeError(f"Waiting sequence {seq.seq_id} still holds cache pages.")
+            share = self._share(seq, budget)
+            if share > budget:
+                return  # a whole prompt that does not fit what is left of this step
+            try:
+                seq.cache = cm.admit(seq.seq_id)
+            except OutOfSlots:
+                return
+            seq.num_cached_tokens = 0
+            if not self._reserve(seq, share):
+                cm.free(seq.cache)
+                seq.cache = None
+                return
+            self.waiting.popleft()
+            seq.status = SequenceStatus.RUNNING
+            self.running.append(seq)
+            step.append(seq)
+            budget -= share
 
-        index = 0
-        while index < len(self.running) and token_budget > 0:
-            seq = self.running[index]
-            num_new = len(seq) - seq.num_cached_tokens
-            if self.enable_chunked:
-                num_new = min(num_new, token_budget)
-            num_new = min(num_new, self.max_model_len - 1 - seq.num_cached_tokens)
-            if num_new <= 0:
-                raise RuntimeError(
-                    f"Expected a positive num_new_tokens for running sequence {seq.seq_id}, but got {num_new}.")
-            while True:
-                start = seq.num_cached_tokens
-                if cm.can_extend(seq.cache, start, start + num_new):
-                    seq.num_new_tokens = num_new
-                    cm.extend(seq.cache, start, start + num_new)
-                    break
-                victim = self.running.pop()
-                self.preempt(victim)
-                preempted.append(victim)
-                if len(self.running) == index:
-                    break
-            if len(self.running) == index:
-                break
-            scheduled_running.append(seq)
-            token_budget -= seq.num_new_tokens
-            index += 1
-
-        if not preempted:
-            while self.waiting and token_budget > 0 and len(self.running) < self.max_num_seqs:
-                seq = self.waiting[0]
-                if seq.cache is not None:
-                    raise RuntimeError(f"Waiting sequence {seq.seq_id} still holds cache pages.")
-                num_new = len(seq)
-                if self.enable_chunked:
-                    num_new = min(num_new, token_budget)
-                num_new = min(num_new, self.max_model_len - 1)
-                if num_new > token_budget:
-                    break
-                try:
-                    rc = cm.admit(seq.seq_id)
-                except OutOfSlots:
-                    break
-                if not cm.can_extend(rc, 0, num_new):
-                    cm.free(rc)
-                    break
-                cm.extend(rc, 0, num_new)
-                seq.cache = rc
-                seq.num_cached_tokens = 0
-                seq.num_new_tokens = num_new
-                token_budget -= num_new
-                seq.status = SequenceStatus.RUNNING
-                self.waiting.popleft()
-                self.running.append(seq)
-                scheduled_new.append(seq)
-
-        scheduled = scheduled_running + scheduled_new
-        if not scheduled:
+    def schedule(self) -> list[Sequence]:
+        """The sequences of the next step, each with `num_new_tokens` set and pages reserved."""
+        step: list[Sequence] = []
+        budget, evicted = self._continue_running(self.max_num_batched_tokens, step)
+        if not evicted:  # a step that took somebody's pages admits nobody
+            self._admit_waiting(budget, step)
+        if not step:
             raise RuntimeError(
-                "Scheduler.schedule produced an empty schedule: the next request alone needs more "
-                "cache pages (or a larger token budget) than the engine has.")
+                "empty schedule: the next request alone needs more cache pages (or a larger token "
+                "budget) than the engine has.")
         self.num_steps += 1
-        return scheduled
+        return step
 
     def preempt(self, seq: Sequence) -> None:
-        """Back to the front of the waiting queue; everything it cached is dropped."""
+        """Out of the running list and back to the front of the waiting queue; everything it
+        cached is dropped."""
+        if seq in self.running:
+            self.running.remove(seq)
         seq.status = SequenceStatus.WAITING
         self._release(seq)
         seq.num_preemptions += 1
@@ -153,28 +169,37 @@ class Scheduler:
         seq.num_cached_tokens = 0
         seq.num_new_tokens = 0
 
-    def postprocess(self, seqs: list[Sequence], token_ids: list[int], seq_need_compute_logits: list[int]) -> None:
-        if len(token_ids) != len(seq_need_compute_logits):
-            raise ValueError(
-                "token_ids and seq_need_compute_logits must have equal length, "
-                f"got {len(token_ids)} and {len(seq_need_compute_logits)}.")
-        for seq_index, token_id in zip(seq_need_compute_logits, token_ids):
-            seq = seqs[seq_index]
-            seq.append_token(token_id)
-            if (
-                (not seq.ignore_eos and token_id == self.eos)
-                or seq.num_completion_tokens == seq.max_tokens
-                or len(seq) >= self.max_model_len
-            ):
-                if len(seq) >= self.max_model_len:
-                    log.info("Sequence %s reached max_model_len %s.", seq.seq_id, self.max_model_len)
-                seq.status = SequenceStatus.FINISHED
-                self._release(seq)
-                self.running.remove(seq)
+    def _ends_by_count(self, seq: Sequence) -> bool:
+        """Ends that depend on lengths alone: the request's max_tokens, the model's length."""
+        if len(seq) >= self.max_model_len:
+            log.info("Sequence %s reached max_model_len %s.", seq.seq_id, self.max_model_len)
+            return True
+        return seq.num_completion_tokens == seq.max_tokens
+
+    def _finish(self, seq: Sequence) -> None:
+        seq.status = SequenceStatus.FINISHED
+        self._release(seq)
+        if seq in self.running:
+            self.running.remove(seq)
+
+    def _commit(self, seqs: list[Sequence]) -> None:
+        """What the step ran is cached now."""
         for seq in seqs:
             if seq.status != SequenceStatus.FINISHED:
                 seq.num_cached_tokens += seq.num_new_tokens
                 seq.num_new_tokens = 0
+
+    def postprocess(self, seqs: list[Sequence], token_ids: list[int], seq_need_compute_logits: list[int]) -> None:
+        """After a step: `token_ids[r]` was sampled for `seqs[seq_need_compute_logits[r]]`."""
+        if len(token_ids) != len(seq_need_compute_logits):
+            raise ValueError(
+                f"{len(token_ids)} sampled tokens for {len(seq_need_compute_logits)} sequences that asked for one.")
+        for row, which in enumerate(seq_need_compute_logits):
+            seq, token = seqs[which], token_ids[row]
+            seq.append_token(token)
+            if (token == self.eos and not seq.ignore_eos) or self._ends_by_count(seq):
+                self._finish(seq)
+        self._commit(seqs)
 
     # -- steps that overlap ------------------------------------------------------------------
     #
@@ -195,16 +220,9 @@ class Scheduler:
             seq.append_token(UNKNOWN_TOKEN)
             seq.unresolved += 1
             seq.sample_row = row
-            if seq.num_completion_tokens == seq.max_tokens or len(seq) >= self.max_model_len:
-                if len(seq) >= self.max_model_len:
-                    log.info("Sequence %s reached max_model_len %s.", seq.seq_id, self.max_model_len)
-                seq.status = SequenceStatus.FINISHED
-                self._release(seq)
-                self.running.remove(seq)
-        for seq in seqs:
-            if seq.status != SequenceStatus.FINISHED:
-                seq.num_cached_tokens += seq.num_new_tokens
-                seq.num_new_tokens = 0
+            if self._ends_by_count(seq):
+                self._finish(seq)
+        self._commit(seqs)
         return positions
 
     def resolve(self, seqs: list[Sequence], seq_need_compute_logits: list[int], positions: list[int],
@@ -245,3 +263,7 @@ class Scheduler:
             self.waiting.remove(seq)
         self._release(seq)
         seq.status = SequenceStatus.FINISHED
+        # nothing of it is reported any more: tokens still in flight for it are dropped
+        seq.ended_at = min(seq.ended_at, len(seq) - 1) if seq.ended_at >= 0 else seq.num_prompt_tokens - 1
+        seq.unresolved = 0
+        seq.reported = True
