@@ -244,7 +244,7 @@ def run_ours(args) -> dict:
     import torch
 
     from tokensprint_b200.config.registry import get_model_config, get_preset_dict
-    from tokensprint_b200.config.model_config import Qwen3Config
+    from tokensprint_b200.models.qwen3 import Qwen3Config
     from tokensprint_b200.engine.runner import ModelRunner
     from tokensprint_b200.models.api import random_model
 
@@ -336,7 +336,7 @@ def run_probe(args) -> int:
     import torch
 
     from tokensprint_b200 import ops
-    from tokensprint_b200.config.model_config import Qwen3Config
+    from tokensprint_b200.models.qwen3 import Qwen3Config
     from tokensprint_b200.config.registry import get_preset_dict
     from tokensprint_b200.engine.runner import ModelRunner, StepEntry
     from tokensprint_b200.models.api import random_model

@@ -20,7 +20,7 @@ import torch
 
 def embedding(table: torch.Tensor, ids: Sequence[int]) -> torch.Tensor:
     """h[t] = E[ids[t]]  (engine/model.py:65)."""
-    return table[torch.as_tensor(list(ids), dtype=torch.long)]
+    return table[torch.as_tensor(list(ids), dtype=torch.long, device=table.device)]
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -47,8 +47,8 @@ def apply_rope(x: torch.Tensor, angles: torch.Tensor) -> torch.Tensor:
     x'[j+d/2] = x[j+d/2] cos + x[j] sin  (engine/nn/rope.py:111-123;
     engine/kernels/triton/rope.py:53-62).  x: [T, heads, d]; angles: [T, d/2]."""
     half = x.shape[-1] // 2
-    cos = angles.to(x.dtype).cos()[:, None, :]
-    sin = angles.to(x.dtype).sin()[:, None, :]
+    cos = angles.to(x.device, x.dtype).cos()[:, None, :]
+    sin = angles.to(x.device, x.dtype).sin()[:, None, :]
     re, im = x[..., :half], x[..., half:]
     return torch.cat([re * cos - im * sin, im * cos + re * sin], dim=-1)
 
@@ -66,7 +66,7 @@ def causal_attention(
     nkv = k.shape[1]
     group = nq // nkv
     out = torch.empty_like(q)
-    t_idx = torch.arange(T)
+    t_idx = torch.arange(T, device=q.device)
     visible = t_idx[None, :] <= t_idx[:, None]
     if window is not None and window > 0:
         visible &= t_idx[None, :] > (t_idx[:, None] - window)
@@ -146,9 +146,21 @@ def layer_windows(cfg: Mapping) -> list[Optional[int]]:
     return [cfg["sliding_window"] if t == "sliding_attention" else None for t in types]
 
 
+class _Converted:
+    """The weights in the run's dtype and on its device, converted when asked for (and not kept:
+    a model of many layers is never held twice)."""
+
+    def __init__(self, weights: Mapping[str, torch.Tensor], dtype: torch.dtype, device, rounding) -> None:
+        self.weights, self.dtype, self.device, self.rounding = weights, dtype, device, rounding
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        v = self.weights[name].to(device=self.device, dtype=self.dtype)
+        return v if v.dim() == 1 or self.rounding is None else self.rounding(v)
+
+
 def forward_logits(
     weights: Mapping[str, torch.Tensor], cfg: Mapping, token_ids: Sequence[int], dtype: torch.dtype = torch.float64,
-    rounding=None,
+    rounding=None, device=None,
 ) -> torch.Tensor:
     """Logits [T, V] of one whole sequence: embedding, blocks, final norm, head (tied: the
     embedding table)  (engine/model.py:58-95, engine/nn/layers.py:22-23).
@@ -156,9 +168,12 @@ def forward_logits(
     `rounding` (a function tensor -> tensor) is applied to every matrix weight and to every
     activation that one operation hands to the next, the residual stream excepted.  With
     `round_to_bfloat16` this shows how far 8-bit mantissas alone move the logits of a given
-    model and input: the yardstick for a bfloat16 engine's tolerance."""
+    model and input: the yardstick for a bfloat16 engine's tolerance.
+
+    `device`: where the arithmetic runs (default: the CPU).  The same functions, the same dtype;
+    a model of full width is merely done sooner on a GPU."""
     r = rounding or (lambda t: t)
-    w = {k: (v.to(dtype) if v.dim() == 1 else r(v.to(dtype))) for k, v in weights.items()}
+    w = _Converted(weights, dtype, device, rounding)
     positions = list(range(len(token_ids)))
     h = embedding(w["model.embed_tokens.weight"], token_ids)
     for i, window in enumerate(layer_windows(cfg)):

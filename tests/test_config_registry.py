@@ -7,7 +7,8 @@ import pytest
 from tests.tiny_configs import TINY_A, TINY_B, TINY_C
 from tokensprint_b200.config import registry
 from tokensprint_b200.config.engine_config import Config, SamplingParams, canonical_dtype
-from tokensprint_b200.config.model_config import ConfigError, Qwen3Config
+from tokensprint_b200.config.model_config import ConfigError
+from tokensprint_b200.models.qwen3 import Qwen3Config
 
 
 def test_config_reads_every_size_from_its_keys():

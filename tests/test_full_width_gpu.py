@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 def folder(request, tmp_path_factory):
     """8B: four query heads per KV head; 32B: eight, width 5120, intermediate 25600; 0.6B: two,
     width 1024 with heads of 128 (heads * head size is twice the width) and a tied head."""
-    from tokensprint_b200.config.model_config import Qwen3Config
+    from tokensprint_b200.models.qwen3 import Qwen3Config
     from tokensprint_b200.config.registry import get_preset_dict
     from tokensprint_b200.weights.loader import write_random_model
 
@@ -94,7 +94,7 @@ def test_many_sequences_decode_through_the_even_share_kernel(tmp_path):
     even-share decode kernel, in a graph whose batch bucket has lanes without a sequence.  bfloat16
     against the float32 path, the same trace."""
     from tokensprint_b200 import ops
-    from tokensprint_b200.config.model_config import Qwen3Config
+    from tokensprint_b200.models.qwen3 import Qwen3Config
     from tokensprint_b200.config.registry import get_preset_dict
     from tokensprint_b200.engine.replay import TraceReplayer
     from tokensprint_b200.engine.runner import ModelRunner

@@ -817,3 +817,27 @@ def test_feed_tokens():
     assert ids.tolist() == want
     with pytest.raises(ops.KernelError, match="index arrays hold"):
         ops.feed_tokens(ids, source, lanes, rows, 7)
+
+
+def test_a_wait_that_runs_out_becomes_an_exception_and_the_next_launch_is_clean():
+    """The give-up path of the bounded waits: a kernel whose only wait is on an mbarrier that
+    nothing feeds runs out of tries (a few thousand), raises the error word as the tcgen05 kernels
+    do and returns; the host turns the word into a KernelError, clears it, and the stream goes on
+    working.  Nothing faults, traps or hangs."""
+    from tokensprint_b200 import ops
+
+    torch.cuda.synchronize()
+    ops.check_device_errors()  # nothing pending
+    ops.wait_gives_up_probe(torch.device(DEV), limit=4096)
+    torch.cuda.synchronize()
+    with pytest.raises(ops.KernelError, match="gave up"):
+        ops.check_device_errors()
+    ops.check_device_errors()  # the word was cleared
+    x = torch.randn(8, 256, device=DEV).to(torch.bfloat16)
+    w = torch.randn(384, 256, device=DEV).to(torch.bfloat16)
+    out = torch.empty(8, 384, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_skinny_bf16(x, w, out)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    want = x.float() @ w.float().T
+    assert float((out.float() - want).abs().max()) <= 2e-2 * float(want.abs().max())

@@ -290,7 +290,7 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
 def test_run_order_is_data_a_layer_twice_and_a_shared_cache(tmp_path):
     """Run order: layer 0, layer 1, layer 0 again (own cache), layer 2 reading layer 1's cache."""
     from tests.tiny_configs import TINY_B, tiny_weights, write_model_folder
-    from tokensprint_b200.config.model_config import Qwen3Config
+    from tokensprint_b200.models.qwen3 import Qwen3Config
     from tokensprint_b200.engine.replay import TraceReplayer
     from tokensprint_b200.engine.runner import ModelRunner
     from tokensprint_b200.models.model import Model

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from tests.tiny_configs import TINY_A, TINY_B, tensor_shapes, tiny_weights, write_model_folder
-from tokensprint_b200.config.model_config import Qwen3Config
+from tokensprint_b200.models.qwen3 import Qwen3Config
 from tokensprint_b200.models.qwen3 import build_qwen3_spec
 from tokensprint_b200.weights.loader import (
     FolderSource,

@@ -1,12 +1,17 @@
 """The allocation-free entry point of the attention library, called through its exported C symbol.
 
 `ts_attention_paged_mma_noalloc` is for callers that cannot allocate device memory (a host
-program without torch's allocator, code inside a stream capture, a loop that must stay off
-the allocator's locks): the scratch of the split-key decode path lives in the library itself.
-The test calls the symbol with ctypes, twice in a row with different batches, and compares
-each result with the entry point that takes scratch from the caller; it also checks that a
-batch beyond the built-in scratch is refused with its own error code.  This file is collected
-last on purpose: it must pass alone in a fresh process and after every other test.
+program that embeds the kernel without torch's allocator, a process whose memory has been
+handed out in full to other pools, a loop that must stay off the allocator's locks): the
+scratch of the split-key decode path lives in the library itself.  The test calls the
+symbol with ctypes, twice in a row, a large batch with many key splits and then a small one
+with few, so that partial results of another shape lie in the shared array when the second
+call runs.  Both calls are made so that the partial results really pass through the array
+(the merge inside a thread-block cluster is switched off for one pair of calls, and another
+pair uses more splits than a cluster takes); each result is compared with the plain
+attention of tests/plain and with the entry point that takes scratch from the caller.  A
+batch beyond the built-in scratch must be refused with its own error code.  This file is
+collected last on purpose: it must pass alone in a fresh process and after every other test.
 """
 
 import ctypes
@@ -78,20 +83,58 @@ def _call(lib, case, splits, noalloc):
     return status, out
 
 
-def test_noalloc_entry_point_matches_the_one_with_caller_scratch_twice_in_a_row():
-    lib = _library()
-    assert lib.ts_attention_noalloc_scratch_floats() == 2 * 1024 * 1024
-    # two calls in a row; the second is smaller and has fewer splits, so anything stale that
-    # the first call left in the shared array would show if it were read
-    for contexts, nq, nkv, splits, seed in [([700, 64, 65, 1, 333, 129], 8, 2, 6, 1), ([90, 257], 4, 4, 3, 2)]:
+def _plain(case):
+    """Float64 attention of the batch's single query per sequence over all its keys."""
+    from tests.plain import qwen3_plain as plain
+
+    kc, vc = case["kc"].double().cpu(), case["vc"].double().cpu()
+    table, ctx = case["table"].cpu(), case["ctx"].cpu().tolist()
+    page, nq, nkv = case["page"], case["nq"], case["nkv"]
+    rows = []
+    for b, n in enumerate(ctx):
+        pages = table[b, : -(-n // page)].long()
+        k = kc[pages].reshape(-1, nkv, HEAD_DIM)[:n]
+        v = vc[pages].reshape(-1, nkv, HEAD_DIM)[:n]
+        q = torch.zeros(n, nq, HEAD_DIM, dtype=torch.float64)
+        q[-1] = case["q"][b].double().cpu().view(nq, HEAD_DIM)
+        rows.append(plain.causal_attention(q, k, v, scale=HEAD_DIM ** -0.5)[-1].reshape(-1))
+    return torch.stack(rows)
+
+
+# (contexts, query heads, KV heads, key splits, seed): the larger call first
+PAIR_FEW_SPLITS = [([700, 64, 65, 1, 333, 129], 8, 2, 6, 1), ([90, 257], 4, 4, 3, 2)]
+PAIR_MANY_SPLITS = [([900, 640, 65, 1, 777, 129, 1000], 8, 2, 12, 3), ([600, 257], 4, 4, 9, 4)]
+
+
+def _check_pair(lib, pair):
+    for contexts, nq, nkv, splits, seed in pair:
         case = _batch(contexts, nq, nkv, 16, seed)
         status, got = _call(lib, case, splits, noalloc=True)
         assert status == 0, lib.ts_attention_noalloc_error_text(status).decode()
-        status, want = _call(lib, case, splits, noalloc=False)
-        assert status == 0
         assert torch.isfinite(got.float()).all()
-        err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
+        want = _plain(case)
+        err = float((got.double().cpu() - want).abs().max() / want.abs().max())
+        assert err < 1e-2, f"no-alloc entry point differs from the plain attention by {err} ({splits} splits)"
+        status, other = _call(lib, case, splits, noalloc=False)
+        assert status == 0
+        err = float((got.float() - other.float()).abs().max() / other.float().abs().max())
         assert err < 1e-2, f"no-alloc entry point differs from the caller-scratch one by {err}"
+    return case
+
+
+def test_noalloc_entry_point_matches_plain_attention_twice_in_a_row():
+    lib = _library()
+    assert lib.ts_attention_noalloc_scratch_floats() == 2 * 1024 * 1024
+    lib.ts_attention_mma_set_cluster_merge.argtypes = [ctypes.c_int]
+    before = lib.ts_attention_mma_cluster_merge()
+    try:
+        # 2..8 splits would merge inside a cluster and never touch the array: switch that off
+        lib.ts_attention_mma_set_cluster_merge(0)
+        _check_pair(lib, PAIR_FEW_SPLITS)
+    finally:
+        lib.ts_attention_mma_set_cluster_merge(before)
+    # more splits than a cluster takes: through the array whatever the switch says
+    case = _check_pair(lib, PAIR_MANY_SPLITS)
     # without key splits no scratch is touched at all
     status, got = _call(lib, case, 1, noalloc=True)
     status2, want = _call(lib, case, 1, noalloc=False)

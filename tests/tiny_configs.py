@@ -3,7 +3,8 @@
 The configurations differ in every size and option: head counts and groups, head_dim
 against the width, sizes that are no power of two, number of layers, vocabulary, the
 norms' eps, rope_theta, tied or untied head, and (TINY_C) sliding-window layers.
-Weights are drawn here, by the tests' own generator, under the checkpoint's tensor names
+Weights are drawn here, by the tests' own generator (plain integer hashing, the same values
+under every torch version), under the checkpoint's tensor names
 (engine/models/qwen/_checkpoint.py:9-24 of the reference lists them).
 """
 
@@ -102,6 +103,31 @@ def tensor_shapes(cfg: dict) -> dict[str, tuple[int, ...]]:
     return shapes
 
 
+def seeded_normal(shape: tuple[int, ...], key: str) -> torch.Tensor:
+    """Float32 values of about unit variance that depend on `key` and nothing else: not on the
+    torch or numpy version, the platform or the device.  Element i is the sum of twelve uniform
+    numbers (21-bit pieces of four splitmix64 hashes of (key, i)) minus six; every step is integer
+    arithmetic or exact in float64, so stored results made from these weights stay valid."""
+    import numpy as np
+
+    n = 1
+    for s in shape:
+        n *= int(s)
+    base = np.uint64(int.from_bytes(hashlib.sha256(key.encode()).digest()[:8], "little"))
+    total = np.zeros(n, dtype=np.uint64)
+    index = np.arange(n, dtype=np.uint64)
+    with np.errstate(over="ignore"):
+        for draw in range(4):
+            z = base + (index * np.uint64(4) + np.uint64(draw + 1)) * np.uint64(0x9E3779B97F4A7C15)
+            z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+            z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+            z = z ^ (z >> np.uint64(31))
+            for piece in range(3):
+                total += (z >> np.uint64(21 * piece)) & np.uint64((1 << 21) - 1)
+    values = (total.astype(np.float64) + 6.0) / float(1 << 21) - 6.0
+    return torch.from_numpy(values.astype(np.float32)).reshape(shape)
+
+
 def tiny_weights(cfg: dict, seed: int, *, std: float = 0.02, norm_std: float = 0.05, sharp: float = 1.0) -> dict[str, torch.Tensor]:
     """Float32 weights: matrices N(0, std), norm weights 1 + N(0, norm_std).
 
@@ -111,9 +137,7 @@ def tiny_weights(cfg: dict, seed: int, *, std: float = 0.02, norm_std: float = 0
     """
     out: dict[str, torch.Tensor] = {}
     for name, shape in tensor_shapes(cfg).items():
-        digest = hashlib.sha256(f"tiny:{seed}:{name}".encode()).digest()
-        g = torch.Generator().manual_seed(int.from_bytes(digest[:7], "little"))
-        x = torch.randn(shape, generator=g, dtype=torch.float32)
+        x = seeded_normal(shape, f"tiny:{seed}:{name}")
         if len(shape) == 1:
             x = 1.0 + norm_std * x
             if name.endswith("q_norm.weight") or name.endswith("k_norm.weight"):

@@ -28,16 +28,13 @@ def groups_of(needs: Sequence[CacheNeed]) -> tuple[list[GroupSpec], list[int]]:
 
 def page_bytes(needs: Sequence[CacheNeed], group_index: Sequence[int], group: int, page_size: int, itemsize: int) -> int:
     """Bytes one page of `group` costs over all caches of the group (keys and values)."""
-    return sum(
-        2 * page_size * n.kv_heads * n.head_dim * itemsize
-        for n, g in zip(needs, group_index)
-        if g == group
-    )
+    return sum(page_size * n.token_elements * itemsize for n, g in zip(needs, group_index) if g == group)
 
 
 @dataclass
 class CacheTensors:
-    """K and V pools [pages, page_size, kv_heads, head_dim] and state [slots, ...] per cache."""
+    """Per cache: the pools [pages, page_size, *k_row] and [pages, page_size, *v_row] (the second
+    may be absent or of another row shape) and the state [slots, ...]."""
 
     k: list[Optional[torch.Tensor]]
     v: list[Optional[torch.Tensor]]
@@ -58,9 +55,9 @@ class CacheTensors:
         k, v, state = [], [], []
         for need, g in zip(needs, group_index):
             if g >= 0:
-                shape = (pages_per_group[g], page_size, need.kv_heads, need.head_dim)
-                k.append(torch.zeros(shape, device=device, dtype=dtype))
-                v.append(torch.zeros(shape, device=device, dtype=dtype))
+                k.append(torch.zeros((pages_per_group[g], page_size, *need.k_row), device=device, dtype=dtype))
+                v.append(None if need.v_row is None else
+                         torch.zeros((pages_per_group[g], page_size, *need.v_row), device=device, dtype=dtype))
             else:
                 k.append(None)
                 v.append(None)
@@ -88,8 +85,11 @@ class CacheTensors:
         """Debug aid: NaN into pages that were given back, so a stale read shows."""
         if not pages:
             return
-        idx = torch.tensor(list(pages), device=self.k[0].device if self.k[0] is not None else None, dtype=torch.long)
+        idx = None
         for c, g in enumerate(self.group_index):
             if g == group and self.k[c] is not None:
+                if idx is None:
+                    idx = torch.tensor(list(pages), device=self.k[c].device, dtype=torch.long)
                 self.k[c][idx] = float("nan")
-                self.v[c][idx] = float("nan")
+                if self.v[c] is not None:
+                    self.v[c][idx] = float("nan")

@@ -130,8 +130,8 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // Bounded wait for a phase of an mbarrier.  False: gave up (or another role already did).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t limit = SPIN_LIMIT) {
+  for (uint32_t i = 0; i < limit; ++i) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -617,6 +617,23 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
   }
 }
 
+// The give-up path of the bounded waits, alone: one CTA waits, with a small limit, on an mbarrier
+// that nothing feeds, and then does what the GEMM's CTAs do when a wait ran out: it records the
+// fact in the error word and returns.  Nothing traps, nothing hangs; the context stays usable.
+__global__ void wait_gives_up_kernel(int* error, uint32_t limit) {
+  __shared__ __align__(8) uint64_t nobody_arrives;
+  __shared__ int abort_s;
+  if (threadIdx.x == 0) {
+    abort_s = 0;
+    mbar_init(smem_u32(&nobody_arrives), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(smem_u32(&nobody_arrives), 0, &abort_s, limit);
+  __syncthreads();
+  if (abort_s != 0 && threadIdx.x == 0) *error = 1;
+}
+
 // ---------------------------------------------------------------------------
 // host side: tensor maps (cached) and launch
 
@@ -736,6 +753,14 @@ TS_EXPORT long long ts_gemm_skinny_scratch_floats(int M, int N, int K) {
 }
 
 TS_EXPORT int ts_gemm_skinny_max_rows() { return 128; }
+
+// For tests of the error path: a kernel whose one bounded wait (at most `limit` tries, capped at
+// 65536) runs out by construction and sets `error` as the GEMM does.  It faults and hangs nothing.
+TS_EXPORT int ts_wait_gives_up_probe(int* error, int limit, void* stream_) {
+  if (error == nullptr || limit < 1) return TS_ERR_BAD_ARGUMENT;
+  if (limit > 65536) limit = 65536;
+  return ts_launch(wait_gives_up_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream_, error, (uint32_t)limit);
+}
 
 // out[M, ldo] (bf16, or f32 when out_f32) = x[M, K] (row stride ldx) * w[N, K]^T (row stride ldw).
 // `partial`: ts_gemm_skinny_scratch_floats(M, N, K) floats.  `counters`: ints, one per 128-row

@@ -1716,6 +1716,14 @@ static int ts_attention_cluster_merge = 1;
 TS_EXPORT void ts_attention_mma_set_cluster_merge(int on) { ts_attention_cluster_merge = on ? 1 : 0; }
 TS_EXPORT int ts_attention_mma_cluster_merge(void) { return ts_attention_cluster_merge; }
 
+// What the Python side plans with: CTAs of the decode kernel that run at once, the most query
+// rows (tokens x heads of a group) a sequence may bring to be served by the decode kernels, and
+// how many kernels the last call of ts_attention_paged_mma_fused launched (1, or 2 with the merge).
+TS_EXPORT long long ts_attention_mma_decode_slots(void) { return decode_slots(); }
+TS_EXPORT int ts_attention_mma_decode_rows(void) { return 16; }
+static int ts_attention_last_launches = 0;
+TS_EXPORT int ts_attention_mma_last_launches(void) { return ts_attention_last_launches; }
+
 TS_EXPORT int ts_attention_paged_mma_fused(const void* q, const void* kcache, const void* vcache, void* out,
                                            float* scratch, const int* cu_q, const int* ctx_len,
                                            const int* block_table, const int* seq_index, int max_blocks,
@@ -1770,8 +1778,10 @@ TS_EXPORT int ts_attention_paged_mma_fused(const void* q, const void* kcache, co
       status = launch<8, false>(p, B, stream);
   }
   if (status != 0) return status;
+  ts_attention_last_launches = 1;
   if (splits > 1 && p.counters == nullptr && !p.cluster) {
     const int total = T * nq;
+    ts_attention_last_launches = 2;
     status = ts_launch(attention_combine_kernel, dim3((total + 3) / 4), dim3(128), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, seq_index, total, nq, splits);
   }
   return status;

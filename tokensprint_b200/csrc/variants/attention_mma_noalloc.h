@@ -3,14 +3,13 @@
 // This entry point has no counterpart in the reference (mirceamironenco/tokensprint): it
 // exists for callers of this library that cannot allocate device memory.
 //
-// Who they are.  A host program that embeds the attention kernel without torch, or any
-// caller sitting inside a region where cudaMalloc is not allowed or not wanted: between
-// the begin and end of a stream capture, inside a latency-critical loop that must not
-// touch the allocator's locks, or in a process whose memory has been handed out in full
-// to other pools.  The split-key decode path of ts_attention_paged_mma needs scratch
-// memory for the partial results of the key splits, and there the caller has to bring
-// it.  ts_attention_paged_mma_noalloc brings its own: a file-scope device array inside
-// the library.
+// Who they are.  A host program that embeds the attention kernel without torch and has
+// no allocator of its own, a latency-critical loop that must not touch the allocator's
+// locks, or a process whose device memory has been handed out in full to other pools, so
+// that a cudaMalloc at this point would fail.  The split-key decode path of
+// ts_attention_paged_mma needs scratch memory for the partial results of the key splits,
+// and there the caller has to bring it.  ts_attention_paged_mma_noalloc brings its own:
+// a file-scope device array inside the library.
 //
 // The limit.  The array holds TS_ATTENTION_NOALLOC_SCRATCH_FLOATS float32 values (8 MiB).
 // Every GPU on which this library is loaded holds that array from load until the

@@ -22,12 +22,25 @@ from typing import IO, Any, Optional
 import numpy as np
 import torch
 
+from tokensprint_b200 import ops
 from tokensprint_b200.cache.manager import RequestCache
 from tokensprint_b200.engine.runner import ModelRunner, StepEntry
 from tokensprint_b200.models.api import load_model
 
+# Defaults of the command line; every one of them is an option.
 PAGE_SIZE = 16
 MAX_LIVE_REQUESTS = 16
+TOKEN_ROUNDING = 64  # --max-tokens counts each live request rounded up to a multiple of this
+
+
+def pages_for(max_tokens: int, page_size: int, max_live: int) -> int:
+    """Pages that hold `max_tokens` tokens of live requests, each request's count rounded up to
+    TOKEN_ROUNDING: exactly max_tokens / page_size when pages divide that rounding; larger pages
+    round every live request up to a page of their own, so one page more per request."""
+    pages = -(-max(max_tokens, 1) // page_size)
+    if TOKEN_ROUNDING % page_size:
+        pages += max_live
+    return pages
 
 
 class TraceError(ValueError):
@@ -45,11 +58,17 @@ class TraceReplayer:
 
     @classmethod
     def from_folder(cls, model_dir: str | Path, dtype: str, max_tokens: int, out_dir: Optional[str | Path] = None,
-                    device: str = "cuda", page_size: int = PAGE_SIZE) -> "TraceReplayer":
-        model, _ = load_model(model_dir, device=device, dtype=dtype)
-        pages = max(1, -(-max_tokens // page_size))
-        runner = ModelRunner(model, page_size=page_size, num_pages=pages, num_slots=MAX_LIVE_REQUESTS,
-                             max_num_batched_tokens=max(max_tokens, 1))
+                    device: str = "cuda", page_size: int = PAGE_SIZE, num_pages: Optional[int] = None,
+                    max_live: int = MAX_LIVE_REQUESTS, graphs: bool = False, max_model_len: Optional[int] = None) -> "TraceReplayer":
+        """A replayer for a model folder.  The pool holds `num_pages` pages per cache group, or,
+        when that is None, what `max_tokens` tokens of live requests need (see pages_for).  With
+        `graphs`, steps of single tokens replay CUDA graphs as generation does (bfloat16 models
+        whose parts allow it); `max_model_len` bounds the positions such a graph serves."""
+        model, config = load_model(model_dir, device=device, dtype=dtype)
+        pages = num_pages if num_pages is not None else pages_for(max_tokens, page_size, max_live)
+        longest = max_model_len or min(int(getattr(config, "max_position_embeddings", 0) or pages * page_size), pages * page_size)
+        runner = ModelRunner(model, page_size=page_size, num_pages=pages, num_slots=max_live,
+                             max_num_batched_tokens=max(max_tokens, 1), enforce_eager=not graphs, max_model_len=longest)
         return cls(runner, out_dir)
 
     def run_step(self, record: dict[str, Any]) -> Optional[np.ndarray]:
@@ -83,6 +102,7 @@ class TraceReplayer:
                     result.tofile(self.out_dir / f"{record['step']}.f32")
             else:
                 torch.cuda.synchronize(self.runner.device)
+            ops.check_device_errors()  # the copy back (or the synchronize) has just waited for the step
         for rid in record.get("end", []) or []:
             rid = str(rid)
             rc = self.live.pop(rid, None)
@@ -113,11 +133,21 @@ def main(argv: Optional[list[str]] = None) -> int:
     p.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     p.add_argument("--out", required=True, help="folder for <step>.f32 files")
     p.add_argument("--max-tokens", type=int, required=True,
-                   help="most tokens live requests hold at any time (each rounded up to 64); sizes the cache pool")
+                   help=f"most tokens live requests hold at any time, each request's count rounded up to a multiple of "
+                        f"{TOKEN_ROUNDING} (to whole pages where pages are larger); sizes the cache pool")
+    p.add_argument("--page-size", type=int, default=PAGE_SIZE, help=f"tokens per cache page (default {PAGE_SIZE})")
+    p.add_argument("--num-pages", type=int, default=None, help="pages per cache group (default: what --max-tokens needs)")
+    p.add_argument("--max-live", type=int, default=MAX_LIVE_REQUESTS, help=f"most requests live at a time (default {MAX_LIVE_REQUESTS})")
+    p.add_argument("--graphs", action="store_true", help="steps of single tokens replay CUDA graphs, as generation does")
+    p.add_argument("--max-model-len", type=int, default=None, help="longest request a captured graph serves (default: what the pool holds)")
     args = p.parse_args(argv)
+    if args.page_size < 1 or args.max_live < 1 or (args.num_pages is not None and args.num_pages < 1):
+        p.error("--page-size, --max-live and --num-pages must be positive")
     if not torch.cuda.is_available():
         print("trace_run: no CUDA device is visible; this engine has no CPU path", file=sys.stderr)
         return 1
-    replayer = TraceReplayer.from_folder(args.model, args.dtype, args.max_tokens, args.out)
+    replayer = TraceReplayer.from_folder(args.model, args.dtype, args.max_tokens, args.out, page_size=args.page_size,
+                                         num_pages=args.num_pages, max_live=args.max_live, graphs=args.graphs,
+                                         max_model_len=args.max_model_len)
     replayer.run_stream(sys.stdin)
     return 0

@@ -120,22 +120,7 @@ class ModelRunner:
         self.groups, self.cache_group = groups_of(needs)
         itemsize = torch.empty((), dtype=model.dtype).element_size()
         self.page_bytes = [page_bytes(needs, self.cache_group, g, page_size, itemsize) for g in range(len(self.groups))]
-        if num_pages is None:
-            pages = self._pages_from_free_memory(gpu_memory_utilization)
-        elif isinstance(num_pages, int):
-            pages = [num_pages] * len(self.groups)
-        else:
-            pages = list(num_pages)
-        if len(pages) != len(self.groups) or any(p < 1 for p in pages):
-            raise ValueError(f"need one positive page count per cache group ({len(self.groups)}), got {pages}")
-        self.num_pages = pages
-        self.cache_manager = CacheManager(self.groups, page_size, pages, num_slots)
-        self.cache_tensors = CacheTensors.allocate(
-            needs, self.cache_group, pages, page_size, num_slots, self.device, model.dtype)
-        self.layer_caches = [
-            self.cache_tensors.layer_cache(model.run_cache[i], run.writes_cache)
-            for i, run in enumerate(model.spec.run_order)
-        ]
+        self._needs = needs
         self._pinned: list[torch.Tensor] = []
         self._pinned_events: list[Optional[torch.cuda.Event]] = []
         self._pinned_next = 0
@@ -150,26 +135,82 @@ class ModelRunner:
                               if b <= max(1, min(max_graph_batch, num_slots))]
         self._graphs: dict[int, "_DecodeGraph"] = {}
         self._graph_pool = None
+        self._capture_stream: Optional[torch.cuda.Stream] = None
         self.graph_launches = 0  # kernels of this library replayed inside graphs so far
+        self.sizing: Optional[dict] = None  # how the page count was derived, when it came from free memory
+
+        if num_pages is None:
+            pages = self._pages_from_free_memory(gpu_memory_utilization)
+        elif isinstance(num_pages, int):
+            pages = [num_pages] * len(self.groups)
+        else:
+            pages = list(num_pages)
+        if len(pages) != len(self.groups) or any(p < 1 for p in pages):
+            raise ValueError(f"need one positive page count per cache group ({len(self.groups)}), got {pages}")
+        self._bind_cache(pages)
+
+    def _bind_cache(self, pages: Sequence[int]) -> None:
+        """A cache manager and device pools of `pages` pages per group, bound to the model's runs."""
+        self.num_pages = list(pages)
+        self.cache_manager = CacheManager(self.groups, self.page_size, self.num_pages, self.num_slots)
+        self.cache_tensors = CacheTensors.allocate(
+            self._needs, self.cache_group, self.num_pages, self.page_size, self.num_slots, self.device, self.model.dtype)
+        self.layer_caches = [
+            self.cache_tensors.layer_cache(self.model.run_cache[i], run.writes_cache)
+            for i, run in enumerate(self.model.spec.run_order)
+        ]
 
     # -- sizing ---------------------------------------------------------------------
 
     def _pages_from_free_memory(self, utilization: float) -> list[int]:
-        """Pages from what is free on the device (engine/generation/model_runner.py:392-411),
-        less an allowance for the activations of the largest step."""
-        free, _ = torch.cuda.mem_get_info(self.device)
-        spec = self.model.spec
-        widest = 0
-        for entry in self.model.cache_plan:
-            widest = max(widest, entry.need.kv_heads * entry.need.head_dim)
-        act = self.max_num_batched_tokens * (24 * spec.hidden_size + 64 * widest) * 4
-        act += 2 * self.num_slots * spec.vocab_size * 4 + (1 << 30)
-        budget = int(free * utilization) - act
+        """Pages from what is free on the device once the largest step has run.
+
+        The reference sizes its cache from free memory less the peak of a warm-up run
+        (engine/generation/model_runner.py:392-411).  Here the peak is measured the same way: a
+        step of `max_num_batched_tokens` tokens runs once against a throw-away pool just large
+        enough for it, torch's peak statistics give what its activations need, and the pool gets
+        `utilization` of what is free afterwards less that peak and less what the decode graphs
+        will hold (their static logits).  All groups get the same number of pages."""
+        P = self.page_size
+        tokens = max(1, self.max_num_batched_tokens)
+        per_request = max(1, min(tokens, self.max_model_len - 1))
+        lengths = [per_request] * (tokens // per_request) + ([tokens % per_request] if tokens % per_request else [])
+        lengths = lengths[: self.num_slots]
+        probe_pages = sum(-(-n // P) for n in lengths) + 1
+        self._bind_cache([probe_pages] * len(self.groups))
+        torch.cuda.synchronize(self.device)
+        torch.cuda.reset_peak_memory_stats(self.device)
+        before = torch.cuda.memory_allocated(self.device)
+        entries = []
+        for i, n in enumerate(lengths):
+            rc = self.cache_manager.admit(("sizing", i))
+            self.cache_manager.extend(rc, 0, n)
+            entries.append(StepEntry(rc, [0] * n, 0, [n - 1]))
+        graphs, self.use_graphs = self.use_graphs, False
+        self.step(entries)
+        self.use_graphs = graphs
+        torch.cuda.synchronize(self.device)
+        peak = torch.cuda.max_memory_allocated(self.device) - before
+        self.steps_run = 0
+        self.h2d_bytes = 0
+        del entries
+        self.cache_manager = self.cache_tensors = self.layer_caches = None
+        torch.cuda.empty_cache()
+        free, total = torch.cuda.mem_get_info(self.device)
+        graph_reserve = 0
+        if self.use_graphs:  # every bucket keeps its logits [bucket, vocab] float32, and a little beside
+            graph_reserve = int(sum(self.graph_buckets) * self.vocab_size * 4 * 1.25)
+        margin = 256 << 20
+        budget = int(free * utilization) - peak - graph_reserve - margin
         per_page = sum(self.page_bytes)
         n = budget // max(per_page, 1)
+        self.sizing = {"free_bytes": int(free), "total_bytes": int(total), "utilization": utilization,
+                       "step_tokens": sum(lengths), "step_peak_bytes": int(peak), "graph_reserve_bytes": graph_reserve,
+                       "margin_bytes": margin, "bytes_per_page": int(per_page), "pages": int(n)}
         if n < 1:
             raise RuntimeError(
-                f"Insufficient GPU memory for the cache: {budget} bytes after activations, {per_page} bytes per page")
+                f"Insufficient GPU memory for the cache: {budget} bytes are left after a step of {sum(lengths)} tokens "
+                f"({peak} bytes) and the graphs' reserve ({graph_reserve}); one page costs {per_page} bytes")
         return [int(n)] * len(self.groups)
 
     # -- the step ----------------------------------------------------------------------
@@ -403,16 +444,22 @@ class ModelRunner:
         step.rows_all = True  # in a graph every lane's logits are computed
         rows = layout.view(dev, "rows")
         torch.cuda.synchronize(self.device)
-        side = torch.cuda.Stream(self.device)
+        # The warm-up runs on the stream the capture will use: it loads libraries, sets kernel
+        # attributes, fills the allocator and, above all, creates and zeroes the kernels' per-stream
+        # scratch (ticket counters, partial sums, error word) outside any capture, so that no graph
+        # holds the only memset of a buffer that later graphs rely on.
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream(self.device)
+        side = self._capture_stream
         side.wait_stream(torch.cuda.current_stream(self.device))
-        with torch.cuda.stream(side):  # warm-up: loads libraries, sets kernel attributes, fills the allocator
+        with torch.cuda.stream(side):
             for _ in range(2):
                 self.model.forward(step, self.layer_caches, rows, bucket)
         torch.cuda.current_stream(self.device).wait_stream(side)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count
-        with torch.cuda.graph(graph, pool=self._graph_pool):
+        with torch.cuda.graph(graph, pool=self._graph_pool, stream=side):
             logits = self.model.forward(step, self.layer_caches, rows, bucket)
         kernels = ops.launch_count - before
         if self._graph_pool is None:

@@ -38,7 +38,11 @@ class Model:
         ctx = BuildContext(device=self.device, dtype=dtype)
         self.blocks = [build_part("block", s, ctx) for s in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, ctx)
-        self.graph_safe = all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+        self.embedding_transform = None if spec.embedding_transform is None else build_part("transform", spec.embedding_transform, ctx)
+        self.logits_transform = None if spec.logits_transform is None else build_part("transform", spec.logits_transform, ctx)
+        self._transforms = [t for t in (self.embedding_transform, self.logits_transform) if t is not None]
+        self.graph_safe = (all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+                           and all(t.graph_safe for t in self._transforms))
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
 
@@ -64,7 +68,7 @@ class Model:
                 raise ValueError(f"run {i} reads cache {keys[c]} that no run writes")
             need = self.blocks[run.layer].mixer.cache_need()
             w = plan[c].need
-            if (need.group_key, need.kv_heads, need.head_dim, need.state_shape) != (w.group_key, w.kv_heads, w.head_dim, w.state_shape):
+            if (need.group_key, need.k_row, need.v_row, need.state_shape) != (w.group_key, w.k_row, w.v_row, w.state_shape):
                 raise ValueError(f"run {i} and run {plan[c].writer_run} share a cache but need different ones")
         self.cache_plan: list[CachePlanEntry] = [p for p in plan if p is not None]
 
@@ -83,6 +87,8 @@ class Model:
         for block in self.blocks:
             block.load(tensors)
         self.final_norm.load(tensors)
+        for transform in self._transforms:
+            transform.load(tensors)
 
     def weight_bytes(self) -> int:
         """Bytes of every weight a step reads once (the decode roofline's numerator)."""
@@ -102,6 +108,8 @@ class Model:
         for b in self.blocks:
             walk(b)
         walk(self.final_norm)
+        for transform in self._transforms:
+            walk(transform)
         if self.head is not None and self.head.data_ptr() not in seen:
             total += self.head.numel() * self.head.element_size()
         return total
@@ -113,6 +121,8 @@ class Model:
         T = step.num_tokens
         hidden = torch.empty((T, self.spec.hidden_size), device=self.device, dtype=torch.float32)
         ops.embed_gather(hidden, self.embedding, step.token_ids)
+        if self.embedding_transform is not None:
+            hidden = self.embedding_transform.forward(hidden, step)
         pending = None
         order = self.spec.run_order
         # the final norm may be prepared by the last block when every row's logits are wanted
@@ -128,8 +138,15 @@ class Model:
         return hidden, pending
 
     def logits(self, hidden: torch.Tensor, pending, rows: torch.Tensor, num_rows: int) -> torch.Tensor:
-        """Final norm on the wanted rows only, then the head: float32 [R, V] (engine/model.py:75-86).
+        """Final norm on the wanted rows only, then the head (and what the architecture does to the
+        logits after it): float32 [R, V] (engine/model.py:75-86).
         `pending`: the last branch output not yet added, or a PreNormed of the final norm."""
+        out = self._head_product(hidden, pending, rows, num_rows)
+        if self.logits_transform is not None:
+            out = self.logits_transform.forward(out, None)
+        return out
+
+    def _head_product(self, hidden: torch.Tensor, pending, rows: torch.Tensor, num_rows: int) -> torch.Tensor:
         if isinstance(pending, PreNormed):
             if num_rows == hidden.shape[0] and folding_possible(num_rows, self.dtype, self.head):
                 return linear_scaled(pending, self.head, float32_out=True)

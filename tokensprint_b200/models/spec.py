@@ -39,6 +39,10 @@ class ModelSpec:
     eos_token_id: int = -1
     # Names that may sit in a checkpoint without being used (lm_head beside tied embeddings).
     ignorable_tensors: tuple[str, ...] = ()
+    # Optional "transform" parts: what happens to the embedding rows before the first block
+    # (float32 [T, width]) and to the logits after the head (float32 [rows, vocab]).
+    embedding_transform: Optional[PartSpec] = None
+    logits_transform: Optional[PartSpec] = None
 
     def __post_init__(self) -> None:
         if not self.run_order:
@@ -66,6 +70,10 @@ class ModelSpec:
                 add(s)
         for s in build_part("norm", self.final_norm, ctx).tensor_specs():
             add(s)
+        for transform in (self.embedding_transform, self.logits_transform):
+            if transform is not None:
+                for s in build_part("transform", transform, ctx).tensor_specs():
+                    add(s)
         if self.lm_head is not None:
             add(TensorSpec(self.lm_head, (self.vocab_size, self.hidden_size)))
         return list(specs.values())

@@ -367,11 +367,27 @@ ATTENTION_DECODE_TMA = _os.environ.get("TS_ATTENTION_TMA", "1") != "0"
 _attention_error: Optional[torch.Tensor] = None
 
 
+def _pinned_word() -> torch.Tensor:
+    """One zeroed int32 in pinned host memory that kernels may write and the host reads without a
+    copy.  Made outside inference mode, so that the host may clear it from anywhere."""
+    with torch.inference_mode(False):
+        return torch.zeros(1, dtype=torch.int32).pin_memory()
+
+
+def _word_is_set(word: torch.Tensor) -> bool:
+    """Reads and clears an error word through its numpy view (plain memory, no tensor dispatch)."""
+    view = word.numpy()
+    if int(view[0]) == 0:
+        return False
+    view[0] = 0
+    return True
+
+
 def _attention_error_word() -> torch.Tensor:
     """One int in pinned host memory that the decode attention sets when a bounded wait gave up."""
     global _attention_error
     if _attention_error is None:
-        _attention_error = torch.zeros(1, dtype=torch.int32).pin_memory()
+        _attention_error = _pinned_word()
     return _attention_error
 
 
@@ -410,16 +426,47 @@ def _attention_mma_fns(head_dim: int):
         lib.ts_attention_decode_flat_ctas.restype = _c_int
         lib.ts_attention_decode_flat_scratch_floats.argtypes = [_c_int, _c_int]
         lib.ts_attention_decode_flat_scratch_floats.restype = _c_ll
+        lib.ts_attention_mma_decode_slots.restype = _c_ll
+        lib.ts_attention_mma_decode_rows.restype = _c_int
+        lib.ts_attention_mma_last_launches.restype = _c_int
         _attention_flat[head_dim] = lib
         fns = (run, scratch)
         _attention_mma[head_dim] = fns
     return fns
 
 
+_decode_slot_counts: dict[int, int] = {}
+
+
 def _decode_slots(head_dim: int) -> int:
-    """CTAs of the decode attention kernel that run at once (shared memory allows a few per SM)."""
-    smem = (16 + 4 * 64) * (head_dim + 8) * 2
-    return max(1, (227 * 1024) // smem) * 148
+    """CTAs of the decode attention kernel that run at once on this device, as the library's
+    occupancy query for the real kernel says."""
+    n = _decode_slot_counts.get(head_dim)
+    if n is None:
+        _attention_mma_fns(head_dim)
+        n = _decode_slot_counts[head_dim] = max(1, int(_attention_flat[head_dim].ts_attention_mma_decode_slots()))
+    return n
+
+
+def attention_decode_rows(head_dim: int) -> int:
+    """The most query rows (tokens of the step x query heads per key/value head) of one sequence
+    that the decode kernels take; steps with more go to the prompt kernels."""
+    _attention_mma_fns(head_dim)
+    return int(_attention_flat[head_dim].ts_attention_mma_decode_rows())
+
+
+# The context length the split count of a decode step is planned for when the step may serve any
+# length up to the model's (a captured graph does): long enough that a few thousand keys are spread
+# over all SMs, short enough that a sequence of a few hundred keys is not cut into slivers
+# (TS_DECODE_PLAN_CONTEXT overrides it for measurements).
+ATTENTION_DECODE_PLAN_CONTEXT = int(_os.environ.get("TS_DECODE_PLAN_CONTEXT", "2048"))
+
+
+def attention_decode_plan_context(max_context: int, window: int = 0) -> int:
+    """The context length to plan a decode step's key splits for: the longest the step can meet,
+    capped by the window (plus one key block) or by ATTENTION_DECODE_PLAN_CONTEXT."""
+    cap = window + 64 if window > 0 else ATTENTION_DECODE_PLAN_CONTEXT
+    return max(1, min(max_context, cap))
 
 
 def attention_decode_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: int = 128) -> int:
@@ -524,18 +571,16 @@ def attention_paged_mma(
         if scratch is None or scratch.dtype != torch.float32 or not scratch.is_cuda or scratch.numel() < need:
             raise KernelError(f"attention: splits={splits} needs {need} float32 of scratch")
     counters = None
-    if fuse_merge and _FUSE_ATTENTION_MERGE and splits > 1 and max_seqlen_q * (nq // nkv) <= 16 and num_seqs * nkv <= _GEMM_MAX_TILES:
+    if fuse_merge and _FUSE_ATTENTION_MERGE and splits > 1 and max_seqlen_q * (nq // nkv) <= attention_decode_rows(d) and num_seqs * nkv <= _GEMM_MAX_TILES:
         counters = _attention_counters(q.device).data_ptr()
     _check("attention_paged_mma", run(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _ptr(scratch),
         cu_seqlens_q.data_ptr(), context_lens.data_ptr(), block_table.data_ptr(), seq_index.data_ptr(),
         block_table.shape[1], page_size, T, num_seqs, max_seqlen_q, nq, nkv, float(scale), int(window), int(splits),
         int(keys_per_split), counters, _stream()))
-    in_cluster = (1 < splits <= 8 and max_seqlen_q * (nq // nkv) <= 16 and keys_per_split == 0 and ATTENTION_CLUSTER_MERGE
-                  and num_seqs * nkv * splits <= _decode_slots(d))
-    if splits > 1 and counters is None and not in_cluster:
+    if splits > 1:
         global launch_count
-        launch_count += 1  # the combine kernel
+        launch_count += _attention_flat[d].ts_attention_mma_last_launches() - 1  # the combine kernel, if one ran
 
 
 # Decode steps whose (sequence, KV head) pairs times key splits do not all run at once go to the
@@ -757,12 +802,13 @@ def _gemm_workspace(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
     ws = _gemm_workspaces.get(key)
     if ws is None:
         counters = torch.zeros(_GEMM_MAX_TILES, dtype=torch.int32, device=device)
-        error = torch.zeros(1, dtype=torch.int32).pin_memory()
+        error = _pinned_word()
         ws = _gemm_workspaces[key] = (counters, error)
     return ws
 
 
 _gemm_partials: dict[tuple[int, int], torch.Tensor] = {}
+_gemm_partials_outgrown: list[torch.Tensor] = []
 _gemm_scratch_need: dict[tuple[int, int, int], int] = {}
 
 
@@ -778,6 +824,8 @@ def _gemm_partial(device: torch.device, M: int, N: int, K: int) -> torch.Tensor:
     key = (device.index or 0, _stream())
     buf = _gemm_partials.get(key)
     if buf is None or buf.numel() < need:
+        if buf is not None:
+            _gemm_partials_outgrown.append(buf)  # a captured graph may still name it: never handed back
         buf = _gemm_partials[key] = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=device)
     return buf
 
@@ -969,13 +1017,23 @@ def gemm_qk_rope_store(
         _stream()))
 
 
+_SIGNATURES["ts_wait_gives_up_probe"] = [_c_void_p, _c_int, _c_void_p]
+
+
+def wait_gives_up_probe(device: torch.device, limit: int = 4096) -> None:
+    """Launches a kernel whose only bounded wait runs out (an mbarrier nothing feeds, `limit`
+    tries) and which then raises the current stream's error word exactly as the tcgen05 kernels
+    do: the way to see the error path work without a fault.  check_device_errors() raises after
+    the next synchronisation."""
+    _, error = _gemm_workspace(device)
+    _check("wait_gives_up_probe", _fn("ts_wait_gives_up_probe")(error.data_ptr(), int(limit), _stream()))
+
+
 def check_device_errors() -> None:
     """Raises if a kernel reported that one of its bounded waits gave up.  Cheap: reads
     pinned host words; call it wherever the host has just synchronised anyway."""
-    if _attention_error is not None and int(_attention_error[0]) != 0:
-        _attention_error[0] = 0
+    if _attention_error is not None and _word_is_set(_attention_error):
         raise KernelError("decode attention: a wait on an mbarrier gave up (the kernel returned early)")
     for (dev, _), (_, error) in _gemm_workspaces.items():
-        if int(error[0]) != 0:
-            error[0] = 0
+        if _word_is_set(error):
             raise KernelError(f"a tcgen05 kernel on cuda:{dev} (skinny GEMM or prompt attention): a wait on an mbarrier gave up (the kernel returned early)")

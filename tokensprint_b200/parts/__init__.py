@@ -7,6 +7,7 @@ from tokensprint_b200.parts.base import (  # noqa: F401
     MIXERS,
     NORMS,
     POSITION_ENCODINGS,
+    TRANSFORMS,
     Block,
     BuildContext,
     CacheNeed,
@@ -20,6 +21,7 @@ from tokensprint_b200.parts.base import (  # noqa: F401
     PositionEncoding,
     StepContext,
     TensorSpec,
+    Transform,
     build_part,
     register_part,
     unregister_part,

@@ -162,11 +162,11 @@ class AttentionMixer(Mixer):
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         if q.dtype == torch.bfloat16 and ops.attention_mma_supported(d):
             splits, chunk, scratch = 1, 0, None
-            if step.max_seqlen_q * (nq // nkv) <= 16:  # decode: spread each sequence's keys over CTAs
+            if step.max_seqlen_q * (nq // nkv) <= ops.attention_decode_rows(d):  # few rows per sequence: the decode kernels, keys spread over CTAs
                 # The count must not depend on the step's actual lengths (a captured graph is
                 # replayed for all of them): plan for a typical context, each sequence then
                 # divides its own keys evenly.
-                context = min(step.max_context_len, 2048) if self.window <= 0 else min(step.max_context_len, self.window + 64)
+                context = ops.attention_decode_plan_context(step.max_context_len, self.window)
                 splits = ops.attention_decode_splits(step.num_seqs, nkv, context, d)
                 if (ops.attention_decode_prefers_flat(step.num_seqs, nkv, splits, d)
                         and ops.attention_decode_flat_supported(nq, nkv, d, step.page_size, step.num_seqs, step.max_seqlen_q)):

@@ -50,6 +50,11 @@ class CacheNeed:
     kind "full": all keys stay; "window": keys older than `window` positions before the
     next query may be given back; "none": no pages.  `state_shape` asks for a slot of
     that fixed shape per request (None: no state).
+
+    What is paged per token: `k_row` is the shape of one token's entry in the first pool and
+    `v_row` that of the second pool (None: the mixer pages one tensor only, e.g. a latent).  The
+    two may differ (values narrower than keys).  An attention mixer gives `kv_heads` and
+    `head_dim` instead, which stand for k_row = v_row = (kv_heads, head_dim).
     """
 
     kind: str = "none"
@@ -58,10 +63,39 @@ class CacheNeed:
     head_dim: int = 0
     state_shape: Optional[tuple[int, ...]] = None
     state_dtype: torch.dtype = torch.float32
+    k_row: Optional[tuple[int, ...]] = None
+    v_row: Optional[tuple[int, ...]] = None
+    single_pool: bool = False  # True: only the first pool exists (v_row stays None)
+
+    def __post_init__(self) -> None:
+        if self.kind == "none":
+            return
+        if self.k_row is None:
+            if self.kv_heads <= 0 or self.head_dim <= 0:
+                raise ValueError("a paged cache needs k_row, or kv_heads and head_dim")
+            object.__setattr__(self, "k_row", (int(self.kv_heads), int(self.head_dim)))
+        else:
+            object.__setattr__(self, "k_row", tuple(int(n) for n in self.k_row))
+        if self.v_row is None and not self.single_pool:
+            object.__setattr__(self, "v_row", self.k_row)
+        elif self.v_row is not None:
+            object.__setattr__(self, "v_row", tuple(int(n) for n in self.v_row))
 
     @property
     def group_key(self) -> tuple[str, int]:
         return (self.kind, self.window if self.kind == "window" else 0)
+
+    @property
+    def token_elements(self) -> int:
+        """Elements one token occupies in the pools of this cache."""
+        n = 0
+        for row in (self.k_row, self.v_row):
+            if row is not None:
+                size = 1
+                for extent in row:
+                    size *= extent
+                n += size
+        return n
 
 
 # ---------------------------------------------------------------------------
@@ -142,8 +176,8 @@ class LayerCache:
     """What one run of a mixer may touch of the cache."""
 
     group: int = -1  # index into StepContext.groups; -1: no pages
-    k_pages: Optional[torch.Tensor] = None  # [pages, page, kv_heads, head_dim]
-    v_pages: Optional[torch.Tensor] = None
+    k_pages: Optional[torch.Tensor] = None  # [pages, page, *k_row] (attention: [pages, page, kv_heads, head_dim])
+    v_pages: Optional[torch.Tensor] = None  # [pages, page, *v_row], or None for a cache of one pool
     state: Optional[torch.Tensor] = None  # [slots, *state_shape]
     writes: bool = True  # False: reads a cache that another run filled
 
@@ -220,6 +254,19 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Transform(Part):
+    """A step on the way into or out of the stack of blocks that belongs to no layer: what an
+    architecture does to the embedding rows before the first block (a multiplier, an added
+    table) or to the logits after the head (a scale, a soft cap, a bias).  A `ModelSpec` names
+    them as `embedding_transform` and `logits_transform`; the model calls them and knows
+    nothing of what they do."""
+
+    def forward(self, x: torch.Tensor, step: Optional[StepContext]) -> torch.Tensor:
+        """Returns the transformed tensor (it may be `x`, changed in place).  Embedding rows:
+        float32 [T, width] with the step's context; logits: float32 [rows, vocab], step None."""
+        raise NotImplementedError
+
+
 class Block(Part):
     """An arrangement of mixer, feed-forward and norms around the residual stream.
 
@@ -268,6 +315,7 @@ FEED_FORWARDS: dict[str, PartFactory] = {}
 NORMS: dict[str, PartFactory] = {}
 POSITION_ENCODINGS: dict[str, PartFactory] = {}
 BLOCKS: dict[str, PartFactory] = {}
+TRANSFORMS: dict[str, PartFactory] = {}
 
 _TABLES = {
     "mixer": MIXERS,
@@ -275,6 +323,7 @@ _TABLES = {
     "norm": NORMS,
     "position_encoding": POSITION_ENCODINGS,
     "block": BLOCKS,
+    "transform": TRANSFORMS,
 }
 
 
