@@ -540,3 +540,216 @@ def test_norms_and_activation_folded_into_the_products_change_nothing_but_roundi
     err_f = sum(float(abs(folded[k] - exact[k]).mean()) for k in exact)
     err_u = sum(float(abs(plain_path[k] - exact[k]).mean()) for k in exact)
     assert err_f < 1.5 * err_u
+
+
+# ---------------------------------------------------------------------------
+# a third toy architecture: what happens outside the layers (an embedding multiplier, a soft cap
+# and a bias on the logits) and a mixer whose cache rows are not attention's (keys wider than
+# values, one head) - all defined here
+
+
+@dataclass(frozen=True)
+class ToyWideKeyConfig:
+    vocab_size: int = 83
+    hidden_size: int = 40
+    num_hidden_layers: int = 2
+    key_size: int = 24
+    value_size: int = 8
+    intermediate_size: int = 56
+    embedding_multiplier: float = 3.5
+    logit_cap: float = 4.0
+    rms_norm_eps: float = 1e-6
+    architectures: tuple = ("ToyWideKeyForCausalLM",)
+
+    def to_dict(self):
+        d = asdict(self)
+        d["architectures"] = list(self.architectures)
+        return d
+
+    def save(self, folder):
+        import json
+        from pathlib import Path
+
+        Path(folder).mkdir(parents=True, exist_ok=True)
+        (Path(folder) / "config.json").write_text(json.dumps(self.to_dict()))
+
+
+def _register_wide_key_toy():
+    from tokensprint_b200.config.registry import register_architecture
+    from tokensprint_b200.models.spec import ModelSpec
+    from tokensprint_b200.parts.base import CacheNeed, Mixer, PartSpec, TensorSpec, Transform, register_part
+
+    @register_part("transform", "toy_multiplier", replace=True)
+    class Multiplier(Transform):
+        graph_safe = True
+
+        def __init__(self, bctx, *, factor):
+            self.factor = float(factor)
+
+        def forward(self, x, step):
+            return x.mul_(self.factor)
+
+    @register_part("transform", "toy_cap_and_bias", replace=True)
+    class CapAndBias(Transform):
+        """logits -> cap * tanh(logits / cap) + bias, the bias a tensor of the checkpoint."""
+
+        graph_safe = True
+
+        def __init__(self, bctx, *, cap, bias, size):
+            self.cap, self.bias_name, self.size = float(cap), bias, size
+
+        def tensor_specs(self):
+            return [TensorSpec(self.bias_name, (self.size,), "vector")]
+
+        def load(self, tensors):
+            self.bias = tensors[self.bias_name]
+
+        def forward(self, x, step):
+            return torch.tanh(x / self.cap) * self.cap + self.bias
+
+    @register_part("mixer", "toy_wide_keys", replace=True)
+    class WideKeyMixer(Mixer):
+        """One head, keys of `key_size` and values of `value_size` entries, both paged: the two
+        pools of its cache have different row shapes.  Plain torch on the pages and tables it is
+        handed; the host's copies of the step's lengths say which rows belong to whom."""
+
+        def __init__(self, bctx, *, hidden_size, key_size, value_size, prefix):
+            self.H, self.dk, self.dv, self.prefix = hidden_size, key_size, value_size, prefix
+
+        def cache_need(self):
+            return CacheNeed(kind="full", k_row=(self.dk,), v_row=(self.dv,))
+
+        def tensor_specs(self):
+            p = self.prefix
+            return [TensorSpec(p + "q", (self.dk, self.H)), TensorSpec(p + "k", (self.dk, self.H)),
+                    TensorSpec(p + "v", (self.dv, self.H)), TensorSpec(p + "o", (self.H, self.dv))]
+
+        def load(self, tensors):
+            self.w = {n: tensors[self.prefix + n] for n in "qkvo"}
+
+        def forward(self, x, step, cache):
+            P = step.page_size
+            assert cache.k_pages.shape[1:] == (P, self.dk) and cache.v_pages.shape[1:] == (P, self.dv)
+            tables = step.groups[cache.group]
+            q, k, v = x @ self.w["q"].t(), x @ self.w["k"].t(), x @ self.w["v"].t()
+            k_flat, v_flat = cache.k_pages.view(-1, self.dk), cache.v_pages.view(-1, self.dv)
+            slots = tables.slot_mapping[: x.shape[0]].long()
+            k_flat[slots] = k
+            v_flat[slots] = v
+            out = torch.empty((x.shape[0], self.dv), device=x.device, dtype=x.dtype)
+            t0 = 0
+            for b, (start, n) in enumerate(zip(step.host_seq_starts, step.host_seq_lens)):
+                pos = torch.arange(start + n, device=x.device)
+                held = tables.block_table[b].long()[pos // P] * P + pos % P
+                scores = (q[t0 : t0 + n] @ k_flat[held].t()) * self.dk**-0.5
+                hidden_keys = pos[None, :] > (start + torch.arange(n, device=x.device))[:, None]
+                out[t0 : t0 + n] = torch.softmax(scores.masked_fill(hidden_keys, float("-inf")), dim=-1) @ v_flat[held]
+                t0 += n
+            return out @ self.w["o"].t()
+
+    @register_architecture("ToyWideKeyForCausalLM", config_from_dict=lambda d: ToyWideKeyConfig(**{k: (tuple(v) if isinstance(v, list) else v) for k, v in d.items()}))
+    def build(cfg: ToyWideKeyConfig):
+        layers = []
+        for i in range(cfg.num_hidden_layers):
+            p = f"w.{i}."
+            norm = {"dim": cfg.hidden_size, "eps": cfg.rms_norm_eps}
+            layers.append(PartSpec("pre_norm", {
+                "mixer": PartSpec("toy_wide_keys", {"hidden_size": cfg.hidden_size, "key_size": cfg.key_size, "value_size": cfg.value_size, "prefix": p + "mix."}),
+                "feed_forward": PartSpec("swiglu", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size,
+                                                    "gate": p + "gate", "up": p + "up", "down": p + "down"}),
+                "mixer_norm": PartSpec("rmsnorm", {**norm, "weight": p + "n1"}),
+                "ffn_norm": PartSpec("rmsnorm", {**norm, "weight": p + "n2"})}))
+        return ModelSpec(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, embedding="w.embed", layers=layers,
+                         final_norm=PartSpec("rmsnorm", {"dim": cfg.hidden_size, "eps": cfg.rms_norm_eps, "weight": "w.norm"}),
+                         lm_head=None, max_positions=512,
+                         embedding_transform=PartSpec("toy_multiplier", {"factor": cfg.embedding_multiplier}),
+                         logits_transform=PartSpec("toy_cap_and_bias", {"cap": cfg.logit_cap, "bias": "w.logit_bias", "size": cfg.vocab_size}))
+
+
+def _plain_wide_key_toy(weights, cfg: ToyWideKeyConfig, ids):
+    w = {k: v.double() for k, v in weights.items()}
+    T = len(ids)
+    h = plain.embedding(w["w.embed"], ids) * cfg.embedding_multiplier
+    causal = torch.ones(T, T, dtype=torch.bool).tril()
+    for i in range(cfg.num_hidden_layers):
+        p = f"w.{i}."
+        x = plain.rms_norm(h, w[p + "n1"], cfg.rms_norm_eps)
+        q, k, v = x @ w[p + "mix.q"].T, x @ w[p + "mix.k"].T, x @ w[p + "mix.v"].T
+        scores = (q @ k.T * cfg.key_size**-0.5).masked_fill(~causal, float("-inf"))
+        h = h + (torch.softmax(scores, dim=-1) @ v) @ w[p + "mix.o"].T
+        x = plain.rms_norm(h, w[p + "n2"], cfg.rms_norm_eps)
+        g, u = x @ w[p + "gate"].T, x @ w[p + "up"].T
+        h = h + (g * torch.sigmoid(g) * u) @ w[p + "down"].T
+    logits = plain.rms_norm(h, w["w.norm"], cfg.rms_norm_eps) @ w["w.embed"].T
+    return torch.tanh(logits / cfg.logit_cap) * cfg.logit_cap + w["w.logit_bias"]
+
+
+def test_a_toy_model_with_transforms_outside_the_layers_and_keys_wider_than_values(tmp_path):
+    """An embedding multiplier, a soft cap and a bias on the logits, and a cache whose two pools
+    have different row shapes: registered here, built from config.json, stepped in all four
+    cuttings with pages used again, without a change to the framework's files."""
+    from tokensprint_b200.config.registry import unregister_architecture
+    from tokensprint_b200.engine.replay import TraceReplayer
+    from tokensprint_b200.parts.base import unregister_part
+    from tokensprint_b200.weights.loader import write_random_model
+    from tokensprint_b200.weights.safetensors_io import SafetensorsFolder
+
+    _register_wide_key_toy()
+    try:
+        cfg = ToyWideKeyConfig()
+        folder = write_random_model(tmp_path / "wide", cfg, seed=13, dtype="float32", std=0.2)
+        files = SafetensorsFolder(folder)
+        weights = {n: files.tensor(n).clone() for n in files.keys()}
+        assert weights["w.0.mix.k"].shape == (24, 40) and weights["w.0.mix.v"].shape == (8, 40) and "w.logit_bias" in weights
+        g = torch.Generator().manual_seed(9)
+        requests = {f"r{i}": torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for i, n in enumerate((2, 19, 40, 66))}
+        want = {rid: _plain_wide_key_toy(weights, cfg, ids) for rid, ids in requests.items()}
+        assert max(float(v.abs().max()) for v in want.values()) > 0.8 * cfg.logit_cap, "the cap is not exercised"
+        many = dict(requests)
+        many.update({k + "x": v for k, v in requests.items()})
+        for steps, reqs in ((trace_whole(requests), requests), (trace_decode_tail(requests, 16), requests),
+                            (trace_portions(requests), requests), (trace_mixed(many, 256, seed=4), many)):
+            replayer = TraceReplayer.from_folder(folder, "float32", 256, max_live=4)
+            replayer.runner.poison_freed_pages = True
+            tensors = replayer.runner.cache_tensors
+            assert tensors.k[0].shape[2:] == (24,) and tensors.v[0].shape[2:] == (8,)
+            assert replayer.runner.page_bytes == [2 * 16 * (24 + 8) * 4]
+            got = replay_in_process(replayer, steps)
+            for (rid, pos), row in got.items():
+                ref = want[rid.rstrip("x")][pos].numpy()
+                assert abs(row - ref).max() < 1e-4 * abs(want[rid.rstrip("x")]).max(), f"{rid} position {pos}"
+            assert len(got) == sum(len(v) for v in reqs.values())
+    finally:
+        unregister_architecture("ToyWideKeyForCausalLM")
+        for category, name in (("mixer", "toy_wide_keys"), ("transform", "toy_multiplier"), ("transform", "toy_cap_and_bias")):
+            unregister_part(category, name)
+
+
+def test_cache_size_comes_from_free_memory_when_no_page_count_is_given(tmp_path):
+    """A runner built without a page count measures a step of the largest size, sizes its pool from
+    what is free after it, and generates with it."""
+    from tests.tiny_configs import TINY_B, tiny_weights, write_model_folder
+    from tokensprint_b200.config.engine_config import Config, SamplingParams
+    from tokensprint_b200.engine.llm_engine import LLMEngine
+    from tokensprint_b200.models.api import load_model
+
+    folder = write_model_folder(tmp_path / "m", TINY_B, tiny_weights(TINY_B, 3, std=0.05))
+    model, _ = load_model(folder, device=DEV, dtype="bfloat16")
+    torch.cuda.synchronize()
+    free_before, total = torch.cuda.mem_get_info()
+    utilization = 0.05  # a small share: the test must not take the GPU's memory from whoever runs beside it
+    engine = LLMEngine(model, Config(model=str(folder), max_model_len=256, max_num_batched_tokens=512, max_num_seqs=8,
+                                     kvcache_block_size=16, num_kvcache_blocks=-1, gpu_memory_utilization=utilization, dtype="bfloat16"))
+    runner = engine.model_runner
+    s = runner.sizing
+    assert s is not None and s["pages"] == runner.num_pages[0] == engine.config.num_kvcache_blocks
+    assert s["step_tokens"] == 512 and s["step_peak_bytes"] > 512 * TINY_B["hidden_size"] * 4  # at least the residual stream
+    assert s["bytes_per_page"] == 2 * 16 * TINY_B["num_key_value_heads"] * TINY_B["head_dim"] * 2 * TINY_B["num_hidden_layers"]
+    pool_bytes = s["pages"] * s["bytes_per_page"]
+    budget = s["free_bytes"] * utilization - s["step_peak_bytes"] - s["graph_reserve_bytes"] - s["margin_bytes"]
+    assert 0 <= budget - pool_bytes < s["bytes_per_page"], "the pool is what the budget allows, to the page"
+    assert pool_bytes < free_before * utilization
+    assert s["graph_reserve_bytes"] > 0  # graphs are on by default and keep their logits
+    out = engine.generate([[1, 2, 3, 4, 5], list(range(10, 60))], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True), use_tqdm=False)
+    assert [len(o) for o in out] == [6, 6]
+    assert runner.cache_manager.pages_in_use() == 0
