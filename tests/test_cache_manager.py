@@ -21,7 +21,7 @@ def test_pages_follow_the_tokens():
     assert rc.tables[0] == [0, 1]
     cm.extend(rc, 8, 9)
     assert rc.tables[0] == [0, 1, 2]
-    assert cm.slots_for(rc, 0, 3, 4) == [3, 4, 5, 6]
+    assert cm.slots_for(rc, 0, 3, 4).tolist() == [3, 4, 5, 6]
     cm.check_invariants()
     cm.free(rc)
     assert cm.pools[0].num_free == 8 and len(cm.free_slots) == 4

@@ -19,6 +19,7 @@ every page here has exactly one owner.
 from __future__ import annotations
 
 from collections import deque
+import numpy as np
 from dataclasses import dataclass, field
 from typing import Hashable, Optional, Sequence
 
@@ -215,16 +216,17 @@ class CacheManager:
 
     # -- what a step needs ---------------------------------------------------------
 
-    def slots_for(self, rc: RequestCache, g: int, start: int, count: int) -> list[int]:
+    def slots_for(self, rc: RequestCache, g: int, start: int, count: int) -> "np.ndarray":
         """Flat cache slots (page * page_size + offset) of positions start..start+count-1."""
-        table, P = rc.tables[g], self.page_size
-        out = []
-        for pos in range(start, start + count):
-            page = table[pos // P]
-            if page < 0:
-                raise CacheError(f"request {rc.request!r}: position {pos} lies in a page that was given back")
-            out.append(page * P + pos % P)
-        return out
+        P = self.page_size
+        first = start // P
+        pages = np.asarray(rc.tables[g][first : (start + count - 1) // P + 1], dtype=np.int64)
+        positions = np.arange(start, start + count, dtype=np.int64)
+        held = pages[positions // P - first]
+        if held.size and held.min() < 0:
+            pos = int(positions[int(np.argmax(held < 0))])
+            raise CacheError(f"request {rc.request!r}: position {pos} lies in a page that was given back")
+        return held * P + positions % P
 
     # -- checks --------------------------------------------------------------------
 

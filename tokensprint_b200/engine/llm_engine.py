@@ -25,6 +25,47 @@ from tokensprint_b200.sampling.sampler import Sampler, sample_key
 
 log = logging.getLogger(__name__)
 
+STEP_KINDS = ("decode", "mixed", "prefill")
+
+
+class StepStats:
+    """Where the time of a run goes, step by step (switched on with `LLMEngine.collect_stats()`).
+
+    Every step is of one kind: "decode" (every request brings one decoded token), "prefill" (none
+    does: portions of prompts only) or "mixed".  Per step the host's time to schedule it, build
+    its inputs and launch its kernels is taken with the wall clock, and the device's time with a
+    pair of CUDA events on the launching stream (resolved at `summary()`, after a synchronize)."""
+
+    def __init__(self) -> None:
+        self.records: list[tuple[str, int, float, "torch.cuda.Event", "torch.cuda.Event"]] = []
+
+    def begin(self):
+        start = torch.cuda.Event(enable_timing=True)
+        start.record()
+        return time.perf_counter(), start
+
+    def end(self, begun, kind: str, tokens: int) -> None:
+        t0, start = begun
+        host_ms = (time.perf_counter() - t0) * 1e3
+        stop = torch.cuda.Event(enable_timing=True)
+        stop.record()
+        self.records.append((kind, tokens, host_ms, start, stop))
+
+    def summary(self) -> dict:
+        """Per kind: steps, tokens, host ms and device ms (totals), after waiting for the device."""
+        torch.cuda.synchronize()
+        out = {kind: {"steps": 0, "tokens": 0, "host_ms": 0.0, "device_ms": 0.0} for kind in STEP_KINDS}
+        for kind, tokens, host_ms, start, stop in self.records:
+            row = out[kind]
+            row["steps"] += 1
+            row["tokens"] += tokens
+            row["host_ms"] += host_ms
+            row["device_ms"] += start.elapsed_time(stop)
+        for row in out.values():
+            row["host_ms"] = round(row["host_ms"], 2)
+            row["device_ms"] = round(row["device_ms"], 2)
+        return out
+
 
 class LLMEngine:
     def __init__(self, model: Model, config: Config, tokenizer: Optional[Any] = None) -> None:
@@ -40,6 +81,7 @@ class LLMEngine:
             max_model_len=config.max_model_len,
         )
         config.num_kvcache_blocks = self.model_runner.num_pages[0]
+        self.model_runner.capture_graphs(config.max_num_seqs)  # nothing, if decode steps are not captured
         self.scheduler = Scheduler(config, self.model_runner.cache_manager)
         self.sampler = Sampler(model.device)
         self.tokenizer = tokenizer
@@ -49,6 +91,12 @@ class LLMEngine:
         # (sequences, which of them are sampled for, the positions of their tokens, the ids' ticket).
         self.overlap = bool(getattr(config, "overlap_steps", True))
         self._inflight = None
+        self.stats: Optional[StepStats] = None
+
+    def collect_stats(self) -> StepStats:
+        """From now on every step's kind, tokens, host time and device time are recorded."""
+        self.stats = StepStats()
+        return self.stats
 
     def _token_ids(self, prompt: str | list[int]) -> list[int]:
         """Token ids of a request: a list is taken as it is, text goes through the tokenizer."""
@@ -77,6 +125,7 @@ class LLMEngine:
 
     def _launch(self):
         """Schedules and launches one step; returns what `_inflight` holds."""
+        begun = self.stats.begin() if self.stats is not None else None
         seqs = self.scheduler.schedule()
         entries, need, temps, keys = [], [], [], []
         for i, seq in enumerate(seqs):
@@ -95,7 +144,18 @@ class LLMEngine:
                 temps.append(seq.temperature)
                 keys.append(sample_key(seq.seed, seq.sample_stream, len(seq)))
         logits = self.model_runner.step(entries, self.sampler.device_ids)
+        if begun is not None:
+            single = sum(1 for seq in seqs if seq.num_new_tokens == 1 and seq.num_cached_tokens >= seq.num_prompt_tokens)
+            kind = "decode" if single == len(seqs) else ("prefill" if single == 0 else "mixed")
+            self._step_begun = (begun, kind, sum(seq.num_new_tokens for seq in seqs))
         return seqs, need, logits, temps, keys
+
+    def _step_launched(self) -> None:
+        """Closes the step's record once its sampling has been launched too."""
+        if self.stats is not None and getattr(self, "_step_begun", None) is not None:
+            begun, kind, tokens = self._step_begun
+            self.stats.end(begun, kind, tokens)
+            self._step_begun = None
 
     def step(self) -> tuple[list[tuple[int, list[int]]], int]:
         """One step.  Returns the requests that finished, as (id, completion token ids), and the
@@ -103,7 +163,9 @@ class LLMEngine:
         reads the ids of the step before, so a request's end is reported one call later."""
         if not self.overlap:
             seqs, need, logits, temps, keys = self._launch()
-            token_ids = self.sampler.sample(logits, temps, keys)
+            ticket = self.sampler.sample_async(logits, temps, keys)
+            self._step_launched()
+            token_ids = ticket.result()
             ops.check_device_errors()  # the copy of the sampled ids has just synchronised
             self.scheduler.postprocess(seqs, token_ids, need)
             finished = [seq for seq in seqs if seq.is_finished]
@@ -112,6 +174,7 @@ class LLMEngine:
             if not self.scheduler.is_finished():
                 seqs, need, logits, temps, keys = self._launch()
                 ticket = self.sampler.sample_async(logits, temps, keys)
+                self._step_launched()
                 positions = self.scheduler.advance(seqs, need)
                 launched = (seqs, need, positions, ticket)
             finished = []

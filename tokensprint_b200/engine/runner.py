@@ -466,6 +466,19 @@ class ModelRunner:
             self._graph_pool = graph.pool()
         return _DecodeGraph(bucket, layout, dev, host, graph, logits, kernels, row_marks=[{} for _ in self.groups])
 
+    def capture_graphs(self, largest_batch: Optional[int] = None) -> int:
+        """Captures the decode graphs of every batch bucket up to `largest_batch` now (the reference
+        captures at start-up too: engine/generation/model_runner.py:310-390), so that no step of a
+        run pays for a capture.  Returns how many graphs there are."""
+        if not self.use_graphs:
+            return 0
+        for bucket in self.graph_buckets:
+            if largest_batch is not None and bucket > max(largest_batch, 1) and any(b >= largest_batch for b in self._graphs):
+                break
+            if bucket not in self._graphs:
+                self._graphs[bucket] = self._capture(bucket)
+        return len(self._graphs)
+
     def _step_graph(self, bucket: int, entries: Sequence[StepEntry], fed_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
         g = self._graphs.get(bucket)
         if g is None:
