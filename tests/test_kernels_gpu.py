@@ -841,3 +841,90 @@ def test_a_wait_that_runs_out_becomes_an_exception_and_the_next_launch_is_clean(
     ops.check_device_errors()
     want = x.float() @ w.float().T
     assert float((out.float() - want).abs().max()) <= 2e-2 * float(want.abs().max())
+
+
+def _layer_like_products(ops, M, H, I, nq, nkv, tensors):
+    """The four products between two attention kernels of a decode step: the output projection
+    (into the residual stream, preparing the next norm), gate/up with the activation, down (into the
+    residual stream again), and the next layer's q/k/v projection with norm, rotation and cache
+    store.  Returns everything they wrote."""
+    t = tensors
+    d = 128
+    hidden = t["hidden0"].clone()
+    x1 = torch.empty((M, H), device=DEV, dtype=torch.bfloat16)
+    ssq1 = torch.empty((-(-H // 128), M), device=DEV)
+    ops.gemm_skinny_fused(t["attn"], t["wo"], mode=ops.GEMM_EPILOGUE_RESIDUAL_NORM, hidden=hidden, norm_weight=t["n1"], xprime=x1, ssq_out=ssq1)
+    act = torch.empty((M, I), device=DEV, dtype=torch.bfloat16)
+    ops.gemm_skinny_fused(x1, t["wgu"], out=act, mode=ops.GEMM_EPILOGUE_SWIGLU, scale_ssq=ssq1, scale_width=H, scale_eps=1e-6)
+    x2 = torch.empty((M, H), device=DEV, dtype=torch.bfloat16)
+    ssq2 = torch.empty((-(-H // 128), M), device=DEV)
+    ops.gemm_skinny_fused(act, t["wd"], mode=ops.GEMM_EPILOGUE_RESIDUAL_NORM, hidden=hidden, norm_weight=t["n2"], xprime=x2, ssq_out=ssq2)
+    q = torch.empty((M, nq * d), device=DEV, dtype=torch.bfloat16)
+    kc, vc = torch.zeros_like(t["kc"]), torch.zeros_like(t["kc"])
+    ops.gemm_qk_rope_store(x2, t["wqkv"], q, kc, vc, t["slots"], t["pos"], t["qn"], t["kn"], 1e-6, t["inv_freq"], nq, nkv,
+                           scale_ssq=ssq2, scale_width=H, scale_eps=1e-6)
+    return {"hidden": hidden, "x1": x1, "ssq1": ssq1, "act": act, "x2": x2, "ssq2": ssq2, "q": q, "kc": kc, "vc": vc}
+
+
+@pytest.mark.parametrize("M,H,I,nq,nkv", [(8, 1024, 3072, 16, 8), (1, 4096, 12288, 32, 8), (32, 640, 1408, 5, 1), (17, 5120, 1024, 40, 8)])
+def test_gemm_chain_launches_products_together_and_changes_no_bit(M, H, I, nq, nkv):
+    """Four products that feed one another, once each as a launch of its own and once inside a chain
+    (one kernel: each phase starts fetching its weights while the one before is being finished, and
+    reads its inputs after a barrier over the grid): the same bits, twice in a row, and the float64
+    result within bfloat16 rounding."""
+    from tokensprint_b200 import ops
+
+    d = 128
+    g = torch.Generator().manual_seed(M * 7 + H)
+    bf = lambda *shape, s=1.0: (torch.randn(*shape, generator=g) * s).to(DEV, torch.bfloat16)
+    gate, up = bf(I, H, s=0.03), bf(I, H, s=0.03)
+    t = {
+        "attn": bf(M, nq * d), "wo": bf(H, nq * d, s=0.03), "wd": bf(H, I, s=0.03), "wqkv": bf((nq + 2 * nkv) * d, H, s=0.03),
+        "wgu": torch.stack([gate.view(I // 64, 64, H), up.view(I // 64, 64, H)], dim=1).reshape(2 * I, H).contiguous(),
+        "hidden0": torch.randn(M, H, generator=g).to(DEV), "n1": (1 + 0.1 * torch.randn(H, generator=g)).to(DEV),
+        "n2": (1 + 0.1 * torch.randn(H, generator=g)).to(DEV), "qn": (1 + 0.1 * torch.randn(d, generator=g)).to(DEV),
+        "kn": (1 + 0.1 * torch.randn(d, generator=g)).to(DEV), "inv_freq": plain.rope_inverse_frequencies(d, 1e6).to(DEV),
+        "kc": torch.zeros(64, nkv, d, device=DEV, dtype=torch.bfloat16),
+        "slots": torch.randperm(64, generator=g)[:M].to(DEV, torch.int32), "pos": torch.randint(0, 3000, (M,), generator=g).to(DEV, torch.int32),
+    }
+    one_by_one = _layer_like_products(ops, M, H, I, nq, nkv, t)
+    torch.cuda.synchronize()
+    for _ in range(2):
+        before = ops.launch_count
+        with ops.gemm_chain(torch.device(DEV)):
+            chained = _layer_like_products(ops, M, H, I, nq, nkv, t)
+        assert ops.launch_count - before == 1, "the four products were not one launch"
+        torch.cuda.synchronize()
+        ops.check_device_errors()
+        for name, want in one_by_one.items():
+            assert torch.equal(chained[name], want), f"{name} differs between the chain and single launches"
+    # and the arithmetic itself
+    h1 = t["hidden0"].double() + t["attn"].double() @ t["wo"].double().T
+    assert rel_err(one_by_one["x1"], h1 * t["n1"].double()) < 1e-2
+    n1 = (h1 * torch.rsqrt((h1**2).mean(1, keepdim=True) + 1e-6) * t["n1"].double())
+    gd, ud = n1 @ gate.double().T, n1 @ up.double().T
+    assert rel_err(one_by_one["act"], gd * torch.sigmoid(gd) * ud) < 3e-2
+    h2 = h1 + one_by_one["act"].double() @ t["wd"].double().T
+    assert rel_err(one_by_one["hidden"], h2) < 1e-3
+    # six products in one chain: the list holds four, so two launches; any other op launches what is pending
+    square = (torch.randn(256, 256, generator=g) * 0.06).to(DEV, torch.bfloat16)
+    x0 = (torch.randn(M, 256, generator=g)).to(DEV, torch.bfloat16)
+
+    def six(x):
+        for _ in range(6):
+            out = torch.empty((M, 256), device=DEV, dtype=torch.bfloat16)
+            ops.gemm_skinny_bf16(x, square, out)
+            x = out
+        return x
+
+    want = six(x0)
+    before = ops.launch_count
+    with ops.gemm_chain(torch.device(DEV)):
+        got = six(x0)
+        assert ops.launch_count - before == 1  # the first four went when the fifth arrived
+        ids = torch.zeros(4, dtype=torch.int32, device=DEV)
+        ops.feed_tokens(ids, ids, ids, ids, 0)  # not a product: the two that waited are launched first
+        assert ops.launch_count - before == 3
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    assert torch.equal(got, want)

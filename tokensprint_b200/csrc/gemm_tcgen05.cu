@@ -28,6 +28,17 @@
 // The split of the work depends on the weight's shape and the SM count only, so a token's
 // result does not depend on what else is in the batch.
 //
+// Chains.  Up to MAX_PHASES products that feed one another (a decode layer's output projection,
+// gate/up, down, and the next layer's q/k/v) run as phases of ONE launch: every CTA works through
+// its share of phase after phase.  The copies of a phase's weights start while the phase before
+// is still being finished elsewhere (weights depend on nothing); only the copies of its
+// activations wait, at a barrier over the whole grid that the CTAs pass when everyone has stored
+// the phase before: a counter in device memory that every CTA raises once per phase and polls
+// with a bounded wait.  All CTAs of the grid are resident together (one per SM, never more CTAs
+// than SMs), and a kernel launched behind this one cannot take an SM before all of them are,
+// because it may start only when every CTA here has begun.  The last CTA to leave the kernel
+// zeroes the counters for the next launch.
+//
 // The reference runs these products through nn.Linear (engine/nn/attention.py:122-135,
 // engine/nn/layers.py:61-66); W is row-major [out, in] as there.
 #include <cuda.h>
@@ -38,9 +49,9 @@
 #include "common.cuh"
 
 // Optional timestamps for tuning (compile with -DTS_GEMM_PROBE): every CTA records the
-// nanosecond timer at a few points into args.probe[cta * 8 + i].
+// nanosecond timer at a few points into args.probe[cta * 64 + i] (8 + 8 * phase + k for the stamps of a phase).
 #ifdef TS_GEMM_PROBE
-#define TS_PROBE(i) do { if (args.probe) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); args.probe[blockIdx.x * 8 + (i)] = t_; } } while (0)
+#define TS_PROBE(i) do { if (args.probe) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); args.probe[blockIdx.x * 64 + (i)] = t_; } } while (0)
 #else
 #define TS_PROBE(i) do { } while (0)
 #endif
@@ -67,6 +78,8 @@ constexpr int MAX_CONTRIB = 8;   // most CTAs that may share one tile
 constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_RESIDUAL_NORM = 2, EPI_QK_ROPE = 3;
 constexpr int FUSED_MAX_ROWS = 32;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr int MAX_PHASES = 4;            // products per chained launch
+constexpr uint32_t GRID_SPIN_LIMIT = 1u << 23;  // polls of the grid barrier (each a tenth of a microsecond or more)
 
 template <int MPAD>
 struct Cfg {
@@ -118,6 +131,20 @@ struct GemmArgs {
 #endif
 };
 
+// A chain of products: per phase its arguments and tensor maps, the grid barrier's counters
+// (ts_gemm_chain_sync_words() unsigned ints, zero before the first launch; the kernel leaves them zero).
+struct ChainArgs {
+  GemmArgs g[MAX_PHASES];
+  int n;
+  int hold;   // 1: a phase's copies start only when this CTA has stored the phase before
+  int ahead;  // W tiles asked into the L2 beyond the ring while a phase waits for its inputs
+  unsigned int* sync;
+};
+struct ChainMaps {
+  CUtensorMap w[MAX_PHASES];
+  CUtensorMap x[MAX_PHASES];
+};
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -140,6 +167,34 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         : "=r"(done) : "r"(bar), "r"(parity) : "memory");
     if (done) return true;
     if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+// Grid barrier.  Per phase a counter that every CTA raises once its stores of the phase are done
+// (and visible to the other SMs and their copy engines) and a flag that the last one to arrive
+// sets; waiters poll the flag only, one thread per CTA, with a pause between polls, so that the
+// arrivals do not queue behind the polls.  Each word has a 128-byte line of its own.  Wait: a
+// bounded number of polls; false: gave up (or another role already did).
+constexpr int SYNC_LINE = 32;  // unsigned ints per line
+__device__ __forceinline__ unsigned int* sync_counter(unsigned int* sync, int phase) { return sync + (size_t)(2 * phase) * SYNC_LINE; }
+__device__ __forceinline__ unsigned int* sync_flag(unsigned int* sync, int phase) { return sync + (size_t)(2 * phase + 1) * SYNC_LINE; }
+__device__ __forceinline__ unsigned int* sync_departed(unsigned int* sync) { return sync + (size_t)(2 * MAX_PHASES) * SYNC_LINE; }
+__device__ __forceinline__ void grid_arrive(unsigned int* sync, int phase, unsigned int ctas) {
+  __threadfence();
+  if (atomicAdd(sync_counter(sync, phase), 1u) == ctas - 1) {
+    __threadfence();
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(sync_flag(sync, phase)), "r"(1u) : "memory");
+  }
+}
+__device__ __forceinline__ bool grid_wait(unsigned int* sync, int phase, volatile int* abort_flag) {
+  const unsigned int* flag = sync_flag(sync, phase);
+  for (uint32_t i = 0; i < GRID_SPIN_LIMIT; ++i) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v != 0) return true;
+    if (*abort_flag) return false;
+    __nanosleep(100);
   }
   *abort_flag = 1;
   return false;
@@ -288,9 +343,8 @@ __device__ __forceinline__ void fused_epilogue(const GemmArgs& args, int t, int 
 }
 
 template <int MPAD>
-__global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w,
-                                                                  const __grid_constant__ CUtensorMap map_x,
-                                                                  const GemmArgs args) {
+__global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_constant__ ChainMaps maps,
+                                                                  const __grid_constant__ ChainArgs chain) {
   using C = Cfg<MPAD>;
   constexpr int STAGES = C::STAGES;
   constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MPAD >> 3) << 17) | ((uint32_t)(TILE_N >> 4) << 24);
@@ -304,20 +358,27 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   __shared__ int last_s;
+  __shared__ int go_s;
+  __shared__ int ready_s;  // the last phase whose inputs the producer thread has seen ready
+  __shared__ int arrived_s;  // how many phases this CTA's epilogue warps have stored and reported
   __shared__ __align__(16) float tile_s[(MPAD <= FUSED_MAX_ROWS ? MPAD : 1) * TILE_N];  // a finished tile, for the fused epilogues
   __shared__ float rstd_s[FUSED_MAX_ROWS];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int phases = chain.n;
+  const unsigned int ctas = gridDim.x;
   ts_pdl_launch_dependents();  // the next kernel may begin its own set-up now
-  if (tid == 0) TS_PROBE(0);
-  const Range range = cta_range(args, blockIdx.x);
-  const int chunks = args.chunks;
-  const int t_first = range.u0 / chunks;
-  const int t_last = range.u1 > range.u0 ? (range.u1 - 1) / chunks : t_first - 1;
+  {
+    const GemmArgs& args = chain.g[0];
+    (void)args;
+    if (tid == 0) TS_PROBE(0);
+  }
 
   if (tid == 0) {
     abort_s = 0;
     last_s = 0;
+    ready_s = 0;
+    arrived_s = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
@@ -339,67 +400,115 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_s;
   volatile int* abort_flag = &abort_s;
-  if (tid == 0) TS_PROBE(1);
+  volatile int* ready_flag = &ready_s;
+  volatile int* arrived_flag = &arrived_s;
+  {
+    const GemmArgs& args = chain.g[0];
+    (void)args;
+    if (tid == 0) TS_PROBE(1);
+  }
 
   if (warp == 0) {
     if (lane == 0) {
-      // Producer: TMA loads into the ring, unit after unit, across tile boundaries.
-      const int n_units = range.u1 - range.u0;
-      // The weights are written by no kernel, so the first ring of W tiles is requested before
-      // the kernels ahead in the stream have finished; X (their output) only after the wait.
+      // Producer: TMA loads into the ring, unit after unit, across tile and phase boundaries.  The
+      // weights are written by no kernel, so a phase's W tiles are requested before its inputs are
+      // ready (the kernels ahead in the stream for the first phase, the phase before for the others):
+      // up to a whole ring of them.  X, which is those inputs, follows when the wait is over.
       uint64_t w_policy;
       asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(w_policy));
-      const int early = min(n_units, STAGES);
-      for (int i = 0; i < early; ++i) {
-        const int u = range.u0 + i;
-        const int t = u / chunks, kc = u - t * chunks;
-        const uint32_t bar = smem_u32(&full_bar[i]);
-        mbar_expect_tx(bar, C::A_BYTES + C::B_BYTES);
+      int it = 0;  // units requested so far, over all phases: the ring's clock
+      bool ok = true;
+      for (int p = 0; p < phases && ok; ++p) {
+        const GemmArgs& args = chain.g[p];
+        const Range range = cta_range(args, blockIdx.x);
+        const int chunks = args.chunks;
+        const int n_units = range.u1 - range.u0;
+        const CUtensorMap* map_w = &maps.w[p];
+        const CUtensorMap* map_x = &maps.x[p];
+        const int first = it;   // ring clock of this phase's first unit
+        int x_next = it;        // this phase's units before x_next have their X copy requested
+        bool ready = false;     // the phase's inputs may be read
+        // waits for the phase's inputs and requests the X copies that were held back
+        auto inputs_ready = [&]() -> bool {
+          if (p == 0) {
+            ts_pdl_wait();
+            TS_PROBE(6);
+          } else {
+            if (chain.ahead > 0) {
+              // the ring is full and stands still until the inputs are there: meanwhile ask the L2 for
+              // the W tiles of the units that come after the ring
+              const int from = it - first, upto = min(n_units, from + chain.ahead);
+              for (int j = from; j < upto; ++j) {
+                const int u = range.u0 + j;
+                const int t = u / chunks, kc = u - t * chunks;
+                asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map_w), "r"(kc * TILE_K), "r"(t * TILE_N) : "memory");
+              }
+            }
+            if (!grid_wait(chain.sync, p - 1, abort_flag)) return false;
+            __threadfence();
+            asm volatile("fence.proxy.async;" ::: "memory");  // what other SMs stored is read by this SM's copy engine
+            ready_s = p;  // the epilogue warps of this CTA wait for this word, not for the device's
+          }
+          { const GemmArgs& args = chain.g[0]; (void)args; TS_PROBE(8 + 8 * p + 0); }
+          ready = true;
+          for (; x_next < it; ++x_next) {
+            const int kc = (range.u0 + (x_next - first)) % chunks;
+            const int s = x_next % STAGES;
 #pragma unroll
-        for (int a = 0; a < KATOMS; ++a)
-          tma_load_2d_hint(smem_u32(smem + (size_t)i * C::STAGE_BYTES) + a * C::A_ATOM, &map_w, bar, kc * TILE_K + a * ATOM_K, t * TILE_N, w_policy);
+            for (int a = 0; a < KATOMS; ++a)
+              tma_load_2d(smem_u32(smem + (size_t)s * C::STAGE_BYTES) + C::A_BYTES + a * C::B_ATOM, map_x, smem_u32(&full_bar[s]),
+                          kc * TILE_K + a * ATOM_K, 0);
+          }
+          return true;
+        };
+        if (p == 0 && n_units == 0) ts_pdl_wait();
+        if (p > 0 && chain.hold) {
+          // not before this CTA has stored its own share of the phase before: its last trips to the L2
+          // (partial sums, ticket, the finished tile) would queue behind the copies asked for here
+          for (uint32_t i = 0; i < GRID_SPIN_LIMIT && *arrived_flag < p && !*abort_flag; ++i) __nanosleep(40);
+        }
+        for (int i = 0; i < n_units; ++i, ++it) {
+          const int u = range.u0 + i;
+          const int t = u / chunks, kc = u - t * chunks;
+          const int s = it % STAGES;
+          const uint32_t round = (uint32_t)(it / STAGES);
+          if (round > 0) {
+            // the stage's last user may be a unit of this phase that still lacks its X: then nothing
+            // frees the stage before the inputs are there
+            if (!ready && it - STAGES >= first && !inputs_ready()) { ok = false; break; }
+            if (!mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, abort_flag)) { ok = false; break; }
+          }
+          const uint32_t bar = smem_u32(&full_bar[s]);
+          const uint32_t dst = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
+          mbar_expect_tx(bar, C::A_BYTES + C::B_BYTES);
+#pragma unroll
+          for (int a = 0; a < KATOMS; ++a) tma_load_2d_hint(dst + a * C::A_ATOM, map_w, bar, kc * TILE_K + a * ATOM_K, t * TILE_N, w_policy);
+          if (ready) {
+#pragma unroll
+            for (int a = 0; a < KATOMS; ++a) tma_load_2d(dst + C::A_BYTES + a * C::B_ATOM, map_x, bar, kc * TILE_K + a * ATOM_K, 0);
+            x_next = it + 1;
+          }
+        }
+        if (ok && !ready && n_units > 0 && !inputs_ready()) ok = false;
       }
-      ts_pdl_wait();
-      TS_PROBE(6);
-      for (int i = 0; i < early; ++i) {
-        const int u = range.u0 + i;
-        const int kc = u % chunks;
-#pragma unroll
-        for (int a = 0; a < KATOMS; ++a)
-          tma_load_2d(smem_u32(smem + (size_t)i * C::STAGE_BYTES) + C::A_BYTES + a * C::B_ATOM, &map_x, smem_u32(&full_bar[i]),
-                      kc * TILE_K + a * ATOM_K, 0);
-      }
-      int it = early;
-      for (; it < n_units; ++it) {
-        const int u = range.u0 + it;
-        const int t = u / chunks, kc = u - t * chunks;
-        const int s = it % STAGES;
-        const uint32_t round = (uint32_t)(it / STAGES);
-        if (round > 0 && !mbar_wait(smem_u32(&empty_bar[s]), (round - 1) & 1, abort_flag)) break;
-        const uint32_t bar = smem_u32(&full_bar[s]);
-        const uint32_t dst = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
-        mbar_expect_tx(bar, C::A_BYTES + C::B_BYTES);
-#pragma unroll
-        for (int a = 0; a < KATOMS; ++a) tma_load_2d_hint(dst + a * C::A_ATOM, &map_w, bar, kc * TILE_K + a * ATOM_K, t * TILE_N, w_policy);
-#pragma unroll
-        for (int a = 0; a < KATOMS; ++a) tma_load_2d(dst + C::A_BYTES + a * C::B_ATOM, &map_x, bar, kc * TILE_K + a * ATOM_K, 0);
-      }
-      // All loads of this GEMM are on their way.  While its last tiles are multiplied and stored
+      // All loads of this launch are on their way.  While its last tiles are multiplied and stored
       // (and while the small kernels after it run) HBM would idle: ask for this CTA's share of the
       // next GEMM's weights to be brought into L2.
-      if (args.prefetch != nullptr && !*abort_flag) {
+      const GemmArgs& tail = chain.g[phases - 1];
+      if (tail.prefetch != nullptr && !*abort_flag) {
         constexpr unsigned long long PIECE = 32 * 1024;
-        const unsigned long long pieces = (args.prefetch_bytes + PIECE - 1) / PIECE;
+        const unsigned long long pieces = (tail.prefetch_bytes + PIECE - 1) / PIECE;
         for (unsigned long long i = blockIdx.x; i < pieces; i += gridDim.x) {
           const unsigned long long off = i * PIECE;
-          const unsigned bytes = (unsigned)min(PIECE, args.prefetch_bytes - off) & ~15u;
-          if (bytes) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(args.prefetch + off), "r"(bytes) : "memory");
+          const unsigned bytes = (unsigned)min(PIECE, tail.prefetch_bytes - off) & ~15u;
+          if (bytes) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(tail.prefetch + off), "r"(bytes) : "memory");
         }
       }
       if (*abort_flag) {
-        // Let the copies that are still in flight land before shared memory is given up.
+        // Let the copies that are still in flight land before shared memory is given up.  (A stage
+        // whose X copy was never requested cannot complete; its wait runs out, bounded like the others.)
         for (int i = max(0, it - STAGES); i < it; ++i)
-          mbar_wait(smem_u32(&full_bar[i % STAGES]), (uint32_t)(i / STAGES) & 1, abort_flag);
+          mbar_wait(smem_u32(&full_bar[i % STAGES]), (uint32_t)(i / STAGES) & 1, abort_flag, 1u << 16);
       }
     }
   } else if (warp == 1) {
@@ -407,210 +516,279 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
       // MMA issuer.
       int it = 0, item = 0;
       bool ok = true;
-      for (int t = t_first; t <= t_last && ok; ++t, ++item) {
-        const int k0 = max(range.u0, t * chunks) - t * chunks;
-        const int k1 = min(range.u1, (t + 1) * chunks) - t * chunks;
-        const int acc = item & 1;
-        const uint32_t use = (uint32_t)(item >> 1);
-        if (use > 0 && !mbar_wait(smem_u32(&acc_empty[acc]), (use - 1) & 1, abort_flag)) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * MPAD);
-        for (int kc = k0; kc < k1; ++kc, ++it) {
-          const int s = it % STAGES;
-          if (!mbar_wait(smem_u32(&full_bar[s]), (uint32_t)(it / STAGES) & 1, abort_flag)) {
-            ok = false;
-            break;
-          }
+      for (int p = 0; p < phases && ok; ++p) {
+        const GemmArgs& args = chain.g[p];
+        const Range range = cta_range(args, blockIdx.x);
+        const int chunks = args.chunks;
+        const int t_first = range.u0 / chunks;
+        const int t_last = range.u1 > range.u0 ? (range.u1 - 1) / chunks : t_first - 1;
+        for (int t = t_first; t <= t_last && ok; ++t, ++item) {
+          const int k0 = max(range.u0, t * chunks) - t * chunks;
+          const int k1 = min(range.u1, (t + 1) * chunks) - t * chunks;
+          const int acc = item & 1;
+          const uint32_t use = (uint32_t)(item >> 1);
+          if (use > 0 && !mbar_wait(smem_u32(&acc_empty[acc]), (use - 1) & 1, abort_flag)) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          if (it == 0) TS_PROBE(2);
-          const uint32_t a_addr = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
-          const uint64_t adesc = umma_desc_sw128(a_addr);
-          const uint64_t bdesc = umma_desc_sw128(a_addr + C::A_BYTES);
+          const uint32_t tmem_d = tmem_base + (uint32_t)(acc * MPAD);
+          for (int kc = k0; kc < k1; ++kc, ++it) {
+            const int s = it % STAGES;
+            if (!mbar_wait(smem_u32(&full_bar[s]), (uint32_t)(it / STAGES) & 1, abort_flag)) {
+              ok = false;
+              break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (it == 0) TS_PROBE(2);
+            if (t == t_first && kc == k0) { const GemmArgs& args = chain.g[0]; (void)args; TS_PROBE(8 + 8 * p + 1); }
+            const uint32_t a_addr = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
+            const uint64_t adesc = umma_desc_sw128(a_addr);
+            const uint64_t bdesc = umma_desc_sw128(a_addr + C::A_BYTES);
 #pragma unroll
-          for (int k = 0; k < TILE_K / UMMA_K; ++k) {
-            // 16 bf16 = 32 bytes further along K inside the swizzle atom: +2 in the address field;
-            // the next atom (box) of the stage starts A_ATOM / B_ATOM bytes further
-            const int atom = k / (ATOM_K / UMMA_K), kk = k % (ATOM_K / UMMA_K);
-            umma_bf16(tmem_d, adesc + (uint64_t)(atom * (C::A_ATOM >> 4) + 2 * kk), bdesc + (uint64_t)(atom * (C::B_ATOM >> 4) + 2 * kk), IDESC,
-                      (kc > k0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+              // 16 bf16 = 32 bytes further along K inside the swizzle atom: +2 in the address field;
+              // the next atom (box) of the stage starts A_ATOM / B_ATOM bytes further
+              const int atom = k / (ATOM_K / UMMA_K), kk = k % (ATOM_K / UMMA_K);
+              umma_bf16(tmem_d, adesc + (uint64_t)(atom * (C::A_ATOM >> 4) + 2 * kk), bdesc + (uint64_t)(atom * (C::B_ATOM >> 4) + 2 * kk), IDESC,
+                        (kc > k0 || k > 0) ? 1u : 0u);
+            }
+            umma_commit(smem_u32(&empty_bar[s]));  // arrives when these MMAs have read the stage
           }
-          umma_commit(smem_u32(&empty_bar[s]));  // arrives when these MMAs have read the stage
+          if (ok) umma_commit(smem_u32(&acc_full[acc]));  // arrives when this accumulator is complete
         }
-        if (ok) umma_commit(smem_u32(&acc_full[acc]));  // arrives when this accumulator is complete
+        { const GemmArgs& args = chain.g[0]; (void)args; TS_PROBE(8 + 8 * p + 2); }
       }
-      TS_PROBE(3);
+      {
+        const GemmArgs& args = chain.g[0];
+        (void)args;
+        TS_PROBE(3);
+      }
     }
   } else {
     // Epilogue warps 2..5: TMEM lanes 32 * (warp % 4) .. + 31.
     const int quarter = warp & 3;
     const int etid = (warp - 2) * 32 + lane;  // 0..127 among the epilogue threads
-    if (MPAD <= FUSED_MAX_ROWS && args.mode == EPI_QK_ROPE) {
-      // the step's positions and cache slots and the small weight vectors of the rotation epilogue
-      // (none of them written by a kernel of the step) go to the L1 ahead of their use
-      if (etid < args.M) {
-        asm volatile("prefetch.global.L1 [%0];" ::"l"(args.positions + etid));
-        asm volatile("prefetch.global.L1 [%0];" ::"l"(args.slot_mapping + etid));
-      } else if (etid < 64) {
-        if (args.inv_freq != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.inv_freq + (etid & 7) * 8));
-      } else if (etid < 96) {
-        if (args.q_norm_w != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.q_norm_w + (etid & 15) * 8));
-      } else {
-        if (args.k_norm_w != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.k_norm_w + (etid & 15) * 8));
-      }
-    }
-    ts_pdl_wait();  // nothing is stored before the kernels ahead in the stream are done
-    const bool fused = MPAD <= FUSED_MAX_ROWS && (args.mode != EPI_PLAIN || args.scale_ssq != nullptr);
-    if (fused) {
-      // rstd of every row of x's source, from the per-tile sums of squares the kernel before left
-      if (etid < args.M) {
-        float sum = 0.f;
-        if (args.scale_ssq != nullptr)
-          for (int j = 0; j < args.scale_tiles; ++j) sum += __ldcg(args.scale_ssq + (size_t)j * args.M + etid);
-        rstd_s[etid] = args.scale_ssq != nullptr ? rsqrtf(sum / args.scale_width + args.scale_eps) : 1.f;
-      }
-      epilogue_sync();
-    }
     int item = 0;
-    for (int t = t_first; t <= t_last; ++t, ++item) {
-      const int k0 = max(range.u0, t * chunks) - t * chunks;
-      const int k1 = min(range.u1, (t + 1) * chunks) - t * chunks;
-      const bool whole = (k0 == 0 && k1 == chunks);
-      const int acc = item & 1;
-      if (!mbar_wait(smem_u32(&acc_full[acc]), (uint32_t)(item >> 1) & 1, abort_flag)) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (etid == 0 && t == t_last) TS_PROBE(4);
-      if (fused && args.mode == EPI_RESIDUAL_NORM) {
-        // whoever finishes this tile adds it to the residual stream: ask for those values now,
-        // so that they are in the L1 when the partial sums and the ticket have made their trips
-        for (int idx = etid; idx < args.M * 32; idx += 128) {
-          const int pn = t * TILE_N + (idx & 31) * 4;
-          if (pn < args.N) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.hidden + (size_t)(idx >> 5) * args.ldh + pn));
+    bool alive = true;
+    for (int p = 0; p < phases && alive; ++p) {
+      const GemmArgs& args = chain.g[p];
+      const Range range = cta_range(args, blockIdx.x);
+      const int chunks = args.chunks;
+      const int t_first = range.u0 / chunks;
+      const int t_last = range.u1 > range.u0 ? (range.u1 - 1) / chunks : t_first - 1;
+      if (MPAD <= FUSED_MAX_ROWS && args.mode == EPI_QK_ROPE && t_last >= t_first) {
+        // the step's positions and cache slots and the small weight vectors of the rotation epilogue
+        // (none of them written by a kernel of the step) go to the L1 ahead of their use
+        if (etid < args.M) {
+          asm volatile("prefetch.global.L1 [%0];" ::"l"(args.positions + etid));
+          asm volatile("prefetch.global.L1 [%0];" ::"l"(args.slot_mapping + etid));
+        } else if (etid < 64) {
+          if (args.inv_freq != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.inv_freq + (etid & 7) * 8));
+        } else if (etid < 96) {
+          if (args.q_norm_w != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.q_norm_w + (etid & 15) * 8));
+        } else {
+          if (args.k_norm_w != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.k_norm_w + (etid & 15) * 8));
         }
-        if (etid < 32 && t * TILE_N + etid * 4 < args.N) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.norm_w + t * TILE_N + etid * 4));
       }
-      const int n_local = quarter * 32 + lane;
-      const int n = t * TILE_N + n_local;
-      const int slot = (t == t_first) ? 0 : 1;
-      float* part = args.partial + ((size_t)(blockIdx.x * 2 + slot) * args.M) * TILE_N;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * MPAD);
-      uint32_t r[MPAD / 16][16];
-#pragma unroll
-      for (int c = 0; c < MPAD / 16; ++c) {
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-            : "=r"(r[c][0]), "=r"(r[c][1]), "=r"(r[c][2]), "=r"(r[c][3]), "=r"(r[c][4]), "=r"(r[c][5]), "=r"(r[c][6]),
-              "=r"(r[c][7]), "=r"(r[c][8]), "=r"(r[c][9]), "=r"(r[c][10]), "=r"(r[c][11]), "=r"(r[c][12]), "=r"(r[c][13]),
-              "=r"(r[c][14]), "=r"(r[c][15])
-            : "r"(taddr + c * 16));
+      if (p == 0) {
+        ts_pdl_wait();  // nothing is stored before the kernels ahead in the stream are done
+      } else if (t_last >= t_first) {
+        // this phase reads what every CTA stored in the phase before (row sums, the residual stream)
+        // (the producer thread polls the device-wide flag for the CTA and says so in shared memory)
+        if (etid == 0) {
+          bool there = false;
+          for (uint32_t i = 0; i < GRID_SPIN_LIMIT && !there && !*abort_flag; ++i) {
+            there = *ready_flag >= p;
+            if (!there) __nanosleep(40);
+          }
+          if (there) there = grid_wait(chain.sync, p - 1, abort_flag);  // set by now: one load, and the ordering that goes with it
+          if (there) __threadfence();
+          else *abort_flag = 1;
+          go_s = there ? 1 : 0;
+        }
+        epilogue_sync();
+        if (go_s == 0) break;  // the same for all epilogue threads
+        if (etid == 0) { const GemmArgs& args = chain.g[0]; (void)args; TS_PROBE(8 + 8 * p + 5); }
       }
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      // The accumulator is in registers: hand it back to the MMA warp before storing.
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
+      const bool fused = MPAD <= FUSED_MAX_ROWS && (args.mode != EPI_PLAIN || args.scale_ssq != nullptr);
+      if (fused && t_last >= t_first) {
+        // rstd of every row of x's source, from the per-tile sums of squares the kernel before left
+        if (etid < args.M) {
+          float sum = 0.f;
+          if (args.scale_ssq != nullptr)
+            for (int j = 0; j < args.scale_tiles; ++j) sum += __ldcg(args.scale_ssq + (size_t)j * args.M + etid);
+          rstd_s[etid] = args.scale_ssq != nullptr ? rsqrtf(sum / args.scale_width + args.scale_eps) : 1.f;
+        }
+        epilogue_sync();
+      }
+      for (int t = t_first; t <= t_last; ++t, ++item) {
+        const int k0 = max(range.u0, t * chunks) - t * chunks;
+        const int k1 = min(range.u1, (t + 1) * chunks) - t * chunks;
+        const bool whole = (k0 == 0 && k1 == chunks);
+        const int acc = item & 1;
+        if (!mbar_wait(smem_u32(&acc_full[acc]), (uint32_t)(item >> 1) & 1, abort_flag)) { alive = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (etid == 0 && t == t_last && p == phases - 1) TS_PROBE(4);
+        if (etid == 0 && t == t_last) { const GemmArgs& args = chain.g[0]; (void)args; TS_PROBE(8 + 8 * p + 3); }
+        if (fused && args.mode == EPI_RESIDUAL_NORM) {
+          // whoever finishes this tile adds it to the residual stream: ask for those values now,
+          // so that they are in the L1 when the partial sums and the ticket have made their trips
+          for (int idx = etid; idx < args.M * 32; idx += 128) {
+            const int pn = t * TILE_N + (idx & 31) * 4;
+            if (pn < args.N) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.hidden + (size_t)(idx >> 5) * args.ldh + pn));
+          }
+          if (etid < 32 && t * TILE_N + etid * 4 < args.N) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.norm_w + t * TILE_N + etid * 4));
+        }
+        const int n_local = quarter * 32 + lane;
+        const int n = t * TILE_N + n_local;
+        const int slot = (t == t_first) ? 0 : 1;
+        float* part = args.partial + ((size_t)(blockIdx.x * 2 + slot) * args.M) * TILE_N;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * MPAD);
+        uint32_t r[MPAD / 16][16];
 #pragma unroll
-      for (int c = 0; c < MPAD / 16; ++c) {
+        for (int c = 0; c < MPAD / 16; ++c) {
+          asm volatile(
+              "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+              : "=r"(r[c][0]), "=r"(r[c][1]), "=r"(r[c][2]), "=r"(r[c][3]), "=r"(r[c][4]), "=r"(r[c][5]), "=r"(r[c][6]),
+                "=r"(r[c][7]), "=r"(r[c][8]), "=r"(r[c][9]), "=r"(r[c][10]), "=r"(r[c][11]), "=r"(r[c][12]), "=r"(r[c][13]),
+                "=r"(r[c][14]), "=r"(r[c][15])
+              : "r"(taddr + c * 16));
+        }
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        // The accumulator is in registers: hand it back to the MMA warp before storing.
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int m = c * 16 + i;
-          if (m < args.M) {
-            const float v = __uint_as_float(r[c][i]);
-            if (!whole)
-              part[(size_t)m * TILE_N + n_local] = v;
-            else if (fused)
-              tile_s[(MPAD <= FUSED_MAX_ROWS ? m : 0) * TILE_N + n_local] = v;
-            else if (n < args.N) {
-              if (args.out_f32)
-                reinterpret_cast<float*>(args.out)[(size_t)m * args.ldo + n] = v;
-              else
-                reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)m * args.ldo + n] = __float2bfloat16_rn(v);
+        for (int c = 0; c < MPAD / 16; ++c) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int m = c * 16 + i;
+            if (m < args.M) {
+              const float v = __uint_as_float(r[c][i]);
+              if (!whole)
+                part[(size_t)m * TILE_N + n_local] = v;
+              else if (fused)
+                tile_s[(MPAD <= FUSED_MAX_ROWS ? m : 0) * TILE_N + n_local] = v;
+              else if (n < args.N) {
+                if (args.out_f32)
+                  reinterpret_cast<float*>(args.out)[(size_t)m * args.ldo + n] = v;
+                else
+                  reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)m * args.ldo + n] = __float2bfloat16_rn(v);
+              }
             }
           }
         }
-      }
-      bool last = false;
-      if (!whole) {
-        // Ticket: whoever arrives last for this tile adds the slots, in contributor order.
-        const int c_first = (int)(((long long)t * chunks) / args.units_per);
-        const int c_last = (int)(((long long)(t + 1) * chunks - 1) / args.units_per);
-        __threadfence();
-        epilogue_sync();
-        if (etid == 0) {
-          const int ticket = atomicAdd(&args.counters[t], 1);
-          last_s = (ticket == c_last - c_first) ? 1 : 0;
-        }
-        epilogue_sync();
-        last = last_s != 0;
-        epilogue_sync();  // everyone has read the flag before the next tile may rewrite it
-        if (last) {
+        bool last = false;
+        if (!whole) {
+          // Ticket: whoever arrives last for this tile adds the slots, in contributor order.
+          const int c_first = (int)(((long long)t * chunks) / args.units_per);
+          const int c_last = (int)(((long long)(t + 1) * chunks - 1) / args.units_per);
           __threadfence();
-          // Slot of every contributor for this tile (0: it is that CTA's first tile, else 1).
-          const float* src[MAX_CONTRIB];
-          const int nc = min(c_last - c_first + 1, MAX_CONTRIB);
-#pragma unroll
-          for (int j = 0; j < MAX_CONTRIB; ++j) {
-            const int c = c_first + min(j, nc - 1);
-            const int c_t_first = (int)(((long long)c * args.units_per) / chunks);
-            src[j] = args.partial + (size_t)(c * 2 + ((t == c_t_first) ? 0 : 1)) * args.M * TILE_N;
+          epilogue_sync();
+          if (etid == 0) {
+            const int ticket = atomicAdd(&args.counters[t], 1);
+            last_s = (ticket == c_last - c_first) ? 1 : 0;
           }
-          // Two pieces of four columns per thread and pass, all their loads first (they are
-          // independent: one trip to the L2 per pass, not one per piece), then the sums in contributor order.
-          constexpr int PIECES = 2;
-          const int total = args.M * (TILE_N / 4);
-          for (int base = etid; base < total; base += 128 * PIECES) {
-            float4 v[PIECES][MAX_CONTRIB];
+          epilogue_sync();
+          last = last_s != 0;
+          epilogue_sync();  // everyone has read the flag before the next tile may rewrite it
+          if (last) {
+            __threadfence();
+            // Slot of every contributor for this tile (0: it is that CTA's first tile, else 1).
+            const float* src[MAX_CONTRIB];
+            const int nc = min(c_last - c_first + 1, MAX_CONTRIB);
 #pragma unroll
-            for (int u = 0; u < PIECES; ++u) {
-              const int idx = base + u * 128;
-              if (idx < total) {
-                const size_t off = (size_t)(idx / (TILE_N / 4)) * TILE_N + (idx % (TILE_N / 4)) * 4;
+            for (int j = 0; j < MAX_CONTRIB; ++j) {
+              const int c = c_first + min(j, nc - 1);
+              const int c_t_first = (int)(((long long)c * args.units_per) / chunks);
+              src[j] = args.partial + (size_t)(c * 2 + ((t == c_t_first) ? 0 : 1)) * args.M * TILE_N;
+            }
+            // Two pieces of four columns per thread and pass, all their loads first (they are
+            // independent: one trip to the L2 per pass, not one per piece), then the sums in contributor order.
+            constexpr int PIECES = 2;
+            const int total = args.M * (TILE_N / 4);
+            for (int base = etid; base < total; base += 128 * PIECES) {
+              float4 v[PIECES][MAX_CONTRIB];
+#pragma unroll
+              for (int u = 0; u < PIECES; ++u) {
+                const int idx = base + u * 128;
+                if (idx < total) {
+                  const size_t off = (size_t)(idx / (TILE_N / 4)) * TILE_N + (idx % (TILE_N / 4)) * 4;
+#pragma unroll
+                  for (int j = 0; j < MAX_CONTRIB; ++j)
+                    if (j < nc) v[u][j] = __ldcg(reinterpret_cast<const float4*>(src[j] + off));
+                }
+              }
+#pragma unroll
+              for (int u = 0; u < PIECES; ++u) {
+                const int idx = base + u * 128;
+                if (idx >= total) continue;
+                const int m = idx / (TILE_N / 4), nl = (idx % (TILE_N / 4)) * 4;
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                 for (int j = 0; j < MAX_CONTRIB; ++j)
-                  if (j < nc) v[u][j] = __ldcg(reinterpret_cast<const float4*>(src[j] + off));
-              }
-            }
+                  if (j < nc) { sum.x += v[u][j].x; sum.y += v[u][j].y; sum.z += v[u][j].z; sum.w += v[u][j].w; }
+                const int nn = t * TILE_N + nl;
+                const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+                if (fused) {
+                  *reinterpret_cast<float4*>(&tile_s[(MPAD <= FUSED_MAX_ROWS ? m : 0) * TILE_N + nl]) = sum;
+                  continue;
+                }
 #pragma unroll
-            for (int u = 0; u < PIECES; ++u) {
-              const int idx = base + u * 128;
-              if (idx >= total) continue;
-              const int m = idx / (TILE_N / 4), nl = (idx % (TILE_N / 4)) * 4;
-              float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-              for (int j = 0; j < MAX_CONTRIB; ++j)
-                if (j < nc) { sum.x += v[u][j].x; sum.y += v[u][j].y; sum.z += v[u][j].z; sum.w += v[u][j].w; }
-              const int nn = t * TILE_N + nl;
-              const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
-              if (fused) {
-                *reinterpret_cast<float4*>(&tile_s[(MPAD <= FUSED_MAX_ROWS ? m : 0) * TILE_N + nl]) = sum;
-                continue;
-              }
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (nn + j < args.N) {
-                  if (args.out_f32)
-                    reinterpret_cast<float*>(args.out)[(size_t)m * args.ldo + nn + j] = vals[j];
-                  else
-                    reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)m * args.ldo + nn + j] = __float2bfloat16_rn(vals[j]);
+                for (int j = 0; j < 4; ++j) {
+                  if (nn + j < args.N) {
+                    if (args.out_f32)
+                      reinterpret_cast<float*>(args.out)[(size_t)m * args.ldo + nn + j] = vals[j];
+                    else
+                      reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)m * args.ldo + nn + j] = __float2bfloat16_rn(vals[j]);
+                  }
                 }
               }
             }
+            if (etid == 0) args.counters[t] = 0;
           }
-          if (etid == 0) args.counters[t] = 0;
+        }
+        if (fused && (whole || last)) {  // the same for all epilogue threads
+          epilogue_sync();  // tile_s holds the tile's final sums
+          fused_epilogue<MPAD>(args, t, etid, lane, tile_s, rstd_s);
+          epilogue_sync();  // before the next tile overwrites tile_s
         }
       }
-      if (fused && (whole || last)) {  // the same for all epilogue threads
-        epilogue_sync();  // tile_s holds the tile's final sums
-        fused_epilogue<MPAD>(args, t, etid, lane, tile_s, rstd_s);
-        epilogue_sync();  // before the next tile overwrites tile_s
+      if (alive && p + 1 < phases) {
+        // this CTA's share of the phase is stored: say so to the grid (the next phase's copy engines
+        // read it, hence the proxy fence)
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence();
+        epilogue_sync();
+        if (etid == 0) {
+          grid_arrive(chain.sync, p, ctas);
+          arrived_s = p + 1;
+        }
+        if (etid == 0) { const GemmArgs& args = chain.g[0]; (void)args; TS_PROBE(8 + 8 * p + 4); }
       }
     }
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (tid == 0) TS_PROBE(5);
-  if (abort_s != 0 && tid == 0) *args.error = 1;
+  {
+    const GemmArgs& args = chain.g[0];
+    (void)args;
+    if (tid == 0) TS_PROBE(5);
+  }
+  if (abort_s != 0 && tid == 0) *chain.g[0].error = 1;
+  if (phases > 1 && tid == 0) {
+    // the last CTA to leave zeroes the barrier's counters: by then everyone has passed every wait
+    __threadfence();
+    if (atomicAdd(sync_departed(chain.sync), 1u) == ctas - 1) {
+      for (int i = 0; i < MAX_PHASES; ++i) {
+        *sync_counter(chain.sync, i) = 0;
+        *sync_flag(chain.sync, i) = 0;
+      }
+      *sync_departed(chain.sync) = 0;
+      __threadfence();
+    }
+  }
   if (warp == 0) {
     __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
@@ -700,14 +878,58 @@ int tensor_map(const void* ptr, long long rows, long long cols, long long ld, in
 }
 
 template <int MPAD>
-int launch_skinny(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, int ctas, cudaStream_t stream) {
+int launch_skinny(const ChainMaps& maps, const ChainArgs& chain, int ctas, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<MPAD>::SMEM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return ts_launch(gemm_skinny_kernel<MPAD>, dim3(ctas), dim3(NUM_THREADS), Cfg<MPAD>::SMEM, stream, mw, mx, a);
+  return ts_launch(gemm_skinny_kernel<MPAD>, dim3(ctas), dim3(NUM_THREADS), Cfg<MPAD>::SMEM, stream, maps, chain);
+}
+
+// Products waiting to be launched together (see ts_gemm_chain_begin).  One list for the process:
+// the engine records and launches from one thread, on one stream at a time.
+struct PendingChain {
+  ChainMaps maps;
+  ChainArgs args;
+  int mpad = 0;
+  int ctas = 0;
+  cudaStream_t stream = nullptr;
+  bool recording = false;
+  unsigned int* sync = nullptr;
+  int launches = 0;  // kernels launched by the flushes since the last ts_gemm_chain_begin
+};
+PendingChain pending;
+
+int launch_pending() {
+  if (pending.args.n == 0) return 0;
+  ChainArgs& c = pending.args;
+  for (int i = 0; i + 1 < c.n; ++i) {  // the next phase streams its weights itself: nothing to ask ahead
+    c.g[i].prefetch = nullptr;
+    c.g[i].prefetch_bytes = 0;
+  }
+  c.sync = pending.sync;
+  static int hold = -1, ahead = -1;
+  if (hold < 0) {
+    const char* v = getenv("TS_GEMM_HOLD");
+    hold = v ? atoi(v) : 1;
+    v = getenv("TS_GEMM_AHEAD");
+    ahead = v ? atoi(v) : 0;
+  }
+  c.hold = hold;
+  c.ahead = ahead;
+  int st;
+  switch (pending.mpad) {
+    case 16: st = launch_skinny<16>(pending.maps, c, pending.ctas, pending.stream); break;
+    case 32: st = launch_skinny<32>(pending.maps, c, pending.ctas, pending.stream); break;
+    case 64: st = launch_skinny<64>(pending.maps, c, pending.ctas, pending.stream); break;
+    default: st = launch_skinny<128>(pending.maps, c, pending.ctas, pending.stream); break;
+  }
+  c.n = 0;
+  pending.ctas = 0;
+  pending.launches += 1;
+  return st;
 }
 
 int sm_count() {
@@ -831,18 +1053,52 @@ static int run_gemm(const void* x, const void* w, int M, int N, int K, long long
   a.prefetch = (prefetch_bytes > 0 && ((uintptr_t)prefetch % 16) == 0) ? (const char*)prefetch : nullptr;
   a.prefetch_bytes = prefetch_bytes > 0 ? (unsigned long long)prefetch_bytes : 0ull;
 #ifdef TS_GEMM_PROBE
-  // every launch writes a region of its own (256 CTAs x 8 stamps), 512 regions in turn
+  // every product writes a region of its own (256 CTAs x 64 stamps), 64 regions in turn; the stamps of a chain land in its first product's region
   static int probe_launch = 0;
-  a.probe = ts_gemm_probe_buffer ? ts_gemm_probe_buffer + (size_t)(probe_launch++ % 512) * 2048 : nullptr;
+  a.probe = ts_gemm_probe_buffer ? ts_gemm_probe_buffer + (size_t)(probe_launch++ % 64) * 16384 : nullptr;
 #endif
   cudaStream_t stream = (cudaStream_t)stream_;
-  switch (mpad) {
-    case 16: return launch_skinny<16>(mw, mx, a, ctas, stream);
-    case 32: return launch_skinny<32>(mw, mx, a, ctas, stream);
-    case 64: return launch_skinny<64>(mw, mx, a, ctas, stream);
-    default: return launch_skinny<128>(mw, mx, a, ctas, stream);
+  // While a chain is being recorded the product joins it (same row count and stream, and room
+  // left; otherwise what is pending is launched first); else it is a launch of its own.
+  if (pending.args.n > 0 && (!pending.recording || pending.mpad != mpad || pending.args.g[0].M != M || pending.stream != stream ||
+                             pending.args.n == MAX_PHASES)) {
+    st = launch_pending();
+    if (st != 0) return st;
   }
+  const int i = pending.args.n;
+  pending.args.g[i] = a;
+  pending.maps.w[i] = mw;
+  pending.maps.x[i] = mx;
+  pending.args.n = i + 1;
+  pending.mpad = mpad;
+  pending.stream = stream;
+  if (ctas > pending.ctas) pending.ctas = ctas;
+  if (pending.recording && pending.sync != nullptr) return 0;
+  return launch_pending();
 }
+
+// Chains.  Between ts_gemm_chain_begin and ts_gemm_chain_end the products of this file are not
+// launched when they are called but collected, up to MAX_PHASES of them, and launched as ONE kernel
+// by ts_gemm_chain_flush (or when the list is full, or when a product with another row count or
+// stream arrives): each reads what the one before it wrote.  The caller flushes before anything
+// else reads a collected product's output, and keeps every buffer alive until then.  `sync`:
+// ts_gemm_chain_sync_words() unsigned ints in device memory, zero before the first chain (the
+// kernel leaves them zero); chains that share them must not run at the same time (one stream).
+TS_EXPORT void ts_gemm_chain_begin(unsigned int* sync) {
+  pending.recording = true;
+  pending.sync = sync;
+  pending.launches = 0;
+}
+TS_EXPORT int ts_gemm_chain_flush(void) { return launch_pending(); }
+TS_EXPORT int ts_gemm_chain_end(void) {
+  const int st = launch_pending();
+  pending.recording = false;
+  return st;
+}
+// Kernels that the flushes launched since ts_gemm_chain_begin.
+TS_EXPORT int ts_gemm_chain_launches(void) { return pending.launches; }
+TS_EXPORT int ts_gemm_chain_max_phases(void) { return MAX_PHASES; }
+TS_EXPORT int ts_gemm_chain_sync_words(void) { return (2 * MAX_PHASES + 1) * SYNC_LINE; }
 
 TS_EXPORT int ts_gemm_skinny_fused(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
                                    long long ldw, long long ldo, int out_f32, int mode, const float* scale_ssq,

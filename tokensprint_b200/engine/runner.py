@@ -518,10 +518,11 @@ class ModelRunner:
                     raise ValueError(f"request {e.cache.request!r}: wanted place outside its 1 token")
             return self._step_graph(bucket, entries, fed_ids)
         step, rows, R = self.build_context(entries, fed_ids)
-        hidden, pending = self.model.forward_hidden(step, self.layer_caches)
-        if R == 0:
-            return torch.empty((0, self.vocab_size), device=self.device, dtype=torch.float32)
-        return self.model.logits(hidden, pending, rows, R)
+        with self.model.chain_scope(step.num_tokens):
+            hidden, pending = self.model.forward_hidden(step, self.layer_caches)
+            if R == 0:
+                return torch.empty((0, self.vocab_size), device=self.device, dtype=torch.float32)
+            return self.model.logits(hidden, pending, rows, R)
 
     # -- cache life cycle (thin wrappers that keep device memory in step) ------------------
 

@@ -133,15 +133,27 @@ class Model:
             last = i + 1 == len(order)
             step.weight_after = self.head if last else self.blocks[order[i + 1].layer].first_weight()
             step.norm_after = (self.final_norm if fold_final else None) if last else self.blocks[order[i + 1].layer].entry_norm()
-            pending = self.blocks[run.layer].forward(hidden, pending, step, caches[i])
+            block = self.blocks[run.layer]
+            if not block.reads_through_ops:
+                ops.flush_gemm_chain()
+            pending = block.forward(hidden, pending, step, caches[i])
         step.weight_after = step.norm_after = None
         return hidden, pending
+
+    def chain_scope(self, num_tokens: int) -> "ops.gemm_chain":
+        """The context in which a step of `num_tokens` tokens runs: where ops.GEMM_CHAIN is switched on,
+        the engine's own products of a step of few tokens in bfloat16 that follow one another are
+        launched together (ops.gemm_chain)."""
+        return ops.gemm_chain(self.device, enabled=ops.GEMM_CHAIN and folding_possible(num_tokens, self.dtype))
 
     def logits(self, hidden: torch.Tensor, pending, rows: torch.Tensor, num_rows: int) -> torch.Tensor:
         """Final norm on the wanted rows only, then the head (and what the architecture does to the
         logits after it): float32 [R, V] (engine/model.py:75-86).
         `pending`: the last branch output not yet added, or a PreNormed of the final norm."""
+        if not self.final_norm.reads_through_ops:
+            ops.flush_gemm_chain()
         out = self._head_product(hidden, pending, rows, num_rows)
+        ops.flush_gemm_chain()  # the logits leave this package's ops here
         if self.logits_transform is not None:
             out = self.logits_transform.forward(out, None)
         return out
@@ -156,5 +168,6 @@ class Model:
         return linear_float32_out(normed, self.head)
 
     def forward(self, step: StepContext, caches: list[LayerCache], rows: torch.Tensor, num_rows: int) -> torch.Tensor:
-        hidden, pending = self.forward_hidden(step, caches)
-        return self.logits(hidden, pending, rows, num_rows)
+        with self.chain_scope(step.num_tokens):
+            hidden, pending = self.forward_hidden(step, caches)
+            return self.logits(hidden, pending, rows, num_rows)

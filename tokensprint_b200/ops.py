@@ -116,10 +116,94 @@ def _act_code(name: str, t: torch.Tensor) -> int:
 
 
 # ---------------------------------------------------------------------------
+# chains of products: several skinny GEMMs that feed one another, launched as one kernel
+
+# Whether a model step chains its products by itself (Model.chain_scope).  Off: measured on B200 at
+# Qwen3-8B sizes, the four products of a decode layer take 87 us as four launches (programmatic
+# dependent launch already overlaps a kernel's start with its predecessor's end) and 102 to 109 us
+# as one chained launch: what separates two products is the chain of trips to the L2 at the end of
+# the first (partial sums, ticket, sums, the finished tile) and the first copies of the second, about
+# 8 us either way, and inside one kernel the copies that early CTAs ask for the next phase delay the
+# last copies of the late ones.  TS_GEMM_CHAIN=1 switches it on for measurements.
+GEMM_CHAIN = _os.environ.get("TS_GEMM_CHAIN", "0") == "1"
+_chain_open = False
+_chain_keep: list = []  # tensors that products waiting in the chain read or write
+_chain_counted = 0
+
+
+def _chain_sync_words(device: torch.device) -> torch.Tensor:
+    """Per (device, stream): the counters of the chained kernel's grid barrier (zero between launches)."""
+    counters, _ = _gemm_workspace(device)
+    return counters[_GEMM_MAX_TILES:]
+
+
+class gemm_chain:
+    """While this context is open, the engine's own few-row products are not launched when they are
+    called: they are collected, and up to `ts_gemm_chain_max_phases` of them that follow one another
+    are launched as ONE kernel, in which each starts fetching its weights while the one before it is
+    still being finished.  Every other op of this module launches what is pending before it runs, so
+    a caller that only uses these ops sees no difference; code that reads a product's output by
+    other means (a torch op) calls `flush_gemm_chain()` first.  Nothing happens when `enabled` is
+    false, and chains do not nest."""
+
+    def __init__(self, device: torch.device, enabled: bool = True) -> None:
+        self.device, self.enabled = device, bool(enabled)
+
+    def __enter__(self):
+        global _chain_open, _chain_counted
+        self.mine = self.enabled and not _chain_open
+        if self.mine:
+            fn = library().ts_gemm_chain_begin
+            fn.argtypes = [_c_void_p]
+            fn.restype = None
+            fn(_chain_sync_words(self.device).data_ptr())
+            _chain_open = True
+            _chain_counted = 0
+        return self
+
+    def __exit__(self, *exc):
+        global _chain_open
+        if self.mine:
+            try:
+                flush_gemm_chain(end=True)
+            finally:
+                _chain_open = False
+                _chain_keep.clear()
+        return False
+
+
+def flush_gemm_chain(end: bool = False) -> None:
+    """Launches the products that wait in the chain (nothing, if no chain is open)."""
+    global launch_count, _chain_counted
+    if not _chain_open:
+        return
+    lib = library()
+    status = (lib.ts_gemm_chain_end if end else lib.ts_gemm_chain_flush)()
+    launched = lib.ts_gemm_chain_launches()
+    launch_count += launched - _chain_counted
+    _chain_counted = launched
+    _chain_keep.clear()
+    if status != 0:
+        raise KernelError(f"chained products: CUDA error {status} at launch")
+
+
+def _check_product(name: str, status: int, *tensors) -> None:
+    """_check for a product that may have joined a chain instead of being launched."""
+    global launch_count, _chain_counted
+    if not _chain_open:
+        _check(name, status)
+        return
+    _chain_keep.append(tensors)
+    launched = library().ts_gemm_chain_launches()  # a full list, or another row count, launched what was pending
+    launch_count += launched - _chain_counted
+    _chain_counted = launched
+    if status != 0:
+        _check(name, status)
 
 
 def embed_gather(hidden: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
     """hidden[t] = table[ids[t]] widened to float32.  hidden [T,H] f32, table [V,H], ids [T] i32."""
+    flush_gemm_chain()
     _cuda_contig("hidden", hidden, torch.float32)
     _cuda_contig("table", table)
     _cuda_contig("ids", ids, torch.int32)
@@ -134,6 +218,7 @@ def embed_gather(hidden: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -
 def feed_tokens(ids: torch.Tensor, source: torch.Tensor, lanes: torch.Tensor, rows: torch.Tensor, n: int) -> None:
     """ids[lanes[i]] = source[rows[i]] for i < n (all int32, on the device): token ids that an
     earlier kernel produced go into a step's inputs without passing through the host."""
+    flush_gemm_chain()
     for name, t in (("ids", ids), ("source", source), ("lanes", lanes), ("rows", rows)):
         _cuda_contig(name, t, torch.int32)
     if n > lanes.numel() or n > rows.numel():
@@ -154,6 +239,7 @@ def add_rmsnorm(
     hidden [T,H] f32; delta [T,H] of out's dtype or None; weight [H] f32; out [rows,H].
     With `row_index` ([rows] i32) only those rows are normed and hidden is left as it is.
     """
+    flush_gemm_chain()
     _cuda_contig("hidden", hidden, torch.float32)
     _cuda_contig("weight", weight, torch.float32)
     _cuda_contig("out", out)
@@ -178,6 +264,7 @@ def add_rmsnorm(
 
 def residual_add(hidden: torch.Tensor, delta: torch.Tensor) -> None:
     """hidden += delta in float32.  hidden [T,H] f32, delta [T,H] f32 or bf16."""
+    flush_gemm_chain()
     _cuda_contig("hidden", hidden, torch.float32)
     _cuda_contig("delta", delta)
     if delta.shape != hidden.shape:
@@ -189,6 +276,7 @@ def residual_add(hidden: torch.Tensor, delta: torch.Tensor) -> None:
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
     """out[t,i] = silu(gate[t,i]) * up[t,i].  gate_up [T,2I], out [T,I].  block 0: gate i at column
     i, up at I + i; block 64: blocks of 128 columns, 64 gates and then their 64 ups."""
+    flush_gemm_chain()
     _cuda_contig("gate_up", gate_up)
     _cuda_contig("out", out, gate_up.dtype)
     T, I = out.shape
@@ -224,6 +312,7 @@ def qk_norm_rope_store(
     Norm weights [d] f32 or None (no norm); inv_freq [rot/2] f32 or None (no rotation);
     a rotation narrower than d leaves the upper dims as they are.
     """
+    flush_gemm_chain()
     _cuda_contig("qkv", qkv)
     _cuda_contig("q_out", q_out, qkv.dtype)
     _cuda_contig("positions", positions, torch.int32)
@@ -288,6 +377,7 @@ def attention_paged_simple(
     q/out [T,nq*d]; caches [pages,page,nkv,d]; positions, seq_index [T] i32;
     block_table [B,max_blocks] i32.  window > 0: a query sees its last `window` keys.
     """
+    flush_gemm_chain()
     _cuda_contig("q", q)
     _cuda_contig("k_cache", k_cache, q.dtype)
     _cuda_contig("v_cache", v_cache, q.dtype)
@@ -321,6 +411,7 @@ def sample(
 ) -> None:
     """One token per row of float32 logits [R,V]: argmax where temperature is 0, else the
     exponential race keyed by keys[r] (int64, the noise stream of that row).  out [R] i32."""
+    flush_gemm_chain()
     if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
         raise KernelError("sample: logits must be a float32 CUDA matrix with unit inner stride")
     _cuda_contig("temperature", temperature, torch.float32)
@@ -343,6 +434,7 @@ def sample(
 
 def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[M,N] = a[M,K] @ w[N,K]^T in true float32 (FFMA)."""
+    flush_gemm_chain()
     for name, t in (("a", a), ("w", w), ("out", out)):
         if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
             raise KernelError(f"sgemm_nt: {name} must be a float32 CUDA matrix with unit inner stride")
@@ -545,6 +637,7 @@ def attention_paged_mma(
     0 divides each sequence's keys evenly.  In decode steps the last CTA of each (sequence, KV
     head) pair merges the pair's splits itself (`fuse_merge`); otherwise a second kernel does.
     """
+    flush_gemm_chain()
     run, _ = _attention_mma_fns(head_dim)
     for name, t in (("q", q), ("k_cache", k_cache), ("v_cache", v_cache), ("out", out)):
         _cuda_contig(name, t, torch.bfloat16)
@@ -645,6 +738,7 @@ def attention_decode_flat(
     form one list that the CTAs of a fixed grid divide evenly on the device, whatever the lengths
     are; pairs that several CTAs share are merged by a second kernel.  `ctas` (0: as many as run
     at once) sets the grid."""
+    flush_gemm_chain()
     _attention_mma_fns(head_dim)
     lib = _attention_flat[head_dim]
     for name, t in (("q", q), ("k_cache", k_cache), ("v_cache", v_cache), ("out", out)):
@@ -749,6 +843,7 @@ def attention_prefill_tcgen05(
     `mode`: 1 one tile of 128 rows per CTA, 2 two tiles per CTA with the roles in warps of
     their own, 0 chooses by the longest portion.
     """
+    flush_gemm_chain()
     run, ok = _attention_tcgen05_fns()
     d = ATTENTION_TCGEN05_HEAD_DIM
     for name, t in (("q", q), ("k_cache", k_cache), ("v_cache", v_cache), ("out", out)):
@@ -792,6 +887,7 @@ _SIGNATURES["ts_gemm_skinny_bf16"] = [
 # overrides it for measurements.
 GEMM_PREFETCH_BYTES = int(_os.environ.get("TS_GEMM_PREFETCH_MB", "16")) << 20
 _gemm_workspaces: dict[tuple[int, int], tuple[torch.Tensor, torch.Tensor]] = {}
+_CHAIN_SYNC_WORDS = 512  # at least ts_gemm_chain_sync_words(), on a 128-byte boundary behind the tickets
 
 
 def _gemm_workspace(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
@@ -801,7 +897,7 @@ def _gemm_workspace(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
     key = (device.index or 0, _stream())
     ws = _gemm_workspaces.get(key)
     if ws is None:
-        counters = torch.zeros(_GEMM_MAX_TILES, dtype=torch.int32, device=device)
+        counters = torch.zeros(_GEMM_MAX_TILES + _CHAIN_SYNC_WORDS, dtype=torch.int32, device=device)  # tickets, then the chain's barrier words
         error = _pinned_word()
         ws = _gemm_workspaces[key] = (counters, error)
     return ws
@@ -859,11 +955,11 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, prefet
         raise KernelError(f"gemm_skinny_bf16: shapes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
     partial = _gemm_partial(x.device, M, N, K)
     counters, error = _gemm_workspace(x.device)
-    _check("gemm_skinny_bf16", _fn("ts_gemm_skinny_bf16")(
+    _check_product("gemm_skinny_bf16", _fn("ts_gemm_skinny_bf16")(
         x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0), out.stride(0),
         1 if out.dtype == torch.float32 else 0, _ptr(partial), counters.data_ptr(), error.data_ptr(),
         _ptr(prefetch), 0 if prefetch is None else min(prefetch.numel() * prefetch.element_size(), GEMM_PREFETCH_BYTES),
-        _stream()))
+        _stream()), x, w, out, partial)
 
 
 _SIGNATURES["ts_gemm_skinny_fused"] = [
@@ -939,13 +1035,13 @@ def gemm_skinny_fused(
         scale_tiles = scale_ssq.shape[0]
     partial = _gemm_partial(x.device, M, N, K)
     counters, error = _gemm_workspace(x.device)
-    _check("gemm_skinny_fused", _fn("ts_gemm_skinny_fused")(
+    _check_product("gemm_skinny_fused", _fn("ts_gemm_skinny_fused")(
         x.data_ptr(), w.data_ptr(), _ptr(out), M, N, K, x.stride(0), w.stride(0), ldo, out_f32,
         int(mode), _ptr(scale_ssq), scale_tiles, float(scale_width), float(scale_eps),
         _ptr(hidden), N, _ptr(norm_weight), _ptr(xprime), _ptr(ssq_out),
         _ptr(partial), counters.data_ptr(), error.data_ptr(),
         _ptr(prefetch), 0 if prefetch is None else min(prefetch.numel() * prefetch.element_size(), GEMM_PREFETCH_BYTES),
-        _stream()))
+        _stream()), x, w, out, scale_ssq, hidden, norm_weight, xprime, ssq_out, partial)
 
 
 _SIGNATURES["ts_gemm_skinny_qk_rope"] = [
@@ -1007,14 +1103,14 @@ def gemm_qk_rope_store(
         scale_tiles = scale_ssq.shape[0]
     partial = _gemm_partial(x.device, M, w.shape[0], K)
     counters, error = _gemm_workspace(x.device)
-    _check("gemm_qk_rope_store", _fn("ts_gemm_skinny_qk_rope")(
+    _check_product("gemm_qk_rope_store", _fn("ts_gemm_skinny_qk_rope")(
         x.data_ptr(), w.data_ptr(), M, K, x.stride(0), w.stride(0), nq, nkv,
         q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), slot_mapping.data_ptr(), positions.data_ptr(),
         _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps), _ptr(inv_freq),
         _ptr(scale_ssq), scale_tiles, float(scale_width), float(scale_eps),
         _ptr(partial), counters.data_ptr(), error.data_ptr(),
         _ptr(prefetch), 0 if prefetch is None else min(prefetch.numel() * prefetch.element_size(), GEMM_PREFETCH_BYTES),
-        _stream()))
+        _stream()), x, w, q_out, k_cache, v_cache, slot_mapping, positions, q_norm_weight, k_norm_weight, inv_freq, scale_ssq, partial)
 
 
 _SIGNATURES["ts_wait_gives_up_probe"] = [_c_void_p, _c_int, _c_void_p]
@@ -1025,6 +1121,7 @@ def wait_gives_up_probe(device: torch.device, limit: int = 4096) -> None:
     tries) and which then raises the current stream's error word exactly as the tcgen05 kernels
     do: the way to see the error path work without a fault.  check_device_errors() raises after
     the next synchronisation."""
+    flush_gemm_chain()
     _, error = _gemm_workspace(device)
     _check("wait_gives_up_probe", _fn("ts_wait_gives_up_probe")(error.data_ptr(), int(limit), _stream()))
 

@@ -37,6 +37,9 @@ class AttentionMixer(Mixer):
     """
 
     folds_norms = True
+    # its own kernels only; a position encoding that rewrites q and k itself gets them from a kernel
+    # that has run (not from a product that may still wait in a chain)
+    reads_through_ops = True
 
     def __init__(
         self,

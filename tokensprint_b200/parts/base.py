@@ -194,6 +194,12 @@ class Part:
     # data): only a model whose parts all say so has its decode steps captured in CUDA graphs.
     graph_safe = False
 
+    # True when the part touches the tensors it is handed (inputs, the residual stream, the cache)
+    # only through the ops of this package.  Those launch any chained products that are still
+    # pending before they run (ops.gemm_chain); before a part that does not say so, its caller
+    # launches them itself.  A part written with torch operations leaves this False.
+    reads_through_ops = False
+
     def first_weight(self) -> Optional[torch.Tensor]:
         """The first large weight this part reads in a step, for the part before it to prefetch."""
         return None

@@ -6,6 +6,7 @@ from typing import Mapping, Optional
 
 import torch
 
+from tokensprint_b200 import ops
 from tokensprint_b200.parts.base import (
     Block,
     BuildContext,
@@ -37,6 +38,9 @@ class PreNormBlock(Block):
         self.ffn_norm = build_part("norm", ffn_norm, ctx)
         self._parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
         self.graph_safe = all(p.graph_safe for p in self._parts)
+        # the block itself only hands tensors on; before a part that reads them by other means
+        # than this package's ops, products that still wait in a chain are launched
+        self.reads_through_ops = True
 
     def tensor_specs(self) -> list[TensorSpec]:
         return [s for p in self._parts for s in p.tensor_specs()]
@@ -65,20 +69,29 @@ class PreNormBlock(Block):
             x = pending
         else:
             x = torch.empty(hidden.shape, device=hidden.device, dtype=self.dtype)
+            self._before(self.mixer_norm)
             self.mixer_norm.forward(hidden, None if isinstance(pending, PreNormed) else pending, x)
         step.weight_after = self.feed_forward.first_weight()
         ffn_norm = self.ffn_norm.params()
+        self._before(self.mixer)
         if mixer_folds and ffn_folds and ffn_norm is not None:
             x = self.mixer.forward(x, step, cache, fold=ResidualNorm(hidden, ffn_norm))
         else:
             mixed = self.mixer.forward(x, step, cache)
             x = torch.empty(hidden.shape, device=hidden.device, dtype=self.dtype)
+            self._before(self.ffn_norm)
             self.ffn_norm.forward(hidden, mixed, x)
         step.weight_after = after_block
         next_norm = norm_after.params() if norm_after is not None else None
+        self._before(self.feed_forward)
         if ffn_folds and next_norm is not None:
             return self.feed_forward.forward(x, step, fold=ResidualNorm(hidden, next_norm))
         return self.feed_forward.forward(x, step)
+
+    @staticmethod
+    def _before(part) -> None:
+        if not part.reads_through_ops:
+            ops.flush_gemm_chain()
 
     def first_weight(self):
         return self.mixer.first_weight()

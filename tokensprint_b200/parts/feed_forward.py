@@ -23,6 +23,7 @@ class SwiGLUFeedForward(FeedForward):
     """
 
     graph_safe = True
+    reads_through_ops = True
     folds_norms = True
 
     def __init__(self, ctx: BuildContext, *, hidden_size: int, intermediate_size: int, gate: str, up: str, down: str) -> None:

@@ -43,6 +43,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
         if T <= SKINNY_ROWS and ops.gemm_skinny_supported(x, weight):
             ops.gemm_skinny_bf16(x, weight, out, next_weight)
         else:
+            ops.flush_gemm_chain()  # the library reads x by itself
             torch.mm(x, weight.t(), out=out)
     else:
         raise ops.KernelError(f"linear: unsupported dtype {x.dtype}")
@@ -107,4 +108,6 @@ def linear_float32_out(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
         out = torch.empty((x.shape[0], weight.shape[0]), device=x.device, dtype=torch.float32)
         ops.gemm_skinny_bf16(x, weight, out)
         return out
-    return linear(x, weight).float()
+    out = linear(x, weight)
+    ops.flush_gemm_chain()
+    return out.float()

@@ -18,6 +18,7 @@ class RMSNorm(Norm):
     """
 
     graph_safe = True
+    reads_through_ops = True
 
     def __init__(self, ctx: BuildContext, *, dim: int, eps: float, weight: str) -> None:
         self.dim, self.eps, self.weight_name = int(dim), float(eps), weight
