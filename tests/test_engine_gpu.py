@@ -95,9 +95,14 @@ def test_overlapping_steps_change_no_token(tmp_path, eager):
     folder, _ = make_folder(tmp_path, TINY_B, 6, sharp=2.0)
     prompts = [random_tokens(TINY_B, n, 40 + n) for n in (1, 9, 31, 100, 150, 200, 3, 60)]
     sps = [SamplingParams(temperature=0.9, max_tokens=40 - 3 * i, ignore_eos=(i % 3 == 0), seed=21) for i in range(len(prompts))]
+    # the end-of-sequence token: one that the requests which heed it do sample, a few tokens in
+    free = make_engine(folder, "float32", kvcache_block_size=32, num_kvcache_blocks=64, max_num_batched_tokens=64,
+                       overlap_steps=False).generate(prompts, sps, use_tqdm=False)
+    seen = [t for c, sp in zip(free, sps) if not sp.ignore_eos for t in c[3:]]
+    eos = max(set(seen), key=seen.count)
     runs = {}
     for overlap in (False, True):
-        kw = dict(kvcache_block_size=32, num_kvcache_blocks=14, max_num_batched_tokens=64, eos=7, enforce_eager=eager,
+        kw = dict(kvcache_block_size=32, num_kvcache_blocks=14, max_num_batched_tokens=64, eos=eos, enforce_eager=eager,
                   overlap_steps=overlap)
         engine = make_engine(folder, "float32", **kw)
         assert engine.overlap == overlap
@@ -107,7 +112,7 @@ def test_overlapping_steps_change_no_token(tmp_path, eager):
         engine.model_runner.cache_manager.check_invariants()
     assert runs[True] == runs[False]
     ended_early = [c for c, sp in zip(runs[True], sps) if len(c) < sp.max_tokens]
-    assert ended_early and all(c[-1] == 7 for c in ended_early), "no request ended with the end-of-sequence token"
+    assert ended_early and all(c[-1] == eos for c in ended_early), "no request ended with the end-of-sequence token"
 
 
 @pytest.mark.parametrize("graphs", [False, True])

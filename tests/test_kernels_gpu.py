@@ -487,12 +487,15 @@ PROMPTS = [(1, 1), (1, 77), (5, 5), (3, 130), (64, 64), (37, 200), (2, 65), (1, 
 @pytest.mark.parametrize(
     "nq,nkv,page,window",
     [(32, 8, 16, 0), (4, 4, 16, 0), (8, 1, 8, 0), (16, 1, 64, 0), (2, 1, 32, 0), (6, 3, 16, 0), (128, 1, 16, 0),
-     (32, 8, 16, 100), (8, 2, 32, 7), (4, 1, 8, 64), (3, 3, 16, 300), (32, 8, 256, 0), (8, 2, 128, 90), (4, 1, 192, 0)],
+     (32, 8, 16, 100), (8, 2, 32, 7), (4, 1, 8, 64), (3, 3, 16, 300), (32, 8, 256, 0), (8, 2, 128, 90), (4, 1, 192, 0),
+     (40, 8, 16, 0), (5, 1, 16, 33), (6, 2, 8, 0), (7, 1, 64, 0), (12, 1, 16, 50), (100, 1, 16, 0), (20, 2, 32, 0)],
 )
 @pytest.mark.parametrize("mode", [1, 2])
 def test_attention_tcgen05_mixed(nq, nkv, page, window, mode):
-    """Prompt portions and single tokens of many lengths in one launch, every group size that
-    divides 128, pages of 8 to 256 slots in shuffled order, NaN in every slot nobody wrote."""
+    """Prompt portions and single tokens of many lengths in one launch, group sizes that divide 128
+    and group sizes that do not (5: a tile holds 25 tokens and leaves three rows empty; 3, 7, 12,
+    100: one token and 28 empty rows), pages of 8 to 256 slots in shuffled order, NaN in every slot
+    nobody wrote."""
     case = finish_case(paged_case(PROMPTS, nq, nkv, 128, page, torch.bfloat16, seed=nq + page))
     got = run_tcgen05(case, window, mode)
     want = plain_attention(case, window)
@@ -514,11 +517,12 @@ def test_attention_tcgen05_says_what_it_takes():
 
     assert ops.attention_tcgen05_supported(32, 8, 128, 16)
     assert not ops.attention_tcgen05_supported(32, 8, 64, 16)  # head size
-    assert not ops.attention_tcgen05_supported(40, 8, 128, 16)  # groups of 5
+    assert ops.attention_tcgen05_supported(40, 8, 128, 16)  # groups of 5: 25 tokens to a tile
+    assert not ops.attention_tcgen05_supported(129, 1, 128, 16)  # more heads to a group than a tile has rows
     assert not ops.attention_tcgen05_supported(32, 8, 128, 4)  # pages too small for one copy each
     assert not ops.attention_tcgen05_supported(32, 8, 128, 96)  # pages that straddle the 64-key blocks
-    case = finish_case(paged_case([(5, 9)], 10, 2, 128, 16, torch.bfloat16))
-    with pytest.raises(ops.KernelError, match="group size"):
+    case = finish_case(paged_case([(5, 9)], 10, 2, 128, 4, torch.bfloat16))
+    with pytest.raises(ops.KernelError, match="page size"):
         run_tcgen05(case)
 
 
@@ -549,6 +553,29 @@ def test_attention_tcgen05_finds_one_key_that_stands_out(target, mode):
     else:
         assert float((row - 10.0).abs().max()) < 0.05, f"the key at {where} was not found"
     assert rel_err(got, plain_attention(case, window)) < 1e-2
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("target", ["first", "tile_edge_before", "tile_edge_after", "own"])
+def test_attention_tcgen05_groups_of_five_find_one_key_that_stands_out(target, mode):
+    """Qwen3-14B's heads (40 over 8): a tile holds 25 tokens, so token 25 of a portion is the first
+    row of the second tile.  One query head of one token finds one key, on both sides of that edge."""
+    nq, nkv, d, page, ctx, ql = 40, 8, 128, 16, 300, 60
+    qi = {"tile_edge_before": 24, "tile_edge_after": 25}.get(target, 40)
+    qpos = ctx - ql + qi
+    where = {"first": 0, "own": qpos}.get(target, 111)
+    case = paged_case([(3, 40), (ql, ctx)], nq, nkv, d, page, torch.bfloat16, seed=6)
+    q, k, v = case["dense"][1]
+    k.mul_(0.05)
+    k[where, 3] = q[qi, 17] * 3.0  # head 17 belongs to KV head 17 // 5 = 3
+    v[where, 3] = 10.0
+    case = finish_case(case)
+    got = run_tcgen05(case, 0, mode)
+    row = got.view(-1, nq, d)[3 + qi, 17].float()
+    assert float((row - 10.0).abs().max()) < 0.05, f"the key at {where} was not found"
+    other = got.view(-1, nq, d)[3 + qi, 12].float()  # a head of KV head 2 does not see it
+    assert float(other.abs().max()) < 5.0
+    assert rel_err(got, plain_attention(case, 0)) < 1e-2
 
 
 def test_attention_tcgen05_ignores_pages_that_are_not_held():
@@ -607,6 +634,29 @@ def test_sample_matches_the_plain_race_and_the_distribution():
     assert out2.tolist() == got
     ops.sample(logits, temps, keys + 1, out2)
     assert out2.tolist() != got
+
+
+def test_sample_race_draw_by_draw_on_odd_widths_and_unaligned_rows():
+    """Rows that do not start on 16-byte boundaries (a width that is no multiple of four), a
+    vocabulary that ends in the middle of a thread's four entries, several chunks: every draw is the
+    plain race's draw (the noise of entry i comes from the hash of (key, i // 2))."""
+    from tokensprint_b200 import ops
+
+    g = torch.Generator().manual_seed(17)
+    R, V = 24, 4099
+    logits = (torch.randn(R, V, generator=g) * 2.0).to(DEV)
+    temps = torch.tensor([0.5 + 0.05 * r for r in range(R)], device=DEV)
+    keys = (torch.arange(R, dtype=torch.int64) * 104729 - 55).to(DEV)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.sample(logits, temps, keys, out)
+    for r in range(R):
+        assert int(out[r]) == plain.sample_token(logits[r].cpu(), float(temps[r]), int(keys[r])), f"row {r}"
+    # a view with a row stride that is larger than the width
+    wide = torch.zeros(R, V + 5, device=DEV)
+    wide[:, :V] = logits
+    out2 = torch.empty_like(out)
+    ops.sample(wide[:, :V], temps, keys, out2)
+    assert torch.equal(out, out2)
 
 
 # ---------------------------------------------------------------------------

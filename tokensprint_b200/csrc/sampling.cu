@@ -3,9 +3,13 @@
 // Reference (engine/generation/sampler.py:11-16): probs = softmax(logits / T);
 // token = argmax(probs / max(E, 1e-10)) with E ~ Exp(1) drawn per entry.  Dividing by
 // the softmax's sum and taking a log change no argmax, so the kernel compares
-// logits / T - log(max(E, 1e-10)) and never forms the softmax.  E comes from a counter
-// hash of (key, vocabulary index); the host makes `key` from (seed, request, position),
-// so a request draws the same noise however it was batched, cut or recomputed.
+// logits / T - ln(E) and never forms the softmax.  E = -ln(u) comes from a counter hash:
+// one 64-bit hash of (key, index / 2) gives the 24-bit uniforms of the entries 2k (its top
+// bits) and 2k + 1 (the 24 bits below).  u <= 1 - 2^-25 keeps E above 2.9e-8, so the
+// reference's floor of 1e-10 never acts.  With ln = ln2 * lg2 the score is
+// logits / T - ln2 * lg2(-lg2(u)) up to a constant that no argmax sees: two hardware
+// logarithms and one hash per two entries.  The host makes `key` from (seed, request,
+// position), so a request draws the same noise however it was batched, cut or recomputed.
 // Temperature 0 is greedy.  Ties go to the lowest index.
 #include "common.cuh"
 
@@ -16,11 +20,16 @@ __device__ __forceinline__ uint64_t ts_mix64(uint64_t z) {
   return z ^ (z >> 31);
 }
 
-// Exp(1) noise for (key, index): u in (0, 1) from 24 bits, E = -log(u).
-__device__ __forceinline__ float ts_exp_noise(uint64_t key, int index) {
-  const uint64_t h = ts_mix64(key ^ ts_mix64((uint64_t)(uint32_t)index));
-  const float u = ((float)(uint32_t)(h >> 40) + 0.5f) * (1.0f / 16777216.0f);
-  return -logf(u);
+// The hash that the entries 2 * pair and 2 * pair + 1 of a row with this key share.
+__device__ __forceinline__ uint64_t ts_pair_hash(uint64_t key, uint32_t pair) {
+  return ts_mix64(key ^ ((uint64_t)pair * 0xD1342543DE82EF95ull));
+}
+
+// What the race subtracts from logit / T for a 24-bit uniform number: ln2 * lg2(-lg2(u)),
+// u = (bits + 0.5) / 2^24, which is ln(E) for E = -ln(u) less a constant.
+__device__ __forceinline__ float ts_race_penalty(uint32_t bits24) {
+  const float u = ((float)bits24 + 0.5f) * (1.0f / 16777216.0f);
+  return 0.69314718056f * __log2f(-__log2f(u));
 }
 
 #define SAMPLE_CHUNK 2048
@@ -65,7 +74,9 @@ __device__ __forceinline__ Best block_best(Best x, Best* shared /* [32] */) {
   return x;  // valid in warp 0
 }
 
-// Stage 1: one CTA per (chunk of the vocabulary, row) finds the best entry of its chunk.
+// Stage 1: one CTA per (chunk of the vocabulary, row) finds the best entry of its chunk.  A thread
+// takes four neighbouring entries at a time (two hashes); rows whose start is 16-byte aligned are
+// read four floats at once.
 __global__ void sample_partial_kernel(const float* __restrict__ logits, int V, long long row_stride,
                                       const float* __restrict__ temperature,
                                       const unsigned long long* __restrict__ keys, Best* __restrict__ partial) {
@@ -75,18 +86,39 @@ __global__ void sample_partial_kernel(const float* __restrict__ logits, int V, l
   const float* row = logits + (size_t)r * row_stride;
   const float temp = temperature[r];
   const bool greedy = !(temp > 1e-10f);
+  const float inv_temp = greedy ? 1.f : 1.f / temp;
   const uint64_t key = keys ? keys[r] : 0ull;
+  const bool vector = ((uintptr_t)row & 15) == 0;
   Best best;
   best.v = -INFINITY;
   best.i = 0x7fffffff;
   const int end = min(V, (chunk + 1) * SAMPLE_CHUNK);
-  for (int i = chunk * SAMPLE_CHUNK + threadIdx.x; i < end; i += SAMPLE_THREADS) {
-    float v = row[i];
-    if (!greedy) v = v / temp - logf(fmaxf(ts_exp_noise(key, i), 1e-10f));
-    Best cand;
-    cand.v = v;
-    cand.i = i;
-    best = better(best, cand);
+  for (int i0 = chunk * SAMPLE_CHUNK + threadIdx.x * 4; i0 < end; i0 += SAMPLE_THREADS * 4) {
+    float v[4];
+    if (vector && i0 + 3 < end) {
+      const float4 f = *reinterpret_cast<const float4*>(row + i0);
+      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = i0 + j < end ? row[i0 + j] : -INFINITY;
+    }
+    if (!greedy) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const uint64_t h = ts_pair_hash(key, (uint32_t)(i0 >> 1) + half);
+        v[2 * half] = v[2 * half] * inv_temp - ts_race_penalty((uint32_t)(h >> 40));
+        v[2 * half + 1] = v[2 * half + 1] * inv_temp - ts_race_penalty((uint32_t)(h >> 16) & 0xFFFFFFu);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (i0 + j < end) {
+        Best cand;
+        cand.v = v[j];
+        cand.i = i0 + j;
+        best = better(best, cand);
+      }
+    }
   }
   best = block_best(best, shared);
   if (threadIdx.x == 0) partial[(size_t)r * gridDim.x + chunk] = best;

@@ -211,12 +211,16 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
   const int ctx = p.ctx_len[b];
   const int start_pos = ctx - q_len;
   const int rows_total = q_len * G;
-  const int seq_tiles = (rows_total + BM - 1) / BM;
+  // A tile holds whole tokens: 128 / G of them, that is RT = (128 / G) * G rows; where G does not
+  // divide 128 the tile's last rows (RT..127) belong to nobody and are masked like rows beyond the
+  // sequence's end.
+  const int RT = (BM / G) * G;
+  const int seq_tiles = (rows_total + RT - 1) / RT;
   const int row_tile = seq_tiles - 1 - (int)(blockIdx.x / (p.nkv * p.num_seqs));
   if (q_len <= 0 || row_tile < 0) return;
-  const int r0 = row_tile * BM;
+  const int r0 = row_tile * RT;
 
-  const int last_row = min(r0 + BM, rows_total) - 1;
+  const int last_row = min(r0 + RT, rows_total) - 1;
   const int hi = start_pos + last_row / G;          // last key any row of the tile sees
   const int first_pos = start_pos + r0 / G;         // position of the tile's first row
   const int lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
@@ -289,7 +293,7 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
   };
 
   if (tid == 0) {
-    mbar_expect_tx(smem_u32(&q_full), Q_BYTES);
+    mbar_expect_tx(smem_u32(&q_full), (uint32_t)(2 * RT * 128));  // two half-head boxes of RT rows
     for (int half = 0; half < 2; ++half)
       tma_load_4d(sm + OFF_Q + half * (BM * 128), &map_q, smem_u32(&q_full), half * 64, 0, hk, q_begin + r0 / G);
     load_kv(0);
@@ -303,7 +307,7 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
 
   // Row state of this thread.
   const int r = r0 + tid;
-  const int row_pos = r < rows_total ? start_pos + r / G : -1;
+  const int row_pos = (tid < RT && r < rows_total) ? start_pos + r / G : -1;
   const int row_lo = (p.window > 0 && row_pos >= 0) ? max(0, row_pos - p.window + 1) : 0;
   float o[D];
 #pragma unroll
@@ -332,7 +336,7 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
     }
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 
-    const bool unmasked = (kbase + BN - 1 <= first_pos) && (r0 + BM <= rows_total) &&
+    const bool unmasked = (kbase + BN - 1 <= first_pos) && RT == BM && (r0 + BM <= rows_total) &&
                           (p.window <= 0 || kbase >= start_pos + (r0 + BM - 1) / G - p.window + 1);
     float m_new = m_run;
     if (unmasked) {
@@ -416,7 +420,7 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
   }
 
   __syncthreads();
-  if (abort_s == 0 && r < rows_total) {
+  if (abort_s == 0 && tid < RT && r < rows_total) {
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
     __nv_bfloat16* dst = p.out + ((size_t)(q_begin + r / G) * p.nq + hk * G + r % G) * D;
 #pragma unroll
@@ -554,11 +558,12 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
   const int ctx = p.ctx_len[b];
   const int start_pos = ctx - q_len;
   const int rows_total = q_len * G;
-  const int seq_pairs = (rows_total + 2 * BM - 1) / (2 * BM);
+  const int RT = (BM / G) * G;  // rows of a tile that belong to tokens (see the other kernel)
+  const int seq_pairs = (rows_total + 2 * RT - 1) / (2 * RT);
   const int pair = seq_pairs - 1 - (int)(blockIdx.x / (p.nkv * p.num_seqs));
   if (q_len <= 0 || pair < 0) return;
-  const int r0 = pair * 2 * BM;
-  const int ntiles = rows_total - r0 > BM ? 2 : 1;
+  const int r0 = pair * 2 * RT;
+  const int ntiles = rows_total - r0 > RT ? 2 : 1;
 
   // per tile: the last key any of its rows sees, and how many key blocks it walks
   const int first_pos = start_pos + r0 / G;
@@ -567,7 +572,7 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
   int hi_t[2], n_t[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
-    const int last_row = min(r0 + (t + 1) * BM, rows_total) - 1;
+    const int last_row = min(r0 + (t + 1) * RT, rows_total) - 1;
     hi_t[t] = start_pos + last_row / G;
     n_t[t] = t < ntiles ? hi_t[t] / BN - kb0 + 1 : 0;
   }
@@ -621,11 +626,11 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
   if (warp == 8) {
     // ---------------- copies: lane 0 announces the bytes, lanes 0..2*copies-1 each ask for one box ----------------
     if (lane == 0) {
-      mbar_expect_tx(smem_u32(&q_full), (uint32_t)ntiles * Q_BYTES);
+      mbar_expect_tx(smem_u32(&q_full), (uint32_t)(ntiles * 2 * RT * 128));  // per tile two half-head boxes of RT rows
       for (int t = 0; t < ntiles; ++t)
         for (int half = 0; half < 2; ++half)
           tma_load_4d(sm + P2_OFF_Q + t * Q_BYTES + half * (BM * 128), &map_q, smem_u32(&q_full), half * 64, 0, hk,
-                      q_begin + (r0 + t * BM) / G);
+                      q_begin + (r0 + t * RT) / G);
     }
     const int c = lane >> 1, half = lane & 1;  // this lane's copy within a block, and its half of the head
     const bool copies = c < copies_per_block;
@@ -768,12 +773,12 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
     // ---------------- softmax: thread `row` of tile t owns one row ----------------
     const int t = warp >> 2;
     const int row = tid & 127;
-    const int r = r0 + t * BM + row;
-    const int row_pos = r < rows_total ? start_pos + r / G : -1;
+    const int r = r0 + t * RT + row;
+    const int row_pos = (row < RT && r < rows_total) ? start_pos + r / G : -1;
     const int row_lo = (p.window > 0 && row_pos >= 0) ? max(0, row_pos - p.window + 1) : 0;
-    const int tile_first_pos = start_pos + (r0 + t * BM) / G;
-    const int tile_last_pos = start_pos + (r0 + t * BM + BM - 1) / G;
-    const bool tile_full = r0 + (t + 1) * BM <= rows_total;
+    const int tile_first_pos = start_pos + (r0 + t * RT) / G;
+    const int tile_last_pos = start_pos + (r0 + t * RT + RT - 1) / G;
+    const bool tile_full = RT == BM && r0 + (t + 1) * BM <= rows_total;
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t o_addr = lane_addr + 256 + t * 128;
     const int n = nblocks;
@@ -905,7 +910,6 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
     const bool good = __all_sync(0xffffffffu, ok) && *abort_flag == 0;
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
     unsigned char* o_tile = smem + P2_OFF_Q + t * Q_BYTES;
-    const int g_shift = __ffs(G) - 1;
     if (good) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // The tile goes through shared memory (where its Q lay: the tensor core is done with it), so
@@ -936,11 +940,10 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
       for (int it = 0; it < 16; ++it) {
         const int idx = it * BM + row;
         const int rr = idx >> 4, piece = idx & 15;
-        const int rg = r0 + t * BM + rr;
-        if (rg < rows_total) {
+        const int rg = r0 + t * RT + rr;
+        if (rr < RT && rg < rows_total) {
           const uint4 chunk = *reinterpret_cast<const uint4*>(o_tile + rr * 256 + ((piece ^ (rr & 15)) << 4));
-          // the group size divides 128: a power of two
-          __nv_bfloat16* dst = p.out + ((size_t)(q_begin + (rg >> g_shift)) * p.nq + hk * G + (rg & (G - 1))) * D + piece * 8;
+          __nv_bfloat16* dst = p.out + ((size_t)(q_begin + rg / G) * p.nq + hk * G + rg % G) * D + piece * 8;
           *reinterpret_cast<uint4*>(dst) = chunk;
         }
       }
@@ -997,7 +1000,7 @@ TS_EXPORT void ts_attention_tcgen05_set_probe(long long* buffer) { probe_buffer 
 TS_EXPORT int ts_attention_tcgen05_supported(int nq, int nkv, int page) {
   if (nq <= 0 || nkv <= 0 || nq % nkv) return 0;
   const int G = nq / nkv;
-  if (G > BM || BM % G) return 0;
+  if (G > BM) return 0;
   if (page < 8 || (BN % page && page % BN)) return 0;
   return 1;
 }
@@ -1014,7 +1017,7 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
   if (T <= 0 || B <= 0) return 0;
   if (!ts_attention_tcgen05_supported(nq, nkv, page) || max_blocks <= 0 || max_q <= 0 || error == nullptr)
     return TS_ERR_BAD_ARGUMENT;
-  if (total_slots > 0x7fffffffLL - page || ((long long)max_q * (nq / nkv) / BM + 1) * nkv * B > 0x7fffffffLL) return TS_ERR_UNSUPPORTED_SIZE;
+  if (total_slots > 0x7fffffffLL - page || ((long long)max_q * (nq / nkv) / ((BM / (nq / nkv)) * (nq / nkv)) + 1) * nkv * B > 0x7fffffffLL) return TS_ERR_UNSUPPORTED_SIZE;
   if (((uintptr_t)q | (uintptr_t)kcache | (uintptr_t)vcache | (uintptr_t)out) % 16) return TS_ERR_UNSUPPORTED_SIZE;
   CUtensorMap mq, mk, mv;
   int st = query_map(q, T, nq, nkv, &mq);
@@ -1039,8 +1042,9 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
   p.scale_log2 = scale * 1.4426950408889634f;
   p.probe = probe_buffer;
   const int G = nq / nkv;
+  const int RT = (BM / G) * G;  // rows of a tile that belong to tokens
   const long long rows = (long long)max_q * G;
-  const bool pairs = mode == 2 || (mode == 0 && rows > BM);
+  const bool pairs = mode == 2 || (mode == 0 && rows > RT);
   if (pairs) {
     const size_t smem = P2_SMEM + 1024;
     static bool configured = false;
@@ -1049,7 +1053,7 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    return ts_launch(attention_tcgen05_pair_kernel, dim3((unsigned)(((rows + 2 * BM - 1) / (2 * BM)) * nkv * B)), dim3(352), smem,
+    return ts_launch(attention_tcgen05_pair_kernel, dim3((unsigned)(((rows + 2 * RT - 1) / (2 * RT)) * nkv * B)), dim3(352), smem,
                      (cudaStream_t)stream_, mq, mk, mv, p);
   }
   const size_t smem = SMEM_TILES + 1024;
@@ -1059,6 +1063,6 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return ts_launch(attention_tcgen05_kernel, dim3((unsigned)(((rows + BM - 1) / BM) * nkv * B)), dim3(128), smem, (cudaStream_t)stream_, mq, mk,
+  return ts_launch(attention_tcgen05_kernel, dim3((unsigned)(((rows + RT - 1) / RT) * nkv * B)), dim3(128), smem, (cudaStream_t)stream_, mq, mk,
                    mv, p);
 }
