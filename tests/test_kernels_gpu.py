@@ -97,7 +97,7 @@ def test_sgemm_is_true_float32(M, N, K):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T", [11, 300])
+@pytest.mark.parametrize("T", [11, 64, 130, 300])
 @pytest.mark.parametrize("nq,nkv,d,theta,rot", [(5, 1, 48, 5e4, 48), (4, 2, 16, 1e4, 16), (3, 3, 80, 1e6, 32), (8, 2, 256, 1e6, 256), (32, 8, 128, 1e6, 128)])
 def test_qk_norm_rope_store(dtype, nq, nkv, d, theta, rot, T):
     from tokensprint_b200 import ops

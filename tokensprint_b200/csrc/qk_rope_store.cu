@@ -315,9 +315,15 @@ template <int LPR>
 static int launch_vec8(const void* qkv, void* q_out, void* k_dst, void* v_dst, const int* slot_mapping, const int* positions,
                        const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq, int T, int nq, int nkv,
                        cudaStream_t s) {
-  // two warps per token where a token has enough heads for both
+  // A warp takes `rows` heads of a token at a time.  Many tokens: two warps per token where a token
+  // has enough heads for both; fewer tokens (a decode step of a large batch): more warps per token,
+  // up to one per `rows` heads, so that a few thousand warps are in flight all the same.
   const int rows = 32 / LPR;
-  const int warps_per_token = (nq + 2 * nkv) >= 4 * rows ? 2 : 1;
+  const int heads = nq + 2 * nkv;
+  int warps_per_token = heads >= 4 * rows ? 2 : 1;
+  const int most = (heads + rows - 1) / rows;
+  const int wanted = (int)((2048 + (long long)T - 1) / T);
+  if (wanted > warps_per_token) warps_per_token = wanted < most ? wanted : most;
   const unsigned blocks = (unsigned)(((long long)T * warps_per_token + QKR_WARPS - 1) / QKR_WARPS);
   return ts_launch(qk_norm_rope_store_vec8_kernel<LPR>, dim3(blocks), dim3(QKR_WARPS * 32), 0, s, (const __nv_bfloat16*)qkv,
                    (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_dst, (__nv_bfloat16*)v_dst, slot_mapping, positions, q_norm_w, k_norm_w,
@@ -344,8 +350,8 @@ TS_EXPORT int ts_qk_norm_rope_store(const void* qkv, int act_dtype, void* q_out,
   const int heads_per_warp = T >= 256 ? 8 : 1;
   const int groups = (nq + 2 * nkv + heads_per_warp - 1) / heads_per_warp;
   const unsigned pair_blocks = (unsigned)(((long long)T * groups + QKR_WARPS - 1) / QKR_WARPS);
-  // prompt-sized bfloat16 batches with a power-of-two head size: 16-byte accesses, several heads per warp
-  const bool vec8 = pairs && act_dtype == TS_DTYPE_BF16 && T >= 256 && d >= 16 && (d & (d - 1)) == 0 &&
+  // bfloat16 batches of 48 tokens or more with a power-of-two head size: 16-byte accesses, several heads per warp
+  const bool vec8 = pairs && act_dtype == TS_DTYPE_BF16 && T >= 48 && d >= 16 && (d & (d - 1)) == 0 &&
                     (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_dst | (uintptr_t)v_dst | (uintptr_t)q_norm_w |
                       (uintptr_t)k_norm_w) % 16 == 0) && ((uintptr_t)inv_freq % 4 == 0);
   if (vec8) {
