@@ -133,17 +133,23 @@ struct GemmArgs {
 
 // A chain of products: per phase its arguments and tensor maps, the grid barrier's counters
 // (ts_gemm_chain_sync_words() unsigned ints, zero before the first launch; the kernel leaves them zero).
-struct ChainArgs {
-  GemmArgs g[MAX_PHASES];
+// (Templated on the most phases a launch holds: a product launched alone takes the one-phase
+// form, whose parameters are as small as a single product's and are read at fixed offsets.)
+template <int NPH>
+struct ChainArgsT {
+  GemmArgs g[NPH];
   int n;
   int hold;   // 1: a phase's copies start only when this CTA has stored the phase before
   int ahead;  // W tiles asked into the L2 beyond the ring while a phase waits for its inputs
   unsigned int* sync;
 };
-struct ChainMaps {
-  CUtensorMap w[MAX_PHASES];
-  CUtensorMap x[MAX_PHASES];
+template <int NPH>
+struct ChainMapsT {
+  CUtensorMap w[NPH];
+  CUtensorMap x[NPH];
 };
+using ChainArgs = ChainArgsT<MAX_PHASES>;
+using ChainMaps = ChainMapsT<MAX_PHASES>;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -342,9 +348,9 @@ __device__ __forceinline__ void fused_epilogue(const GemmArgs& args, int t, int 
   }
 }
 
-template <int MPAD>
-__global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_constant__ ChainMaps maps,
-                                                                  const __grid_constant__ ChainArgs chain) {
+template <int MPAD, int NPH>
+__global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_constant__ ChainMapsT<NPH> maps,
+                                                                  const __grid_constant__ ChainArgsT<NPH> chain) {
   using C = Cfg<MPAD>;
   constexpr int STAGES = C::STAGES;
   constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MPAD >> 3) << 17) | ((uint32_t)(TILE_N >> 4) << 24);
@@ -365,7 +371,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
   __shared__ float rstd_s[FUSED_MAX_ROWS];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int phases = chain.n;
+  const int phases = NPH == 1 ? 1 : chain.n;
   const unsigned int ctas = gridDim.x;
   ts_pdl_launch_dependents();  // the next kernel may begin its own set-up now
   {
@@ -877,15 +883,30 @@ int tensor_map(const void* ptr, long long rows, long long cols, long long ld, in
   return 0;
 }
 
-template <int MPAD>
-int launch_skinny(const ChainMaps& maps, const ChainArgs& chain, int ctas, cudaStream_t stream) {
+template <int MPAD, int NPH>
+int launch_phases(const ChainMapsT<NPH>& maps, const ChainArgsT<NPH>& chain, int ctas, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<MPAD>::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MPAD, NPH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<MPAD>::SMEM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return ts_launch(gemm_skinny_kernel<MPAD>, dim3(ctas), dim3(NUM_THREADS), Cfg<MPAD>::SMEM, stream, maps, chain);
+  return ts_launch(gemm_skinny_kernel<MPAD, NPH>, dim3(ctas), dim3(NUM_THREADS), Cfg<MPAD>::SMEM, stream, maps, chain);
+}
+
+template <int MPAD>
+int launch_skinny(const ChainMaps& maps, const ChainArgs& chain, int ctas, cudaStream_t stream) {
+  if (chain.n > 1) return launch_phases<MPAD, MAX_PHASES>(maps, chain, ctas, stream);
+  ChainMapsT<1> one_map;
+  ChainArgsT<1> one;
+  one_map.w[0] = maps.w[0];
+  one_map.x[0] = maps.x[0];
+  one.g[0] = chain.g[0];
+  one.n = 1;
+  one.hold = 0;
+  one.ahead = 0;
+  one.sync = nullptr;
+  return launch_phases<MPAD, 1>(one_map, one, ctas, stream);
 }
 
 // Products waiting to be launched together (see ts_gemm_chain_begin).  One list for the process:
