@@ -1,7 +1,7 @@
 """Times the engine's kernels one at a time, at the layer sizes of a named preset and over a
 range of batch sizes and context lengths, and prints each one's share of its roofline.
 
-    python -m tokensprint_b200.kernel_bench [--preset qwen3-8b] [--only decode,prompt,gemm,small]
+    python -m tokensprint_b200.kernel_bench [--preset qwen3-8b] [--only decode,prompt,gemm,small,layer]
 
 Every kernel runs after a read of a buffer larger than the L2 cache, so it reads its operands
 from device memory as it does inside a model step, and is timed on the device inside a CUDA graph,
@@ -74,6 +74,27 @@ class Timer:
     def __call__(self, fn) -> float:
         """Microseconds of one call of fn."""
         return max(0.0, self._time(fn) - self.base) / self.reps
+
+    def whole_graph(self, body) -> float:
+        """Microseconds of `body` (a sequence of launches that defeats the L2 by itself) captured as
+        one graph: the best of a few replays."""
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(self.stream):
+            body()
+            self.stream.synchronize()
+            with torch.cuda.graph(graph, stream=self.stream):
+                body()
+            best = None
+            for _ in range(self.replays):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(self.stream)
+                graph.replay()
+                e1.record(self.stream)
+                e1.synchronize()
+                t = e0.elapsed_time(e1) * 1e3
+                best = t if best is None else min(best, t)
+        return best
 
 
 def _paged(B: int, ctx: int, nkv: int, d: int, page: int, device):
@@ -208,7 +229,58 @@ def small_kernels(cfg, timer, pk, rows, device):
     ops.check_device_errors()
 
 
-GROUPS = {"decode": decode_attention, "prompt": prompt_attention, "gemm": skinny_gemm, "small": small_kernels}
+def layer_products(cfg, timer, pk, rows, device):
+    """The four products between two attention kernels of a decode step (output projection into the
+    residual stream, gate/up with the activation, down into the residual stream, the next layer's
+    q/k/v with norm, rotation and cache store), with all their fused epilogues: once as four
+    launches (programmatic dependent launch overlaps their ends and starts), once as one chained
+    launch (ops.gemm_chain).  Eight sets of weights take turns, so every launch reads its weights
+    from device memory; the figure is a layer's share of a graph of 40 layers."""
+    H, I = cfg.hidden_size, cfg.intermediate_size
+    nq, nkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    if d != ops.GEMM_QK_ROPE_HEAD_DIM or I % 64:
+        return
+    sets, reps = 8, 40
+    bf = lambda *shape, s=0.03: (torch.randn(*shape, device=device) * s).bfloat16()
+    weights = [dict(o=bf(H, nq * d), gu=bf(2 * I, H), down=bf(H, I), qkv=bf((nq + 2 * nkv) * d, H)) for _ in range(sets)]
+    layer_bytes = sum(w.numel() * 2 for w in weights[0].values())
+    n1, n2 = torch.ones(H, device=device), torch.ones(H, device=device)
+    qn, kn = torch.ones(d, device=device), torch.ones(d, device=device)
+    inv_freq = (cfg.rope_theta ** (-torch.arange(0, d, 2, device=device).float() / d)).contiguous()
+    for M in (1, 8, 32):
+        attn, hidden = bf(M, nq * d, s=1.0), torch.randn(M, H, device=device)
+        x1, x2 = (torch.empty((M, H), device=device, dtype=torch.bfloat16) for _ in range(2))
+        ssq1, ssq2 = (torch.empty((-(-H // 128), M), device=device) for _ in range(2))
+        act = torch.empty((M, I), device=device, dtype=torch.bfloat16)
+        q = torch.empty((M, nq * d), device=device, dtype=torch.bfloat16)
+        kc = torch.zeros(64, nkv, d, device=device, dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        slots = torch.arange(M, device=device, dtype=torch.int32)
+        pos = torch.arange(M, device=device, dtype=torch.int32)
+
+        def layer(w, nxt):
+            ops.gemm_skinny_fused(attn, w["o"], mode=ops.GEMM_EPILOGUE_RESIDUAL_NORM, hidden=hidden, norm_weight=n1, xprime=x1, ssq_out=ssq1, prefetch=w["gu"])
+            ops.gemm_skinny_fused(x1, w["gu"], out=act, mode=ops.GEMM_EPILOGUE_SWIGLU, scale_ssq=ssq1, scale_width=H, scale_eps=1e-6, prefetch=w["down"])
+            ops.gemm_skinny_fused(act, w["down"], mode=ops.GEMM_EPILOGUE_RESIDUAL_NORM, hidden=hidden, norm_weight=n2, xprime=x2, ssq_out=ssq2, prefetch=w["qkv"])
+            ops.gemm_qk_rope_store(x2, w["qkv"], q, kc, vc, slots, pos, qn, kn, 1e-6, inv_freq, nq, nkv,
+                                   scale_ssq=ssq2, scale_width=H, scale_eps=1e-6, prefetch=nxt["o"])
+
+        for chained in (False, True):
+            def body():
+                for r in range(reps):
+                    if chained:
+                        with ops.gemm_chain(device):
+                            layer(weights[r % sets], weights[(r + 1) % sets])
+                    else:
+                        layer(weights[r % sets], weights[(r + 1) % sets])
+
+            us = timer.whole_graph(body) / reps
+            gbs = layer_bytes / 1e9 / (us * 1e-6)
+            rows.append(("a layer's four products", f"M={M}, {'one chained launch' if chained else 'four launches'}", us, gbs, "GB/s", gbs / pk["hbm_gbs"]))
+    ops.check_device_errors()
+
+
+GROUPS = {"decode": decode_attention, "prompt": prompt_attention, "gemm": skinny_gemm, "small": small_kernels, "layer": layer_products}
 
 
 def main(argv=None) -> int:

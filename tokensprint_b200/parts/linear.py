@@ -108,6 +108,8 @@ def linear_float32_out(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
         out = torch.empty((x.shape[0], weight.shape[0]), device=x.device, dtype=torch.float32)
         ops.gemm_skinny_bf16(x, weight, out)
         return out
-    out = linear(x, weight)
+    if not x.is_cuda or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise ops.KernelError(f"linear: bfloat16 CUDA tensors wanted (there is no CPU path), got {x.dtype} on {x.device}")
+    # the library product with a float32 result: the sums are not rounded to bfloat16 on the way out
     ops.flush_gemm_chain()
-    return out.float()
+    return torch.mm(x, weight.t(), out_dtype=torch.float32)
