@@ -927,13 +927,63 @@ def _gemm_partial(device: torch.device, M: int, N: int, K: int) -> torch.Tensor:
     return buf
 
 
+class _MatrixFacts:
+    """What the GEMM wrappers ask of a weight matrix again and again, looked up once and kept on the
+    tensor object (a weight does not change its place or shape while it lives)."""
+
+    __slots__ = ("ok", "ptr", "rows", "cols", "ld", "nbytes")
+
+    def __init__(self, w: torch.Tensor) -> None:
+        self.ptr = w.data_ptr()
+        self.rows, self.cols = (int(w.shape[0]), int(w.shape[1])) if w.dim() == 2 else (0, 0)
+        self.ld = int(w.stride(0)) if w.dim() == 2 else 0
+        self.nbytes = w.numel() * w.element_size()
+        self.ok = bool(
+            w.dim() == 2 and w.is_cuda and w.dtype == torch.bfloat16 and self.cols % 8 == 0 and w.stride(1) == 1
+            and self.ld % 8 == 0 and self.ptr % 16 == 0 and -(-self.rows // 128) <= _GEMM_MAX_TILES)
+
+
+def _facts(w: torch.Tensor) -> _MatrixFacts:
+    f = getattr(w, "_ts_facts", None)
+    if f is None or f.ptr != w.data_ptr():
+        f = _MatrixFacts(w)
+        try:
+            w._ts_facts = f
+        except (AttributeError, RuntimeError):  # an object that takes no attributes: look it up every time
+            pass
+    return f
+
+
+def matrix_streams_through_own_gemm(w: Optional[torch.Tensor]) -> bool:
+    """Whether `w` ([out, in], bfloat16, on the device, rows on 16-byte boundaries, in % 8 == 0) is a
+    weight the engine's own few-row GEMM takes."""
+    return w is not None and _facts(w).ok
+
+
 def gemm_skinny_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
     M, K = x.shape
     return (
-        x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < M <= GEMM_SKINNY_MAX_ROWS
-        and K % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
-        and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and -(-w.shape[0] // 128) <= _GEMM_MAX_TILES
+        _facts(w).ok and x.dtype == torch.bfloat16 and 0 < M <= GEMM_SKINNY_MAX_ROWS and K % 8 == 0
+        and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
     )
+
+
+_gemm_scratch_ptrs: dict[tuple[int, int], tuple[int, int, int, int]] = {}
+
+
+def _gemm_scratch(device: torch.device, M: int, N: int, K: int) -> tuple[int, int, int, int]:
+    """(partial sums, ticket counters, error word, stream) as plain addresses for one launch on the
+    current stream: the buffers of _gemm_partial and _gemm_workspace, looked up with one query of
+    the stream."""
+    stream = _stream()
+    key = (device.index or 0, stream)
+    need = _gemm_scratch_need.get((M, N, K))
+    got = _gemm_scratch_ptrs.get(key)
+    if need is None or got is None or got[3] < need:
+        partial = _gemm_partial(device, M, N, K)
+        counters, error = _gemm_workspace(device)
+        got = _gemm_scratch_ptrs[key] = (partial.data_ptr(), counters.data_ptr(), error.data_ptr(), partial.numel())
+    return got[0], got[1], got[2], stream
 
 
 def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, prefetch: Optional[torch.Tensor] = None) -> None:
@@ -954,13 +1004,13 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, prefet
     N = w.shape[0]
     if w.shape[1] != K or tuple(out.shape) != (M, N) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"gemm_skinny_bf16: shapes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
-    partial = _gemm_partial(x.device, M, N, K)
-    counters, error = _gemm_workspace(x.device)
+    partial, counters, error, stream = _gemm_scratch(x.device, M, N, K)
+    pf = None if prefetch is None else _facts(prefetch)
     _check_product("gemm_skinny_bf16", _fn("ts_gemm_skinny_bf16")(
         x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0), w.stride(0), out.stride(0),
-        1 if out.dtype == torch.float32 else 0, _ptr(partial), counters.data_ptr(), error.data_ptr(),
-        _ptr(prefetch), 0 if prefetch is None else min(prefetch.numel() * prefetch.element_size(), GEMM_PREFETCH_BYTES),
-        _stream()), x, w, out, partial)
+        1 if out.dtype == torch.float32 else 0, partial, counters, error,
+        None if pf is None else pf.ptr, 0 if pf is None else min(pf.nbytes, GEMM_PREFETCH_BYTES),
+        stream), x, w, out)
 
 
 _SIGNATURES["ts_gemm_skinny_fused"] = [
@@ -1034,15 +1084,15 @@ def gemm_skinny_fused(
         if scale_ssq.dtype != torch.float32 or not scale_ssq.is_contiguous() or scale_ssq.dim() != 2 or scale_ssq.shape[1] != M:
             raise KernelError("gemm_skinny_fused: scale_ssq must be float32 [tiles, M]")
         scale_tiles = scale_ssq.shape[0]
-    partial = _gemm_partial(x.device, M, N, K)
-    counters, error = _gemm_workspace(x.device)
+    partial, counters, error, stream = _gemm_scratch(x.device, M, N, K)
+    pf = None if prefetch is None else _facts(prefetch)
     _check_product("gemm_skinny_fused", _fn("ts_gemm_skinny_fused")(
         x.data_ptr(), w.data_ptr(), _ptr(out), M, N, K, x.stride(0), w.stride(0), ldo, out_f32,
         int(mode), _ptr(scale_ssq), scale_tiles, float(scale_width), float(scale_eps),
         _ptr(hidden), N, _ptr(norm_weight), _ptr(xprime), _ptr(ssq_out),
-        _ptr(partial), counters.data_ptr(), error.data_ptr(),
-        _ptr(prefetch), 0 if prefetch is None else min(prefetch.numel() * prefetch.element_size(), GEMM_PREFETCH_BYTES),
-        _stream()), x, w, out, scale_ssq, hidden, norm_weight, xprime, ssq_out, partial)
+        partial, counters, error,
+        None if pf is None else pf.ptr, 0 if pf is None else min(pf.nbytes, GEMM_PREFETCH_BYTES),
+        stream), x, w, out, scale_ssq, hidden, norm_weight, xprime, ssq_out)
 
 
 _SIGNATURES["ts_gemm_skinny_qk_rope"] = [
@@ -1102,16 +1152,16 @@ def gemm_qk_rope_store(
         if scale_ssq.dtype != torch.float32 or not scale_ssq.is_contiguous() or scale_ssq.dim() != 2 or scale_ssq.shape[1] != M:
             raise KernelError("gemm_qk_rope_store: scale_ssq must be float32 [tiles, M]")
         scale_tiles = scale_ssq.shape[0]
-    partial = _gemm_partial(x.device, M, w.shape[0], K)
-    counters, error = _gemm_workspace(x.device)
+    partial, counters, error, stream = _gemm_scratch(x.device, M, w.shape[0], K)
+    pf = None if prefetch is None else _facts(prefetch)
     _check_product("gemm_qk_rope_store", _fn("ts_gemm_skinny_qk_rope")(
         x.data_ptr(), w.data_ptr(), M, K, x.stride(0), w.stride(0), nq, nkv,
         q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), slot_mapping.data_ptr(), positions.data_ptr(),
         _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps), _ptr(inv_freq),
         _ptr(scale_ssq), scale_tiles, float(scale_width), float(scale_eps),
-        _ptr(partial), counters.data_ptr(), error.data_ptr(),
-        _ptr(prefetch), 0 if prefetch is None else min(prefetch.numel() * prefetch.element_size(), GEMM_PREFETCH_BYTES),
-        _stream()), x, w, q_out, k_cache, v_cache, slot_mapping, positions, q_norm_weight, k_norm_weight, inv_freq, scale_ssq, partial)
+        partial, counters, error,
+        None if pf is None else pf.ptr, 0 if pf is None else min(pf.nbytes, GEMM_PREFETCH_BYTES),
+        stream), x, w, q_out, k_cache, v_cache, slot_mapping, positions, q_norm_weight, k_norm_weight, inv_freq, scale_ssq)
 
 
 _SIGNATURES["ts_wait_gives_up_probe"] = [_c_void_p, _c_int, _c_void_p]

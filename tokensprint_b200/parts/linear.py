@@ -59,8 +59,10 @@ def folding_possible(num_tokens: int, dtype: torch.dtype, *weights: torch.Tensor
     folded into them): bfloat16, few rows, shapes the kernel takes."""
     if not FOLD_NORMS or dtype != torch.bfloat16 or not 0 < num_tokens <= min(SKINNY_ROWS, ops.GEMM_FUSED_MAX_ROWS):
         return False
-    return all(w is not None and w.is_cuda and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.stride(1) == 1
-               and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0 for w in weights)
+    for w in weights:
+        if not ops.matrix_streams_through_own_gemm(w):
+            return False
+    return True
 
 
 def linear_scaled(x: "PreNormed | torch.Tensor", weight: torch.Tensor, next_weight: Optional[torch.Tensor] = None,
