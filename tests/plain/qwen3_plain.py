@@ -201,12 +201,16 @@ def _mix64(z: int) -> int:
 
 def exponential_noise(key: int, index: int) -> float:
     """Exp(1) noise of (key, index) as the engine's sampler defines it: the entries 2k and 2k + 1
-    share one splitmix-style hash of (key, k); its top 24 bits give u in (0,1) for the even entry,
+    share one hash of (key, k) (one multiply and two shifts over key ^ k * constant; the key is a
+    full hash already); its top 24 bits give u in (0,1) for the even entry,
     the 24 bits below them for the odd one; E = -log(u)."""
     import numpy as np
 
     m = (1 << 64) - 1
-    h = _mix64((key & m) ^ (((index >> 1) * 0xD1342543DE82EF95) & m))
+    z = (key & m) ^ (((index >> 1) * 0xD1342543DE82EF95) & m)
+    z ^= z >> 32
+    z = (z * 0x94D049BB133111EB) & m
+    h = z ^ (z >> 29)
     bits = (h >> 40) if index % 2 == 0 else ((h >> 16) & 0xFFFFFF)
     u = np.float32((np.float32(bits) + np.float32(0.5)) * np.float32(1.0 / 16777216.0))
     return float(-np.log(u, dtype=np.float32))

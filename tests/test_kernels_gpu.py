@@ -978,3 +978,22 @@ def test_gemm_chain_launches_products_together_and_changes_no_bit(M, H, I, nq, n
     torch.cuda.synchronize()
     ops.check_device_errors()
     assert torch.equal(got, want)
+
+
+def test_sample_noise_is_uniform_over_a_large_vocabulary_with_one_key():
+    """One key, flat logits, many entries: the winner's index is uniform over the vocabulary, so over
+    many draws (keys that differ in one bit each) the winners spread evenly over 16 ranges of indices,
+    and neighbouring entries (which share a hash) win equally often."""
+    from tokensprint_b200 import ops
+
+    R, V = 4096, 40000
+    logits = torch.zeros(R, V, device=DEV)
+    temps = torch.ones(R, device=DEV)
+    keys = torch.tensor([plain._mix64(7) ^ (1 << (i % 64)) ^ (i // 64) for i in range(R)], dtype=torch.uint64).view(torch.int64).to(DEV)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.sample(logits, temps, keys, out)
+    got = out.cpu().numpy()
+    counts = np.bincount(got * 16 // V, minlength=16)
+    assert np.abs(counts - R / 16).max() < 5 * np.sqrt(R / 16), f"winners are not spread evenly: {counts.tolist()}"
+    odd = int((got % 2).sum())
+    assert abs(odd - R / 2) < 5 * np.sqrt(R / 4), f"odd entries won {odd} of {R} draws"

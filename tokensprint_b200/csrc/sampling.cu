@@ -20,9 +20,14 @@ __device__ __forceinline__ uint64_t ts_mix64(uint64_t z) {
   return z ^ (z >> 31);
 }
 
-// The hash that the entries 2 * pair and 2 * pair + 1 of a row with this key share.
+// The hash that the entries 2 * pair and 2 * pair + 1 of a row with this key share.  The key is a
+// full hash of (seed, request, position) already (the host makes it); per pair one multiply and two
+// shifts spread the pair's index over the 48 bits that are used.
 __device__ __forceinline__ uint64_t ts_pair_hash(uint64_t key, uint32_t pair) {
-  return ts_mix64(key ^ ((uint64_t)pair * 0xD1342543DE82EF95ull));
+  uint64_t z = key ^ ((uint64_t)pair * 0xD1342543DE82EF95ull);
+  z ^= z >> 32;
+  z *= 0x94D049BB133111EBull;
+  return z ^ (z >> 29);
 }
 
 // What the race subtracts from logit / T for a 24-bit uniform number: ln2 * lg2(-lg2(u)),
