@@ -334,3 +334,48 @@ def test_many_requests_through_a_tight_pool_all_finish_and_every_page_comes_back
     first_tokens = sum(a[0] == b[0] for a, b in zip(got, want))
     assert first_tokens >= len(prompts) - 4, f"{len(prompts) - first_tokens} first tokens changed under preemption"
     ops.check_device_errors()
+
+
+def test_a_long_request_in_portions_and_decoded_against_the_plain_model(tmp_path):
+    """5,000 tokens at Qwen3-0.6B widths: the prompt in portions of 2,048 (the later portions attend
+    over thousands of cached keys), then 24 tokens one by one (key splits over a long context), eager
+    and in graphs.  bfloat16 against the plain model on the device at every wanted position: the last
+    rows of every portion and all decoded tokens."""
+    from tokensprint_b200.config.registry import get_preset_dict
+    from tokensprint_b200.models.qwen3 import Qwen3Config
+    from tokensprint_b200.weights.loader import write_random_model
+    from tokensprint_b200.weights.safetensors_io import SafetensorsFolder
+
+    d = get_preset_dict("qwen3-0.6b")
+    d["num_hidden_layers"] = 2
+    path = write_random_model(tmp_path / "m", Qwen3Config.from_dict(d), seed=31, dtype="bfloat16", std=0.02)
+    ids = random_tokens(d, 5000, 41)
+    files = SafetensorsFolder(path)
+    weights = {n: files.tensor(n) for n in files.keys()}
+    want = plain.forward_logits(weights, d, ids, dtype=torch.float64, device="cuda").cpu().numpy()
+    del weights
+    torch.cuda.empty_cache()
+    scale = float(abs(want).max())
+
+    steps, pos = [], 0
+    for size in (2048, 2048, 880):
+        steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": ids[pos : pos + size], "want": list(range(size - 8, size))}], "end": []})
+        pos += size
+    for t in range(pos, len(ids)):
+        steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": [ids[t]], "want": [0]}], "end": ["a"] if t == len(ids) - 1 else []})
+    wanted = [p for base, size in ((0, 2048), (2048, 2048), (4096, 880)) for p in range(base + size - 8, base + size)] + list(range(4976, 5000))
+
+    from tokensprint_b200.engine.replay import TraceReplayer
+    from tokensprint_b200.engine.runner import ModelRunner
+    from tokensprint_b200.models.api import load_model
+
+    for graphs in (False, True):
+        model, _ = load_model(path, device="cuda", dtype="bfloat16")
+        runner = ModelRunner(model, page_size=16, num_pages=320, num_slots=4, enforce_eager=not graphs, max_model_len=5120,
+                             max_num_batched_tokens=2048)
+        got = replay_in_process(TraceReplayer(runner), steps)
+        assert sorted(p for _, p in got) == wanted
+        assert not graphs or runner._graphs
+        for p in wanted:
+            err = float(abs(got[("a", p)].astype("float64") - want[p]).max()) / scale
+            assert err < 4e-2, f"graphs={graphs}: position {p} strays {err:.3g} from the plain model"
