@@ -487,7 +487,7 @@ PROMPTS = [(1, 1), (1, 77), (5, 5), (3, 130), (64, 64), (37, 200), (2, 65), (1, 
 @pytest.mark.parametrize(
     "nq,nkv,page,window",
     [(32, 8, 16, 0), (4, 4, 16, 0), (8, 1, 8, 0), (16, 1, 64, 0), (2, 1, 32, 0), (6, 3, 16, 0), (128, 1, 16, 0),
-     (32, 8, 16, 100), (8, 2, 32, 7), (4, 1, 8, 64), (3, 3, 16, 300), (32, 8, 256, 0), (8, 2, 128, 90), (4, 1, 192, 0),
+     (32, 8, 16, 100), (8, 2, 32, 7), (4, 1, 8, 64), (3, 3, 16, 300), (32, 8, 256, 0), (8, 2, 128, 90), (4, 1, 384, 0),
      (40, 8, 16, 0), (5, 1, 16, 33), (6, 2, 8, 0), (7, 1, 64, 0), (12, 1, 16, 50), (100, 1, 16, 0), (20, 2, 32, 0)],
 )
 @pytest.mark.parametrize("mode", [1, 2])
@@ -521,6 +521,8 @@ def test_attention_tcgen05_says_what_it_takes():
     assert not ops.attention_tcgen05_supported(129, 1, 128, 16)  # more heads to a group than a tile has rows
     assert not ops.attention_tcgen05_supported(32, 8, 128, 4)  # pages too small for one copy each
     assert not ops.attention_tcgen05_supported(32, 8, 128, 96)  # pages that straddle the 64-key blocks
+    assert not ops.attention_tcgen05_supported(32, 8, 128, 192)  # and pages that straddle the 128-key blocks of the two-tile kernel
+    assert ops.attention_tcgen05_supported(32, 8, 128, 384)
     case = finish_case(paged_case([(5, 9)], 10, 2, 128, 4, torch.bfloat16))
     with pytest.raises(ops.KernelError, match="page size"):
         run_tcgen05(case)

@@ -21,9 +21,8 @@
 // Every wait is on an mbarrier fed by this CTA's own copies and MMAs, bounded; a wait that
 // gives up raises the error word and the CTA frees its tensor memory and returns.
 //
-// Limits (the caller falls back to the mma.sync kernel otherwise): head size 128; the group
-// size (query heads per KV head) divides 128; the page size is at least 8 and divides 64 or is a
-// multiple of it.
+// Limits (the caller falls back to the mma.sync kernel otherwise): head size 128; at most 128
+// query heads per KV head; the page size is at least 8 and divides 64 or is a multiple of 128.
 #include "../common.cuh"
 #include "kv_tensor_map.cuh"
 
@@ -446,27 +445,42 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
 // ---------------------------------------------------------------------------
 // Two tiles per CTA, roles in warps of their own (long prompt portions).
 //
-// A CTA owns 256 consecutive rows as two tiles of 128 and walks the keys once for both.
-//   warps 0-3, 4-7  softmax of tile 0 and of tile 1: thread r of a group owns row r;
-//   warp 8          one thread: TMA loads (Q once, then K and V blocks into rings of 3 stages);
-//   warp 9          one thread: every tcgen05.mma;
-//   warp 10         a messenger between the copies and warp 9 (see there).
-// S has two buffers per tile in tensor memory, so S of block j+1 is computed while the threads
-// work on block j; O stays in tensor memory and P V accumulates into it.  The running max of a
-// row is only raised when the new max exceeds it by more than 2^8 (the weights then stay below
-// 2^8, well inside bfloat16 and float32 range, and the final division by the row sum, taken
-// with the same max, cancels it); only then is the row of O rescaled in tensor memory.
+// A CTA owns 256 consecutive rows as two tiles of 128 and walks the keys once for both, in blocks
+// of 128 keys: an S product of 128 keys reads as many bytes of shared memory per clock of tensor
+// work as the tensor core takes (a product of 64 keys reads half as much again as it can use).
+//   warps 0-7, 8-15 softmax of tile 0 and of tile 1: two threads per row, each with 64 of a
+//                   block's 128 keys (a tile's turn is as long as its threads take, so the row
+//                   is cut in two);
+//   warp 16         TMA loads (Q once, then K and V blocks into rings of 2 stages);
+//   warp 17         one elected lane: every tcgen05.mma;
+//   warp 18         a messenger between the copies and warp 17 (see there).
+// Tensor memory holds S of both tiles (128 columns each) and O of both tiles (128 columns each):
+// all 512 columns.  P (bfloat16, two keys per column) is written over the first half of the scores
+// it came from (keys 0..63 at column 0, keys 64..127 at column 64 of the tile's S), and the tensor
+// core reads it from there.  The two tiles take turns: while the threads
+// of one tile work on their scores, the tensor core runs P V and the next S of the other.  O stays
+// in tensor memory and P V accumulates into it.  The running max of a row is only raised when the
+// new max exceeds it by more than 2^8 (the weights then stay below 2^8, well inside bfloat16 and
+// float32 range, and the final division by the row sum, taken with the same max, cancels it);
+// only then is the row of O rescaled in tensor memory.
 // Synchronisation is by mbarriers alone; every wait is bounded.
 
-constexpr int KV_RING = 4;
+constexpr int PBN = 128;                          // keys per block of this kernel
+constexpr uint32_t PKV_HALF = PBN * 128;          // [128 keys x 128 B]: half a head
+constexpr uint32_t PKV_STAGE = 2 * PKV_HALF;      // both halves of the head
+constexpr int KV_RING = 2;
 constexpr uint32_t P2_OFF_Q = 0;                                   // 2 tiles x 32 KB
 constexpr uint32_t P2_OFF_K = P2_OFF_Q + 2 * Q_BYTES;
-constexpr uint32_t P2_OFF_V = P2_OFF_K + KV_RING * KV_STAGE;
-constexpr uint32_t P2_SMEM = P2_OFF_V + KV_RING * KV_STAGE;        // 196,608 bytes
+constexpr uint32_t P2_OFF_V = P2_OFF_K + KV_RING * PKV_STAGE;
+constexpr uint32_t P2_SMEM = P2_OFF_V + KV_RING * PKV_STAGE;       // 196,608 bytes
 constexpr uint32_t P2_TMEM_COLS = 512;
-// columns: S[tile][buffer] at tile * 128 + buffer * 64; O[tile] at 256 + tile * 128.  P of a
-// block (bfloat16, two keys per column) takes the first 32 columns of the S buffer it came from.
+// columns: S[tile] at tile * 128; O[tile] at 256 + tile * 128.  P of a block takes the first 64
+// columns of its tile's S.
 constexpr float RESCALE_THRESHOLD = 8.f;
+// of every four pairs of weights, how many take their exponentials on the FMA pipe (the rest on the special-function unit)
+#ifndef TS_ATT_FMA_PAIRS
+#define TS_ATT_FMA_PAIRS 1
+#endif
 
 // two float32 in one 64-bit register, and the packed arithmetic on them
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
@@ -534,20 +548,27 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 
-__global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_q,
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+__global__ void __launch_bounds__(608, 1) attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                         const __grid_constant__ CUtensorMap map_k,
                                                                         const __grid_constant__ CUtensorMap map_v,
                                                                         const Params p) {
-  if (threadIdx.x == 0) PROBE(1, 63, 6);
   ts_pdl_wait();  // see the other kernel: tensor memory is never held while waiting for another kernel
-  if (threadIdx.x == 0) PROBE(1, 62, 6);
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t q_full, k_full[KV_RING], k_empty[KV_RING], v_full[KV_RING], v_empty[KV_RING];
-  __shared__ __align__(8) uint64_t s_done[2], p_ready, pv_done, all_done;  // s_done per S buffer; all of them for both tiles
+  __shared__ __align__(8) uint64_t s_done[2], p_ready[2], all_done;  // per tile
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   __shared__ int table_s[MAX_TABLE];
+  __shared__ float sum_s[2][2][BM];  // [tile][half of the keys][row]: what the two threads of a row tell each other (a block's largest score; at the end their sums)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // the CTAs with the most keys to walk are launched first (see the other kernel)
@@ -565,23 +586,16 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
   const int r0 = pair * 2 * RT;
   const int ntiles = rows_total - r0 > RT ? 2 : 1;
 
-  // per tile: the last key any of its rows sees, and how many key blocks it walks
+  // the last key any row of the pair sees, and how many key blocks the pair walks
   const int first_pos = start_pos + r0 / G;
   const int lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
-  const int kb0 = lo / BN;
-  int hi_t[2], n_t[2];
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int last_row = min(r0 + (t + 1) * RT, rows_total) - 1;
-    hi_t[t] = start_pos + last_row / G;
-    n_t[t] = t < ntiles ? hi_t[t] / BN - kb0 + 1 : 0;
-  }
-  const int hi = hi_t[ntiles - 1];
-  // Both tiles walk all blocks of the later one (its last block or two are fully masked for the
-  // earlier tile): one barrier then serves both.
-  const int nblocks = n_t[ntiles - 1];
-  const int box_rows = min(p.page, BN);
-  const int copies_per_block = BN / box_rows;
+  const int kb0 = lo / PBN;
+  const int hi = start_pos + (min(r0 + ntiles * RT, rows_total) - 1) / G;
+  // Both tiles walk all blocks of the later one (its last block may be fully masked for the
+  // earlier tile): the two tiles stay in step.
+  const int nblocks = hi / PBN - kb0 + 1;
+  const int box_rows = min(p.page, PBN);
+  const int copies_per_block = PBN / box_rows;
 
   if (tid == 0) {
     abort_s = 0;
@@ -593,14 +607,14 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
       mbar_init(smem_u32(&v_full[s]), 1);
       mbar_init(smem_u32(&v_empty[s]), 1);
     }
-    mbar_init(smem_u32(&s_done[0]), 1);
-    mbar_init(smem_u32(&s_done[1]), 1);
-    mbar_init(smem_u32(&p_ready), 4 * ntiles + 1);  // one arrival per softmax warp, one from the messenger warp
-    mbar_init(smem_u32(&pv_done), 1);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(smem_u32(&s_done[t]), 1);
+      mbar_init(smem_u32(&p_ready[t]), t == 0 ? 9 : 8);  // one arrival per softmax warp; tile 0's also one from the messenger warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  const int first_entry = (kb0 * BN) / p.page;
+  const int first_entry = (kb0 * PBN) / p.page;
   {
     const int n_entries = min(hi / p.page - first_entry + 1, MAX_TABLE);
     const int* table = p.block_table + (size_t)b * p.max_blocks;
@@ -621,9 +635,8 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
   const uint32_t tmem_base = tmem_base_s;
   volatile int* abort_flag = &abort_s;
   const uint32_t sm = smem_u32(smem);
-  if (tid == 0) PROBE(1, 61, 6);
 
-  if (warp == 8) {
+  if (warp == 16) {
     // ---------------- copies: lane 0 announces the bytes, lanes 0..2*copies-1 each ask for one box ----------------
     if (lane == 0) {
       mbar_expect_tx(smem_u32(&q_full), (uint32_t)(ntiles * 2 * RT * 128));  // per tile two half-head boxes of RT rows
@@ -634,7 +647,7 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
     }
     const int c = lane >> 1, half = lane & 1;  // this lane's copy within a block, and its half of the head
     const bool copies = c < copies_per_block;
-    const uint32_t lane_off = (uint32_t)half * KV_HALF + (uint32_t)(c * box_rows) * 128u;
+    const uint32_t lane_off = (uint32_t)half * PKV_HALF + (uint32_t)(c * box_rows) * 128u;
     int issued[2] = {0, 0};  // K and V blocks asked for
     bool ok = true;
     for (int blk = 0; ok && blk < nblocks; ++blk) {
@@ -643,8 +656,8 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
       // where this lane's box starts in the cache
       int slot = p.total_slots;  // beyond the end: the copy engine fills zeros (a page that is not held)
       if (copies) {
-        const int key0 = (kb0 + blk) * BN + c * box_rows;
-        const int e = p.page < BN ? (kb0 + blk) * copies_per_block + c : key0 / p.page;
+        const int key0 = (kb0 + blk) * PBN + c * box_rows;
+        const int e = p.page < PBN ? (kb0 + blk) * copies_per_block + c : key0 / p.page;
         if (key0 <= hi && e < p.max_blocks) {
           const int page_id = e - first_entry < MAX_TABLE ? table_s[e - first_entry] : p.block_table[(size_t)b * p.max_blocks + e];
           if (page_id >= 0) slot = page_id * p.page + (key0 - e * p.page);
@@ -657,10 +670,10 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
         if (blk >= KV_RING) ok = mbar_wait(empty, (use - 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (lane == 0) mbar_expect_tx(full, KV_STAGE);
+        if (lane == 0) mbar_expect_tx(full, PKV_STAGE);
         __syncwarp();
         if (copies)
-          tma_load_3d(sm + (which == 0 ? P2_OFF_K : P2_OFF_V) + st * KV_STAGE + lane_off, which == 0 ? &map_k : &map_v, full,
+          tma_load_3d(sm + (which == 0 ? P2_OFF_K : P2_OFF_V) + st * PKV_STAGE + lane_off, which == 0 ? &map_k : &map_v, full,
                       half * 64, hk, slot);
         issued[which] = blk + 1;
       }
@@ -673,158 +686,150 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
         for (int blk = max(0, issued[which] - KV_RING); blk < issued[which]; ++blk)
           mbar_wait(smem_u32(which == 0 ? &k_full[blk % KV_RING] : &v_full[blk % KV_RING]), (uint32_t)(blk / KV_RING) & 1, own);
     }
-  } else if (warp == 10) {
+  } else if (warp == 18) {
     // ---------------- messenger: tells the MMA warp that what a round needs has landed ----------------
-    // It arrives on p_ready for block j (beside the softmax warps) once V of j and K of j + 2 are
-    // there.  An arrival counts for the barrier's current phase, so it waits until the phase of
-    // block j - 1 is over; the copies it looks at landed long before that as a rule.
+    // It arrives on tile 0's p_ready for block j (beside that tile's softmax warps) once V of j and
+    // K of j + 1 are there.  An arrival counts for the barrier's current phase, so it waits until
+    // the phase of block j - 1 is over; the copies it looks at landed long before that as a rule.
     bool ok = true;
     for (int j = 0; ok && j < nblocks; ++j) {
       ok = mbar_wait(smem_u32(&v_full[j % KV_RING]), (uint32_t)(j / KV_RING) & 1, abort_flag);
-      if (ok && j + 2 < nblocks) ok = mbar_wait(smem_u32(&k_full[(j + 2) % KV_RING]), (uint32_t)((j + 2) / KV_RING) & 1, abort_flag);
-      if (ok && j >= 1) ok = mbar_wait(smem_u32(&p_ready), (uint32_t)(j - 1) & 1, abort_flag);
+      if (ok && j + 1 < nblocks) ok = mbar_wait(smem_u32(&k_full[(j + 1) % KV_RING]), (uint32_t)((j + 1) / KV_RING) & 1, abort_flag);
+      if (ok && j >= 1) ok = mbar_wait(smem_u32(&p_ready[0]), (uint32_t)(j - 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
-      if (ok && lane == 0) mbar_arrive(smem_u32(&p_ready));
+      if (ok && lane == 0) mbar_arrive(smem_u32(&p_ready[0]));
     }
-  } else if (warp == 9) {
+  } else if (warp == 17) {
     // ---------------- tensor core: the warp runs together, one elected lane issues ----------------
-    // Order of issue: S(0), S(1), then for every block j: P V of j, S of j + 2.  S(j + 2) goes to
-    // the buffer that held S and then P of block j; the tensor core runs what one thread issues in
-    // order, so P V of j has read P before S(j + 2) overwrites it.  p_ready for block j gathers the
-    // softmax warps (P of j is written) and the messenger warp (V of j and K of j + 2 have landed), so
-    // that one wait a round is all this warp needs: each of its instructions is slow beside
-    // eight busy warps.
-    {
-      // descriptors differ only in their address field (bytes / 16): prepared once, offsets added per instruction
-      const uint64_t q_desc = desc_k_major(sm + P2_OFF_Q), k_desc = desc_k_major(sm + P2_OFF_K);
-      const uint64_t v_desc = desc_mn_major(sm + P2_OFF_V, KV_HALF);
-      const bool two = ntiles > 1;
-      auto issue_s = [&](int blk) {  // S of block blk for both tiles, in turns
-        const int st = blk % KV_RING, buf = blk & 1;
-        const uint64_t kd = k_desc + (uint64_t)((st * KV_STAGE) >> 4);
-        const uint32_t s_addr = tmem_base + buf * 64;
-        if (elect_one()) {
+    // Order of issue: S of block 0 for both tiles, then for every block j and tile t in turn: P V
+    // of (t, j), S of (t, j + 1).  S(t, j + 1) goes where S and then P of (t, j) lay; the tensor
+    // core runs what one thread issues in order, so P V has read P before the next S overwrites it.
+    // While the threads of tile t work on S(t, j + 1), the tensor core runs tile 1 - t.  p_ready
+    // of tile 0 for block j also gathers the messenger warp (V of j and K of j + 1 have landed),
+    // so that one wait per tile and block is all this warp needs: each of its instructions is slow
+    // beside eight busy warps.
+    const uint64_t q_desc = desc_k_major(sm + P2_OFF_Q), k_desc = desc_k_major(sm + P2_OFF_K);
+    const uint64_t v_desc = desc_mn_major(sm + P2_OFF_V, PKV_HALF);
+    auto issue_s = [&](int t, int blk) {  // S of block blk for tile t; the block's K is free again after the last tile's
+      const int st = blk % KV_RING;
+      const uint64_t kd = k_desc + (uint64_t)((st * PKV_STAGE) >> 4);
+      const uint64_t qd = q_desc + (uint64_t)((t * Q_BYTES) >> 4);
+      const uint32_t s_addr = tmem_base + t * 128;
+      if (elect_one()) {
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off_q = ((ks >> 2) * (BM * 128) + (ks & 3) * 32) >> 4, off_k = ((ks >> 2) * KV_HALF + (ks & 3) * 32) >> 4;
-            if (two) {
-              if (ks == 0)
-                umma_bf16_first(s_addr + 128, q_desc + ((Q_BYTES >> 4) + off_q), kd + off_k, idesc(BN, false));
-              else
-                umma_bf16_more(s_addr + 128, q_desc + ((Q_BYTES >> 4) + off_q), kd + off_k, idesc(BN, false));
-            }
-            if (ks == 0)
-              umma_bf16_first(s_addr, q_desc + off_q, kd + off_k, idesc(BN, false));
-            else
-              umma_bf16_more(s_addr, q_desc + off_q, kd + off_k, idesc(BN, false));
-          }
-          umma_commit(smem_u32(&s_done[buf]));  // the products of both tiles are done when this arrives
-          umma_commit(smem_u32(&k_empty[st]));
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off_q = ((ks >> 2) * (BM * 128) + (ks & 3) * 32) >> 4, off_k = ((ks >> 2) * PKV_HALF + (ks & 3) * 32) >> 4;
+          if (ks == 0)
+            umma_bf16_first(s_addr, qd + off_q, kd + off_k, idesc(PBN, false));
+          else
+            umma_bf16_more(s_addr, qd + off_q, kd + off_k, idesc(PBN, false));
         }
-        __syncwarp();
-      };
-      bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&q_full), 0, abort_flag));
-      for (int blk = 0; ok && blk < min(2, nblocks); ++blk) {
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&k_full[blk]), 0, abort_flag));
-        if (ok) {
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_s(blk);
-        }
+        umma_commit(smem_u32(&s_done[t]));
+        if (t == ntiles - 1) umma_commit(smem_u32(&k_empty[st]));
       }
-      for (int j = 0; ok && j < nblocks; ++j) {
-        const int st = j % KV_RING;
-        if (lane == 0) PROBE(1, j, 0);
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&p_ready), (uint32_t)j & 1, abort_flag));
-        if (lane == 0) PROBE(1, j, 1);
+      __syncwarp();
+    };
+    bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&q_full), 0, abort_flag));
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&k_full[0]), 0, abort_flag));
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      for (int t = 0; t < ntiles; ++t) issue_s(t, 0);
+    }
+    for (int j = 0; ok && j < nblocks; ++j) {
+      const int st = j % KV_RING;
+      const uint64_t vd = v_desc + (uint64_t)((st * PKV_STAGE) >> 4);
+      for (int t = 0; ok && t < ntiles; ++t) {
+        if (lane == 0) PROBE(1, j, t * 3);
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&p_ready[t]), (uint32_t)j & 1, abort_flag));
         if (!ok) break;
+        if (lane == 0) PROBE(1, j, t * 3 + 1);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t vd = v_desc + (uint64_t)((st * KV_STAGE) >> 4);
-        const uint32_t o_addr = tmem_base + 256;
-        const uint32_t p_addr = tmem_base + (j & 1) * 64;  // 16 keys of P: 8 columns
+        const uint32_t o_addr = tmem_base + 256 + t * 128;
+        const uint32_t p_addr = tmem_base + t * 128;  // 16 keys of P: 8 columns; keys 0..63 from column 0, keys 64..127 from column 64
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < BN / 16; ++kk) {
-            if (two) {
-              if (kk == 0 && j == 0)
-                umma_bf16_tmem_a_first(o_addr + 128, p_addr + 128, vd, idesc(D, true));
-              else
-                umma_bf16_tmem_a_more(o_addr + 128, p_addr + 128 + kk * 8, vd + ((kk * 2048) >> 4), idesc(D, true));
-            }
+          for (int kk = 0; kk < PBN / 16; ++kk) {
             if (kk == 0 && j == 0)
               umma_bf16_tmem_a_first(o_addr, p_addr, vd, idesc(D, true));
             else
-              umma_bf16_tmem_a_more(o_addr, p_addr + kk * 8, vd + ((kk * 2048) >> 4), idesc(D, true));
+              umma_bf16_tmem_a_more(o_addr, p_addr + (kk >> 2) * 64 + (kk & 3) * 8, vd + ((kk * 2048) >> 4), idesc(D, true));
           }
-          umma_commit(smem_u32(&pv_done));
-          umma_commit(smem_u32(&v_empty[st]));
+          if (t == ntiles - 1) umma_commit(smem_u32(&v_empty[st]));
         }
         __syncwarp();
-        if (lane == 0) PROBE(1, j, 2);
-        if (j + 2 < nblocks) issue_s(j + 2);
-        if (lane == 0) PROBE(1, j, 3);
+        if (j + 1 < nblocks) issue_s(t, j + 1);
+        if (lane == 0) PROBE(1, j, t * 3 + 2);
       }
-      // Everything this CTA asked of the tensor core is done when this arrives, the arrivals of
-      // the commits above included: nobody leaves before (an arrival after the CTA's end would
-      // land in the barriers of the next CTA on this SM).
-      if (elect_one()) umma_commit(smem_u32(&all_done));
-      __syncwarp();
     }
-  } else if (warp < 4 * ntiles) {
-    // ---------------- softmax: thread `row` of tile t owns one row ----------------
-    const int t = warp >> 2;
-    const int row = tid & 127;
+    // Everything this CTA asked of the tensor core is done when this arrives, the arrivals of
+    // the commits above included: nobody leaves before (an arrival after the CTA's end would
+    // land in the barriers of the next CTA on this SM).
+    if (elect_one()) umma_commit(smem_u32(&all_done));
+    __syncwarp();
+  } else if (warp < 8 * ntiles) {
+    // ---------------- softmax: two threads per row, 64 of a block's 128 keys each ----------------
+    // Warps 8 t .. 8 t + 7 belong to tile t; warp 8 t + 4 h + quad takes keys 64 h .. 64 h + 63 of
+    // rows 32 quad .. 32 quad + 31 (a warp reaches the tensor-memory lanes of its number modulo 4).
+    const int t = warp >> 3;
+    const int h = (warp >> 2) & 1;
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
     const int r = r0 + t * RT + row;
     const int row_pos = (row < RT && r < rows_total) ? start_pos + r / G : -1;
     const int row_lo = (p.window > 0 && row_pos >= 0) ? max(0, row_pos - p.window + 1) : 0;
     const int tile_first_pos = start_pos + (r0 + t * RT) / G;
     const int tile_last_pos = start_pos + (r0 + t * RT + RT - 1) / G;
     const bool tile_full = RT == BM && r0 + (t + 1) * BM <= rows_total;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-    const uint32_t o_addr = lane_addr + 256 + t * 128;
-    const int n = nblocks;
-    float m_run = -INFINITY, l_run = 0.f;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t s_addr = lane_addr + t * 128 + h * 64;        // this thread's 64 scores; its P goes over the first 32 of them
+    const int pair_bar = 3 + t * 4 + quad;                       // hardware barrier of the two warps that share rows
+    const uint32_t o_addr = lane_addr + 256 + t * 128 + h * 64;  // its half of the row of O
+    float m_run = -INFINITY, l_run = 0.f;  // l_run: the sum over this thread's keys only
     bool ok = true;
 
-    for (int blk = 0; blk < n; ++blk) {
-      const int buf = blk & 1;
-      const int kbase = (kb0 + blk) * BN;
-      if (row == 0) PROBE(t * 2, blk, 0);
-      ok = mbar_wait(smem_u32(&s_done[buf]), (uint32_t)(blk >> 1) & 1, abort_flag);
-      if (!__all_sync(0xffffffffu, ok)) break;
-      if (row == 0) PROBE(t * 2, blk, 1);
+    for (int blk = 0; blk < nblocks; ++blk) {
+      const int kbase = (kb0 + blk) * PBN + h * 64;
+      if (h == 0 && row == 0) PROBE(t * 2, blk, 0);
+      mbar_wait(smem_u32(&s_done[t]), (uint32_t)blk & 1, abort_flag);  // if it gives up: on to the barrier below, and out there
+      __syncwarp();
+      if (h == 0 && row == 0) PROBE(t * 2, blk, 1);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      float s[BN];
+      const bool unmasked = tile_full && (kbase + 63 <= tile_first_pos) && (p.window <= 0 || kbase >= tile_last_pos - p.window + 1);
+      // First walk over this thread's 64 scores: their largest.
+      float m_blk;
       {
         uint32_t v0[32], v1[32];
-        tmem_ld32(lane_addr + t * 128 + buf * 64, v0);
-        tmem_ld32(lane_addr + t * 128 + buf * 64 + 32, v1);
+        tmem_ld32(s_addr, v0);
+        tmem_ld32(s_addr + 32, v1);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: the warp has few others to hide latency behind
+        if (unmasked) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          s[i] = __uint_as_float(v0[i]);
-          s[32 + i] = __uint_as_float(v1[i]);
+          for (int i = 0; i < 32; i += 4) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) mx[u] = fmaxf(mx[u], fmaxf(__uint_as_float(v0[i + u]), __uint_as_float(v1[i + u])));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key0 = kbase + i, key1 = key0 + 32;
+            if (key0 <= row_pos && key0 >= row_lo) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v0[i]));
+            if (key1 <= row_pos && key1 >= row_lo) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v1[i]));
+          }
         }
+        m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       }
-      if (row == 0) PROBE(t * 2, blk, 2);
-
-      const bool unmasked = tile_full && (kbase + BN - 1 <= tile_first_pos) &&
-                            (p.window <= 0 || kbase >= tile_last_pos - p.window + 1);
-      if (!unmasked) {
-#pragma unroll
-        for (int j = 0; j < BN; ++j) {
-          const int key = kbase + j;
-          s[j] = (key <= row_pos && key >= row_lo) ? s[j] : -INFINITY;
-        }
-      }
-      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: the warp has few others to hide latency behind
-#pragma unroll
-      for (int j = 0; j < BN; j += 4) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) mx[i] = fmaxf(mx[i], s[j + i]);
-      }
-      const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      // raise the running max only when it is far behind
-      if (row == 0) PROBE(t * 2, blk, 3);
+      if (h == 0 && row == 0) PROBE(t * 2, blk, 2);
+      // The row's largest score of the block is the larger of the two halves'.  The two warps that
+      // share rows meet at a hardware barrier once per block, and it is the only place where they
+      // leave the loop: a wait that gave up has raised abort_s, which both see after the barrier,
+      // so neither is ever left waiting for the other.
+      sum_s[t][h][row] = m_blk;
+      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+      if (*abort_flag) break;
+      m_blk = fmaxf(m_blk, sum_s[t][h ^ 1][row]);
+      if (h == 0 && row == 0) PROBE(t * 2, blk, 3);
+      // raise the running max only when it is far behind (both threads of a row decide alike)
       const bool raise = (m_blk - m_run) * p.scale_log2 > RESCALE_THRESHOLD;  // also true when m_run is -inf and m_blk is not
       if (__any_sync(0xffffffffu, raise)) {
         const float m_new = raise ? m_blk : m_run;
@@ -832,11 +837,10 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
         m_run = m_new;
         l_run *= corr;
         if (blk > 0) {
-          ok = mbar_wait(smem_u32(&pv_done), (uint32_t)(blk - 1) & 1, abort_flag);
-          if (!__all_sync(0xffffffffu, ok)) break;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          // (P V of the block before is complete: the tensor core finishes what one thread issues in
+          // order, and S of this block, issued after it, is)
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
+          for (int c = 0; c < 2; ++c) {
             uint32_t v[32];
             tmem_ld32(o_addr + c * 32, v);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -849,65 +853,80 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
       }
       const float m_off = m_run == -INFINITY ? 0.f : m_run * p.scale_log2;
       // Weights p = 2^(s * scale - m * scale), two at a time.  The special-function unit does 16
-      // exponentials a clock per SM, which is what bounds this loop, so every other pair is
-      // computed on the FMA pipe instead (exp2_pair_fma).
-      float sum[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t packed[BN / 2];
+      // exponentials a clock per SM; one pair in four is computed on the FMA pipe instead
+      // (exp2_pair_fma).  (Measured at 8,192 tokens: none 543 us, one 524, two 525, three 566.)
+      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};  // four chains of two float32 sums each (0 is +0.0 twice)
       const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), off2 = pack2(-m_off, -m_off);
+      // Second walk, 32 scores at a time.  P goes over the first half of the scores it came from
+      // (this thread's own lane and columns): P of keys 32 g .. 32 g + 31 to columns 16 g .. 16 g + 15,
+      // over scores that have been read.
 #pragma unroll
-      for (int j = 0; j < BN; j += 8) {
+      for (int g = 0; g < 2; ++g) {
+        uint32_t v[32];
+        tmem_ld32(s_addr + g * 32, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (!unmasked) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint64_t x = fma2(pack2(s[j + 2 * i], s[j + 2 * i + 1]), scale2, off2);
-          float p0, p1;
-          if (i & 1) {
-            exp2_pair_fma(x, p0, p1);
-          } else {
-            float x0, x1;
-            unpack2(x, x0, x1);
-            p0 = fast_exp2(x0);
-            p1 = fast_exp2(x1);
+          for (int i = 0; i < 32; ++i) {
+            const int key = kbase + g * 32 + i;
+            if (!(key <= row_pos && key >= row_lo)) v[i] = __float_as_uint(-INFINITY);
           }
-          sum[i] += p0 + p1;
-          packed[(j >> 1) + i] = pack_bf16(p0, p1);
         }
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float p0, p1;
+            if (i < TS_ATT_FMA_PAIRS) {
+              const uint64_t x = fma2(pack2(__uint_as_float(v[j + 2 * i]), __uint_as_float(v[j + 2 * i + 1])), scale2, off2);
+              exp2_pair_fma(x, p0, p1);
+            } else {
+              p0 = fast_exp2(fmaf(__uint_as_float(v[j + 2 * i]), p.scale_log2, -m_off));
+              p1 = fast_exp2(fmaf(__uint_as_float(v[j + 2 * i + 1]), p.scale_log2, -m_off));
+            }
+            sum2[i] = add2(sum2[i], pack2(p0, p1));
+            packed[(j >> 1) + i] = pack_bf16(p0, p1);
+          }
+        }
+        tmem_st16(s_addr + g * 16, packed);
       }
-      l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-      if (row == 0) PROBE(t * 2, blk, 4);
-      if (row == 0) PROBE(t * 2, blk, 5);
-      // P over the first half of the S buffer it came from (this thread's own lane)
-      tmem_st32(lane_addr + t * 128 + buf * 64, packed);
+      {
+        float even, odd;
+        unpack2(add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3])), even, odd);
+        l_run += even + odd;
+      }
+      if (h == 0 && row == 0) PROBE(t * 2, blk, 4);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      if (row == 0) PROBE(t * 2, blk, 6);
-      // rows of V that no request has written (beyond the last key): zeros, by the last tile
-      if (t == ntiles - 1 && kbase + BN - 1 > hi) {
+      if (h == 0 && row == 0) PROBE(t * 2, blk, 5);
+      // Rows of V that no request has written (beyond the last key): zeros (a masked key's weight
+      // is zero, but zero times garbage must stay zero).  Both tiles write them: each tile's P V
+      // waits for its own threads only.
+      if ((kb0 + blk) * PBN + PBN - 1 > hi) {
         const int st = blk % KV_RING;
-        ok = mbar_wait(smem_u32(&v_full[st]), (uint32_t)(blk / KV_RING) & 1, abort_flag);
-        if (!__all_sync(0xffffffffu, ok)) break;
-        const int first_bad = hi - kbase + 1;
-        for (int i = row; i < (BN - first_bad) * 16; i += BM) {
+        mbar_wait(smem_u32(&v_full[st]), (uint32_t)(blk / KV_RING) & 1, abort_flag);  // if it gives up: the next barrier ends the loop
+        __syncwarp();
+        const int first_bad = hi - (kb0 + blk) * PBN + 1;
+        for (int i = h * BM + row; i < (PBN - first_bad) * 16; i += 2 * BM) {
           const int vrow = first_bad + i / 16, piece = i % 16;
-          *reinterpret_cast<uint4*>(smem + P2_OFF_V + st * KV_STAGE + (piece >> 3) * KV_HALF + vrow * 128 + ((piece & 7) << 4)) =
+          *reinterpret_cast<uint4*>(smem + P2_OFF_V + st * PKV_STAGE + (piece >> 3) * PKV_HALF + vrow * 128 + ((piece & 7) << 4)) =
               make_uint4(0u, 0u, 0u, 0u);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
-      // Every phase of pv_done is waited for, so that a later wait cannot take an older phase
-      // for the one it means; P V of the block before is long done by now.
-      if (blk > 0) {
-        ok = mbar_wait(smem_u32(&pv_done), (uint32_t)(blk - 1) & 1, abort_flag);
-        if (!__all_sync(0xffffffffu, ok)) break;
-      }
+      if (h == 0 && row == 0) PROBE(t * 2, blk, 6);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&p_ready));
-      if (row == 0) PROBE(t * 2, blk, 7);
+      if (lane == 0) mbar_arrive(smem_u32(&p_ready[t]));
+      if (h == 0 && row == 0) PROBE(t * 2, blk, 7);
     }
 
-    if (tid == 0) PROBE(1, 60, 6);
     ok = mbar_wait(smem_u32(&all_done), 0, abort_flag);
-    if (tid == 0) PROBE(1, 59, 6);
     const bool good = __all_sync(0xffffffffu, ok) && *abort_flag == 0;
+    // the row's sum: both halves'.  (The eight warps of the tile meet whatever happened before.)
+    sum_s[t][h][row] = l_run;
+    asm volatile("bar.sync %0, 256;" ::"r"(1 + t) : "memory");
+    l_run += sum_s[t][h ^ 1][row];
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
     unsigned char* o_tile = smem + P2_OFF_Q + t * Q_BYTES;
     if (good) {
@@ -916,7 +935,7 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
       // that rows leave as whole 256-byte lines: row `row` at row * 256, its 16-byte piece c at
       // position c ^ (row % 16), which spreads both the writes and the reads over the banks.
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
         tmem_ld32(o_addr + c * 32, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -927,18 +946,16 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
           chunk.y = pack_bf16(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
           chunk.z = pack_bf16(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
           chunk.w = pack_bf16(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
-          *reinterpret_cast<uint4*>(o_tile + row * 256 + (((c * 4 + i) ^ (row & 15)) << 4)) = chunk;
+          *reinterpret_cast<uint4*>(o_tile + row * 256 + (((h * 8 + c * 4 + i) ^ (row & 15)) << 4)) = chunk;
         }
       }
     }
-    // the four warps of this tile meet here whatever happened before
-    if (tid == 0) PROBE(1, 56, 6);
-    asm volatile("bar.sync %0, 128;" ::"r"(1 + t) : "memory");
-    if (tid == 0) PROBE(1, 55, 6);
+    asm volatile("bar.sync %0, 256;" ::"r"(1 + t) : "memory");
     if (good) {
+      const int me = h * BM + row;  // 0..255 among the tile's threads
 #pragma unroll 4
-      for (int it = 0; it < 16; ++it) {
-        const int idx = it * BM + row;
+      for (int it = 0; it < 8; ++it) {
+        const int idx = it * 2 * BM + me;
         const int rr = idx >> 4, piece = idx & 15;
         const int rg = r0 + t * RT + rr;
         if (rr < RT && rg < rows_total) {
@@ -950,7 +967,6 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
     }
   }
 
-  if (tid == 0) PROBE(1, 58, 6);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (abort_s != 0 && tid == 0) *p.error = 1;
@@ -958,7 +974,6 @@ __global__ void __launch_bounds__(352, 1) attention_tcgen05_pair_kernel(const __
     __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(P2_TMEM_COLS) : "memory");
   }
-  if (tid == 0) PROBE(1, 57, 6);
 }
 
 // ---------------------------------------------------------------------------
@@ -1001,7 +1016,7 @@ TS_EXPORT int ts_attention_tcgen05_supported(int nq, int nkv, int page) {
   if (nq <= 0 || nkv <= 0 || nq % nkv) return 0;
   const int G = nq / nkv;
   if (G > BM) return 0;
-  if (page < 8 || (BN % page && page % BN)) return 0;
+  if (page < 8 || (BN % page && page % PBN)) return 0;  // a page divides 64, or is a multiple of 128
   return 1;
 }
 
@@ -1019,13 +1034,6 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
     return TS_ERR_BAD_ARGUMENT;
   if (total_slots > 0x7fffffffLL - page || ((long long)max_q * (nq / nkv) / ((BM / (nq / nkv)) * (nq / nkv)) + 1) * nkv * B > 0x7fffffffLL) return TS_ERR_UNSUPPORTED_SIZE;
   if (((uintptr_t)q | (uintptr_t)kcache | (uintptr_t)vcache | (uintptr_t)out) % 16) return TS_ERR_UNSUPPORTED_SIZE;
-  CUtensorMap mq, mk, mv;
-  int st = query_map(q, T, nq, nkv, &mq);
-  if (st) return st;
-  st = ts_kv_cache_map(kcache, total_slots, nkv, D, page < BN ? page : BN, &mk);
-  if (st) return st;
-  st = ts_kv_cache_map(vcache, total_slots, nkv, D, page < BN ? page : BN, &mv);
-  if (st) return st;
   Params p;
   p.out = (__nv_bfloat16*)out;
   p.cu_q = cu_q;
@@ -1045,6 +1053,14 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
   const int RT = (BM / G) * G;  // rows of a tile that belong to tokens
   const long long rows = (long long)max_q * G;
   const bool pairs = mode == 2 || (mode == 0 && rows > RT);
+  const int block_keys = pairs ? PBN : BN;  // keys per copy: a whole page, or a block's worth of a larger one
+  CUtensorMap mq, mk, mv;
+  int st = query_map(q, T, nq, nkv, &mq);
+  if (st) return st;
+  st = ts_kv_cache_map(kcache, total_slots, nkv, D, page < block_keys ? page : block_keys, &mk);
+  if (st) return st;
+  st = ts_kv_cache_map(vcache, total_slots, nkv, D, page < block_keys ? page : block_keys, &mv);
+  if (st) return st;
   if (pairs) {
     const size_t smem = P2_SMEM + 1024;
     static bool configured = false;
@@ -1053,7 +1069,7 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    return ts_launch(attention_tcgen05_pair_kernel, dim3((unsigned)(((rows + 2 * RT - 1) / (2 * RT)) * nkv * B)), dim3(352), smem,
+    return ts_launch(attention_tcgen05_pair_kernel, dim3((unsigned)(((rows + 2 * RT - 1) / (2 * RT)) * nkv * B)), dim3(608), smem,
                      (cudaStream_t)stream_, mq, mk, mv, p);
   }
   const size_t smem = SMEM_TILES + 1024;

@@ -813,12 +813,12 @@ def _attention_tcgen05_fns():
 def attention_tcgen05_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
     """Whether the tcgen05 prompt-attention kernel takes these sizes: head size 128, at most 128
     query heads per key/value head (a tile of 128 rows holds whole tokens: 128 // group of them), a
-    page size of at least 8 that divides 64 or is a multiple of it."""
+    page size of at least 8 that divides 64 or is a multiple of 128."""
     if not _USE_ATTENTION_TCGEN05 or head_dim != ATTENTION_TCGEN05_HEAD_DIM:
         return False
     if num_kv_heads <= 0 or num_heads % num_kv_heads or num_heads // num_kv_heads > 128:
         return False
-    return page_size >= 8 and (64 % page_size == 0 or page_size % 64 == 0)
+    return page_size >= 8 and (64 % page_size == 0 or page_size % 128 == 0)
 
 
 def attention_prefill_tcgen05(
@@ -855,7 +855,7 @@ def attention_prefill_tcgen05(
     nq, nkv = num_heads, num_kv_heads
     if not ok(nq, nkv, page_size):
         raise KernelError(
-            f"attention_prefill_tcgen05: needs at most 128 query heads per key/value head and a page size of at least 8 that divides 64 or is a multiple of it; "
+            f"attention_prefill_tcgen05: needs at most 128 query heads per key/value head and a page size of at least 8 that divides 64 or is a multiple of 128; "
             f"got {nq} query heads, {nkv} key/value heads, pages of {page_size}")
     if q.numel() != T * nq * d or out.numel() != T * nq * d:
         raise KernelError("attention_prefill_tcgen05: q/out do not match [T, heads*128]")
