@@ -247,6 +247,15 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
       table_s[i] = e < p.max_blocks ? table[e] : -1;
     }
   }
+  if (RT < BM) {
+    // the rows of the Q tile that no copy fills (they belong to nobody): zeros, so that their scores are
+    // numbers like any others
+    for (int i = tid; i < 2 * (BM - RT) * 8; i += 128) {
+      const int half = i / ((BM - RT) * 8), rest = i % ((BM - RT) * 8);
+      *reinterpret_cast<uint4*>(smem + OFF_Q + half * (BM * 128) + (RT + rest / 8) * 128 + (rest % 8) * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
   if (warp == 0) {
     __syncwarp();
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
@@ -335,8 +344,9 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
     }
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 
-    const bool unmasked = (kbase + BN - 1 <= first_pos) && RT == BM && (r0 + BM <= rows_total) &&
-                          (p.window <= 0 || kbase >= start_pos + (r0 + BM - 1) / G - p.window + 1);
+    // every key of the block is seen by every row of the tile that belongs to a token (rows that belong
+    // to nobody need no mask: a row's result depends on that row alone, and theirs is never stored)
+    const bool unmasked = (kbase + BN - 1 <= first_pos) && (p.window <= 0 || kbase >= start_pos + last_row / G - p.window + 1);
     float m_new = m_run;
     if (unmasked) {
 #pragma unroll
@@ -623,6 +633,16 @@ __global__ void __launch_bounds__(608, 1) attention_tcgen05_pair_kernel(const __
       table_s[i] = e < p.max_blocks ? table[e] : -1;
     }
   }
+  if (RT < BM) {
+    // the rows of the Q tiles that no copy fills (they belong to nobody): zeros, so that their scores are
+    // numbers like any others
+    for (int i = tid; i < 4 * (BM - RT) * 8; i += blockDim.x) {
+      const int part = i / ((BM - RT) * 8), rest = i % ((BM - RT) * 8);  // part: tile * 2 + half of the head
+      *reinterpret_cast<uint4*>(smem + P2_OFF_Q + (part >> 1) * Q_BYTES + (part & 1) * (BM * 128) + (RT + rest / 8) * 128 + (rest % 8) * 16) =
+          make_uint4(0u, 0u, 0u, 0u);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
   if (warp == 0) {
     __syncwarp();
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(P2_TMEM_COLS) : "memory");
@@ -778,8 +798,7 @@ __global__ void __launch_bounds__(608, 1) attention_tcgen05_pair_kernel(const __
     const int row_pos = (row < RT && r < rows_total) ? start_pos + r / G : -1;
     const int row_lo = (p.window > 0 && row_pos >= 0) ? max(0, row_pos - p.window + 1) : 0;
     const int tile_first_pos = start_pos + (r0 + t * RT) / G;
-    const int tile_last_pos = start_pos + (r0 + t * RT + RT - 1) / G;
-    const bool tile_full = RT == BM && r0 + (t + 1) * BM <= rows_total;
+    const int tile_last_pos = start_pos + (min(r0 + t * RT + RT, rows_total) - 1) / G;  // of the tile's rows that belong to a token
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     const uint32_t s_addr = lane_addr + t * 128 + h * 64;        // this thread's 64 scores; its P goes over the first 32 of them
     const int pair_bar = 3 + t * 4 + quad;                       // hardware barrier of the two warps that share rows
@@ -794,7 +813,9 @@ __global__ void __launch_bounds__(608, 1) attention_tcgen05_pair_kernel(const __
       __syncwarp();
       if (h == 0 && row == 0) PROBE(t * 2, blk, 1);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const bool unmasked = tile_full && (kbase + 63 <= tile_first_pos) && (p.window <= 0 || kbase >= tile_last_pos - p.window + 1);
+      // every one of these 64 keys is seen by every row of the tile that belongs to a token (rows that
+      // belong to nobody need no mask: a row's result depends on that row alone, and theirs is never stored)
+      const bool unmasked = (kbase + 63 <= tile_first_pos) && (p.window <= 0 || kbase >= tile_last_pos - p.window + 1);
       // First walk over this thread's 64 scores: their largest.
       float m_blk;
       {
