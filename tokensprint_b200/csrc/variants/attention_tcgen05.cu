@@ -578,6 +578,7 @@ __global__ void __launch_bounds__(608, 1) attention_tcgen05_pair_kernel(const __
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   __shared__ int table_s[MAX_TABLE];
+  __shared__ int quit_s[2][4][2];   // [tile][quarter of the rows][block parity]: see the softmax warps
   __shared__ float sum_s[2][2][BM];  // [tile][half of the keys][row]: what the two threads of a row tell each other (a block's largest score; at the end their sums)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -843,11 +844,14 @@ __global__ void __launch_bounds__(608, 1) attention_tcgen05_pair_kernel(const __
       if (h == 0 && row == 0) PROBE(t * 2, blk, 2);
       // The row's largest score of the block is the larger of the two halves'.  The two warps that
       // share rows meet at a hardware barrier once per block, and it is the only place where they
-      // leave the loop: a wait that gave up has raised abort_s, which both see after the barrier,
-      // so neither is ever left waiting for the other.
+      // leave the loop, both or neither: a wait that gave up has raised abort_s; the first warp of
+      // the two looks at it before the barrier and leaves what it saw where both read it after the
+      // barrier (in turns in two places, so that the next block's word never overtakes this one's).
+      // So neither is ever left waiting for the other.
       sum_s[t][h][row] = m_blk;
+      if (h == 0 && lane == 0) quit_s[t][quad][blk & 1] = *abort_flag;
       asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-      if (*abort_flag) break;
+      if (quit_s[t][quad][blk & 1] != 0) break;
       m_blk = fmaxf(m_blk, sum_s[t][h ^ 1][row]);
       if (h == 0 && row == 0) PROBE(t * 2, blk, 3);
       // raise the running max only when it is far behind (both threads of a row decide alike)
