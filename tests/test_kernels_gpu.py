@@ -828,6 +828,17 @@ def test_gemm_skinny_qk_rope_store(M, nq, nkv, K, rope, norm):
     q2, (kc2, vc2) = torch.empty_like(q), caches()
     ops.gemm_qk_rope_store(x, w, q2, kc2, vc2, slots, positions, qw, kw, 1e-5, inv_freq, nq, nkv, scale_ssq=ssq, scale_width=K, scale_eps=1e-6)
     assert torch.equal(q, q2) and torch.equal(kc, kc2) and torch.equal(vc, vc2)
+    if rope:
+        # with the step's table of cosines and sines instead of the epilogue's own: the same bits
+        table = ops.rope_cos_sin(positions, inv_freq, M)
+        want = torch.stack([torch.cos(positions.float()[:, None] * inv_freq[None, :]), torch.sin(positions.float()[:, None] * inv_freq[None, :])], dim=-1)
+        assert table.shape == (M, d // 2, 2) and float((table - want).abs().max()) < 2e-6
+        q3, (kc3, vc3) = torch.empty_like(q), caches()
+        ops.gemm_qk_rope_store(x, w, q3, kc3, vc3, slots, positions, qw, kw, 1e-5, inv_freq, nq, nkv, scale_ssq=ssq, scale_width=K, scale_eps=1e-6,
+                               cos_sin=table)
+        assert torch.equal(q, q3) and torch.equal(kc, kc3) and torch.equal(vc, vc3)
+        with pytest.raises(ops.KernelError, match="cos_sin"):
+            ops.gemm_qk_rope_store(x, w, q3, kc3, vc3, slots, positions, qw, kw, 1e-5, inv_freq, nq, nkv, cos_sin=table[: M - 1] if M > 1 else table.half())
 
 
 def test_gemm_skinny_refuses_what_it_cannot_take():

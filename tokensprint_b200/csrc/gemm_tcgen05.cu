@@ -124,6 +124,7 @@ struct GemmArgs {
   const float* q_norm_w;         //   [128] or null
   const float* k_norm_w;
   const float* inv_freq;         //   [64] or null (no rotation)
+  const float2* rope_cs;         //   [M, 64] (cos, sin) of positions[m] * inv_freq[j], or null: computed here
   float qk_eps;
   int nq, nkv;
 #ifdef TS_GEMM_PROBE
@@ -253,8 +254,47 @@ __device__ __forceinline__ Range cta_range(const GemmArgs& a, int cta) {
 //   EPI_RESIDUAL_NORM: hidden[m][n] += sum; xprime = bf16(hidden * norm_w[n]); ssq_out[t][m] =
 //     the sum over the tile's columns of hidden^2 (a warp takes a whole row of the tile, so
 //     the sum needs shuffles only and is the same in every run).
+// `ahead` (EPI_RESIDUAL_NORM): what this thread will need from device memory, asked for when the
+// tile's accumulator was taken (hidden values in the order of the loop below, then the norm's four
+// weights), so that the trips are over when the sums are there.
 template <int MPAD>
-__device__ __forceinline__ void fused_epilogue(const GemmArgs& args, int t, int etid, int lane, const float* tile, const float* rstd) {
+struct EpilogueAhead {
+  static constexpr int ROUNDS = MPAD / 4;  // passes of the 128 threads over a tile of MPAD rows x 32 pieces
+  float4 hidden[ROUNDS];
+  float4 norm_w;
+};
+template <int MPAD>
+__device__ __forceinline__ void load_ahead(const GemmArgs& args, int t, int etid, EpilogueAhead<MPAD>& ahead) {
+  const int nl = (etid & 31) * 4, n0 = t * TILE_N + nl;
+  const bool whole = n0 + 3 < args.N && (args.ldh & 3) == 0;  // the four columns exist and the rows are 16-byte aligned
+#pragma unroll
+  for (int it = 0; it < EpilogueAhead<MPAD>::ROUNDS; ++it) {
+    const int m = (etid + it * 128) >> 5;
+    float4 h = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (m < args.M) {
+      const float* hp = args.hidden + (size_t)m * args.ldh + n0;
+      if (whole) {
+        h = __ldcg(reinterpret_cast<const float4*>(hp));
+      } else {
+        if (n0 < args.N) h.x = __ldcg(hp);
+        if (n0 + 1 < args.N) h.y = __ldcg(hp + 1);
+        if (n0 + 2 < args.N) h.z = __ldcg(hp + 2);
+        if (n0 + 3 < args.N) h.w = __ldcg(hp + 3);
+      }
+    }
+    ahead.hidden[it] = h;
+  }
+  float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (n0 < args.N) w.x = args.norm_w[n0];
+  if (n0 + 1 < args.N) w.y = args.norm_w[n0 + 1];
+  if (n0 + 2 < args.N) w.z = args.norm_w[n0 + 2];
+  if (n0 + 3 < args.N) w.w = args.norm_w[n0 + 3];
+  ahead.norm_w = w;
+}
+
+template <int MPAD>
+__device__ __forceinline__ void fused_epilogue(const GemmArgs& args, int t, int etid, int lane, const float* tile, const float* rstd,
+                                               const EpilogueAhead<MPAD>& ahead) {
   if (args.mode == EPI_SWIGLU) {
     const int half_n = args.N >> 1;
     for (int idx = etid; idx < args.M * 16; idx += 128) {
@@ -269,20 +309,39 @@ __device__ __forceinline__ void fused_epilogue(const GemmArgs& args, int t, int 
         if (t * 64 + j + i < half_n) dst[i] = __float2bfloat16_rn(gs[i] / (1.f + __expf(-gs[i])) * us[i]);
     }
   } else if (args.mode == EPI_RESIDUAL_NORM) {
-    for (int idx = etid; idx < args.M * 32; idx += 128) {
-      const int m = idx >> 5, nl = (idx & 31) * 4;  // the 32 lanes of a warp share m
+    const int nl = (etid & 31) * 4, n0 = t * TILE_N + nl;  // the 32 lanes of a warp share m
+    const bool whole = n0 + 3 < args.N && (args.ldh & 3) == 0;
+    const float nw[4] = {ahead.norm_w.x, ahead.norm_w.y, ahead.norm_w.z, ahead.norm_w.w};
+#pragma unroll
+    for (int it = 0; it < EpilogueAhead<MPAD>::ROUNDS; ++it) {
+      const int m = (etid + it * 128) >> 5;
+      if (m >= args.M) break;  // the same for the whole warp
       const float4 v = *reinterpret_cast<const float4*>(tile + m * TILE_N + nl);
       const float vals[4] = {v.x, v.y, v.z, v.w};
-      const int n0 = t * TILE_N + nl;
+      const float old[4] = {ahead.hidden[it].x, ahead.hidden[it].y, ahead.hidden[it].z, ahead.hidden[it].w};
+      float h[4];
       float ss = 0.f;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        if (n0 + i < args.N) {
-          float* hp = args.hidden + (size_t)m * args.ldh + n0 + i;
-          const float h = *hp + vals[i] * rstd[m];
-          *hp = h;
-          args.xprime[(size_t)m * args.ldh + n0 + i] = __float2bfloat16_rn(h * args.norm_w[n0 + i]);
-          ss += h * h;
+        h[i] = old[i] + vals[i] * rstd[m];
+        if (n0 + i < args.N) ss += h[i] * h[i];
+      }
+      float* hp = args.hidden + (size_t)m * args.ldh + n0;
+      __nv_bfloat16* xp = args.xprime + (size_t)m * args.ldh + n0;
+      if (whole) {
+        *reinterpret_cast<float4*>(hp) = make_float4(h[0], h[1], h[2], h[3]);
+        __nv_bfloat162 lo = __floats2bfloat162_rn(h[0] * nw[0], h[1] * nw[1]), hi = __floats2bfloat162_rn(h[2] * nw[2], h[3] * nw[3]);
+        uint2 packed;
+        packed.x = *reinterpret_cast<unsigned*>(&lo);
+        packed.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(xp) = packed;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (n0 + i < args.N) {
+            hp[i] = h[i];
+            xp[i] = __float2bfloat16_rn(h[i] * nw[i]);
+          }
         }
       }
       ss = ts_warp_sum(ss);
@@ -309,12 +368,21 @@ __device__ __forceinline__ void fused_epilogue(const GemmArgs& args, int t, int 
         if (args.inv_freq != nullptr) {
           const float pos = (float)args.positions[m];
           const bool upper = nl >= 64;
+          float sn[4], cs[4];
+          if (args.rope_cs != nullptr) {
+            // the step's table: the same float32 values that sincosf gives here, computed once for all layers
+            const float4 a = *reinterpret_cast<const float4*>(args.rope_cs + (size_t)m * 64 + (nl & 63));
+            const float4 b = *reinterpret_cast<const float4*>(args.rope_cs + (size_t)m * 64 + (nl & 63) + 2);
+            cs[0] = a.x; sn[0] = a.y; cs[1] = a.z; sn[1] = a.w;
+            cs[2] = b.x; sn[2] = b.y; cs[3] = b.z; sn[3] = b.w;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sincosf(pos * args.inv_freq[(nl & 63) + i], &sn[i], &cs[i]);
+          }
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float partner = __shfl_xor_sync(0xffffffffu, v[i], 16);
-            float sn, cs;
-            sincosf(pos * args.inv_freq[(nl & 63) + i], &sn, &cs);
-            v[i] = upper ? v[i] * cs + partner * sn : v[i] * cs - partner * sn;
+            v[i] = upper ? v[i] * cs[i] + partner * sn[i] : v[i] * cs[i] - partner * sn[i];
           }
         }
       }
@@ -635,14 +703,13 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
         __syncwarp();
         if (etid == 0 && t == t_last && p == phases - 1) TS_PROBE(4);
         if (etid == 0 && t == t_last) { const GemmArgs& args = chain.g[0]; (void)args; TS_PROBE(8 + 8 * p + 3); }
-        if (fused && args.mode == EPI_RESIDUAL_NORM) {
-          // whoever finishes this tile adds it to the residual stream: ask for those values now,
-          // so that they are in the L1 when the partial sums and the ticket have made their trips
-          for (int idx = etid; idx < args.M * 32; idx += 128) {
-            const int pn = t * TILE_N + (idx & 31) * 4;
-            if (pn < args.N) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.hidden + (size_t)(idx >> 5) * args.ldh + pn));
-          }
-          if (etid < 32 && t * TILE_N + etid * 4 < args.N) asm volatile("prefetch.global.L1 [%0];" ::"l"(args.norm_w + t * TILE_N + etid * 4));
+        EpilogueAhead<MPAD <= FUSED_MAX_ROWS ? MPAD : 4> ahead;
+        if (MPAD <= FUSED_MAX_ROWS && fused && args.mode == EPI_RESIDUAL_NORM) {
+          // whoever finishes this tile adds it to the residual stream: ask for those values now (into
+          // registers), so that they are here when the partial sums and the ticket have made their
+          // trips.  Nobody else writes them before this tile is finished: a tile's columns are
+          // written by the CTA that finishes it, and by kernels that are over.
+          load_ahead<MPAD <= FUSED_MAX_ROWS ? MPAD : 4>(args, t, etid, ahead);
         }
         const int n_local = quarter * 32 + lane;
         const int n = t * TILE_N + n_local;
@@ -756,7 +823,7 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
         }
         if (fused && (whole || last)) {  // the same for all epilogue threads
           epilogue_sync();  // tile_s holds the tile's final sums
-          fused_epilogue<MPAD>(args, t, etid, lane, tile_s, rstd_s);
+          fused_epilogue<MPAD <= FUSED_MAX_ROWS ? MPAD : 4>(args, t, etid, lane, tile_s, rstd_s, ahead);
           epilogue_sync();  // before the next tile overwrites tile_s
         }
       }
@@ -1030,13 +1097,15 @@ TS_EXPORT int ts_gemm_skinny_fused(const void* x, const void* w, void* out, int 
 // The q/k/v projection of an attention layer with head size 128 (w: nq query heads, then nkv key
 // heads, then nkv value heads, 128 rows each), with what follows it done where each head's tile is
 // finished: per-head RMS norm of queries and keys (weights [128] or null), rotate-half rotation
-// with angle = position * inv_freq[j] (inv_freq [64] or null), queries to q_out [M, nq * 128], keys
+// with angle = position * inv_freq[j] (inv_freq [64] or null; rope_cos_sin [M, 64, 2] or null: the
+// cosines and sines of those angles if the caller has them, as ts_rope_cos_sin leaves them),
+// queries to q_out [M, nq * 128], keys
 // and values to slot slot_mapping[m] of the caches [slots, nkv, 128] (-1: not stored).
 // scale_ssq as in ts_gemm_skinny_fused.
 TS_EXPORT int ts_gemm_skinny_qk_rope(const void* x, const void* w, int M, int K, long long ldx, long long ldw, int nq, int nkv,
                                      void* q_out, void* k_cache, void* v_cache, const int* slot_mapping, const int* positions,
                                      const float* q_norm_w, const float* k_norm_w, float qk_eps, const float* inv_freq,
-                                     const float* scale_ssq, int scale_tiles, float scale_width, float scale_eps,
+                                     const float* rope_cos_sin, const float* scale_ssq, int scale_tiles, float scale_width, float scale_eps,
                                      float* partial, int* counters, int* error, const void* prefetch, long long prefetch_bytes,
                                      void* stream_);
 
@@ -1152,14 +1221,14 @@ TS_EXPORT int ts_gemm_skinny_fused(const void* x, const void* w, void* out, int 
 TS_EXPORT int ts_gemm_skinny_qk_rope(const void* x, const void* w, int M, int K, long long ldx, long long ldw, int nq, int nkv,
                                      void* q_out, void* k_cache, void* v_cache, const int* slot_mapping, const int* positions,
                                      const float* q_norm_w, const float* k_norm_w, float qk_eps, const float* inv_freq,
-                                     const float* scale_ssq, int scale_tiles, float scale_width, float scale_eps,
+                                     const float* rope_cos_sin, const float* scale_ssq, int scale_tiles, float scale_width, float scale_eps,
                                      float* partial, int* counters, int* error, const void* prefetch, long long prefetch_bytes,
                                      void* stream_) {
   if (M <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || q_out == nullptr || k_cache == nullptr || v_cache == nullptr || slot_mapping == nullptr ||
       (inv_freq != nullptr && positions == nullptr))
     return TS_ERR_BAD_ARGUMENT;
-  if (((uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) % 8) return TS_ERR_UNSUPPORTED_SIZE;
+  if (((uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) % 8 || (uintptr_t)rope_cos_sin % 16) return TS_ERR_UNSUPPORTED_SIZE;
   GemmArgs a = {};
   a.mode = EPI_QK_ROPE;
   a.scale_ssq = scale_ssq;
@@ -1174,6 +1243,7 @@ TS_EXPORT int ts_gemm_skinny_qk_rope(const void* x, const void* w, int M, int K,
   a.q_norm_w = q_norm_w;
   a.k_norm_w = k_norm_w;
   a.inv_freq = inv_freq;
+  a.rope_cs = inv_freq != nullptr ? reinterpret_cast<const float2*>(rope_cos_sin) : nullptr;
   a.qk_eps = qk_eps;
   a.nq = nq;
   a.nkv = nkv;

@@ -387,3 +387,26 @@ TS_EXPORT int ts_qk_norm_rope_store(const void* qkv, int act_dtype, void* q_out,
     return TS_ERR_BAD_ARGUMENT;
   return ts_launch_status();
 }
+
+// The rotation's cosines and sines for every token of a step, once for all layers that rotate with
+// the same frequencies: out[t][j] = (cos, sin)(positions[t] * inv_freq[j]), j < half, with the
+// same float32 product and the same sincosf as the kernels that rotate by themselves
+// (engine/nn/rope.py:105-123 of the reference: angles and trigonometry in float32).
+__global__ void rope_cos_sin_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int T, int half,
+                                    float2* __restrict__ out) {
+  ts_pdl_prologue();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * half) return;
+  const int t = i / half, j = i - t * half;
+  float sn, cs;
+  sincosf((float)positions[t] * inv_freq[j], &sn, &cs);
+  out[i] = make_float2(cs, sn);
+}
+
+TS_EXPORT int ts_rope_cos_sin(const int* positions, const float* inv_freq, int T, int half, float* out, void* stream) {
+  if (T <= 0 || half <= 0) return 0;
+  if (positions == nullptr || inv_freq == nullptr || out == nullptr || ((uintptr_t)out % 8)) return TS_ERR_BAD_ARGUMENT;
+  const int n = T * half;
+  return ts_launch(rope_cos_sin_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, positions, inv_freq, T, half,
+                   reinterpret_cast<float2*>(out));
+}

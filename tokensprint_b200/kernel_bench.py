@@ -257,13 +257,14 @@ def layer_products(cfg, timer, pk, rows, device):
         vc = torch.zeros_like(kc)
         slots = torch.arange(M, device=device, dtype=torch.int32)
         pos = torch.arange(M, device=device, dtype=torch.int32)
+        cos_sin = ops.rope_cos_sin(pos, inv_freq, M)  # once a step in the engine: not part of a layer
 
         def layer(w, nxt):
             ops.gemm_skinny_fused(attn, w["o"], mode=ops.GEMM_EPILOGUE_RESIDUAL_NORM, hidden=hidden, norm_weight=n1, xprime=x1, ssq_out=ssq1, prefetch=w["gu"])
             ops.gemm_skinny_fused(x1, w["gu"], out=act, mode=ops.GEMM_EPILOGUE_SWIGLU, scale_ssq=ssq1, scale_width=H, scale_eps=1e-6, prefetch=w["down"])
             ops.gemm_skinny_fused(act, w["down"], mode=ops.GEMM_EPILOGUE_RESIDUAL_NORM, hidden=hidden, norm_weight=n2, xprime=x2, ssq_out=ssq2, prefetch=w["qkv"])
             ops.gemm_qk_rope_store(x2, w["qkv"], q, kc, vc, slots, pos, qn, kn, 1e-6, inv_freq, nq, nkv,
-                                   scale_ssq=ssq2, scale_width=H, scale_eps=1e-6, prefetch=nxt["o"])
+                                   scale_ssq=ssq2, scale_width=H, scale_eps=1e-6, prefetch=nxt["o"], cos_sin=cos_sin)
 
         for chained in (False, True):
             def body():

@@ -119,6 +119,7 @@ class Model:
     def forward_hidden(self, step: StepContext, caches: list[LayerCache]) -> tuple[torch.Tensor, Optional[torch.Tensor]]:
         """Runs the blocks; returns the float32 residual and the last branch not yet added."""
         T = step.num_tokens
+        step.shared.clear()  # what parts share lasts one run of the blocks (a step's description may be run again: warm-up, then capture)
         hidden = torch.empty((T, self.spec.hidden_size), device=self.device, dtype=torch.float32)
         ops.embed_gather(hidden, self.embedding, step.token_ids)
         if self.embedding_transform is not None:

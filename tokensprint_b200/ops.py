@@ -1098,11 +1098,27 @@ def gemm_skinny_fused(
 _SIGNATURES["ts_gemm_skinny_qk_rope"] = [
     _c_void_p, _c_void_p, _c_int, _c_int, _c_ll, _c_ll, _c_int, _c_int,
     _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
-    _c_void_p, _c_void_p, _c_float, _c_void_p,
+    _c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p,
     _c_void_p, _c_int, _c_float, _c_float,
     _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_ll, _c_void_p,
 ]
 GEMM_QK_ROPE_HEAD_DIM = 128
+
+_SIGNATURES["ts_rope_cos_sin"] = [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p]
+
+
+def rope_cos_sin(positions: torch.Tensor, inv_freq: torch.Tensor, num_tokens: int) -> torch.Tensor:
+    """[num_tokens, len(inv_freq), 2] float32: (cos, sin) of positions[t] * inv_freq[j], the float32
+    product and functions that the rotating kernels use themselves.  A step computes it once for
+    all layers that rotate with the same frequencies."""
+    _cuda_contig("positions", positions, torch.int32)
+    _cuda_contig("inv_freq", inv_freq, torch.float32)
+    if positions.numel() < num_tokens:
+        raise KernelError("rope_cos_sin: positions are shorter than the tokens")
+    half = inv_freq.numel()
+    out = torch.empty((num_tokens, half, 2), device=positions.device, dtype=torch.float32)
+    _check("rope_cos_sin", _fn("ts_rope_cos_sin")(positions.data_ptr(), inv_freq.data_ptr(), num_tokens, half, out.data_ptr(), _stream()))
+    return out
 
 
 def gemm_qk_rope_store(
@@ -1124,11 +1140,14 @@ def gemm_qk_rope_store(
     scale_width: int = 1,
     scale_eps: float = 0.0,
     prefetch: Optional[torch.Tensor] = None,
+    cos_sin: Optional[torch.Tensor] = None,
 ) -> None:
     """The q/k/v projection (w [(nq + 2 nkv) * 128, K], heads of 128) with qk_norm_rope_store's work
     done in the product's epilogue: per-head RMS norm of q and k, rotate-half rotation over the
     whole head (inv_freq [64]) or none, q to q_out [M, nq * 128], k and v to their cache slots.
-    At most 32 rows.  scale_ssq as in gemm_skinny_fused."""
+    At most 32 rows.  scale_ssq as in gemm_skinny_fused.  cos_sin: rope_cos_sin(positions, inv_freq,
+    M) if the caller has it (the epilogue then reads the angles' cosines and sines instead of
+    computing them)."""
     nq, nkv, d = num_heads, num_kv_heads, GEMM_QK_ROPE_HEAD_DIM
     if not gemm_skinny_supported(x, w) or x.shape[0] > GEMM_FUSED_MAX_ROWS:
         raise KernelError(f"gemm_qk_rope_store: needs bfloat16, at most {GEMM_FUSED_MAX_ROWS} rows and 16-byte aligned rows")
@@ -1152,16 +1171,19 @@ def gemm_qk_rope_store(
         if scale_ssq.dtype != torch.float32 or not scale_ssq.is_contiguous() or scale_ssq.dim() != 2 or scale_ssq.shape[1] != M:
             raise KernelError("gemm_qk_rope_store: scale_ssq must be float32 [tiles, M]")
         scale_tiles = scale_ssq.shape[0]
+    if cos_sin is not None and (inv_freq is None or cos_sin.dtype != torch.float32 or not cos_sin.is_cuda or not cos_sin.is_contiguous()
+                                or cos_sin.numel() < M * d):
+        raise KernelError(f"gemm_qk_rope_store: cos_sin must be float32 [M, {d // 2}, 2] on the device, beside inv_freq")
     partial, counters, error, stream = _gemm_scratch(x.device, M, w.shape[0], K)
     pf = None if prefetch is None else _facts(prefetch)
     _check_product("gemm_qk_rope_store", _fn("ts_gemm_skinny_qk_rope")(
         x.data_ptr(), w.data_ptr(), M, K, x.stride(0), w.stride(0), nq, nkv,
         q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), slot_mapping.data_ptr(), positions.data_ptr(),
-        _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps), _ptr(inv_freq),
+        _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps), _ptr(inv_freq), _ptr(cos_sin),
         _ptr(scale_ssq), scale_tiles, float(scale_width), float(scale_eps),
         partial, counters, error,
         None if pf is None else pf.ptr, 0 if pf is None else min(pf.nbytes, GEMM_PREFETCH_BYTES),
-        stream), x, w, q_out, k_cache, v_cache, slot_mapping, positions, q_norm_weight, k_norm_weight, inv_freq, scale_ssq)
+        stream), x, w, q_out, k_cache, v_cache, slot_mapping, positions, q_norm_weight, k_norm_weight, inv_freq, cos_sin, scale_ssq)
 
 
 _SIGNATURES["ts_wait_gives_up_probe"] = [_c_void_p, _c_int, _c_void_p]

@@ -137,7 +137,8 @@ class AttentionMixer(Mixer):
                 xt, self.qkv_weight, q, cache.k_pages, cache.v_pages, tables.slot_mapping, step.positions,
                 self.q_norm_weight, self.k_norm_weight, self.qk_norm_eps, inv_freq, nq, nkv,
                 scale_ssq=None if pre is None else pre.ssq, scale_width=1 if pre is None else pre.width,
-                scale_eps=0.0 if pre is None else pre.eps, prefetch=self.o_weight)
+                scale_eps=0.0 if pre is None else pre.eps, prefetch=self.o_weight,
+                cos_sin=None if inv_freq is None else self.position.rotary_cos_sin(step))
             out = torch.empty((T, nq * d), device=xt.device, dtype=xt.dtype)
             self._attend(q, out, step, cache, tables)
             if fold is not None:

@@ -138,6 +138,9 @@ class StepContext:
     # Likewise the norm that will read the residual stream after the part returns (a block's
     # last part may prepare that norm's input, see ResidualNorm).
     norm_after: Optional["Norm"] = None
+    # What a part computes once in a step and parts of its kind in other layers use again (the key
+    # names the thing and the constants it was made from); it lives as long as the step.
+    shared: dict = field(default_factory=dict)
 
 
 @dataclass
@@ -233,6 +236,11 @@ class PositionEncoding(Part):
 
     def rotary_inv_freq(self) -> Optional[torch.Tensor]:
         """[rot/2] float32 inverse frequencies for the fused rotate-half kernel, or None."""
+        return None
+
+    def rotary_cos_sin(self, step: StepContext) -> Optional[torch.Tensor]:
+        """[T, rot/2, 2] float32 cosines and sines of the step's angles (position * inverse frequency)
+        for a kernel that would otherwise compute them itself, or None."""
         return None
 
     def apply(self, q: torch.Tensor, k: torch.Tensor, step: StepContext) -> None:

@@ -6,7 +6,8 @@ from typing import Optional
 
 import torch
 
-from tokensprint_b200.parts.base import BuildContext, PositionEncoding, register_part
+from tokensprint_b200 import ops
+from tokensprint_b200.parts.base import BuildContext, PositionEncoding, StepContext, register_part
 
 
 def rope_inverse_frequencies(dim: int, theta: float) -> torch.Tensor:
@@ -35,3 +36,12 @@ class RotaryEncoding(PositionEncoding):
 
     def rotary_inv_freq(self) -> Optional[torch.Tensor]:
         return self.inv_freq
+
+    def rotary_cos_sin(self, step: StepContext) -> Optional[torch.Tensor]:
+        """The table of the step, made by the first layer that asks and used by all layers with the
+        same width and base (angles, cosines and sines in float32, as in the rotating kernels)."""
+        key = ("rotary_cos_sin", self.dim, self.theta)
+        table = step.shared.get(key)
+        if table is None:
+            table = step.shared[key] = ops.rope_cos_sin(step.positions, self.inv_freq, step.num_tokens)
+        return table
