@@ -72,6 +72,28 @@ def test_position_part_owns_the_reference_frequencies():
         build_part("position_encoding", PartSpec("rotary", {"dim": 7, "theta": 1e4}), ctx(torch.float32))
 
 
+def test_position_part_makes_a_step_s_cosines_and_sines_once():
+    """The table that the fused q/k/v product reads: the reference's angles (float32 position times
+    float32 inverse frequency), made by the first layer that asks in a step, found again by a part
+    with the same width and base, not by one with another base, and not kept for the next run."""
+    from tokensprint_b200.parts.base import PartSpec, build_part
+
+    step, _ = one_sequence_step(11, 8, torch.float32, start=1000)
+    a = build_part("position_encoding", PartSpec("rotary", {"dim": 128, "theta": 1e6}), ctx(torch.bfloat16))
+    b = build_part("position_encoding", PartSpec("rotary", {"dim": 128, "theta": 1e6}), ctx(torch.bfloat16))
+    c = build_part("position_encoding", PartSpec("rotary", {"dim": 128, "theta": 1e4}), ctx(torch.bfloat16))
+    table = a.rotary_cos_sin(step)
+    angles = plain.rope_angles(list(range(1000, 1011)), 128, 1e6)  # [T, 64] float32
+    assert table.shape == (11, 64, 2) and table.dtype == torch.float32
+    assert float((table[..., 0].cpu().double() - torch.cos(angles.double())).abs().max()) < 1e-6
+    assert float((table[..., 1].cpu().double() - torch.sin(angles.double())).abs().max()) < 1e-6
+    assert b.rotary_cos_sin(step) is table
+    assert c.rotary_cos_sin(step) is not table
+    step.shared.clear()  # what a model does before it runs its blocks again
+    again = a.rotary_cos_sin(step)
+    assert again is not table and torch.equal(again, table)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_feed_forward_part(dtype):
     from tokensprint_b200.parts.base import PartSpec, build_part
