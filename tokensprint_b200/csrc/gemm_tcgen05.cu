@@ -49,7 +49,8 @@
 #include "common.cuh"
 
 // Optional timestamps for tuning (compile with -DTS_GEMM_PROBE): every CTA records the
-// nanosecond timer at a few points into args.probe[cta * 64 + i] (8 + 8 * phase + k for the stamps of a phase).
+// nanosecond timer at a few points into args.probe[cta * 64 + i] (8 + 8 * phase + k for the stamps of a phase;
+// 40..43 for the end of the CTA's last shared tile: partial sums fenced, ticket known, sums added, epilogue done).
 #ifdef TS_GEMM_PROBE
 #define TS_PROBE(i) do { if (args.probe) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); args.probe[blockIdx.x * 64 + (i)] = t_; } } while (0)
 #else
@@ -754,28 +755,32 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
         bool last = false;
         if (!whole) {
           // Ticket: whoever arrives last for this tile adds the slots, in contributor order.
-          const int c_first = (int)(((long long)t * chunks) / args.units_per);
-          const int c_last = (int)(((long long)(t + 1) * chunks - 1) / args.units_per);
+          // (units are counted in 32 bits: the host refuses a weight with more than 2^31 of them)
+          const int c_first = (int)(((unsigned)t * (unsigned)chunks) / (unsigned)args.units_per);
+          const int c_last = (int)((((unsigned)t + 1u) * (unsigned)chunks - 1u) / (unsigned)args.units_per);
+          // Slot of every contributor for this tile (0: it is that CTA's first tile, else 1): worked out
+          // while the partial sums are on their way, whoever will need it.
+          const float* src[MAX_CONTRIB];
+          const int nc = min(c_last - c_first + 1, MAX_CONTRIB);
+#pragma unroll
+          for (int j = 0; j < MAX_CONTRIB; ++j) {
+            const int c = c_first + min(j, nc - 1);
+            const int c_t_first = (int)(((unsigned)c * (unsigned)args.units_per) / (unsigned)chunks);
+            src[j] = args.partial + (size_t)(c * 2 + ((t == c_t_first) ? 0 : 1)) * args.M * TILE_N;
+          }
           __threadfence();
           epilogue_sync();
+          if (etid == 0 && t == t_last) TS_PROBE(40);
           if (etid == 0) {
             const int ticket = atomicAdd(&args.counters[t], 1);
             last_s = (ticket == c_last - c_first) ? 1 : 0;
           }
           epilogue_sync();
           last = last_s != 0;
+          if (etid == 0 && t == t_last) TS_PROBE(41);
           epilogue_sync();  // everyone has read the flag before the next tile may rewrite it
           if (last) {
             __threadfence();
-            // Slot of every contributor for this tile (0: it is that CTA's first tile, else 1).
-            const float* src[MAX_CONTRIB];
-            const int nc = min(c_last - c_first + 1, MAX_CONTRIB);
-#pragma unroll
-            for (int j = 0; j < MAX_CONTRIB; ++j) {
-              const int c = c_first + min(j, nc - 1);
-              const int c_t_first = (int)(((long long)c * args.units_per) / chunks);
-              src[j] = args.partial + (size_t)(c * 2 + ((t == c_t_first) ? 0 : 1)) * args.M * TILE_N;
-            }
             // Two pieces of four columns per thread and pass, all their loads first (they are
             // independent: one trip to the L2 per pass, not one per piece), then the sums in contributor order.
             constexpr int PIECES = 2;
@@ -819,12 +824,14 @@ __global__ void __launch_bounds__(NUM_THREADS) gemm_skinny_kernel(const __grid_c
               }
             }
             if (etid == 0) args.counters[t] = 0;
+            if (etid == 0 && t == t_last) TS_PROBE(42);
           }
         }
         if (fused && (whole || last)) {  // the same for all epilogue threads
           epilogue_sync();  // tile_s holds the tile's final sums
           fused_epilogue<MPAD <= FUSED_MAX_ROWS ? MPAD : 4>(args, t, etid, lane, tile_s, rstd_s, ahead);
           epilogue_sync();  // before the next tile overwrites tile_s
+          if (etid == 0 && t == t_last) TS_PROBE(43);
         }
       }
       if (alive && p + 1 < phases) {
@@ -1129,6 +1136,7 @@ static int run_gemm(const void* x, const void* w, int M, int N, int K, long long
   const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   int ctas;
   plan(N, K, &a.tiles, &a.chunks, &a.units_per, &ctas);
+  if ((long long)a.tiles * a.chunks + a.units_per >= (1ll << 31)) return TS_ERR_UNSUPPORTED_SIZE;  // the kernel counts units in 32 bits
   CUtensorMap mw, mx;
   int st = tensor_map(w, N, K, ldw, TILE_N, &mw);
   if (st != 0) return st;
