@@ -641,6 +641,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int r = g + 8 * h;
+      if (r0 + r >= rows_total) continue;  // a row of the tile that belongs to nobody is not merged either
       if (tq == 0) {
         m_s[warp * 16 + r] = m_run[h] * p.scale_log2;  // log2 units from here on (-inf stays -inf)
         l_s[warp * 16 + r] = l_run[h];
