@@ -337,6 +337,24 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   // the stage held.  A page that is not held is asked for at a coordinate beyond the declared
   // pool: the copy engine then writes zeros and touches no memory.
   const int box_rows = min(p.page, BN), copies = BN / box_rows;
+  // where box `item` of block `blk` starts in the pool (the block table is read here)
+  auto slot_of = [&](int blk, int item) -> int {
+    const int key0 = (kb0 + blk) * BN + (item / (2 * HALVES)) * box_rows;
+    const int e = key0 / p.page;
+    int page_id = -1;
+    if (key0 <= hi && e < p.max_blocks) page_id = table[e];
+    return page_id >= 0 ? (int)((long long)page_id * p.page + key0 % p.page) : (int)SLOT_BOUND;
+  };
+  // The first blocks' places are looked up once, before the wait (the block table is the step's own,
+  // written before its first kernel): a trip to the table while a stage waits to be filled again
+  // cost the walk more than a microsecond after the wait.  (A lane keeps the place of its own box;
+  // blocks of more than 32 boxes, and later blocks, are looked up when they are asked for.)
+  constexpr int PLACES = 4;
+  const bool places_kept = USE_TMA && copies * 2 * HALVES <= 32;
+  int place[PLACES];
+#pragma unroll
+  for (int i = 0; i < PLACES; ++i)
+    place[i] = (places_kept && warp == 0 && i < nblocks && lane < copies * 2 * HALVES) ? slot_of(i, lane) : (int)SLOT_BOUND;
   auto tma_ask = [&](int blk) -> bool {
     const int stage = blk % TSTAGES;
     bool ok = true;
@@ -347,13 +365,13 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     __syncwarp();
     for (int item = lane; item < copies * 2 * HALVES; item += 32) {
       const int c = item / (2 * HALVES), which = (item / HALVES) & 1, half = item % HALVES;
-      const int key0 = (kb0 + blk) * BN + c * box_rows;
-      const int e = key0 / p.page;
-      int page_id = -1;
-      if (key0 <= hi && e < p.max_blocks) page_id = table[e];
-      const long long slot = page_id >= 0 ? (long long)page_id * p.page + key0 % p.page : SLOT_BOUND;
+      int slot;
+      if (places_kept && blk < PLACES)
+        slot = blk == 0 ? place[0] : (blk == 1 ? place[1] : (blk == 2 ? place[2] : place[3]));
+      else
+        slot = slot_of(blk, item);
       unsigned char* dst = kv_tma + (which * TSTAGES + stage) * KV_TILE + half * (BN * 128) + c * box_rows * 128;
-      tma_load_3d(smem_u32(dst), which ? &map_v : &map_k, smem_u32(&full_bar[stage]), half * 64, hk, (int)slot);
+      tma_load_3d(smem_u32(dst), which ? &map_v : &map_k, smem_u32(&full_bar[stage]), half * 64, hk, slot);
     }
     return true;
   };
