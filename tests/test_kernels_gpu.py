@@ -850,6 +850,17 @@ def test_gemm_skinny_refuses_what_it_cannot_take():
         ops.gemm_skinny_bf16(x, w, torch.empty(129, 128, device=DEV, dtype=torch.bfloat16))
     with pytest.raises(ops.KernelError):
         ops.gemm_skinny_bf16(x[:4, :60], w[:, :60], torch.empty(4, 128, device=DEV, dtype=torch.bfloat16))
+    # a weight of 2^31 or more (128-row tile x 64-wide chunk) units: the kernel counts them in 32 bits and the entry
+    # point says so before anything is read (the pointers are of small buffers: nothing may touch them)
+    scratch = torch.zeros(4096, device=DEV)
+    counters = torch.zeros(4096, device=DEV, dtype=torch.int32)
+    error = torch.zeros(1, device=DEV, dtype=torch.int32)
+    N, K = 1 << 27, 1 << 17
+    status = ops._fn("ts_gemm_skinny_bf16")(x.data_ptr(), w.data_ptr(), scratch.data_ptr(), 1, N, K, K, K, N, 0,
+                                            scratch.data_ptr(), counters.data_ptr(), error.data_ptr(), None, 0, None)
+    assert status == -2  # TS_ERR_UNSUPPORTED_SIZE
+    torch.cuda.synchronize()
+    assert int(error.item()) == 0 and int(counters.abs().sum()) == 0
 
 
 def test_kernel_bench_runs_a_small_case(capsys):
