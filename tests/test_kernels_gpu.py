@@ -742,7 +742,7 @@ def test_gemm_skinny_fused_swiglu(M, I, K):
     assert torch.equal(out, out2)
 
 
-@pytest.mark.parametrize("M,N,K", [(8, 384, 256), (5, 200, 520), (2, 4096, 12288), (32, 4096, 4096), (7, 100, 64)])
+@pytest.mark.parametrize("M,N,K", [(8, 384, 256), (5, 200, 520), (2, 4096, 12288), (32, 4096, 4096), (7, 100, 64), (3, 202, 64), (20, 99, 128), (17, 131, 72)])
 def test_gemm_skinny_fused_residual_and_norm_input(M, N, K):
     """hidden += product, the next norm's input (without its 1/rms) and the sums of squares that
     give the 1/rms, all from the GEMM; then a second GEMM uses them and matches norm + product."""
