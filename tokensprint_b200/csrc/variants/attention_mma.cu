@@ -375,6 +375,18 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     }
     return true;
   };
+  // decode: where this thread's pieces of the queries lie (nothing of it depends on the kernel ahead;
+  // the copies themselves are asked for after the wait)
+  constexpr int Q_COPIES = SPLIT_KEYS ? (BM * CH + NT - 1) / NT : 1;
+  const __nv_bfloat16* q_src[Q_COPIES];
+#pragma unroll
+  for (int i = 0; i < Q_COPIES; ++i) {
+    q_src[i] = nullptr;
+    if constexpr (SPLIT_KEYS) {
+      const int c = tid + i * NT, row = c / CH, r = r0 + row;
+      if (c < BM * CH && r < rows_total) q_src[i] = p.q + ((size_t)(q_begin + r / G) * p.nq + hk * G + r % G) * D + (c % CH) * 8;
+    }
+  }
   int asked = 0;  // blocks asked for so far (warp 0 keeps count; the other warps do not use it)
   if constexpr (USE_TMA) {
     if (tid == 0) {
@@ -416,14 +428,22 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     __syncwarp();
   }
 
-  // Queries of the tile.
-  for (int c = tid; c < BM * CH; c += NT) {
-    const int row = c / CH, ch = c - row * CH;
-    const int r = r0 + row;
-    const bool valid = r < rows_total;
-    const __nv_bfloat16* src = p.q;
-    if (valid) src = p.q + ((size_t)(q_begin + r / G) * p.nq + hk * G + r % G) * D + ch * 8;
-    cp_async16(q_s + row * LD + ch * 8, src, valid);
+  // Queries of the tile (in decode from addresses worked out before the wait).
+  if constexpr (SPLIT_KEYS) {
+#pragma unroll
+    for (int i = 0; i < Q_COPIES; ++i) {
+      const int c = tid + i * NT;
+      if (c < BM * CH) cp_async16(q_s + (c / CH) * LD + (c % CH) * 8, q_src[i] != nullptr ? q_src[i] : p.q, q_src[i] != nullptr);
+    }
+  } else {
+    for (int c = tid; c < BM * CH; c += NT) {
+      const int row = c / CH, ch = c - row * CH;
+      const int r = r0 + row;
+      const bool valid = r < rows_total;
+      const __nv_bfloat16* src = p.q;
+      if (valid) src = p.q + ((size_t)(q_begin + r / G) * p.nq + hk * G + r % G) * D + ch * 8;
+      cp_async16(q_s + row * LD + ch * 8, src, valid);
+    }
   }
   if constexpr (USE_TMA) {
     cp_async_commit();  // the queries
