@@ -524,6 +524,169 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding(tmp_path):
         unregister_part("position_encoding", "toy_learned_offsets")
 
 
+# ---------------------------------------------------------------------------
+# a toy norm and a toy arrangement of a block, again defined here (the two kinds of part that the
+# toys above took from the framework)
+
+
+@dataclass(frozen=True)
+class ToyParallelConfig:
+    vocab_size: int = 53
+    hidden_size: int = 48
+    num_hidden_layers: int = 3
+    intermediate_size: int = 40
+    max_positions: int = 128
+    norm_eps: float = 3e-5
+    architectures: tuple = ("ToyParallelForCausalLM",)
+
+    def to_dict(self):
+        d = asdict(self)
+        d["architectures"] = list(self.architectures)
+        return d
+
+    def save(self, folder):
+        import json
+        from pathlib import Path
+
+        Path(folder).mkdir(parents=True, exist_ok=True)
+        (Path(folder) / "config.json").write_text(json.dumps(self.to_dict()))
+
+
+def _register_parallel_toy():
+    from tokensprint_b200.config.registry import register_architecture
+    from tokensprint_b200.models.spec import ModelSpec
+    from tokensprint_b200.parts.base import Block, Norm, PartSpec, TensorSpec, build_part, register_part
+
+    @register_part("norm", "toy_centered", replace=True)
+    class CenteredNorm(Norm):
+        """y = (x - mean x) * rsqrt(var x + eps) * weight + bias: a norm that subtracts the mean and
+        has a bias, so nobody can fold it into a product (params() stays None)."""
+
+        graph_safe = True  # a fixed sequence of device operations
+
+        def __init__(self, bctx, *, dim, eps, weight, bias):
+            self.dim, self.eps, self.weight_name, self.bias_name = dim, eps, weight, bias
+
+        def tensor_specs(self):
+            return [TensorSpec(self.weight_name, (self.dim,), "vector"), TensorSpec(self.bias_name, (self.dim,), "vector")]
+
+        def load(self, tensors):
+            self.weight, self.bias = tensors[self.weight_name], tensors[self.bias_name]
+
+        def forward(self, hidden, delta, out, row_index=None):
+            if delta is not None:
+                hidden += delta.float()
+            rows = hidden if row_index is None else hidden[row_index.long()[: out.shape[0]]]
+            centred = rows - rows.mean(dim=-1, keepdim=True)
+            out.copy_((centred * torch.rsqrt(centred.square().mean(dim=-1, keepdim=True) + self.eps) * self.weight + self.bias).to(out.dtype))
+
+    @register_part("block", "toy_parallel", replace=True)
+    class ParallelBlock(Block):
+        """h = h + Mixer(N(h)) + FeedForward(N(h)): one norm, both branches read it, their sum is the
+        block's pending output."""
+
+        def __init__(self, bctx, *, mixer, feed_forward, norm):
+            self.dtype = bctx.dtype
+            self.mixer = build_part("mixer", mixer, bctx)
+            self.feed_forward = build_part("feed_forward", feed_forward, bctx)
+            self.norm = build_part("norm", norm, bctx)
+            self._parts = (self.norm, self.mixer, self.feed_forward)
+            self.graph_safe = all(p.graph_safe for p in self._parts)
+
+        def tensor_specs(self):
+            return [s for p in self._parts for s in p.tensor_specs()]
+
+        def load(self, tensors):
+            for p in self._parts:
+                p.load(tensors)
+
+        def forward(self, hidden, pending, step, cache):
+            x = torch.empty(hidden.shape, device=hidden.device, dtype=self.dtype)
+            self.norm.forward(hidden, pending, x)
+            return self.mixer.forward(x, step, cache) + self.feed_forward.forward(x, step)
+
+        def first_weight(self):
+            return self.mixer.first_weight()
+
+    @register_architecture("ToyParallelForCausalLM", config_from_dict=lambda d: ToyParallelConfig(**{k: (tuple(v) if isinstance(v, list) else v) for k, v in d.items()}))
+    def build(cfg: ToyParallelConfig):
+        layers = []
+        for i in range(cfg.num_hidden_layers):
+            p = f"t.{i}."
+            mixer = PartSpec("attention", {"hidden_size": cfg.hidden_size, "num_heads": 6, "num_kv_heads": 3, "head_dim": 16,
+                                           "position": PartSpec("rotary", {"dim": 16, "theta": 500.0}),
+                                           "q": p + "q", "k": p + "k", "v": p + "v", "o": p + "o"})
+            ffn = PartSpec("swiglu", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size,
+                                      "gate": p + "g", "up": p + "u", "down": p + "d"})
+            layers.append(PartSpec("toy_parallel", {"mixer": mixer, "feed_forward": ffn,
+                                                    "norm": PartSpec("toy_centered", {"dim": cfg.hidden_size, "eps": cfg.norm_eps, "weight": p + "nw", "bias": p + "nb"})}))
+        return ModelSpec(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, embedding="t.embed", layers=layers,
+                         final_norm=PartSpec("toy_centered", {"dim": cfg.hidden_size, "eps": cfg.norm_eps, "weight": "t.nw", "bias": "t.nb"}),
+                         lm_head="t.head", max_positions=cfg.max_positions)
+
+
+def _plain_parallel_toy(weights, cfg: ToyParallelConfig, ids):
+    w = {k: v.double() for k, v in weights.items()}
+    T = len(ids)
+
+    def centred_norm(x, weight, bias):
+        c = x - x.mean(dim=-1, keepdim=True)
+        return c * torch.rsqrt(c.square().mean(dim=-1, keepdim=True) + cfg.norm_eps) * weight + bias
+
+    h = plain.embedding(w["t.embed"], ids)
+    angles = plain.rope_angles(list(range(T)), 16, 500.0)
+    for i in range(cfg.num_hidden_layers):
+        p = f"t.{i}."
+        x = centred_norm(h, w[p + "nw"], w[p + "nb"])
+        q = plain.apply_rope((x @ w[p + "q"].T).view(T, 6, 16), angles)
+        k = plain.apply_rope((x @ w[p + "k"].T).view(T, 3, 16), angles)
+        v = (x @ w[p + "v"].T).view(T, 3, 16)
+        attn = plain.causal_attention(q, k, v, scale=16**-0.5).reshape(T, 96) @ w[p + "o"].T
+        gate = x @ w[p + "g"].T
+        ffn = (gate * torch.sigmoid(gate) * (x @ w[p + "u"].T)) @ w[p + "d"].T
+        h = h + attn + ffn
+    return centred_norm(h, w["t.nw"], w["t.nb"]) @ w["t.head"].T
+
+
+def test_a_toy_norm_and_a_toy_arrangement_of_a_block(tmp_path):
+    """A norm with a mean and a bias and a block whose two branches read one norm, registered here,
+    around the framework's own attention and SwiGLU parts: built from config.json and stepped in
+    every way of cutting, eager and (the parts being fixed sequences of device work) in graphs."""
+    from tokensprint_b200.config.registry import unregister_architecture
+    from tokensprint_b200.engine.replay import TraceReplayer
+    from tokensprint_b200.parts.base import unregister_part
+    from tokensprint_b200.weights.loader import write_random_model
+    from tokensprint_b200.weights.safetensors_io import SafetensorsFolder
+
+    _register_parallel_toy()
+    try:
+        cfg = ToyParallelConfig()
+        folder = write_random_model(tmp_path / "parallel", cfg, seed=23, dtype="float32", std=0.2)
+        files = SafetensorsFolder(folder)
+        weights = {n: files.tensor(n).clone() for n in files.keys()}
+        assert "t.1.nb" in weights and "t.nb" in weights and weights["t.0.nw"].dtype == torch.float32
+        g = torch.Generator().manual_seed(9)
+        requests = {f"r{i}": torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for i, n in enumerate((3, 19, 45, 66))}
+        want = {rid: _plain_parallel_toy(weights, cfg, ids) for rid, ids in requests.items()}
+        many = dict(requests)
+        many.update({k + "x": v for k, v in requests.items()})
+        for steps, reqs, graphs in ((trace_whole(requests), requests, False), (trace_decode_tail(requests, 16), requests, False),
+                                    (trace_decode_tail(requests, 16), requests, True), (trace_portions(requests), requests, False),
+                                    (trace_mixed(many, 320, seed=4), many, True)):
+            replayer = TraceReplayer.from_folder(folder, "float32", 320, graphs=graphs)
+            assert replayer.runner.model.graph_safe
+            got = replay_in_process(replayer, steps)
+            assert not graphs or replayer.runner._graphs
+            for (rid, pos), row in got.items():
+                ref = want[rid.rstrip("x")][pos].numpy()
+                assert abs(row - ref).max() < 1e-4 * abs(want[rid.rstrip("x")]).max(), f"{rid} position {pos} (graphs={graphs})"
+            assert len(got) == sum(len(v) for v in reqs.values())
+    finally:
+        unregister_architecture("ToyParallelForCausalLM")
+        unregister_part("norm", "toy_centered")
+        unregister_part("block", "toy_parallel")
+
+
 def test_norms_and_activation_folded_into_the_products_change_nothing_but_rounding(tmp_path, monkeypatch):
     """Steps of few tokens fold the norms, the residual sums and the SwiGLU activation into the
     epilogues of the engine's own GEMM (widths that are multiples of 64 allow it).  The same
