@@ -650,7 +650,7 @@ def run_workload(args) -> dict:
     # one short request first, as the reference's harness does (benchmark.py:129-131)
     engine.generate([random_ids(32, cfg.vocab_size, 1)], SamplingParams(temperature=0.6, max_tokens=8, ignore_eos=True), use_tqdm=False)
     torch.cuda.synchronize()
-    stats = engine.collect_stats()
+    stats = engine.collect_stats(kernels=args.kernel_classes)
     clocks = ClockSampler(period=0.05)
     launches0 = _launches(engine)
     with clocks:
@@ -659,6 +659,7 @@ def run_workload(args) -> dict:
         torch.cuda.synchronize()
         wall = time.perf_counter() - t0
     kinds = stats.summary()
+    kernel_classes = kinds.pop("kernels", None)  # --kernel-classes: device time per launching function, eager steps only
     runner = engine.model_runner
     extra = {
         "steps": {k: v["steps"] for k, v in kinds.items()},
@@ -676,6 +677,8 @@ def run_workload(args) -> dict:
     record = workload_record(args, w, cfg, "ours", prompts, outputs, wall, sum(len(c) for c in completions), extra)
     record["config"]["layers_full"] = full_cfg.num_hidden_layers
     record["config"]["kv_block"] = PAGE_SIZE
+    if kernel_classes is not None:
+        record["kernel_classes_ms"] = {name: row["ms"] for name, row in sorted(kernel_classes.items(), key=lambda kv: -kv[1]["ms"])}
     return record
 
 
@@ -729,6 +732,9 @@ def main() -> int:
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in the record)")
     p.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
     p.add_argument("--eager", action="store_true", help="no CUDA graphs for decode steps")
+    p.add_argument("--kernel-classes", action="store_true",
+                   help="with --workload: device time per launching function of the engine, for the steps that do not replay a graph "
+                        "(the events cost host time: take the throughput from a run without this option)")
     p.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
                    help="a serving loop through generate() instead of the decode benchmark (one JSON line)")
     p.add_argument("--probe", choices=["decode", "prefill"], default=None,

@@ -48,6 +48,32 @@ def test_greedy_generation_equals_the_plain_model(tmp_path, cfg, eager):
     assert engine.model_runner.cache_manager.pages_in_use() == 0
 
 
+def test_timers_per_kernel_class_for_eager_steps(tmp_path):
+    """`collect_stats(kernels=True)`: every launching function of the engine is bracketed by CUDA
+    events while the run lasts, the tokens are what they are without timers, and afterwards the
+    functions are the plain ones again."""
+    from tokensprint_b200 import ops
+    from tokensprint_b200.config.engine_config import SamplingParams
+
+    folder, _ = make_folder(tmp_path, TINY_A, 3, sharp=2.0)
+    prompts = [random_tokens(TINY_A, n, 50 + n) for n in (5, 17, 33)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    want = make_engine(folder, "bfloat16").generate(prompts, sp, use_tqdm=False)
+    plain_embed = ops.embed_gather
+    engine = make_engine(folder, "bfloat16")
+    stats = engine.collect_stats(kernels=True)
+    assert ops.embed_gather is not plain_embed
+    assert engine.generate(prompts, sp, use_tqdm=False) == want
+    summary = stats.summary()
+    assert ops.embed_gather is plain_embed and not ops._plain_functions
+    kernels = summary["kernels"]
+    steps = sum(summary[kind]["steps"] for kind in ("decode", "prefill", "mixed"))
+    assert kernels["embed_gather"]["calls"] == steps and kernels["sample"]["calls"] == steps
+    assert sum(row["calls"] for name, row in kernels.items() if name.startswith("attention")) == steps * TINY_A["num_hidden_layers"]
+    assert all(row["ms"] > 0 for row in kernels.values())
+    assert sum(row["ms"] for row in kernels.values()) <= sum(summary[kind]["device_ms"] for kind in ("decode", "prefill", "mixed")) * 1.05
+
+
 def test_generation_is_the_same_however_it_is_cut_and_batched(tmp_path):
     """Whole prompts, small chunks, one request at a time, eager or graphs: same tokens
     (float32 greedy, and temperature sampling under a fixed seed)."""

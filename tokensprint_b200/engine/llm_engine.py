@@ -36,8 +36,14 @@ class StepStats:
     its inputs and launch its kernels is taken with the wall clock, and the device's time with a
     pair of CUDA events on the launching stream (resolved at `summary()`, after a synchronize)."""
 
-    def __init__(self) -> None:
+    def __init__(self, kernels: bool = False) -> None:
         self.records: list[tuple[str, int, float, "torch.cuda.Event", "torch.cuda.Event"]] = []
+        self.kernels = kernels
+        if kernels:
+            from tokensprint_b200 import ops
+
+            ops.kernel_times()  # forget what was recorded before
+            ops.time_kernels(True)
 
     def begin(self):
         start = torch.cuda.Event(enable_timing=True)
@@ -64,6 +70,11 @@ class StepStats:
         for row in out.values():
             row["host_ms"] = round(row["host_ms"], 2)
             row["device_ms"] = round(row["device_ms"], 2)
+        if self.kernels:
+            from tokensprint_b200 import ops
+
+            out["kernels"] = ops.kernel_times()
+            ops.time_kernels(False)
         return out
 
 
@@ -93,9 +104,11 @@ class LLMEngine:
         self._inflight = None
         self.stats: Optional[StepStats] = None
 
-    def collect_stats(self) -> StepStats:
-        """From now on every step's kind, tokens, host time and device time are recorded."""
-        self.stats = StepStats()
+    def collect_stats(self, kernels: bool = False) -> StepStats:
+        """From now on every step's kind, tokens, host time and device time are recorded.  With
+        `kernels`, eager steps also time every class of kernel (`ops.time_kernels`; `summary()` then
+        has a "kernels" entry); steps that replay a graph have no calls to time."""
+        self.stats = StepStats(kernels=kernels)
         return self.stats
 
     def _token_ids(self, prompt: str | list[int]) -> list[int]:

@@ -1199,6 +1199,69 @@ def wait_gives_up_probe(device: torch.device, limit: int = 4096) -> None:
     _check("wait_gives_up_probe", _fn("ts_wait_gives_up_probe")(error.data_ptr(), int(limit), _stream()))
 
 
+def library_mm(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None, float32_out: bool = False) -> torch.Tensor:
+    """x [T, in] @ weight[out, in]^T by the library GEMM (cuBLAS through torch.mm), for steps of more
+    rows than the engine's own weight-streaming kernel takes; a float32 result keeps the sums
+    unrounded (the logits)."""
+    flush_gemm_chain()  # the library reads x by itself
+    if float32_out:
+        return torch.mm(x, weight.t(), out_dtype=torch.float32)
+    return torch.mm(x, weight.t(), out=out)
+
+
+# Timers per kernel class, for eager steps (a replayed graph has no calls to time): switched on,
+# every launching function of this module is wrapped so that a pair of CUDA events brackets what it
+# launches; switched off, the functions are the plain ones again and nothing is paid.
+_TIMED = ("embed_gather", "feed_tokens", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_store", "attention_paged_simple",
+          "sample", "sgemm_nt", "attention_paged_mma", "attention_decode_flat", "attention_prefill_tcgen05", "gemm_skinny_bf16",
+          "gemm_skinny_fused", "rope_cos_sin", "gemm_qk_rope_store", "library_mm")
+_plain_functions: dict[str, object] = {}
+_kernel_events: list[tuple[str, "torch.cuda.Event", "torch.cuda.Event"]] = []
+
+
+def time_kernels(on: bool) -> None:
+    """Switches the per-class timers on or off (see kernel_times)."""
+    import functools
+
+    g = globals()
+    if on and not _plain_functions:
+        for name in _TIMED:
+            plain = g[name]
+
+            def timed(*args, _plain=plain, _name=name, **kwargs):
+                if torch.cuda.is_current_stream_capturing():
+                    return _plain(*args, **kwargs)
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                result = _plain(*args, **kwargs)
+                stop.record()
+                _kernel_events.append((_name, start, stop))
+                return result
+
+            _plain_functions[name] = plain
+            g[name] = functools.wraps(plain)(timed)
+    elif not on and _plain_functions:
+        for name, plain in _plain_functions.items():
+            g[name] = plain
+        _plain_functions.clear()
+
+
+def kernel_times() -> dict[str, dict]:
+    """{function: {"calls": n, "ms": device time between the events around its launches}} since the
+    last call, after waiting for the device.  Classes: the function names of this module
+    (`gemm_skinny_fused` includes the norms and activations folded into it; `library_mm` is cuBLAS)."""
+    torch.cuda.synchronize()
+    out: dict[str, dict] = {}
+    for name, start, stop in _kernel_events:
+        row = out.setdefault(name, {"calls": 0, "ms": 0.0})
+        row["calls"] += 1
+        row["ms"] += start.elapsed_time(stop)
+    _kernel_events.clear()
+    for row in out.values():
+        row["ms"] = round(row["ms"], 3)
+    return out
+
+
 def check_device_errors() -> None:
     """Raises if a kernel reported that one of its bounded waits gave up.  Cheap: reads
     pinned host words; call it wherever the host has just synchronised anyway."""

@@ -43,8 +43,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
         if T <= SKINNY_ROWS and ops.gemm_skinny_supported(x, weight):
             ops.gemm_skinny_bf16(x, weight, out, next_weight)
         else:
-            ops.flush_gemm_chain()  # the library reads x by itself
-            torch.mm(x, weight.t(), out=out)
+            ops.library_mm(x, weight, out=out)
     else:
         raise ops.KernelError(f"linear: unsupported dtype {x.dtype}")
     return out
@@ -113,5 +112,4 @@ def linear_float32_out(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     if not x.is_cuda or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         raise ops.KernelError(f"linear: bfloat16 CUDA tensors wanted (there is no CPU path), got {x.dtype} on {x.device}")
     # the library product with a float32 result: the sums are not rounded to bfloat16 on the way out
-    ops.flush_gemm_chain()
-    return torch.mm(x, weight.t(), out_dtype=torch.float32)
+    return ops.library_mm(x, weight, float32_out=True)
