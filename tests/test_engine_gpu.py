@@ -48,6 +48,24 @@ def test_greedy_generation_equals_the_plain_model(tmp_path, cfg, eager):
     assert engine.model_runner.cache_manager.pages_in_use() == 0
 
 
+def test_the_largest_batch_has_a_graph_whatever_the_number_of_slots(tmp_path):
+    """Five slots: the buckets are 1, 2, 4 and 8, and a decode step of five sequences replays the
+    last one (it used to be launched kernel by kernel); the tokens are the eager run's."""
+    from tokensprint_b200.config.engine_config import SamplingParams
+
+    folder, _ = make_folder(tmp_path, TINY_A, 3, sharp=2.0)
+    prompts = [random_tokens(TINY_A, n, 20 + n) for n in (4, 9, 13, 21, 30)]
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    want = make_engine(folder, "float32", max_num_seqs=5).generate(prompts, sp, use_tqdm=False)
+    engine = make_engine(folder, "float32", max_num_seqs=5, enforce_eager=False)
+    runner = engine.model_runner
+    assert runner.graph_buckets == [1, 2, 4, 8]
+    replayed = runner.graph_launches
+    assert engine.generate(prompts, sp, use_tqdm=False) == want
+    # every decode step was a replay: nine steps of five sequences went through the graph of 8
+    assert 8 in runner._graphs and runner.graph_launches - replayed >= 9 * runner._graphs[8].kernels
+
+
 def test_timers_per_kernel_class_for_eager_steps(tmp_path):
     """`collect_stats(kernels=True)`: every launching function of the engine is bracketed by CUDA
     events while the run lasts, the tokens are what they are without timers, and afterwards the
