@@ -132,7 +132,10 @@ class ModelRunner:
         self.max_model_len = max_model_len
         self.use_graphs = (not enforce_eager) and model.graph_safe
         most = max(1, min(max_graph_batch, num_slots))
-        self.graph_buckets = [b for b in (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512) if b <= most]
+        # sizes a decode step is padded to: from 64 sequences on in steps of 16, from 256 on of 32 (a
+        # padded sequence costs no attention, but its row goes through every product and small kernel)
+        sizes = [1, 2, 4, 8, 16, 24, 32, 48] + list(range(64, 256, 16)) + list(range(256, 513, 32))
+        self.graph_buckets = [b for b in sizes if b <= most]
         if self.graph_buckets[-1] < most:
             # the largest batch has a graph too, whatever the number of slots is (a decode step of 33
             # sequences took 5.9 ms launched kernel by kernel, 4.8 ms as the graph of 40)
