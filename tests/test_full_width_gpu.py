@@ -379,3 +379,45 @@ def test_a_long_request_in_portions_and_decoded_against_the_plain_model(tmp_path
         for p in wanted:
             err = float(abs(got[("a", p)].astype("float64") - want[p]).max()) / scale
             assert err < 4e-2, f"graphs={graphs}: position {p} strays {err:.3g} from the plain model"
+
+
+def test_decoded_tokens_beside_portions_go_to_their_own_kernels(folder, monkeypatch):
+    """One step with portions of two prompts and single decoded tokens of two other requests, given
+    in turns: the runner puts the single tokens' requests first, the attention sends them to the
+    decode kernel and the portions to the prompt kernel (two sequences each), and every wanted row
+    comes back in the order of the entries, equal to the plain model's."""
+    from tokensprint_b200 import ops
+    from tokensprint_b200.weights.safetensors_io import SafetensorsFolder
+
+    path, cfg = folder
+    requests = {"a": random_tokens(cfg, 41, 11), "b": random_tokens(cfg, 50, 12), "c": random_tokens(cfg, 71, 13), "d": random_tokens(cfg, 33, 14)}
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": requests["a"][:40], "want": []}, {"id": "c", "tokens": requests["c"][:70], "want": [69]}], "end": []},
+        {"step": 1, "entries": [{"id": "b", "tokens": requests["b"], "want": [10, 49]}, {"id": "a", "tokens": requests["a"][40:], "want": [0]},
+                                {"id": "d", "tokens": requests["d"], "want": [0, 32]}, {"id": "c", "tokens": requests["c"][70:], "want": [0]}],
+         "end": ["a", "b", "c", "d"]},
+    ]
+    calls = []
+    prompt_kernel = ops.attention_prefill_tcgen05
+
+    def spy(q, k, v, out, cu, lens, table, page, num_seqs, max_q, *rest):
+        calls.append((int(num_seqs), int(max_q), q.shape[0]))
+        return prompt_kernel(q, k, v, out, cu, lens, table, page, num_seqs, max_q, *rest)
+
+    monkeypatch.setattr(ops, "attention_prefill_tcgen05", spy)
+    got = _logits(path, "bfloat16", steps)
+    layers = cfg["num_hidden_layers"]
+    assert calls[:layers] == [(2, 70, 110)] * layers  # step 0: two portions
+    assert calls[layers:] == [(2, 50, 85)] * layers    # step 1: the two portions of the four requests; q holds all 85 tokens
+
+    files = SafetensorsFolder(path)
+    weights = {n: files.tensor(n) for n in files.keys()}
+    wanted = {("c", 69), ("b", 10), ("b", 49), ("a", 40), ("d", 0), ("d", 32), ("c", 70)}
+    assert set(got) == wanted
+    for rid in requests:
+        logits = plain.forward_logits(weights, cfg, requests[rid], dtype=torch.float64, device="cuda").cpu().numpy()
+        scale = float(abs(logits).max())
+        for r, pos in wanted:
+            if r == rid:
+                err = float(abs(got[(r, pos)].astype("float64") - logits[pos]).max()) / scale
+                assert err < 4e-2, f"request {r} position {pos} strays {err:.3g} from the plain model"

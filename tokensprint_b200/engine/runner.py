@@ -258,13 +258,30 @@ class ModelRunner:
             raise ValueError("every entry of a step brings at least one token")
         T = sum(lens)
         R = sum(len(e.want) for e in entries)
+        # In a step that carries single decoded tokens beside portions of prompts the single tokens'
+        # requests come first in the batch (a mixer then sees two ranges of sequences, one per kind);
+        # the logits keep the order of the entries as they were given.
+        row_base = None
+        singles = sum(1 for n in lens if n == 1)
+        if 0 < singles < B:
+            order = sorted(range(B), key=lambda i: lens[i] != 1)  # stable: each kind keeps its order
+            if order != list(range(B)):
+                base, acc = [0] * B, 0
+                for i, e in enumerate(entries):
+                    base[i] = acc
+                    acc += len(e.want)
+                row_base = [base[i] for i in order]
+                entries = [entries[i] for i in order]
+                lens = [lens[i] for i in order]
+        else:
+            singles = B if singles == B else 0
         widths = []
         for g in range(len(self.groups)):
             widths.append(max(1, max(-(-(e.start + n) // P) for e, n in zip(entries, lens))))
         layout = _Layout(T, B, R, widths)
         pinned, slot_i = self._pinned_buffer(layout.total)
         host = pinned.numpy()[: layout.total]
-        feeds = self._fill(host, layout, entries, lens)
+        feeds = self._fill(host, layout, entries, lens, row_base=row_base)
 
         dev = torch.empty(layout.total, dtype=torch.int32, device=self.device)
         dev.copy_(pinned[: layout.total], non_blocking=True)
@@ -277,14 +294,17 @@ class ModelRunner:
         step.host_seq_starts = [e.start for e in entries]
         step.host_seq_lens = lens
         step.host_state_slots = [e.cache.slot for e in entries]
-        step.rows_all = all(list(e.want) == list(range(n)) for e, n in zip(entries, lens))
+        step.rows_all = row_base is None and all(list(e.want) == list(range(n)) for e, n in zip(entries, lens))
+        step.decode_seqs = singles
         return step, layout.view(dev, "rows"), R
 
-    def _fill(self, host, layout: _Layout, entries: Sequence[StepEntry], lens: Sequence[int], row_marks=None) -> int:
+    def _fill(self, host, layout: _Layout, entries: Sequence[StepEntry], lens: Sequence[int], row_marks=None, row_base=None) -> int:
         """Writes the step's index arrays into `host` (a numpy view of pinned memory).  A
         layout larger than the step (a graph bucket) is padded with lanes that belong to no
         request: sequence index -1, no cache slot, no tokens in their sequence.  Returns how
-        many token lanes are to be fed on the device (entries with `feed`)."""
+        many token lanes are to be fed on the device (entries with `feed`).  `row_base`: where in
+        the list of wanted rows each entry's rows go (entries that were reordered); None: one after
+        the other."""
         B, widths = layout.B, layout.widths
         tok = layout.view(host, "token_ids")
         pos = layout.view(host, "positions")
@@ -339,6 +359,8 @@ class ModelRunner:
             cu[b + 1] = t0 + n
             ctx_lens[b] = e.start + n
             slots[b] = rc.slot
+            if row_base is not None:
+                r0 = row_base[b]
             for w in e.want:
                 if not (0 <= w < n):
                     raise ValueError(f"request {rc.request!r}: wanted place {w} is outside its {n} tokens")
@@ -389,7 +411,7 @@ class ModelRunner:
                 if row_marks is not None:
                     for b in range(nb, B):
                         row_marks[g].pop(b, None)
-        if r0 < layout.R:
+        if row_base is None and r0 < layout.R:
             rows[r0:] = 0
         return feeds
 

@@ -165,24 +165,25 @@ class AttentionMixer(Mixer):
     def _attend(self, q, out, step: StepContext, cache: LayerCache, tables) -> None:
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         if q.dtype == torch.bfloat16 and ops.attention_mma_supported(d):
-            splits, chunk, scratch = 1, 0, None
-            if step.max_seqlen_q * (nq // nkv) <= ops.attention_decode_rows(d):  # few rows per sequence: the decode kernels, keys spread over CTAs
-                # The count must not depend on the step's actual lengths (a captured graph is
-                # replayed for all of them): plan for a typical context, each sequence then
-                # divides its own keys evenly.
-                context = ops.attention_decode_plan_context(step.max_context_len, self.window)
-                splits = ops.attention_decode_splits(step.num_seqs, nkv, context, d)
-                if (ops.attention_decode_prefers_flat(step.num_seqs, nkv, splits, d)
-                        and ops.attention_decode_flat_supported(nq, nkv, d, step.page_size, step.num_seqs, step.max_seqlen_q)):
-                    # more (sequence, KV head) pairs than CTAs run at once: an even share of all key blocks per CTA
-                    ops.attention_decode_flat(
-                        q, cache.k_pages, cache.v_pages, out, step.cu_seqlens_q, step.context_lens, tables.block_table,
-                        step.seq_index, step.page_size, step.num_seqs, step.max_seqlen_q, nq, nkv, d, self.scale, self.window)
-                    return
-                if splits > 1:
-                    scratch = torch.empty(ops.attention_scratch_floats(q.shape[0] * nq, splits, d),
-                                          device=q.device, dtype=torch.float32)
-            elif ops.attention_tcgen05_supported(nq, nkv, d, step.page_size):
+            B, singles = step.num_seqs, step.decode_seqs
+            few_rows = (nq // nkv) <= ops.attention_decode_rows(d)
+            if step.max_seqlen_q * (nq // nkv) <= ops.attention_decode_rows(d):
+                # few rows per sequence: the decode kernels, keys spread over CTAs
+                self._attend_decode(q, out, step, cache, tables, 0, B, step.max_seqlen_q)
+                return
+            prompts_on_tcgen05 = ops.attention_tcgen05_supported(nq, nkv, d, step.page_size)
+            if prompts_on_tcgen05 and few_rows and 0 < singles < B:
+                # Single decoded tokens beside portions of prompts (the runner put the single tokens'
+                # requests first): each kind to its own kernel.  Through the prompt kernel a decoded
+                # token is a CTA that walks its whole context for a tile of a few rows (measured at
+                # Qwen3-14B's heads, 140 decoded tokens at context 1,500 beside 8 prompts of 1,000:
+                # 587 us in one launch, 179 + 218 us in two).
+                self._attend_decode(q[:singles], out[:singles], step, cache, tables, 0, singles, 1)
+                ops.attention_prefill_tcgen05(
+                    q, cache.k_pages, cache.v_pages, out, step.cu_seqlens_q[singles:], step.context_lens[singles:],
+                    tables.block_table[singles:], step.page_size, B - singles, step.max_seqlen_q, nq, nkv, self.scale, self.window)
+                return
+            if prompts_on_tcgen05:
                 # prompt portions: the tcgen05 kernel, where it takes the sizes
                 ops.attention_prefill_tcgen05(
                     q, cache.k_pages, cache.v_pages, out, step.cu_seqlens_q, step.context_lens, tables.block_table,
@@ -191,12 +192,39 @@ class AttentionMixer(Mixer):
             ops.attention_paged_mma(
                 q, cache.k_pages, cache.v_pages, out, step.cu_seqlens_q, step.context_lens, tables.block_table,
                 step.seq_index, step.page_size, step.num_seqs, step.max_seqlen_q, nq, nkv, d, self.scale,
-                self.window, splits, scratch, chunk)
+                self.window, 1, None, 0)
             return
         # float32 runs, and head sizes the tensor-core kernel does not take
         ops.attention_paged_simple(
             q, cache.k_pages, cache.v_pages, out, step.positions, step.seq_index, tables.block_table,
             step.page_size, self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window)
+
+    def _attend_decode(self, q, out, step: StepContext, cache: LayerCache, tables, first: int, count: int, max_q: int) -> None:
+        """Sequences [first, first + count) of the batch, each with at most `max_q` tokens (few enough
+        rows for the decode kernels); q and out hold exactly their tokens."""
+        nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
+        cu = step.cu_seqlens_q[first : first + count + 1]
+        lens = step.context_lens[first : first + count]
+        table = tables.block_table[first : first + count]
+        seq_index = step.seq_index[: q.shape[0]] if first == 0 else step.seq_index
+        # The count must not depend on the step's actual lengths (a captured graph is
+        # replayed for all of them): plan for a typical context, each sequence then
+        # divides its own keys evenly.
+        context = ops.attention_decode_plan_context(step.max_context_len, self.window)
+        splits = ops.attention_decode_splits(count, nkv, context, d)
+        if (ops.attention_decode_prefers_flat(count, nkv, splits, d)
+                and ops.attention_decode_flat_supported(nq, nkv, d, step.page_size, count, max_q)):
+            # more (sequence, KV head) pairs than CTAs run at once: an even share of all key blocks per CTA
+            ops.attention_decode_flat(
+                q, cache.k_pages, cache.v_pages, out, cu, lens, table, seq_index, step.page_size, count, max_q, nq, nkv, d,
+                self.scale, self.window)
+            return
+        scratch = None
+        if splits > 1:
+            scratch = torch.empty(ops.attention_scratch_floats(q.shape[0] * nq, splits, d), device=q.device, dtype=torch.float32)
+        ops.attention_paged_mma(
+            q, cache.k_pages, cache.v_pages, out, cu, lens, table, seq_index, step.page_size, count, max_q, nq, nkv, d,
+            self.scale, self.window, splits, scratch, 0)
 
     # -- less common paths ----------------------------------------------------
 

@@ -131,6 +131,9 @@ class StepContext:
     host_seq_lens: list[int] = field(default_factory=list)
     host_state_slots: list[int] = field(default_factory=list)
     decode_only: bool = False
+    # how many sequences at the front of the batch bring exactly one token each (the runner puts them
+    # first in a step that also carries portions of prompts, so that a mixer may treat the two kinds apart)
+    decode_seqs: int = 0
     rows_all: bool = False  # the logits of every token are wanted, in the tokens' order
     # A hint, set by whoever calls a part: the first weight matrix that will be read after the
     # part returns (the part may hand it to its last product for prefetching; may be None).
